@@ -1,0 +1,393 @@
+#!/usr/bin/env python
+"""Benchmark of the B200 neighborhood-attention forward path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config c2|c3|c4|c5] [--impl b200|reference]
+
+One "step" is one forward call of the operator (token permute -> fused attention -> unpermute,
+plus dense attention over extra KV and the LSE merge when the config has them) on seeded
+synthetic inputs. The default workload is BASELINE config 2 (na1d bf16, B=4 H=16 L=32768 D=128,
+kernel 2048, causal). With N > 1 (launched by torchrun, one rank per GPU) the (batch x heads)
+units of the same fixed problem are partitioned across ranks with no collective ("strong").
+
+Prints ONE JSON line on rank 0: whole-job effective TFLOP/s (unmasked FLOPs / time) with inputs
+resident in HBM (`value`), the same through host buffers (`e2e`), the dominant kernel against its
+roofline (`roofline`) and a CPU baseline of the oracle on the host cores (`cpu_baseline`).
+
+`--impl reference` times the CPU restatement of the reference's algorithm (oracle/) on all host
+cores on a bounded row sample of the same workload and prints the same line shape.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# name: (op, dtype, batch, heads, shape, head_dim, kernel, stride, dilation, causal, n_extra, input multiplier)
+CONFIGS = {
+    "c2": ("na1d", "bf16", 4, 16, (32768,), 128, (2048,), (1,), (1,), (True,), 0, 1.0),
+    "c3": ("na2d", "bf16", 8, 16, (128, 128), 128, (13, 13), (1, 1), (2, 2), (False, False), 0, 1.0),
+    "c4": ("na2d", "fp16", 1, 24, (256, 256), 128, (32, 32), (16, 16), (1, 1), (False, False), 256, 0.5),
+    "c5": ("na3d", "bf16", 1, 24, (32, 48, 80), 128, (16, 24, 24), (1, 8, 8), (1, 1, 1),
+           (True, False, False), 0, 1.0),
+}
+WORKLOAD_TEXT = {
+    "c2": "BASELINE config 2: na1d bf16 B=4 H=16 L=32768 D=128 kernel=2048 stride=1 dilation=1 causal",
+    "c3": "BASELINE config 3: na2d bf16 B=8 H=16 128x128 D=128 kernel=13x13 dilation=2x2",
+    "c4": "BASELINE config 4: na2d fp16 B=1 H=24 256x256 D=128 kernel=32x32 stride=16x16 + 256 extra KV",
+    "c5": "BASELINE config 5: na3d bf16 B=1 H=24 32x48x80 D=128 kernel=16x24x24 stride=1x8x8 causal=(T,F,F)",
+}
+
+
+def _win(i, k, s, L, causal):
+    wl, wr = k // 2, k // 2 + (k % 2 - 1)
+    if causal:
+        lead = min((i // s) * s + s - 1, L - 1)
+        st = max(lead - wl - wr, 0)
+        return st, min(i + 1, L)
+    lead = min((i // s) * s + s // 2, L - 1)
+    st = max(lead - wl, 0) + ((L - wr - lead - 1) if lead + wr >= L else 0)
+    return st, st + k
+
+
+def attended_pairs(shape, kernel, stride, dilation, causal) -> int:
+    """Sum over queries of the number of attended keys, per (batch, head)."""
+    total = 1
+    for X, k, s, d, c in zip(shape, kernel, stride, dilation, causal):
+        axis = 0
+        for x in range(X):
+            g, i = x % d, x // d
+            L = X // d + (1 - ((g + (d - (X % d))) // d))
+            st, en = _win(i, k, s, L, c)
+            axis += en - st
+        total *= axis
+    return total
+
+
+def algorithmic_flops(cfg, units=None) -> float:
+    """4 * D * attended pairs (QK^T and PV, multiply-add = 2) over `units` (batch x head) slices."""
+    _, _, B, H, shape, D, ks, st, di, ca, n_extra, _ = cfg
+    pairs = attended_pairs(shape, ks, st, di, ca) + n_extra * math.prod(shape)
+    return 4.0 * D * pairs * (B * H if units is None else units)
+
+
+def read_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(hbm_gbs=float(p["hbm_gbs"]), bf16_tflops=float(p["bf16_tflops"]),
+                    bf16_tflops_sustained=float(p.get("bf16_tflops_sustained", p["bf16_tflops"])),
+                    source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower() == "active":
+                    reasons.add(n)
+        return dict(sm_mhz=float(np.median(sm)) if sm else None,
+                    sm_max_mhz=float(max(mx)) if mx else None, reasons=sorted(reasons),
+                    samples=len(sm))
+
+
+def shard_units(B, H, world, rank):
+    """(batch, heads) of this rank's slice when B*H independent units are split over `world`."""
+    units = B * H
+    if units % world != 0:
+        raise SystemExit(f"{units} (batch x heads) units do not divide over {world} ranks")
+    per = units // world
+    b_local = max(1, B // world)
+    h_local = per // b_local
+    assert b_local * h_local == per and h_local <= H
+    return b_local, h_local
+
+
+def make_inputs(cfg, b_local, h_local, seed, device):
+    import torch
+    _, dt, _, _, shape, D, _, _, _, _, n_extra, mul = cfg
+    dtype = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[dt]
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    host = []
+    for _ in range(3):
+        t = torch.randn((b_local, *shape, h_local, D), generator=g, dtype=torch.float32)
+        host.append((t * mul).to(dtype).pin_memory())
+    extra = []
+    if n_extra:
+        for _ in range(2):
+            t = torch.randn((b_local, n_extra, h_local, D), generator=g, dtype=torch.float32)
+            extra.append(t.to(dtype).pin_memory())
+    return host, extra
+
+
+def cpu_baseline(cfg, budget_s=12.0, acc64=False):
+    """Times the oracle (fp32-accumulating port of the reference's naive kernel) on a row sample
+    of one (batch, head) slice; returns effective TFLOP/s of the host cores."""
+    import oracle
+    _, _, _, _, shape, D, ks, st, di, ca, n_extra, mul = cfg
+    rng = np.random.default_rng(0)
+    N = math.prod(shape)
+    q = (rng.standard_normal((1, *shape, 1, D), dtype=np.float32) * mul)
+    k = (rng.standard_normal((1, *shape, 1, D), dtype=np.float32) * mul)
+    v = (rng.standard_normal((1, *shape, 1, D), dtype=np.float32) * mul)
+    ak = av = None
+    if n_extra:
+        ak = rng.standard_normal((1, n_extra, 1, D), dtype=np.float32)
+        av = rng.standard_normal((1, n_extra, 1, D), dtype=np.float32)
+    pairs_per_row = (attended_pairs(shape, ks, st, di, ca) + n_extra * N) / N
+    cores = os.cpu_count() or 1
+    n = min(N, 64 * cores)
+    rows = np.sort(rng.choice(N, size=n, replace=False)).astype(np.int64)
+    t0 = time.perf_counter()
+    oracle.na_forward(q, k, v, ks, st, di, ca, add_k=ak, add_v=av, tok_idx=rows, acc64=acc64)
+    dt = time.perf_counter() - t0
+    # grow the sample towards the time budget
+    n2 = int(min(N, max(n, n * budget_s / max(dt, 1e-3))))
+    rows = np.sort(rng.choice(N, size=n2, replace=False)).astype(np.int64)
+    t0 = time.perf_counter()
+    oracle.na_forward(q, k, v, ks, st, di, ca, add_k=ak, add_v=av, tok_idx=rows, acc64=acc64)
+    dt = time.perf_counter() - t0
+    flops = 4.0 * D * pairs_per_row * n2
+    return dict(value=flops / dt / 1e12, unit="TFLOP/s", cores=cores, kind="port",
+                sample=f"{n2} of {N} query rows of one (batch, head) slice, fp32 accumulation, "
+                       f"OpenMP on {cores} threads, {dt:.1f} s"), dt, n2
+
+
+def run_reference_arm(args, cfg, rank):
+    if rank != 0:
+        return
+    steps, warmup = args.steps, args.warmup
+    per_step_budget = max(1.0, min(12.0, 120.0 / max(1, steps + warmup)))
+    vals, times = [], []
+    info = None
+    for i in range(warmup + steps):
+        info, dt, _ = cpu_baseline(cfg, budget_s=per_step_budget)
+        if i >= warmup:
+            vals.append(info["value"])
+            times.append(dt)
+    v = float(np.mean(vals))
+    info["value"] = v
+    line = dict(metric="FNA fwd effective TFLOPS (unmasked FLOPs)", value=v, unit="TFLOP/s",
+                impl="reference", n_gpus=args.gpus, steps=steps, warmup=warmup,
+                ms_per_step=float(np.mean(times)) * 1e3, higher_is_better=True, scaling="strong",
+                vs_baseline=None, dtype="f32", data="synthetic",
+                config=dict(workload=WORKLOAD_TEXT[args.config], sample=info["sample"]),
+                cpu_baseline=info,
+                e2e=dict(value=v, unit="TFLOP/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0))
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--config", default="c2", choices=sorted(CONFIGS))
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    cfg = CONFIGS[args.config]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference_arm(args, cfg, rank)
+        return
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+    import torch.distributed as dist
+    import natten_b200 as nb
+    import natten_b200._lib as L
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    op, dt, B, H, shape, D, ks, st, di, ca, n_extra, _ = cfg
+    b_local, h_local = shard_units(B, H, world, rank)
+    host, extra = make_inputs(cfg, b_local, h_local, 1000 + rank, dev)
+    fn = getattr(nb, op)
+
+    def call(q, k, v, ak=None, av=None):
+        return fn(q, k, v, kernel_size=ks, stride=st, dilation=di, is_causal=ca,
+                  additional_keys=ak, additional_values=av, return_lse=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    dq, dk, dv = (t.to(dev, non_blocking=True) for t in host)
+    dak, dav = (t.to(dev, non_blocking=True) for t in extra) if n_extra else (None, None)
+    torch.cuda.synchronize()
+
+    # ---- device-resident timing (inputs already in HBM; operands far exceed the 126 MB L2) ----
+    for _ in range(args.warmup):
+        call(dq, dk, dv, dak, dav)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    L.launches = 0
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        out, lse = call(dq, dk, dv, dak, dav)
+    ev1.record()
+    barrier()
+    launches = L.launches
+    clocks = sampler.stop() if rank == 0 else None
+    ms_total = ev0.elapsed_time(ev1)
+    status = L.device_status()
+
+    # ---- the fused attention kernel alone (roofline of the dominant kernel) ----
+    q_tile, kv_tile = nb.choose_tile_shapes(shape, ks, st, di, ca)
+    qp, qkv_shape, q_shape = nb.token_permute_operation(dq, q_tile, di)
+    kp, _, kv_shape = nb.token_permute_operation(dk, kv_tile, di)
+    vp, _, _ = nb.token_permute_operation(dv, kv_tile, di)
+    qp = qp.reshape(-1, math.prod(q_shape), h_local, D)
+    kp = kp.reshape(-1, math.prod(kv_shape), h_local, D)
+    vp = vp.reshape(-1, math.prod(kv_shape), h_local, D)
+    scale = D ** -0.5
+    for _ in range(3):
+        nb.fna_forward_op(qp, kp, vp, qkv_shape, q_shape, kv_shape, ks, st, di, ca, scale, q_tile, kv_tile)
+    torch.cuda.synchronize()
+    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    k0.record()
+    for _ in range(args.steps):
+        nb.fna_forward_op(qp, kp, vp, qkv_shape, q_shape, kv_shape, ks, st, di, ca, scale, q_tile, kv_tile)
+    k1.record()
+    torch.cuda.synchronize()
+    kernel_ms = k0.elapsed_time(k1) / args.steps
+    del qp, kp, vp
+
+    # ---- end to end through the public operator with HOST buffers ----
+    e2e_ms = None
+    h2d = sum(t.numel() * t.element_size() for t in host + extra)
+    d2h = out.numel() * out.element_size() + lse.numel() * lse.element_size()
+    if not args.no_e2e:
+        out_h = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+        lse_h = torch.empty(lse.shape, dtype=lse.dtype).pin_memory()
+
+        def e2e_step():
+            tq, tk, tv = (t.to(dev, non_blocking=True) for t in host)
+            tak, tav = (t.to(dev, non_blocking=True) for t in extra) if n_extra else (None, None)
+            o, l = call(tq, tk, tv, tak, tav)
+            out_h.copy_(o, non_blocking=True)
+            lse_h.copy_(l, non_blocking=True)
+
+        for _ in range(3):
+            e2e_step()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n_e2e = max(3, min(args.steps, 10))
+        e0.record()
+        for _ in range(n_e2e):
+            e2e_step()
+        e1.record()
+        barrier()
+        e2e_ms = e0.elapsed_time(e1) / n_e2e
+
+    # ---- max over ranks ----
+    t = torch.tensor([ms_total, kernel_ms, e2e_ms or 0.0, float(status)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total, kernel_ms_max, e2e_ms_max, status_max = (float(x) for x in t.tolist())
+    if world > 1:
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    if status_max != 0:
+        raise SystemExit(f"device status word {int(status_max)}: a bounded wait expired in the kernel")
+
+    peaks = read_peaks()
+    flops_all = algorithmic_flops(cfg)
+    flops_rank = algorithmic_flops(cfg, units=b_local * h_local)
+    fna_flops_rank = 4.0 * D * attended_pairs(shape, ks, st, di, ca) * b_local * h_local
+    ms_step = ms_total / args.steps
+    value = flops_all / (ms_step * 1e-3) / 1e12
+    achieved = fna_flops_rank / (kernel_ms_max * 1e-3) / 1e12
+    line = dict(
+        metric="FNA fwd effective TFLOPS (unmasked FLOPs)", value=value, unit="TFLOP/s",
+        n_gpus=world, steps=args.steps, warmup=args.warmup, ms_per_step=ms_step,
+        higher_is_better=True, scaling="strong", vs_baseline=None, dtype=dt, data="synthetic",
+        config=dict(workload=WORKLOAD_TEXT[args.config], partition="batch x heads",
+                    units_per_gpu=b_local * h_local, l2="inputs larger than L2 (no flush needed)",
+                    q_tile=list(q_tile), kv_tile=list(kv_tile)),
+        clocks=clocks, gpu_launches=int(launches),
+        roofline=dict(bound="tensor", achieved=achieved, peak=peaks["bf16_tflops"], unit="TFLOP/s",
+                      frac=achieved / peaks["bf16_tflops"], traffic=None,
+                      kernel="fna_fwd_kernel", kernel_ms=kernel_ms_max,
+                      peak_source=peaks["source"] + " burst (kernel timed alone)",
+                      frac_of_sustained=achieved / peaks["bf16_tflops_sustained"]),
+    )
+    if e2e_ms_max > 0:
+        line["e2e"] = dict(value=flops_all / (e2e_ms_max * 1e-3) / 1e12, unit="TFLOP/s",
+                           ms_per_step=e2e_ms_max, h2d_bytes_per_step=int(h2d),
+                           d2h_bytes_per_step=int(d2h))
+    if world == 1 and not args.no_cpu_baseline:
+        info, _, _ = cpu_baseline(cfg)
+        line["cpu_baseline"] = info
+    print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,150 @@
+/*
+ * natten_b200 — C ABI of the B200 (sm_100a) neighborhood-attention forward path.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream handle, launches its
+ * kernels asynchronously on that stream, never allocates or frees device memory, never
+ * synchronises the stream, and returns B200NA_OK or a negative error code (text via
+ * b200na_strerror). The caller owns every buffer, including scratch.
+ *
+ * Tensor layouts are the reference's: heads-last and contiguous.
+ *   token layout tensors   [B, X0(, X1(, X2)), H, D]
+ *   permuted ("tiled")     [B * prod(dilation), S, H, D],  S = prod(R_a * T_a),
+ *                          R_a = ceil(ceil(X_a / T_a) / d_a)
+ *   logsumexp              same without the trailing D, always fp32
+ * Axis arrays (shape, tile, kernel, ...) have `ndim` entries, axis 0 first, exactly as the
+ * reference's Python tuples.
+ */
+#ifndef NATTEN_B200_H_
+#define NATTEN_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200NA_OK 0
+#define B200NA_ERR_INVALID_ARGUMENT (-1) /* a shape / size / flag violates the documented contract */
+#define B200NA_ERR_UNSUPPORTED (-2)      /* valid in the reference, not implemented here          */
+#define B200NA_ERR_ALIGNMENT (-3)        /* a pointer or row pitch is not aligned as required     */
+#define B200NA_ERR_CUDA (-4)             /* a CUDA runtime / driver call failed (see last error)  */
+#define B200NA_ERR_DEVICE (-5)           /* current device is not compute capability 10.x         */
+#define B200NA_ERR_KERNEL_TIMEOUT (-6)   /* a bounded device-side wait expired (see device_status) */
+
+/* Element types of Q/K/V/O. */
+#define B200NA_F32 0
+#define B200NA_F16 1
+#define B200NA_BF16 2
+
+/* Exported-symbol marker (the library is built with hidden visibility by default). */
+#if defined(__GNUC__)
+#define B200NA_API __attribute__((visibility("default")))
+#else
+#define B200NA_API
+#endif
+
+/* Opaque CUDA stream handle (a cudaStream_t / CUstream passed as a pointer; NULL = default). */
+typedef void* b200na_stream_t;
+
+/* Human-readable text for an error code returned by this library. Never NULL. */
+B200NA_API const char* b200na_strerror(int code);
+
+/* Library version (major * 10000 + minor * 100 + patch). */
+B200NA_API int b200na_version(void);
+
+/*
+ * Token permute: replaces natten::token_permute_{1,2,3}d
+ * (reference: csrc/include/natten/token_permute.h:34-52, csrc/src/token_permute.cu:61-266,
+ * kernel csrc/include/natten/cuda/tokperm/token_permute_kernel.cuh:159-378).
+ *   out[b*G + lin(g), lin(r)*|T| + lin(t), h, :] = in[b, (r_a*T_a + t_a)*d_a + g_a ..., h, :]
+ * and zero where a source coordinate is outside `shape` (padding). lin() is colexicographic
+ * (axis 0 fastest) when flip != 0 — what the attention kernels expect — else last axis fastest.
+ * in:  [B, *shape, H, D]; out: [B*prod(dilation), prod(R_a*tile_a), H, D]; bit copy of
+ * elem_bytes-wide elements (1, 2, 4 or 8). `in` and `out` must not overlap.
+ */
+B200NA_API int b200na_token_permute(const void* in, void* out, int ndim, const int* shape, const int* tile,
+                         const int* dilation, int B, int H, int D, int elem_bytes, int flip,
+                         b200na_stream_t stream);
+
+/*
+ * Token unpermute: replaces natten::token_unpermute_{1,2,3}d
+ * (reference: csrc/include/natten/token_permute.h:54-74, csrc/src/token_unpermute.cu).
+ * Exact inverse of b200na_token_permute restricted to valid coordinates (padding dropped).
+ * in: [B*prod(dilation), prod(R_a*tile_a), H, D]; out: [B, *shape, H, D].
+ */
+B200NA_API int b200na_token_unpermute(const void* in, void* out, int ndim, const int* shape, const int* tile,
+                           const int* dilation, int B, int H, int D, int elem_bytes, int flip,
+                           b200na_stream_t stream);
+
+/*
+ * Fused neighborhood attention forward on token-permuted operands: replaces
+ * natten::blackwell_na{1,2,3}d_forward (reference: csrc/include/natten/blackwell_fna.h:36-88,
+ * csrc/src/blackwell_fna_forward.cu:57-267).
+ *   q:   [Bp, Sq, Hq, D]   permuted with q_tile;  k, v: [Bp, Skv, Hkv, D] permuted with kv_tile
+ *   o:   [Bp, Sq, Hq, D]   same element type as q
+ *   lse: [Bp, Sq, Hq] fp32 natural-log logsumexp of the scaled logits; may be NULL
+ *   Bp = batch * prod(dilation); dilation group of a slice = Bp index mod prod(dilation),
+ *   decoded colexicographically (axis 0 fastest).
+ *   qkv_shape: original token layout X; q_shape / kv_shape: padded per-group extents R_a*T_a
+ *   (prod = Sq / Skv). prod(q_tile) must be 256 and prod(kv_tile) 128; tiles divide the shapes.
+ *   kernel/stride/dilation/causal: the reference's kernel_size / stride / dilation / is_causal.
+ *   dtype: B200NA_F16 or B200NA_BF16; D in {64, 128}; Hq % Hkv == 0. scale multiplies q.k.
+ * Rows of o/lse that correspond to padding tokens are left unspecified.
+ */
+B200NA_API int b200na_fna_forward(const void* q, const void* k, const void* v, void* o, float* lse, int ndim,
+                       const int* qkv_shape, const int* q_shape, const int* kv_shape,
+                       const int* kernel, const int* stride, const int* dilation,
+                       const int* causal, const int* q_tile, const int* kv_tile, int Bp, int Hq,
+                       int Hkv, int D, int dtype, float scale, b200na_stream_t stream);
+
+/*
+ * Dense attention forward: replaces natten::blackwell_fmha_forward for the non-varlen case
+ * (reference: csrc/src/blackwell_fmha.cu:55-260; Python caller src/natten/functional.py:74-348),
+ * used for the extra (cross-attention) KV tokens and the self-attention fast path.
+ *   q: [B, Nq, Hq, D]; k, v: [B, Nk, Hkv, D]; o: [B, Nq, Hq, D]; lse: [B, Nq, Hq] or NULL.
+ *   causal != 0 requires Nq == Nk (query i sees keys 0..i). Nq, Nk need not be tile multiples.
+ *   fp16/bf16 with D in {64, 128} run on the tensor cores; fp32 operands and other head dims
+ *   (D <= 256) run on CUDA cores with fp32 arithmetic.
+ */
+B200NA_API int b200na_fmha_forward(const void* q, const void* k, const void* v, void* o, float* lse, int B,
+                        int Nq, int Nk, int Hq, int Hkv, int D, int dtype, float scale, int causal,
+                        b200na_stream_t stream);
+
+/*
+ * Neighborhood attention forward on the ORIGINAL token layout with CUDA-core fp32 arithmetic.
+ * This is the path for fp32 operands (the reference serves fp32 through its CUTLASS 2.x / Flex
+ * backends: src/natten/backends/fna.py, flex.py; semantics csrc/include/natten/cuda/reference/
+ * mask.hpp:47-89, fna_reference_forward.hpp:63-211) and for head dims the tensor-core kernel
+ * does not take. Extra KV tokens are attended by every query (mask.hpp:314-318).
+ *   q: [B, *shape, Hq, D]; k, v: [B, *shape, Hkv, D]; add_k/add_v: [B, n_extra, Hkv, D] or NULL;
+ *   o: [B, *shape, Hq, D]; lse: [B, *shape, Hq] or NULL. dtype: F32, F16 or BF16. D <= 256.
+ */
+B200NA_API int b200na_na_forward_simt(const void* q, const void* k, const void* v, void* o, float* lse,
+                           int ndim, const int* shape, const int* kernel, const int* stride,
+                           const int* dilation, const int* causal, int B, int Hq, int Hkv, int D,
+                           int dtype, float scale, const void* add_k, const void* add_v,
+                           int n_extra, b200na_stream_t stream);
+
+/*
+ * Two-way LSE merge: replaces the elementwise chain of natten.merge_attentions
+ * (reference: src/natten/attn_merge.py:48-105; call site src/natten/functional.py:548-554).
+ *   o = o0 - sigmoid(l1 - l0) * (o0 - o1);  l = l0 - logsigmoid(l0 - l1)   (fp32 arithmetic)
+ *   o0, o1, o: [rows, D] of `dtype`; l0, l1, l: [rows] fp32; rows = B * N * H.
+ * o may alias o0 or o1, l may alias l0 or l1.
+ */
+B200NA_API int b200na_merge(const void* o0, const float* l0, const void* o1, const float* l1, void* o,
+                 float* l, int64_t rows, int D, int dtype, b200na_stream_t stream);
+
+/*
+ * Device-side status of the tensor-core kernels on the current device: 0 if no bounded wait has
+ * expired since the last call, else a non-zero diagnostic word (role and barrier that gave up).
+ * Synchronises the device; resets the word. The reference has no counterpart: its kernels spin
+ * without a bound (csrc/include/natten/cuda/fna_blackwell/kernel/
+ * sm100_fna_fwd_kernel_tma_warpspecialized.hpp).
+ */
+B200NA_API int b200na_device_status(int* status);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NATTEN_B200_H_ */

@@ -1,0 +1,18 @@
+"""natten_b200 — B200 (sm_100a) neighborhood-attention forward path.
+
+Public surface mirrors the reference's for this path (src/natten/__init__.py:66-106):
+``na1d``, ``na2d``, ``na3d``, ``attention``, ``merge_attentions`` plus the token permute
+operators. Importing the package loads ``lib/libnatten_b200.so`` and raises if it is missing.
+"""
+from . import _lib  # noqa: F401  (fails loudly when the CUDA library is not built)
+from .functional import (BACKEND_NAME, FMHA_BACKEND_NAME, attention, choose_tile_shapes,
+                         fna_forward_op, fna_forward_permuted, merge_attentions, na1d, na2d, na3d,
+                         neighborhood_attention_generic, token_permute_operation,
+                         token_unpermute_operation)
+
+__version__ = "0.1.0"
+__all__ = [
+    "na1d", "na2d", "na3d", "attention", "merge_attentions", "neighborhood_attention_generic",
+    "token_permute_operation", "token_unpermute_operation", "fna_forward_op",
+    "fna_forward_permuted", "choose_tile_shapes", "BACKEND_NAME", "FMHA_BACKEND_NAME",
+]

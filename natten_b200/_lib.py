@@ -1,0 +1,101 @@
+"""ctypes binding of libnatten_b200.so (the C ABI declared in include/natten_b200.h).
+
+The product path has no fallback: if the library is missing, importing this module raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Optional, Sequence
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libnatten_b200.so")
+
+OK = 0
+ERR_INVALID_ARGUMENT, ERR_UNSUPPORTED, ERR_ALIGNMENT, ERR_CUDA, ERR_DEVICE, ERR_KERNEL_TIMEOUT = (
+    -1, -2, -3, -4, -5, -6)
+F32, F16, BF16 = 0, 1, 2
+
+# Every symbol include/natten_b200.h declares.
+SYMBOLS = (
+    "b200na_strerror", "b200na_version", "b200na_token_permute", "b200na_token_unpermute",
+    "b200na_fna_forward", "b200na_fmha_forward", "b200na_na_forward_simt", "b200na_merge",
+    "b200na_device_status",
+)
+
+
+class NattenB200Error(RuntimeError):
+    """A C-ABI call returned a non-zero status."""
+
+    def __init__(self, code: int, where: str, text: str):
+        super().__init__(f"{where} failed with code {code}: {text}")
+        self.code = code
+
+
+def _load() -> ctypes.CDLL:
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing. natten_b200 has no fallback path: build the CUDA library first "
+            "with `python -m natten_b200.build` (needs nvcc; targets sm_100a).")
+    lib = ctypes.CDLL(LIB_PATH)
+    c_int, c_void_p, c_float, c_i64 = ctypes.c_int, ctypes.c_void_p, ctypes.c_float, ctypes.c_int64
+    ip = ctypes.POINTER(c_int)
+    lib.b200na_strerror.restype = ctypes.c_char_p
+    lib.b200na_strerror.argtypes = [c_int]
+    lib.b200na_version.restype = c_int
+    lib.b200na_version.argtypes = []
+    for name in ("b200na_token_permute", "b200na_token_unpermute"):
+        fn = getattr(lib, name)
+        fn.restype = c_int
+        fn.argtypes = [c_void_p, c_void_p, c_int, ip, ip, ip, c_int, c_int, c_int, c_int, c_int,
+                       c_void_p]
+    lib.b200na_fna_forward.restype = c_int
+    lib.b200na_fna_forward.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                       ip, ip, ip, ip, ip, ip, ip, ip, ip,
+                                       c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]
+    lib.b200na_fmha_forward.restype = c_int
+    lib.b200na_fmha_forward.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                        c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                                        c_void_p]
+    lib.b200na_na_forward_simt.restype = c_int
+    lib.b200na_na_forward_simt.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                           ip, ip, ip, ip, ip, c_int, c_int, c_int, c_int, c_int,
+                                           c_float, c_void_p, c_void_p, c_int, c_void_p]
+    lib.b200na_merge.restype = c_int
+    lib.b200na_merge.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_i64,
+                                 c_int, c_int, c_void_p]
+    lib.b200na_device_status.restype = c_int
+    lib.b200na_device_status.argtypes = [ip]
+    return lib
+
+
+lib = _load()
+
+
+def ints(x: Optional[Sequence[int]]):
+    if x is None:
+        return None
+    return (ctypes.c_int * len(x))(*[int(v) for v in x])
+
+
+def strerror(code: int) -> str:
+    return lib.b200na_strerror(int(code)).decode()
+
+
+# Kernel launches issued through this binding since it was last reset (each successful
+# kernel-launching C-ABI call counts one); read by the benchmark.
+launches = 0
+
+
+def check(code: int, where: str, kernel_launches: int = 1) -> None:
+    global launches
+    if code != OK:
+        raise NattenB200Error(code, where, strerror(code))
+    launches += kernel_launches
+
+
+def device_status() -> int:
+    """Synchronises the current device and returns (and clears) the kernels' status word."""
+    st = ctypes.c_int(0)
+    check(lib.b200na_device_status(ctypes.byref(st)), "b200na_device_status", kernel_launches=0)
+    return st.value

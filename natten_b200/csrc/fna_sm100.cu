@@ -1,0 +1,831 @@
+// Fused neighborhood attention forward for sm_100a (B200): TMA-fed shared-memory tiles,
+// tcgen05 (UMMA) matrix multiplies accumulating in tensor memory, online softmax in registers.
+//
+// Functional contract = the reference's Blackwell FNA forward
+// (csrc/src/blackwell_fna_forward.cu:57-267 host contract; mask geometry
+// csrc/include/natten/cuda/fna_blackwell/collective/fna_fusion.hpp:88-124, 284-489): operands
+// are token-permuted [B', S, H, D] tensors, a CTA owns a 256-row query tile and walks the
+// bounding box of key/value tiles (128 rows each) its queries' windows touch.
+// The design is this library's own:
+//   * warp roles: 2 softmax warpgroups (one 128-row half each, one thread per row),
+//     1 MMA-issue warp, 1 TMA-load warp; persistent CTAs stride over (q-tile, head, batch').
+//   * TMEM: S0 S1 O0 O1 (128 fp32 columns each at D = 128); P (16-bit) overwrites S in place and
+//     feeds P.V straight from TMEM; the O rescale is lazy (only when a row maximum grows by more
+//     than 2^8) and is done by the softmax threads between the two MMAs of their half.
+//   * every KV tile is classified against the whole query tile in closed form; only boundary
+//     tiles pay for the element mask, built from per-axis prefix bit tables in shared memory.
+//   * the same kernel runs dense attention (extra KV tokens, self-attention fast path).
+//   * every mbarrier wait is bounded: on expiry the CTA records a status word and drains.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <cstdlib>
+#include <mutex>
+#include <type_traits>
+
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace b200na {
+namespace {
+
+constexpr int kQTile = 256;      // query rows per CTA work item
+constexpr int kHalf = 128;       // rows per softmax warpgroup / per MMA (M)
+constexpr int kKVTile = 128;     // key/value rows per tile (N of QK^T, K of P.V)
+constexpr int kThreads = 384;    // 8 softmax warps + MMA warp + load warp + 2 idle warps
+constexpr int kMmaWarp = 8;
+constexpr int kLoadWarp = 9;
+constexpr int kTmemCols = 512;
+constexpr long long kWaitLimitCycles = 4000000000ll;  // ~2 s at 2 GHz
+constexpr float kRescaleThreshold = 8.0f;              // log2 units
+
+// status word: (role << 8) | barrier id, role 1 = softmax, 2 = mma, 3 = load, 4 = setup
+enum : int { kStSQFull = 1, kStSFull, kStPFull, kStOFull, kStOEmpty, kStKVFull, kStKVEmpty,
+             kStQEmpty, kStSmemAlign };
+
+__device__ int g_status_word;
+
+struct FnaParams {
+  int ndim;
+  int X[B200NA_MAX_DIM];
+  int kernel[B200NA_MAX_DIM];
+  int stride[B200NA_MAX_DIM];
+  int dil[B200NA_MAX_DIM];
+  int causal[B200NA_MAX_DIM];
+  int Tq[B200NA_MAX_DIM];
+  int Tkv[B200NA_MAX_DIM];
+  int Rq[B200NA_MAX_DIM];   // query tiles per axis per dilation group
+  int Rkv[B200NA_MAX_DIM];  // kv tiles per axis per dilation group
+  int G;                    // prod(dil)
+  int dense;                // dense attention: one axis, window = all keys (or causal prefix)
+  int Bp, Hq, Hkv;
+  int Sq, Skv;              // rows per batch' in the q / kv tensors
+  int n_qtiles;             // ceil(Sq / 256)
+  long long total_work;     // n_qtiles * Hq * Bp
+  float scale;
+  float scale_log2;
+  void* o;
+  float* lse;
+  int* status;
+  int debug;  // bring-up switches (0 in normal operation)
+};
+
+struct Item {
+  int bp, h, hk, qt;
+  int L[B200NA_MAX_DIM];      // extent of this dilation group (dense: number of keys)
+  int q_lo[B200NA_MAX_DIM];   // first query coordinate of the tile
+  int kv_t0[B200NA_MAX_DIM];  // first kv tile (tile units) per axis
+  int kv_n[B200NA_MAX_DIM];   // kv tiles per axis
+  int ws_hi[B200NA_MAX_DIM];  // window start of the tile's last query
+  int we_lo[B200NA_MAX_DIM];  // window end of the tile's first query
+  int n_tiles;
+  bool skip;
+};
+
+__device__ __forceinline__ void axis_window(const FnaParams& p, int a, int i, int L, int& st,
+                                            int& en) {
+  if (p.dense) {
+    st = 0;
+    en = p.causal[0] ? imin(i + 1, L) : L;
+  } else {
+    st = win_start(i, p.kernel[a], p.stride[a], L, p.causal[a]);
+    en = win_end(i, st, p.kernel[a], L, p.causal[a]);
+  }
+}
+
+__device__ __forceinline__ void decode_item(const FnaParams& p, long long w, Item& it) {
+  it.qt = (int)(w % p.n_qtiles);
+  const long long rest = w / p.n_qtiles;
+  it.h = (int)(rest % p.Hq);
+  it.bp = (int)(rest / p.Hq);
+  it.hk = it.h / (p.Hq / p.Hkv);
+  int gl = it.bp % p.G;
+  int ql = it.qt;
+  it.n_tiles = 1;
+  it.skip = false;
+#pragma unroll
+  for (int a = 0; a < B200NA_MAX_DIM; ++a) {
+    if (a < p.ndim) {
+      const int g = gl % p.dil[a];
+      gl /= p.dil[a];
+      it.L[a] = p.dense ? p.Skv : group_extent(p.X[a], p.dil[a], g);
+      const int r = ql % p.Rq[a];
+      ql /= p.Rq[a];
+      it.q_lo[a] = r * p.Tq[a];
+      const int q_hi = it.q_lo[a] + p.Tq[a] - 1;
+      if (!p.dense && it.q_lo[a] >= it.L[a]) it.skip = true;  // tile holds padding rows only
+      int s_lo, e_lo, s_hi, e_hi;
+      axis_window(p, a, it.q_lo[a], it.L[a], s_lo, e_lo);
+      axis_window(p, a, q_hi, it.L[a], s_hi, e_hi);
+      it.ws_hi[a] = s_hi;
+      it.we_lo[a] = e_lo;
+      it.kv_t0[a] = s_lo / p.Tkv[a];
+      it.kv_n[a] = (e_hi + p.Tkv[a] - 1) / p.Tkv[a] - it.kv_t0[a];
+      it.n_tiles *= it.kv_n[a];
+    } else {
+      it.L[a] = 1; it.q_lo[a] = 0; it.kv_t0[a] = 0; it.kv_n[a] = 1; it.ws_hi[a] = 0; it.we_lo[a] = 1;
+    }
+  }
+  if (p.dense && it.qt * kQTile >= p.Sq) it.skip = true;
+}
+
+// Tile coordinates (tile units) of the `iter`-th kv tile of an item, colexicographic walk.
+__device__ __forceinline__ void kv_tile_coord(const FnaParams& p, const Item& it, int iter,
+                                              int (&c)[B200NA_MAX_DIM]) {
+#pragma unroll
+  for (int a = 0; a < B200NA_MAX_DIM; ++a) {
+    c[a] = it.kv_t0[a] + iter % it.kv_n[a];
+    iter /= it.kv_n[a];
+  }
+}
+__device__ __forceinline__ int kv_tile_row(const FnaParams& p, const int (&c)[B200NA_MAX_DIM]) {
+  return (c[0] + p.Rkv[0] * (c[1] + p.Rkv[1] * c[2])) * kKVTile;
+}
+// True when every key of the tile lies inside the window of every query of the item.
+__device__ __forceinline__ bool kv_tile_interior(const FnaParams& p, const Item& it,
+                                                 const int (&c)[B200NA_MAX_DIM]) {
+  bool in = true;
+#pragma unroll
+  for (int a = 0; a < B200NA_MAX_DIM; ++a) {
+    if (a < p.ndim) {
+      const int lo = c[a] * p.Tkv[a];
+      in = in && (lo >= it.ws_hi[a]) && (lo + p.Tkv[a] <= it.we_lo[a]);
+    }
+  }
+  return in;
+}
+
+template <int D>
+struct Smem {
+  static constexpr int kStages = (D == 128) ? 4 : 6;       // ring slots shared by K and V tiles
+  static constexpr int kTileBytes = kKVTile * D * 2;        // one K or V tile / one Q half
+  static constexpr int kQOff = 0;
+  static constexpr int kKVOff = 2 * kTileBytes;
+  static constexpr int kPrefOff = kKVOff + kStages * kTileBytes;
+  static constexpr int kPrefEntries = 136;                  // sum(T_a + 1) <= 128 + 1 + 2 + 2
+  static constexpr int kBarOff = kPrefOff + kPrefEntries * 16;
+  // barriers: q_full, q_empty, s_full[2], p_full[2], o_full[2], o_empty[2], kv_full[S], kv_empty[S]
+  static constexpr int kNumBars = 10 + 2 * kStages;
+  static constexpr int kMiscOff = kBarOff + kNumBars * 8;
+  static constexpr int kBytes = kMiscOff + 16;
+};
+
+struct Bars {
+  uint64_t* q_full;
+  uint64_t* q_empty;
+  uint64_t* s_full;   // [2]
+  uint64_t* p_full;   // [2]
+  uint64_t* o_full;   // [2]
+  uint64_t* o_empty;  // [2]
+  uint64_t* kv_full;  // [stages]
+  uint64_t* kv_empty; // [stages]
+};
+
+// Bounded mbarrier wait. Returns false when the CTA is draining (this or another wait expired).
+__device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                         int* status, int code) {
+  if (ptx::mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!ptx::mbar_try_wait(bar, parity)) {
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitLimitCycles) {
+      *abort_flag = 1;
+      atomicCAS(status, 0, code);
+      return false;
+    }
+  }
+  return true;
+}
+
+template <bool kBf16>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  if (kBf16) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  } else {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+}
+
+template <int D, bool kBf16>
+__global__ void __launch_bounds__(kThreads, 1)
+fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+               const __grid_constant__ CUtensorMap tm_v, const FnaParams p) {
+  using SM = Smem<D>;
+  constexpr int kStages = SM::kStages;
+  constexpr int kTileBytes = SM::kTileBytes;
+  constexpr int kDBlocks = D / 64;          // 64-element (128-byte) column blocks per row
+  constexpr int kBlockBytes = kKVTile * 128; // one column block of a 128-row tile
+
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* q_sm = smem + SM::kQOff;
+  uint8_t* kv_sm = smem + SM::kKVOff;
+  uint4* pref = reinterpret_cast<uint4*>(smem + SM::kPrefOff);
+  uint64_t* bar_base = reinterpret_cast<uint64_t*>(smem + SM::kBarOff);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SM::kMiscOff);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM::kMiscOff + 4);
+
+  Bars bars;
+  bars.q_full = bar_base + 0;
+  bars.q_empty = bar_base + 1;
+  bars.s_full = bar_base + 2;
+  bars.p_full = bar_base + 4;
+  bars.o_full = bar_base + 6;
+  bars.o_empty = bar_base + 8;
+  bars.kv_full = bar_base + 10;
+  bars.kv_empty = bar_base + 10 + kStages;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  // ---- setup -------------------------------------------------------------------------------
+  if ((ptx::smem_u32(smem) & 1023u) != 0) {  // swizzled tiles need 1024-byte aligned bases
+    if (threadIdx.x == 0) atomicCAS(p.status, 0, (4 << 8) | kStSmemAlign);
+    return;
+  }
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    ptx::mbar_init(bars.q_full, 1);
+    ptx::mbar_init(bars.q_empty, 1);
+    for (int h = 0; h < 2; ++h) {
+      ptx::mbar_init(bars.s_full + h, 1);
+      ptx::mbar_init(bars.p_full + h, kHalf);
+      ptx::mbar_init(bars.o_full + h, 1);
+      ptx::mbar_init(bars.o_empty + h, kHalf);
+    }
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(bars.kv_full + s, 1);
+      ptx::mbar_init(bars.kv_empty + s, 1);
+    }
+    ptx::fence_barrier_init();
+  }
+  // Per-axis prefix bit tables: pref[off_a + x] has bit j set iff the in-tile coordinate of
+  // column j along axis a is < x (columns are ordered colexicographically over Tkv).
+  {
+    int off = 0;
+    for (int a = 0; a < p.ndim; ++a) {
+      int below = 1;
+      for (int b = 0; b < a; ++b) below *= p.Tkv[b];
+      for (int x = threadIdx.x; x <= p.Tkv[a]; x += kThreads) {
+        uint32_t wds[4];
+#pragma unroll
+        for (int wd = 0; wd < 4; ++wd) {
+          uint32_t bits = 0;
+          for (int j = 0; j < 32; ++j) {
+            const int t = ((wd * 32 + j) / below) % p.Tkv[a];
+            if (t < x) bits |= 1u << j;
+          }
+          wds[wd] = bits;
+        }
+        pref[off + x] = make_uint4(wds[0], wds[1], wds[2], wds[3]);
+      }
+      off += p.Tkv[a] + 1;
+    }
+  }
+  if (warp == kMmaWarp) {
+    ptx::tmem_alloc(tmem_slot, kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  if (warp == kLoadWarp && lane == 0) {
+    ptx::prefetch_tensormap(&tm_q);
+    ptx::prefetch_tensormap(&tm_k);
+    ptx::prefetch_tensormap(&tm_v);
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  // TMEM columns: S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [384,384+D); P aliases S.
+  auto s_col = [](int half) -> uint32_t { return (uint32_t)half * 128u; };
+  auto o_col = [](int half) -> uint32_t { return 256u + (uint32_t)half * 128u; };
+
+  if (warp < 8) {
+    // ======================= softmax + correction + epilogue ===============================
+    ptx::reg_alloc<216>();
+    const int half = warp >> 2;
+    const int row = ((warp & 3) << 5) | lane;          // row inside the half = TMEM lane
+    const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) << 5) << 16);
+    const uint32_t s_addr = lane_addr + s_col(half);
+    const uint32_t o_addr = lane_addr + o_col(half);
+    const float c = p.scale_log2;
+    uint32_t ph_s = 0, ph_o = 0;
+    typedef typename std::conditional<kBf16, __nv_bfloat16, __half>::type T;
+    T* o_ptr = reinterpret_cast<T*>(p.o);
+
+    for (long long w = blockIdx.x; w < p.total_work; w += gridDim.x) {
+      Item it;
+      decode_item(p, w, it);
+      if (it.skip) continue;
+      // window of this thread's query row
+      int ws[B200NA_MAX_DIM], we[B200NA_MAX_DIM];
+      {
+        int rl = half * kHalf + row;
+#pragma unroll
+        for (int a = 0; a < B200NA_MAX_DIM; ++a) {
+          if (a < p.ndim) {
+            const int t = rl % p.Tq[a];
+            rl /= p.Tq[a];
+            axis_window(p, a, it.q_lo[a] + t, it.L[a], ws[a], we[a]);
+          } else {
+            ws[a] = 0; we[a] = 1;
+          }
+        }
+      }
+      float m = -INFINITY, sum = 0.f;
+      bool alive = true;
+      for (int iter = 0; iter < it.n_tiles; ++iter) {
+        int tc[B200NA_MAX_DIM];
+        kv_tile_coord(p, it, iter, tc);
+        const bool interior = kv_tile_interior(p, it, tc);
+        if (!wait_bar(bars.s_full + half, ph_s, abort_flag, p.status, (1 << 8) | kStSFull)) {
+          alive = false;
+          break;
+        }
+        ph_s ^= 1;
+        ptx::tc_fence_after_sync();
+        uint32_t sr[4][32];
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) ptx::tmem_ld32(s_addr + q4 * 32, sr[q4]);
+        ptx::tmem_ld_wait();
+        if (!interior) {
+          uint4 mk = make_uint4(~0u, ~0u, ~0u, ~0u);
+          int off = 0;
+#pragma unroll
+          for (int a = 0; a < B200NA_MAX_DIM; ++a) {
+            if (a < p.ndim) {
+              const int base = tc[a] * p.Tkv[a];
+              const int lo = imin(imax(ws[a] - base, 0), p.Tkv[a]);
+              const int hi = imin(imax(we[a] - base, 0), p.Tkv[a]);
+              const uint4 ph = pref[off + hi];
+              const uint4 pl = pref[off + lo];
+              const bool none = hi <= lo;
+              mk.x &= none ? 0u : (ph.x & ~pl.x);
+              mk.y &= none ? 0u : (ph.y & ~pl.y);
+              mk.z &= none ? 0u : (ph.z & ~pl.z);
+              mk.w &= none ? 0u : (ph.w & ~pl.w);
+              off += p.Tkv[a] + 1;
+            }
+          }
+          const uint32_t mw[4] = {mk.x, mk.y, mk.z, mk.w};
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (!((mw[q4] >> j) & 1u)) sr[q4][j] = 0xff800000u;  // -inf
+          }
+        }
+        // row maximum of the raw logits
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          mx0 = fmaxf(mx0, __uint_as_float(sr[0][j]));
+          mx1 = fmaxf(mx1, __uint_as_float(sr[1][j]));
+          mx2 = fmaxf(mx2, __uint_as_float(sr[2][j]));
+          mx3 = fmaxf(mx3, __uint_as_float(sr[3][j]));
+        }
+        const float m_new = fmaxf(fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)), m);
+        // Lazy rescale: keep the stale maximum while the true one is at most 2^8 larger.
+        const bool grow = (m_new - m) * c > kRescaleThreshold;  // NaN (-inf - -inf) -> false
+        if (__any_sync(0xffffffffu, grow)) {
+          const float f = grow ? ptx::ex2((m - m_new) * c) : 1.f;
+          if (grow) {
+            sum *= f;
+            m = m_new;
+          }
+          if (iter > 0) {
+            // O_half is quiescent here: P.V of the previous tile completed before s_full fired.
+#pragma unroll
+            for (int ch = 0; ch < D / 32; ++ch) {
+              uint32_t orr[32];
+              ptx::tmem_ld32(o_addr + ch * 32, orr);
+              ptx::tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 32; ++j) orr[j] = __float_as_uint(__uint_as_float(orr[j]) * f);
+              ptx::tmem_st32(o_addr + ch * 32, orr);
+            }
+          }
+        }
+        const float neg_mc = (m == -INFINITY) ? 0.f : -m * c;
+        float sm0 = 0.f, sm1 = 0.f;
+        uint32_t pk[2][32];
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            const float p0 = ptx::ex2(fmaf(__uint_as_float(sr[q4][j]), c, neg_mc));
+            const float p1 = ptx::ex2(fmaf(__uint_as_float(sr[q4][j + 1]), c, neg_mc));
+            sm0 += p0;
+            sm1 += p1;
+            pk[q4 >> 1][((q4 & 1) << 4) + (j >> 1)] =
+                (p.debug & 2) ? pack2<kBf16>(p1, p0) : pack2<kBf16>(p0, p1);
+          }
+        }
+        sum += sm0 + sm1;
+        ptx::tmem_st32(s_addr, pk[0]);
+        ptx::tmem_st32(s_addr + 32, pk[1]);
+        ptx::tmem_st_wait();
+        ptx::tc_fence_before_sync();
+        ptx::mbar_arrive(bars.p_full + half);
+      }
+      if (!alive) break;
+      // ---- epilogue: O / sum -> global, LSE ----
+      if (!wait_bar(bars.o_full + half, ph_o, abort_flag, p.status, (1 << 8) | kStOFull)) break;
+      ph_o ^= 1;
+      ptx::tc_fence_after_sync();
+      const int q_row = it.qt * kQTile + half * kHalf + row;
+      const bool valid = q_row < p.Sq;
+      const float inv = sum > 0.f ? 1.f / sum : 0.f;
+      T* orow = o_ptr + (((long long)it.bp * p.Sq + q_row) * p.Hq + it.h) * D;
+#pragma unroll
+      for (int ch = 0; ch < D / 32; ++ch) {
+        uint32_t orr[32];
+        ptx::tmem_ld32(o_addr + ch * 32, orr);
+        ptx::tmem_ld_wait();
+        if (valid) {
+#pragma unroll
+          for (int v4 = 0; v4 < 4; ++v4) {
+            uint4 out;
+            out.x = pack2<kBf16>(__uint_as_float(orr[v4 * 8 + 0]) * inv, __uint_as_float(orr[v4 * 8 + 1]) * inv);
+            out.y = pack2<kBf16>(__uint_as_float(orr[v4 * 8 + 2]) * inv, __uint_as_float(orr[v4 * 8 + 3]) * inv);
+            out.z = pack2<kBf16>(__uint_as_float(orr[v4 * 8 + 4]) * inv, __uint_as_float(orr[v4 * 8 + 5]) * inv);
+            out.w = pack2<kBf16>(__uint_as_float(orr[v4 * 8 + 6]) * inv, __uint_as_float(orr[v4 * 8 + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + ch * 32 + v4 * 8) = out;
+          }
+        }
+      }
+      if (p.lse != nullptr && valid)
+        p.lse[((long long)it.bp * p.Sq + q_row) * p.Hq + it.h] = logf(sum) + m * p.scale;
+      ptx::tc_fence_before_sync();
+      ptx::mbar_arrive(bars.o_empty + half);
+    }
+  } else if (warp == kMmaWarp) {
+    // =============================== MMA issue ==============================================
+    ptx::reg_dealloc<80>();
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = ptx::make_idesc(kBf16 ? 1 : 0, 0, 0, kHalf, kKVTile);
+      constexpr uint32_t idesc_pv = ptx::make_idesc(kBf16 ? 1 : 0, 0, 1, kHalf, D);
+      uint32_t ph_q = 0, ph_p[2] = {0, 0}, ph_oe[2] = {1, 1};
+      uint32_t cnt = 0;  // kv ring counter (K and V tiles in load order)
+      const uint32_t q_base = ptx::smem_u32(q_sm);
+      const uint32_t kv_base = ptx::smem_u32(kv_sm);
+      bool alive = true;
+
+      auto issue_qk = [&](int half, uint32_t k_addr) {
+#pragma unroll
+        for (int kb = 0; kb < D / 16; ++kb) {
+          const uint32_t koff = (kb >> 2) * kBlockBytes + (kb & 3) * 32;
+          const uint64_t a = ptx::smem_desc_sw128(q_base + half * kTileBytes + koff, 16);
+          const uint64_t b = ptx::smem_desc_sw128(k_addr + koff, 16);
+          ptx::mma_ss(tmem_base + s_col(half), a, b, idesc_qk, kb > 0 ? 1u : 0u);
+        }
+      };
+      auto issue_pv = [&](int half, uint32_t v_addr, bool first) {
+#pragma unroll
+        for (int ks = 0; ks < kKVTile / 16; ++ks) {
+          const uint64_t b = (p.debug & 1)
+                                 ? ptx::smem_desc_sw128(v_addr + ks * 2048, 1024u, kBlockBytes)
+                                 : ptx::smem_desc_sw128(v_addr + ks * 2048, kBlockBytes, 1024u);
+          ptx::mma_ts(tmem_base + o_col(half), tmem_base + s_col(half) + ks * 8, b, idesc_pv,
+                      (first && ks == 0) ? 0u : 1u);
+        }
+      };
+
+      for (long long w = blockIdx.x; w < p.total_work && alive; w += gridDim.x) {
+        Item it;
+        decode_item(p, w, it);
+        if (it.skip) continue;
+        const int n = it.n_tiles;
+        if (!wait_bar(bars.q_full, ph_q, abort_flag, p.status, (2 << 8) | kStSQFull)) break;
+        ph_q ^= 1;
+        // tile 0: S_h = Q_h K0^T for both halves
+        uint32_t slot_k = cnt % kStages;
+        if (!wait_bar(bars.kv_full + slot_k, (cnt / kStages) & 1, abort_flag, p.status,
+                      (2 << 8) | kStKVFull)) break;
+        ++cnt;
+        ptx::tc_fence_after_sync();
+        for (int h = 0; h < 2; ++h) {
+          issue_qk(h, kv_base + slot_k * kTileBytes);
+          ptx::tc_commit(bars.s_full + h);
+        }
+        ptx::tc_commit(bars.kv_empty + slot_k);
+        if (n == 1) ptx::tc_commit(bars.q_empty);
+        for (int iter = 0; iter < n && alive; ++iter) {
+          const uint32_t slot_v = cnt % kStages;
+          if (!wait_bar(bars.kv_full + slot_v, (cnt / kStages) & 1, abort_flag, p.status,
+                        (2 << 8) | kStKVFull)) { alive = false; break; }
+          ++cnt;
+          const bool more = iter + 1 < n;
+          uint32_t slot_kn = 0;
+          for (int h = 0; h < 2; ++h) {
+            if (!wait_bar(bars.p_full + h, ph_p[h], abort_flag, p.status, (2 << 8) | kStPFull)) {
+              alive = false; break;
+            }
+            ph_p[h] ^= 1;
+            if (iter == 0) {
+              // the previous item's epilogue must have drained O_h before it is overwritten
+              if (!wait_bar(bars.o_empty + h, ph_oe[h], abort_flag, p.status,
+                            (2 << 8) | kStOEmpty)) { alive = false; break; }
+              ph_oe[h] ^= 1;
+            }
+            ptx::tc_fence_after_sync();
+            issue_pv(h, kv_base + slot_v * kTileBytes, iter == 0);
+            if (more) {
+              if (h == 0) {
+                slot_kn = cnt % kStages;
+                if (!wait_bar(bars.kv_full + slot_kn, (cnt / kStages) & 1, abort_flag, p.status,
+                              (2 << 8) | kStKVFull)) { alive = false; break; }
+                ++cnt;
+                ptx::tc_fence_after_sync();
+              }
+              issue_qk(h, kv_base + slot_kn * kTileBytes);
+              ptx::tc_commit(bars.s_full + h);
+            } else {
+              ptx::tc_commit(bars.o_full + h);
+            }
+          }
+          if (!alive) break;
+          ptx::tc_commit(bars.kv_empty + slot_v);
+          if (more) {
+            ptx::tc_commit(bars.kv_empty + slot_kn);
+            if (iter + 2 == n) ptx::tc_commit(bars.q_empty);  // last Q.K^T has been issued
+          }
+        }
+      }
+    }
+  } else {
+    // ====================== TMA loads (warp 9); warps 10-11 only donate registers ===========
+    ptx::reg_dealloc<80>();
+    if (warp == kLoadWarp && lane == 0) {
+      uint32_t ph_qe = 1;
+      uint32_t cnt = 0;
+      bool alive = true;
+      for (long long w = blockIdx.x; w < p.total_work && alive; w += gridDim.x) {
+        Item it;
+        decode_item(p, w, it);
+        if (it.skip) continue;
+        if (!wait_bar(bars.q_empty, ph_qe, abort_flag, p.status, (3 << 8) | kStQEmpty)) break;
+        ph_qe ^= 1;
+        ptx::mbar_arrive_expect_tx(bars.q_full, 2 * kTileBytes);
+        for (int h = 0; h < 2; ++h)
+          for (int db = 0; db < kDBlocks; ++db)
+            ptx::tma_load_4d(q_sm + h * kTileBytes + db * kBlockBytes, &tm_q, bars.q_full, db * 64,
+                             it.h, it.qt * kQTile + h * kHalf, it.bp);
+        for (int iter = 0; iter < it.n_tiles && alive; ++iter) {
+          int tc[B200NA_MAX_DIM];
+          kv_tile_coord(p, it, iter, tc);
+          const int row0 = kv_tile_row(p, tc);
+          for (int kv = 0; kv < 2; ++kv) {
+            const uint32_t slot = cnt % kStages;
+            if (!wait_bar(bars.kv_empty + slot, ((cnt / kStages) & 1) ^ 1, abort_flag, p.status,
+                          (3 << 8) | kStKVEmpty)) { alive = false; break; }
+            ++cnt;
+            ptx::mbar_arrive_expect_tx(bars.kv_full + slot, kTileBytes);
+            for (int db = 0; db < kDBlocks; ++db)
+              ptx::tma_load_4d(kv_sm + slot * kTileBytes + db * kBlockBytes, kv == 0 ? &tm_k : &tm_v,
+                               bars.kv_full + slot, db * 64, it.hk, row0, it.bp);
+          }
+        }
+      }
+    }
+  }
+
+  // ---- teardown ----------------------------------------------------------------------------
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    // Draining after an expired wait: give loads that are still in flight time to land in this
+    // CTA's shared memory before it is released.
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000ll) {
+    }
+    __syncthreads();
+  }
+  if (warp == kMmaWarp) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---- host side -------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int get_encode_fn(EncodeTiledFn* fn) {
+  static std::mutex mu;
+  static EncodeTiledFn cached = nullptr;
+  std::lock_guard<std::mutex> lk(mu);
+  if (!cached) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    B200NA_CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres));
+    if (!sym || qres != cudaDriverEntryPointSuccess) {
+      set_last_cuda_error(cudaErrorUnknown, "cudaGetDriverEntryPoint(cuTensorMapEncodeTiled)");
+      return B200NA_ERR_CUDA;
+    }
+    cached = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  *fn = cached;
+  return B200NA_OK;
+}
+
+// Tensor map over a heads-last [Bp, S, H, D] 16-bit tensor; box = 64 (d) x 1 (h) x 128 (s) x 1.
+int make_tensor_map(CUtensorMap* tm, const void* ptr, int dtype, int Bp, int S, int H, int D) {
+  EncodeTiledFn enc = nullptr;
+  int rc = get_encode_fn(&enc);
+  if (rc != B200NA_OK) return rc;
+  const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)H, (cuuint64_t)S, (cuuint64_t)Bp};
+  const cuuint64_t strides[3] = {(cuuint64_t)D * 2, (cuuint64_t)H * D * 2,
+                                 (cuuint64_t)S * H * D * 2};
+  const cuuint32_t box[4] = {64, 1, (cuuint32_t)kKVTile, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUresult r = enc(tm, dtype == B200NA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                  : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                         4, const_cast<void*>(ptr), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_last_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
+    return B200NA_ERR_CUDA;
+  }
+  return B200NA_OK;
+}
+
+struct DeviceState {
+  bool ready = false;
+  int sms = 0;
+  int* status_ptr = nullptr;
+};
+
+// Per-device one-time setup: capability check, opt-in shared memory, status word address.
+int device_state(DeviceState** out) {
+  static std::mutex mu;
+  static DeviceState states[64];
+  int dev = 0;
+  B200NA_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return B200NA_ERR_DEVICE;
+  std::lock_guard<std::mutex> lk(mu);
+  DeviceState& st = states[dev];
+  if (!st.ready) {
+    int major = 0;
+    B200NA_CUDA_TRY(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+    if (major != 10) return B200NA_ERR_DEVICE;
+    B200NA_CUDA_TRY(cudaDeviceGetAttribute(&st.sms, cudaDevAttrMultiProcessorCount, dev));
+    B200NA_CUDA_TRY(cudaFuncSetAttribute(fna_fwd_kernel<128, true>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<128>::kBytes));
+    B200NA_CUDA_TRY(cudaFuncSetAttribute(fna_fwd_kernel<128, false>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<128>::kBytes));
+    B200NA_CUDA_TRY(cudaFuncSetAttribute(fna_fwd_kernel<64, true>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<64>::kBytes));
+    B200NA_CUDA_TRY(cudaFuncSetAttribute(fna_fwd_kernel<64, false>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<64>::kBytes));
+    void* sp = nullptr;
+    B200NA_CUDA_TRY(cudaGetSymbolAddress(&sp, g_status_word));
+    st.status_ptr = reinterpret_cast<int*>(sp);
+    B200NA_CUDA_TRY(cudaMemset(st.status_ptr, 0, sizeof(int)));
+    st.ready = true;
+  }
+  *out = &st;
+  return B200NA_OK;
+}
+
+int launch_fna(const void* q, const void* k, const void* v, FnaParams& p, int D, int dtype,
+               cudaStream_t stream) {
+  DeviceState* st = nullptr;
+  int rc = device_state(&st);
+  if (rc != B200NA_OK) return rc;
+  const uintptr_t al = reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) |
+                       reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(p.o);
+  if (al % 16 != 0) return B200NA_ERR_ALIGNMENT;
+  CUtensorMap tq, tk, tv;
+  if ((rc = make_tensor_map(&tq, q, dtype, p.Bp, p.Sq, p.Hq, D)) != B200NA_OK) return rc;
+  if ((rc = make_tensor_map(&tk, k, dtype, p.Bp, p.Skv, p.Hkv, D)) != B200NA_OK) return rc;
+  if ((rc = make_tensor_map(&tv, v, dtype, p.Bp, p.Skv, p.Hkv, D)) != B200NA_OK) return rc;
+  {
+    const char* dbg = getenv("B200NA_DEBUG");
+    p.debug = dbg ? atoi(dbg) : 0;
+  }
+  p.status = st->status_ptr;
+  p.total_work = (long long)p.n_qtiles * p.Hq * p.Bp;
+  if (p.total_work == 0) return B200NA_OK;
+  const int grid = (int)(p.total_work < st->sms ? p.total_work : st->sms);
+  const bool bf = dtype == B200NA_BF16;
+  if (D == 128) {
+    if (bf) fna_fwd_kernel<128, true><<<grid, kThreads, Smem<128>::kBytes, stream>>>(tq, tk, tv, p);
+    else fna_fwd_kernel<128, false><<<grid, kThreads, Smem<128>::kBytes, stream>>>(tq, tk, tv, p);
+  } else {
+    if (bf) fna_fwd_kernel<64, true><<<grid, kThreads, Smem<64>::kBytes, stream>>>(tq, tk, tv, p);
+    else fna_fwd_kernel<64, false><<<grid, kThreads, Smem<64>::kBytes, stream>>>(tq, tk, tv, p);
+  }
+  B200NA_CUDA_TRY(cudaGetLastError());
+  return B200NA_OK;
+}
+
+}  // namespace
+}  // namespace b200na
+
+extern "C" B200NA_API int b200na_fna_forward(const void* q, const void* k, const void* v, void* o, float* lse,
+                                  int ndim, const int* qkv_shape, const int* q_shape,
+                                  const int* kv_shape, const int* kernel, const int* stride,
+                                  const int* dilation, const int* causal, const int* q_tile,
+                                  const int* kv_tile, int Bp, int Hq, int Hkv, int D, int dtype,
+                                  float scale, b200na_stream_t stream) {
+  using namespace b200na;
+  if (!q || !k || !v || !o || !qkv_shape || !q_shape || !kv_shape || !kernel || !q_tile || !kv_tile)
+    return B200NA_ERR_INVALID_ARGUMENT;
+  if (Bp < 1 || Hq < 1 || Hkv < 1 || Hq % Hkv != 0) return B200NA_ERR_INVALID_ARGUMENT;
+  if (dtype != B200NA_F16 && dtype != B200NA_BF16) return B200NA_ERR_UNSUPPORTED;
+  if (D != 64 && D != 128) return B200NA_ERR_UNSUPPORTED;
+  if (!(scale > 0.f)) return B200NA_ERR_INVALID_ARGUMENT;
+  NaAxes ax;
+  int rc = fill_axes(ax, ndim, qkv_shape, kernel, stride, dilation, causal);
+  if (rc != B200NA_OK) return rc;
+  FnaParams p;
+  memset(&p, 0, sizeof(p));
+  p.ndim = ndim;
+  p.G = 1;
+  long long sq = 1, skv = 1, tq = 1, tkv = 1;
+  for (int a = 0; a < B200NA_MAX_DIM; ++a) {
+    const bool on = a < ndim;
+    p.X[a] = ax.shape[a]; p.kernel[a] = ax.kernel[a]; p.stride[a] = ax.stride[a];
+    p.dil[a] = ax.dilation[a]; p.causal[a] = ax.causal[a];
+    p.Tq[a] = on ? q_tile[a] : 1;
+    p.Tkv[a] = on ? kv_tile[a] : 1;
+    const int qs = on ? q_shape[a] : 1, ks = on ? kv_shape[a] : 1;
+    if (p.Tq[a] < 1 || p.Tkv[a] < 1 || qs < 1 || ks < 1) return B200NA_ERR_INVALID_ARGUMENT;
+    if (qs % p.Tq[a] != 0 || ks % p.Tkv[a] != 0) return B200NA_ERR_INVALID_ARGUMENT;
+    // padded per-group extents must cover the largest dilation group
+    const int need = (p.X[a] + p.dil[a] - 1) / p.dil[a];
+    if (qs < need || ks < need) return B200NA_ERR_INVALID_ARGUMENT;
+    p.Rq[a] = qs / p.Tq[a];
+    p.Rkv[a] = ks / p.Tkv[a];
+    p.G *= p.dil[a];
+    sq *= qs; skv *= ks; tq *= p.Tq[a]; tkv *= p.Tkv[a];
+  }
+  if (tq != kQTile || tkv != kKVTile) return B200NA_ERR_INVALID_ARGUMENT;
+  if (Bp % p.G != 0) return B200NA_ERR_INVALID_ARGUMENT;
+  if (sq > 0x7fffffffLL || skv > 0x7fffffffLL) return B200NA_ERR_UNSUPPORTED;
+  p.dense = 0;
+  p.Bp = Bp; p.Hq = Hq; p.Hkv = Hkv;
+  p.Sq = (int)sq; p.Skv = (int)skv;
+  p.n_qtiles = (int)(sq / kQTile);
+  p.scale = scale;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.o = o;
+  p.lse = lse;
+  return launch_fna(q, k, v, p, D, dtype, reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" B200NA_API int b200na_fmha_forward(const void* q, const void* k, const void* v, void* o, float* lse,
+                                   int B, int Nq, int Nk, int Hq, int Hkv, int D, int dtype,
+                                   float scale, int causal, b200na_stream_t stream) {
+  using namespace b200na;
+  if (!q || !k || !v || !o) return B200NA_ERR_INVALID_ARGUMENT;
+  if (B < 1 || Nq < 1 || Nk < 1 || Hq < 1 || Hkv < 1 || Hq % Hkv != 0)
+    return B200NA_ERR_INVALID_ARGUMENT;
+  if (causal && Nq != Nk) return B200NA_ERR_INVALID_ARGUMENT;
+  if (dtype != B200NA_F32 && dtype != B200NA_F16 && dtype != B200NA_BF16)
+    return B200NA_ERR_INVALID_ARGUMENT;
+  if (dtype == B200NA_F32 || (D != 64 && D != 128) || !(scale > 0.f))
+    return simt_dense_forward(q, k, v, o, lse, B, Nq, Nk, Hq, Hkv, D, dtype, scale, causal,
+                              reinterpret_cast<cudaStream_t>(stream));
+  FnaParams p;
+  memset(&p, 0, sizeof(p));
+  p.ndim = 1;
+  p.G = 1;
+  for (int a = 0; a < B200NA_MAX_DIM; ++a) {
+    p.X[a] = 1; p.kernel[a] = 1; p.stride[a] = 1; p.dil[a] = 1; p.causal[a] = 0;
+    p.Tq[a] = 1; p.Tkv[a] = 1; p.Rq[a] = 1; p.Rkv[a] = 1;
+  }
+  p.X[0] = Nk;
+  p.causal[0] = causal ? 1 : 0;
+  p.Tq[0] = kQTile;
+  p.Tkv[0] = kKVTile;
+  p.n_qtiles = (Nq + kQTile - 1) / kQTile;
+  p.Rq[0] = p.n_qtiles;
+  p.Rkv[0] = (Nk + kKVTile - 1) / kKVTile;
+  p.dense = 1;
+  p.Bp = B; p.Hq = Hq; p.Hkv = Hkv;
+  p.Sq = Nq; p.Skv = Nk;
+  p.scale = scale;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.o = o;
+  p.lse = lse;
+  return launch_fna(q, k, v, p, D, dtype, reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" B200NA_API int b200na_device_status(int* status) {
+  using namespace b200na;
+  if (!status) return B200NA_ERR_INVALID_ARGUMENT;
+  DeviceState* st = nullptr;
+  int rc = device_state(&st);
+  if (rc != B200NA_OK) return rc;
+  B200NA_CUDA_TRY(cudaDeviceSynchronize());
+  B200NA_CUDA_TRY(cudaMemcpy(status, st->status_ptr, sizeof(int), cudaMemcpyDeviceToHost));
+  if (*status != 0) B200NA_CUDA_TRY(cudaMemset(st->status_ptr, 0, sizeof(int)));
+  return B200NA_OK;
+}

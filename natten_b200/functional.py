@@ -1,0 +1,485 @@
+"""Host-side operators of the B200 neighborhood-attention forward path.
+
+Mirrors the reference's operator interface for this path — same names, argument meaning and error
+behaviour (src/natten/functional.py:74-99, 354-564, 567-1151; src/natten/attn_merge.py:193-289;
+src/natten/token_permute/frontend.py:42-137) — and calls the CUDA kernels through the C ABI in
+``include/natten_b200.h``. PyTorch is used for device memory and streams only. There is no CPU or
+library fallback: tensors must live on a CUDA device of compute capability 10.x.
+
+Forward only: outputs never carry autograd history.
+"""
+from __future__ import annotations
+
+import ctypes
+import functools
+import math
+from typing import Any, Dict, List, Optional, Sequence, Tuple, Union
+
+import torch
+from torch import Tensor
+
+from . import _lib
+from .checks import (CausalArgType, DimensionType, additional_kv_tensor_checks, check_all_args,
+                     check_args_against_input, check_tile_shape, fmha_tensor_checks,
+                     is_self_attention, na_tensor_checks)
+
+BACKEND_NAME = "b200-fna"
+FMHA_BACKEND_NAME = "b200-fmha"
+Q_TILE_SIZE = 256
+KV_TILE_SIZE = 128
+TENSOR_CORE_HEAD_DIMS = (64, 128)
+
+_DTYPE_CODE = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.bfloat16: _lib.BF16}
+
+
+def _ptr(t: Optional[Tensor]):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def _stream(t: Tensor):
+    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _require_cuda(*tensors: Tensor) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError(
+                "natten_b200 runs on CUDA tensors only (no CPU path); got a tensor on "
+                f"{t.device}.")
+
+
+# ------------------------------------------------------------------------------------------------
+# Window arithmetic on the host (same integer semantics as the kernels; reference:
+# csrc/include/natten/cuda/reference/mask.hpp:47-89, 220-225). Used for tile-shape selection and
+# for the multi-GPU halo computation.
+# ------------------------------------------------------------------------------------------------
+
+def window_start(i: int, k: int, s: int, L: int, causal: bool) -> int:
+    wl, wr = k // 2, k // 2 + (k % 2 - 1)
+    if causal:
+        lead = min((i // s) * s + s - 1, L - 1)
+        return max(lead - wl - wr, 0)
+    lead = min((i // s) * s + s // 2, L - 1)
+    return max(lead - wl, 0) + ((L - wr - lead - 1) if lead + wr >= L else 0)
+
+
+def window_end(i: int, start: int, k: int, L: int, causal: bool) -> int:
+    return min(i + 1, L) if causal else start + k
+
+
+def group_extent(X: int, d: int, g: int) -> int:
+    return X // d + (1 - ((g + (d - (X % d))) // d))
+
+
+def _axis_tile_cost(X: int, k: int, s: int, d: int, causal: bool, tq: int, tkv: int) -> int:
+    """KV tiles visited along one axis, summed over that axis' query tiles (largest group)."""
+    L = group_extent(X, d, 0)
+    total = 0
+    for q_lo in range(0, L, tq):
+        q_hi = q_lo + tq - 1
+        st = window_start(q_lo, k, s, L, causal)
+        s_hi = window_start(q_hi, k, s, L, causal)
+        en = window_end(q_hi, s_hi, k, L, causal)
+        total += -(-en // tkv) - st // tkv
+    return total
+
+
+def _pow2_compositions(total_log2: int, n: int):
+    if n == 1:
+        yield (1 << total_log2,)
+        return
+    for e in range(total_log2 + 1):
+        for rest in _pow2_compositions(total_log2 - e, n - 1):
+            yield (1 << e,) + rest
+
+
+@functools.lru_cache(maxsize=256)
+def choose_tile_shapes(shape: DimensionType, kernel_size: DimensionType, stride: DimensionType,
+                       dilation: DimensionType, is_causal: CausalArgType
+                       ) -> Tuple[DimensionType, DimensionType]:
+    """Picks (q_tile_shape, kv_tile_shape), 256 and 128 tokens, that minimise the number of
+    key/value tiles the kernel has to visit (the reference instead offers a fixed list:
+    src/natten/backends/configs/cutlass_blackwell/__init__.py:45-64)."""
+    n = len(shape)
+    if n == 1:
+        return (Q_TILE_SIZE,), (KV_TILE_SIZE,)
+    cost: Dict[Tuple[int, int, int], int] = {}
+    for a in range(n):
+        for eq in range(9):
+            for ek in range(8):
+                cost[(a, 1 << eq, 1 << ek)] = _axis_tile_cost(
+                    shape[a], kernel_size[a], stride[a], dilation[a], is_causal[a], 1 << eq, 1 << ek)
+    best = None
+    for tq in _pow2_compositions(8, n):
+        for tkv in _pow2_compositions(7, n):
+            c = 1
+            for a in range(n):
+                c *= cost[(a, tq[a], tkv[a])]
+            # ties: prefer tiles that are long along the last (memory-contiguous) axis
+            key = (c, -tq[-1], -tkv[-1])
+            if best is None or key < best[0]:
+                best = (key, tq, tkv)
+    assert best is not None
+    return best[1], best[2]
+
+
+# ------------------------------------------------------------------------------------------------
+# Token permute / unpermute (reference: src/natten/token_permute/frontend.py:42-137)
+# ------------------------------------------------------------------------------------------------
+
+def _rest(shape, tile, dilation):
+    return tuple(-(-(-(-x // t)) // d) for x, t, d in zip(shape, tile, dilation))
+
+
+def token_permute_operation(tensor: Tensor, tile_shape: DimensionType,
+                            dilation: Optional[DimensionType] = None,
+                            flip_tiled_dims: bool = True
+                            ) -> Tuple[Tensor, DimensionType, DimensionType]:
+    """``[B, *X, H, D] -> [B * prod(d), prod(R*T), H, D]``; returns (output, X, R*T)."""
+    if tensor.dim() not in [4, 5, 6]:
+        raise ValueError("Expected 4D, 5D, or 6D tensor (corresponding to NA1D, 2D, 3D), "
+                         f"got {tensor.dim()}D input.")
+    na_dim = tensor.dim() - 3
+    if len(tile_shape) != na_dim:
+        raise ValueError(f"Expected {na_dim}D tiler for NA{na_dim}D, got {tile_shape=}.")
+    if dilation is not None and len(dilation) != na_dim:
+        raise ValueError(f"Expected {na_dim}D dilation for NA{na_dim}D, got {dilation=}.")
+    _require_cuda(tensor)
+    dil = tuple(dilation) if dilation is not None else tuple(1 for _ in range(na_dim))
+    tensor = tensor.contiguous()
+    batch, *layout, heads, dim = tensor.shape
+    layout = tuple(layout)
+    rest = _rest(layout, tile_shape, dil)
+    post = tuple(r * t for r, t in zip(rest, tile_shape))
+    # 1-D, undilated, already a tile multiple: the permutation is the identity
+    if na_dim == 1 and dil[0] == 1 and post[0] == layout[0]:
+        return tensor, layout, post
+    out = torch.empty((batch * math.prod(dil), math.prod(post), heads, dim), dtype=tensor.dtype,
+                      device=tensor.device)
+    with torch.cuda.device(tensor.device):
+        _lib.check(_lib.lib.b200na_token_permute(
+            _ptr(tensor), _ptr(out), na_dim, _lib.ints(layout), _lib.ints(tile_shape),
+            _lib.ints(dil), batch, heads, dim, tensor.element_size(), 1 if flip_tiled_dims else 0,
+            _stream(tensor)), "b200na_token_permute")
+    return out, layout, post
+
+
+def token_unpermute_operation(tensor: Tensor, token_layout_shape: DimensionType,
+                              tile_shape: DimensionType,
+                              dilation: Optional[DimensionType] = None,
+                              flip_tiled_dims: bool = True) -> Tensor:
+    """Inverse of :func:`token_permute_operation`: ``[B * prod(d), prod(R*T), H, D] -> [B, *X, H, D]``."""
+    if tensor.dim() != 4:
+        raise ValueError(f"Expected flattened 4D tensor, got {tensor.dim()}D input.")
+    na_dim = len(token_layout_shape)
+    if len(tile_shape) != na_dim:
+        raise ValueError(f"Expected {na_dim}D tiler for NA{na_dim}D, got {tile_shape=}.")
+    if dilation is not None and len(dilation) != na_dim:
+        raise ValueError(f"Expected {na_dim}D dilation for NA{na_dim}D, got {dilation=}.")
+    _require_cuda(tensor)
+    dil = tuple(dilation) if dilation is not None else tuple(1 for _ in range(na_dim))
+    layout = tuple(int(x) for x in token_layout_shape)
+    tensor = tensor.contiguous()
+    bp, seq, heads, dim = tensor.shape
+    groups = math.prod(dil)
+    rest = _rest(layout, tile_shape, dil)
+    post = tuple(r * t for r, t in zip(rest, tile_shape))
+    if bp % groups != 0 or seq != math.prod(post):
+        raise ValueError(f"Permuted tensor of shape {tuple(tensor.shape)} does not match token "
+                         f"layout {layout}, {tile_shape=}, dilation={dil}.")
+    batch = bp // groups
+    if na_dim == 1 and dil[0] == 1 and post[0] == layout[0]:
+        return tensor.reshape(batch, *layout, heads, dim)
+    out = torch.empty((batch, *layout, heads, dim), dtype=tensor.dtype, device=tensor.device)
+    with torch.cuda.device(tensor.device):
+        _lib.check(_lib.lib.b200na_token_unpermute(
+            _ptr(tensor), _ptr(out), na_dim, _lib.ints(layout), _lib.ints(tile_shape),
+            _lib.ints(dil), batch, heads, dim, tensor.element_size(), 1 if flip_tiled_dims else 0,
+            _stream(tensor)), "b200na_token_unpermute")
+    return out
+
+
+# ------------------------------------------------------------------------------------------------
+# merge_attentions (reference: src/natten/attn_merge.py:193-289)
+# ------------------------------------------------------------------------------------------------
+
+def merge_attentions(outputs: List[Tensor], lse_tensors: List[Tensor], torch_compile: bool = True,
+                     use_autograd_fix: bool = True) -> Tuple[Tensor, Tensor]:
+    """Merges attention outputs that share a query as if their KV sets had been concatenated.
+
+    ``torch_compile`` and ``use_autograd_fix`` are accepted for source compatibility and ignored:
+    the merge is one CUDA kernel per pair and this build is forward only."""
+    if len(outputs) < 2:
+        raise ValueError("`merge_attentions` expects at least two tensors.")
+    if len(outputs) != len(lse_tensors):
+        raise ValueError("`merge_attentions` expected number of outputs and LSE tensors to match, "
+                         f"got {len(outputs)=} != {len(lse_tensors)}.")
+    shape = outputs[0].shape
+    for i, (output, lse) in enumerate(zip(outputs, lse_tensors)):
+        if output.dim() != 4:
+            raise ValueError("Output tensors must be rank-4 tensors with (batch, seq, heads, dim), "
+                             f"but got output {i} with rank={output.dim()}.")
+        if output.shape != shape:
+            raise ValueError(f"Output tensors must must match in shape, but got output {i} "
+                             f"with shape={output.shape}.")
+        if lse.dim() != 3:
+            raise ValueError("LSE tensors must be rank-3 tensors with (batch, seq, heads)"
+                             f"but got LSE {i} with rank={lse.dim()}.")
+        if lse.shape != shape[:3]:
+            raise ValueError("LSE tensors must must match outputs in shape except last dim "
+                             f"({shape=}), but got LSE {i} with shape={lse.shape}.")
+        if output.dtype != outputs[0].dtype:
+            raise ValueError("Output tensors must share one dtype.")
+    _require_cuda(*outputs, *lse_tensors)
+    dtype = outputs[0].dtype
+    if dtype not in _DTYPE_CODE:
+        raise NotImplementedError(f"merge_attentions does not support dtype {dtype}.")
+    rows = shape[0] * shape[1] * shape[2]
+    acc_o = outputs[0].detach().contiguous()
+    acc_l = lse_tensors[0].detach().to(torch.float32).contiguous()
+    out = torch.empty_like(acc_o)
+    out_l = torch.empty_like(acc_l)
+    with torch.cuda.device(acc_o.device):
+        for i in range(1, len(outputs)):
+            o_i = outputs[i].detach().contiguous()
+            l_i = lse_tensors[i].detach().to(torch.float32).contiguous()
+            _lib.check(_lib.lib.b200na_merge(_ptr(acc_o), _ptr(acc_l), _ptr(o_i), _ptr(l_i),
+                                             _ptr(out), _ptr(out_l), rows, shape[3],
+                                             _DTYPE_CODE[dtype], _stream(acc_o)), "b200na_merge")
+            acc_o, acc_l = out, out_l  # later pairs merge in place (aliasing is allowed)
+    return out, out_l
+
+
+# ------------------------------------------------------------------------------------------------
+# attention (reference: src/natten/functional.py:74-348) — dense, non-varlen
+# ------------------------------------------------------------------------------------------------
+
+def attention(query: Tensor, key: Tensor, value: Tensor, is_causal: bool = False,
+              scale: Optional[float] = None, seqlens_Q: Optional[Tensor] = None,
+              seqlens_KV: Optional[Tensor] = None, cumulative_seqlen_Q: Optional[Tensor] = None,
+              cumulative_seqlen_KV: Optional[Tensor] = None, max_seqlen_Q: Optional[int] = None,
+              max_seqlen_KV: Optional[int] = None, backend: Optional[str] = None,
+              q_tile_size: Optional[int] = None, kv_tile_size: Optional[int] = None,
+              backward_q_tile_size: Optional[int] = None,
+              backward_kv_tile_size: Optional[int] = None,
+              backward_kv_splits: Optional[int] = None, backward_use_pt_reduction: bool = False,
+              run_persistent_kernel: bool = True, kernel_schedule: Any = None,
+              torch_compile: bool = False, return_lse: bool = False
+              ) -> Union[Tensor, Tuple[Tensor, Tensor]]:
+    """Dense dot-product attention on heads-last ``[B, N, H, D]`` tensors."""
+    fmha_tensor_checks(query, key, value)
+    if any(x is not None for x in (seqlens_Q, seqlens_KV, cumulative_seqlen_Q,
+                                   cumulative_seqlen_KV, max_seqlen_Q, max_seqlen_KV)):
+        raise NotImplementedError("natten_b200.attention does not implement variable-length "
+                                  "(varlen) attention.")
+    if backend not in (None, FMHA_BACKEND_NAME):
+        raise NotImplementedError(f"Unrecognized NATTEN FMHA backend {backend}; natten_b200 "
+                                  f"provides '{FMHA_BACKEND_NAME}' only.")
+    if q_tile_size not in (None, Q_TILE_SIZE) or kv_tile_size not in (None, KV_TILE_SIZE):
+        raise ValueError(f"'{FMHA_BACKEND_NAME}' uses q/kv tile sizes {Q_TILE_SIZE}/{KV_TILE_SIZE}.")
+    _require_cuda(query, key, value)
+    scale = scale or query.shape[-1] ** -0.5
+    B, Nq, Hq, D = query.shape
+    Nk, Hkv = key.shape[1], key.shape[2]
+    if is_causal and Nq != Nk:
+        raise NotImplementedError("Causal attention needs equal query and key lengths here.")
+    q, k, v = (t.detach().contiguous() for t in (query, key, value))
+    lse = torch.empty((B, Nq, Hq), dtype=torch.float32, device=q.device)
+    out = torch.empty_like(q)
+    if q.dtype not in _DTYPE_CODE:
+        raise NotImplementedError(f"natten_b200.attention does not support dtype {q.dtype}.")
+    with torch.cuda.device(q.device):
+        # fp16/bf16 with head dim 64/128 run on tensor cores, everything else on CUDA cores;
+        # the library picks the kernel.
+        _lib.check(_lib.lib.b200na_fmha_forward(
+            _ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(lse), B, Nq, Nk, Hq, Hkv, D,
+            _DTYPE_CODE[q.dtype], float(scale), 1 if is_causal else 0, _stream(q)),
+            "b200na_fmha_forward")
+    return (out, lse) if return_lse else out
+
+
+# ------------------------------------------------------------------------------------------------
+# neighborhood attention (reference: src/natten/functional.py:354-564)
+# ------------------------------------------------------------------------------------------------
+
+def neighborhood_attention_generic(
+        query: Tensor, key: Tensor, value: Tensor, kernel_size: Any, stride: Any = 1,
+        dilation: Any = 1, is_causal: Any = False, scale: Optional[float] = None,
+        additional_keys: Optional[Tensor] = None, additional_values: Optional[Tensor] = None,
+        attention_kwargs: Optional[Dict] = None, backend: Optional[str] = None,
+        q_tile_shape: Optional[DimensionType] = None, kv_tile_shape: Optional[DimensionType] = None,
+        backward_q_tile_shape: Optional[DimensionType] = None,
+        backward_kv_tile_shape: Optional[DimensionType] = None,
+        backward_kv_splits: Optional[DimensionType] = None, backward_use_pt_reduction: bool = False,
+        run_persistent_kernel: bool = True, kernel_schedule: Any = None,
+        torch_compile: bool = False, return_lse: bool = False
+) -> Union[Tensor, Tuple[Tensor, Tensor]]:
+    na_tensor_checks(query, key, value)
+    additional_kv_tensor_checks(query, key, value, additional_keys, additional_values)
+    na_dim = query.dim() - 3
+    kernel_size, stride, dilation, is_causal = check_all_args(na_dim, kernel_size, stride,
+                                                              dilation, is_causal)
+    check_args_against_input(query, kernel_size, stride, dilation, is_causal)
+    if backend not in (None, BACKEND_NAME):
+        raise NotImplementedError(f"Unrecognized NATTEN backend {backend}; natten_b200 provides "
+                                  f"'{BACKEND_NAME}' only.")
+    _require_cuda(query, key, value, additional_keys, additional_values)
+    has_extra = additional_keys is not None and additional_values is not None
+
+    if is_self_attention(query, kernel_size, is_causal, has_extra):
+        query_shape = query.shape
+        q = query.flatten(1, na_dim)
+        k = key.flatten(1, na_dim)
+        v = value.flatten(1, na_dim)
+        if has_extra:
+            k = torch.cat([k, additional_keys], dim=1)
+            v = torch.cat([v, additional_values], dim=1)
+        out, lse = attention(q, k, v, is_causal=is_causal[0], scale=scale, return_lse=True,
+                             **(attention_kwargs or {}))
+        out = out.reshape(*query_shape[:-1], value.shape[-1])
+        lse = lse.reshape(*query_shape[:-1])
+        return (out, lse) if return_lse else out
+
+    scale = scale or query.shape[-1] ** -0.5
+    shape = tuple(query.shape[1:1 + na_dim])
+    B, Hq, D = query.shape[0], query.shape[-2], query.shape[-1]
+    Hkv = key.shape[-2]
+    if query.dtype not in _DTYPE_CODE:
+        raise NotImplementedError(f"natten_b200 does not support dtype {query.dtype}.")
+
+    tensor_core = query.dtype in (torch.float16, torch.bfloat16) and D in TENSOR_CORE_HEAD_DIMS
+    if not tensor_core:
+        # fp32 operands (and other head dims): CUDA-core kernel on the original layout, extra KV
+        # tokens fused into the same softmax.
+        q, k, v = (t.detach().contiguous() for t in (query, key, value))
+        ak = additional_keys.detach().contiguous() if has_extra else None
+        av = additional_values.detach().contiguous() if has_extra else None
+        out = torch.empty_like(q)
+        lse = torch.empty(q.shape[:-1], dtype=torch.float32, device=q.device)
+        with torch.cuda.device(q.device):
+            _lib.check(_lib.lib.b200na_na_forward_simt(
+                _ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(lse), na_dim, _lib.ints(shape),
+                _lib.ints(kernel_size), _lib.ints(stride), _lib.ints(dilation),
+                _lib.ints([1 if c else 0 for c in is_causal]), B, Hq, Hkv, D,
+                _DTYPE_CODE[q.dtype], float(scale), _ptr(ak), _ptr(av),
+                ak.shape[1] if has_extra else 0, _stream(q)), "b200na_na_forward_simt")
+        return (out, lse) if return_lse else out
+
+    if q_tile_shape is None or kv_tile_shape is None:
+        auto_q, auto_kv = choose_tile_shapes(shape, kernel_size, stride, dilation, is_causal)
+        q_tile_shape = q_tile_shape or auto_q
+        kv_tile_shape = kv_tile_shape or auto_kv
+    q_tile_shape = check_tile_shape(na_dim, q_tile_shape, "q_tile_shape", Q_TILE_SIZE)
+    kv_tile_shape = check_tile_shape(na_dim, kv_tile_shape, "kv_tile_shape", KV_TILE_SIZE)
+
+    output, lse = fna_forward_permuted(query.detach(), key.detach(), value.detach(), kernel_size,
+                                       stride, dilation, is_causal, float(scale), q_tile_shape,
+                                       kv_tile_shape)
+    if has_extra:
+        kwargs = dict(attention_kwargs or {})
+        kwargs.pop("torch_compile", None)
+        add_out, add_lse = attention(query.flatten(1, na_dim), additional_keys, additional_values,
+                                     is_causal=False, scale=scale, return_lse=True, **kwargs)
+        m_out, m_lse = merge_attentions([output.flatten(1, na_dim), add_out],
+                                        [lse.flatten(1, na_dim), add_lse])
+        output = m_out.reshape(output.shape)
+        lse = m_lse.reshape(output.shape[:-1])
+    return (output, lse) if return_lse else output
+
+
+def fna_forward_permuted(query: Tensor, key: Tensor, value: Tensor, kernel_size: DimensionType,
+                         stride: DimensionType, dilation: DimensionType, is_causal: CausalArgType,
+                         scale: float, q_tile_shape: DimensionType, kv_tile_shape: DimensionType
+                         ) -> Tuple[Tensor, Tensor]:
+    """permute Q/K/V -> fused kernel -> unpermute O/LSE, the flow of the reference's
+    src/natten/backends/blackwell_fna.py:91-181."""
+    na_dim = query.dim() - 3
+    q_perm, qkv_shape, q_shape = token_permute_operation(query, q_tile_shape, dilation, True)
+    k_perm, _, kv_shape = token_permute_operation(key, kv_tile_shape, dilation, True)
+    v_perm, _, _ = token_permute_operation(value, kv_tile_shape, dilation, True)
+    q_perm = q_perm.reshape(-1, math.prod(q_shape), *q_perm.shape[-2:])
+    k_perm = k_perm.reshape(-1, math.prod(kv_shape), *k_perm.shape[-2:])
+    v_perm = v_perm.reshape(-1, math.prod(kv_shape), *v_perm.shape[-2:])
+    o_perm, lse_perm = fna_forward_op(q_perm, k_perm, v_perm, qkv_shape, q_shape, kv_shape,
+                                      kernel_size, stride, dilation, is_causal, scale,
+                                      q_tile_shape, kv_tile_shape)
+    output = token_unpermute_operation(o_perm, qkv_shape, q_tile_shape, dilation, True)
+    lse = token_unpermute_operation(lse_perm.unsqueeze(-1), qkv_shape, q_tile_shape, dilation,
+                                    True).squeeze(-1)
+    return output, lse
+
+
+def fna_forward_op(q_perm: Tensor, k_perm: Tensor, v_perm: Tensor, qkv_shape: DimensionType,
+                   q_shape: DimensionType, kv_shape: DimensionType, kernel_size: DimensionType,
+                   stride: DimensionType, dilation: DimensionType, is_causal: CausalArgType,
+                   scale: float, q_tile_shape: DimensionType, kv_tile_shape: DimensionType
+                   ) -> Tuple[Tensor, Tensor]:
+    """The fused kernel on token-permuted ``[B', S, H, D]`` operands; allocates O and LSE like the
+    reference's op wrapper (src/natten/_libnatten/torch_wrappers.py:670-714)."""
+    na_dim = len(qkv_shape)
+    bp, sq, hq, d = q_perm.shape
+    hkv = k_perm.shape[2]
+    out = torch.empty_like(q_perm)
+    lse = torch.empty((bp, sq, hq), dtype=torch.float32, device=q_perm.device)
+    with torch.cuda.device(q_perm.device):
+        _lib.check(_lib.lib.b200na_fna_forward(
+            _ptr(q_perm), _ptr(k_perm), _ptr(v_perm), _ptr(out), _ptr(lse), na_dim,
+            _lib.ints(qkv_shape), _lib.ints(q_shape), _lib.ints(kv_shape), _lib.ints(kernel_size),
+            _lib.ints(stride), _lib.ints(dilation), _lib.ints([1 if c else 0 for c in is_causal]),
+            _lib.ints(q_tile_shape), _lib.ints(kv_tile_shape), bp, hq, hkv, d,
+            _DTYPE_CODE[q_perm.dtype], float(scale), _stream(q_perm)), "b200na_fna_forward")
+    return out, lse
+
+
+def _na(na_dim: int, query: Tensor, *args, **kwargs):
+    if query.dim() != na_dim + 3:
+        raise ValueError(f"NA{na_dim}D requires {na_dim + 3}-D input tensors, got {query.dim()=}.")
+    return neighborhood_attention_generic(query, *args, **kwargs)
+
+
+def na1d(query: Tensor, key: Tensor, value: Tensor, kernel_size, stride=1, dilation=1,
+         is_causal=False, scale: Optional[float] = None, additional_keys: Optional[Tensor] = None,
+         additional_values: Optional[Tensor] = None, attention_kwargs: Optional[Dict] = None,
+         backend: Optional[str] = None, q_tile_shape=None, kv_tile_shape=None,
+         backward_q_tile_shape=None, backward_kv_tile_shape=None, backward_kv_splits=None,
+         backward_use_pt_reduction: bool = False, run_persistent_kernel: bool = True,
+         kernel_schedule=None, torch_compile: bool = False, return_lse: bool = False):
+    """1-D neighborhood attention on ``[batch, seqlen, heads, head_dim]`` tensors
+    (reference: src/natten/functional.py:567-753)."""
+    return _na(1, query, key, value, kernel_size, stride, dilation, is_causal, scale,
+               additional_keys, additional_values, attention_kwargs, backend, q_tile_shape,
+               kv_tile_shape, backward_q_tile_shape, backward_kv_tile_shape, backward_kv_splits,
+               backward_use_pt_reduction, run_persistent_kernel, kernel_schedule, torch_compile,
+               return_lse)
+
+
+def na2d(query: Tensor, key: Tensor, value: Tensor, kernel_size, stride=1, dilation=1,
+         is_causal=False, scale: Optional[float] = None, additional_keys: Optional[Tensor] = None,
+         additional_values: Optional[Tensor] = None, attention_kwargs: Optional[Dict] = None,
+         backend: Optional[str] = None, q_tile_shape=None, kv_tile_shape=None,
+         backward_q_tile_shape=None, backward_kv_tile_shape=None, backward_kv_splits=None,
+         backward_use_pt_reduction: bool = False, run_persistent_kernel: bool = True,
+         kernel_schedule=None, torch_compile: bool = False, return_lse: bool = False):
+    """2-D neighborhood attention on ``[batch, X, Y, heads, head_dim]`` tensors
+    (reference: src/natten/functional.py:756-952)."""
+    return _na(2, query, key, value, kernel_size, stride, dilation, is_causal, scale,
+               additional_keys, additional_values, attention_kwargs, backend, q_tile_shape,
+               kv_tile_shape, backward_q_tile_shape, backward_kv_tile_shape, backward_kv_splits,
+               backward_use_pt_reduction, run_persistent_kernel, kernel_schedule, torch_compile,
+               return_lse)
+
+
+def na3d(query: Tensor, key: Tensor, value: Tensor, kernel_size, stride=1, dilation=1,
+         is_causal=False, scale: Optional[float] = None, additional_keys: Optional[Tensor] = None,
+         additional_values: Optional[Tensor] = None, attention_kwargs: Optional[Dict] = None,
+         backend: Optional[str] = None, q_tile_shape=None, kv_tile_shape=None,
+         backward_q_tile_shape=None, backward_kv_tile_shape=None, backward_kv_splits=None,
+         backward_use_pt_reduction: bool = False, run_persistent_kernel: bool = True,
+         kernel_schedule=None, torch_compile: bool = False, return_lse: bool = False):
+    """3-D neighborhood attention on ``[batch, X, Y, Z, heads, head_dim]`` tensors
+    (reference: src/natten/functional.py:955-1151)."""
+    return _na(3, query, key, value, kernel_size, stride, dilation, is_causal, scale,
+               additional_keys, additional_values, attention_kwargs, backend, q_tile_shape,
+               kv_tile_shape, backward_q_tile_shape, backward_kv_tile_shape, backward_kv_splits,
+               backward_use_pt_reduction, run_persistent_kernel, kernel_schedule, torch_compile,
+               return_lse)

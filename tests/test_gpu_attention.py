@@ -1,0 +1,214 @@
+"""Attention kernels through the public operators / C ABI against the reference's own outputs
+(tests/golden/) and the CPU oracle.
+
+Tolerances (max-abs, on output and logsumexp): 1e-4 for fp32 operands, 2e-2 for fp16/bf16."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import natten_b200 as nb
+import natten_b200._lib as L
+import oracle
+from golden_io import attn_cases, na_case_names, na_cases
+
+pytestmark = pytest.mark.gpu
+
+TOL_F32 = 1e-4
+TOL_16 = 2e-2
+
+
+def _na_fn(nd):
+    return {1: nb.na1d, 2: nb.na2d, 3: nb.na3d}[nd]
+
+
+def _run(c, dtype, **kw):
+    dev = "cuda"
+    q, k, v = (torch.from_numpy(t).to(dev).to(dtype) for t in (c.q, c.k, c.v))
+    ak = torch.from_numpy(c.add_k).to(dev).to(dtype) if c.n_extra else None
+    av = torch.from_numpy(c.add_v).to(dev).to(dtype) if c.n_extra else None
+    out, lse = _na_fn(len(c.shape))(q, k, v, kernel_size=c.kernel_size, stride=c.stride,
+                                    dilation=c.dilation, is_causal=c.is_causal,
+                                    additional_keys=ak, additional_values=av, return_lse=True,
+                                    **kw)
+    assert L.device_status() == 0
+    assert out.dtype == dtype and lse.dtype == torch.float32
+    return out.float().cpu().numpy(), lse.cpu().numpy()
+
+
+@pytest.mark.parametrize("name", na_case_names())
+def test_fp32_path_matches_reference(name):
+    c = na_cases()[name]
+    out, lse = _run(c, torch.float32)
+    assert out.shape == c.out.shape and lse.shape == c.lse.shape
+    assert np.abs(out - c.out).max() <= TOL_F32
+    assert np.abs(lse - c.lse).max() <= TOL_F32
+
+
+@pytest.mark.parametrize("name", [n for n in na_case_names() if n != "c1_na2d_32x32_k7"])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_16bit_path_matches_reference(name, dtype):
+    """bf16-exact operands: head dims 64/128 run on the tensor-core kernel, others on CUDA cores."""
+    c = na_cases()[name]
+    out, lse = _run(c, dtype)
+    assert np.isfinite(out).all() and np.isfinite(lse).all()
+    assert np.abs(out - c.out).max() <= TOL_16
+    assert np.abs(lse - c.lse).max() <= TOL_16
+
+
+@pytest.mark.parametrize("name,qt,kvt", [
+    ("c3s_na2d_32x32_k13_d2", (16, 16), (16, 8)),
+    ("c3s_na2d_32x32_k13_d2", (8, 32), (4, 32)),
+    ("c3s_na2d_32x32_k13_d2", (64, 4), (2, 64)),
+    ("c4s_na2d_32x32_k8_s4_extra24", (16, 16), (8, 16)),
+    ("c4s_na2d_32x32_k8_s4_extra24", (256, 1), (1, 128)),
+    ("c5s_na3d_8x12x20_k4x6x6_s1x2x2_causalT", (8, 4, 8), (4, 4, 8)),
+    ("c5s_na3d_8x12x20_k4x6x6_s1x2x2_causalT", (2, 8, 16), (2, 8, 8)),
+    ("c5s_na3d_8x12x20_k4x6x6_s1x2x2_causalT", (1, 16, 16), (1, 2, 64)),
+])
+def test_tensor_core_kernel_with_explicit_tile_shapes(name, qt, kvt):
+    c = na_cases()[name]
+    out, lse = _run(c, torch.bfloat16, q_tile_shape=qt, kv_tile_shape=kvt)
+    assert np.abs(out - c.out).max() <= TOL_16
+    assert np.abs(lse - c.lse).max() <= TOL_16
+
+
+def test_dense_attention_matches_reference():
+    z, meta = attn_cases()
+    for name, m in meta.items():
+        for dtype, tol in ((torch.float32, TOL_F32), (torch.bfloat16, TOL_16), (torch.float16, TOL_16)):
+            q, k, v = (torch.from_numpy(z[f"attn/{name}/{t}"]).cuda().to(dtype) for t in "qkv")
+            out, lse = nb.attention(q, k, v, is_causal=m["is_causal"], return_lse=True)
+            assert L.device_status() == 0
+            assert np.abs(out.float().cpu().numpy() - z[f"attn/{name}/out"]).max() <= tol, (name, dtype)
+            assert np.abs(lse.cpu().numpy() - z[f"attn/{name}/lse"]).max() <= tol, (name, dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_dense_causal_attention_matches_oracle(dtype):
+    """Causal dense attention is not runnable on the reference's CPU backend, so the pin here is
+    the oracle (mask.hpp semantics for a full causal window)."""
+    torch.manual_seed(5)
+    q, k, v = (torch.randn(2, 300, 2, 64).bfloat16().float() for _ in range(3))
+    want_o, want_l = oracle.dense_attention(q.numpy(), k.numpy(), v.numpy(), is_causal=True)
+    out, lse = nb.attention(q.cuda().to(dtype), k.cuda().to(dtype), v.cuda().to(dtype),
+                            is_causal=True, return_lse=True)
+    tol = TOL_F32 if dtype == torch.float32 else TOL_16
+    assert np.abs(out.float().cpu().numpy() - want_o).max() <= tol
+    assert np.abs(lse.cpu().numpy() - want_l).max() <= tol
+    # the 1-D full-window fast path of na1d takes the same route
+    out2 = nb.na1d(q.cuda().to(dtype), k.cuda().to(dtype), v.cuda().to(dtype), kernel_size=300,
+                   is_causal=True)
+    assert torch.equal(out2, out)
+
+
+def test_merge_matches_reference():
+    z, _ = attn_cases()
+    for dtype, tol in ((torch.float32, 1e-6), (torch.bfloat16, 1e-2)):
+        outs = [torch.from_numpy(z[f"merge/merge3/o{i}"]).cuda().to(dtype) for i in range(3)]
+        lses = [torch.from_numpy(z[f"merge/merge3/l{i}"]).cuda() for i in range(3)]
+        o2, l2 = nb.merge_attentions(outs[:2], lses[:2])
+        if dtype == torch.float32:
+            assert np.abs(o2.cpu().numpy() - z["merge/merge2/out"]).max() <= tol
+            assert np.abs(l2.cpu().numpy() - z["merge/merge2/lse"]).max() <= tol
+        o3, l3 = nb.merge_attentions(outs, lses)
+        assert np.abs(o3.float().cpu().numpy() - z["merge/merge3/out"]).max() <= max(tol, 2e-6) * 4
+        assert np.abs(l3.cpu().numpy() - z["merge/merge3/lse"]).max() <= 4e-6
+
+
+def test_merge_equals_attention_over_concatenated_keys():
+    """The property the reference's own merge test uses (tests/test_attn_merge.py:92-114)."""
+    torch.manual_seed(2)
+    q = torch.randn(1, 384, 2, 128, device="cuda").bfloat16()
+    k = torch.randn(1, 640, 2, 128, device="cuda").bfloat16()
+    v = torch.randn(1, 640, 2, 128, device="cuda").bfloat16()
+    full, full_l = nb.attention(q, k, v, return_lse=True)
+    parts = [nb.attention(q, k[:, a:b], v[:, a:b], return_lse=True) for a, b in ((0, 200), (200, 640))]
+    m, ml = nb.merge_attentions([p[0] for p in parts], [p[1] for p in parts])
+    assert (m.float() - full.float()).abs().max().item() <= TOL_16
+    assert (ml - full_l).abs().max().item() <= 1e-2
+
+
+def _sample_rows(shape, n, seed):
+    """Flat token indices covering every border class plus a random interior sample."""
+    rng = np.random.default_rng(seed)
+    N = int(np.prod(shape))
+    pick = {0, N - 1}
+    strides = np.cumprod((1,) + tuple(shape[::-1]))[:-1][::-1]
+    for a, X in enumerate(shape):
+        for c in (0, 1, X // 2, X - 2, X - 1):
+            base = [int(rng.integers(0, x)) for x in shape]
+            base[a] = c
+            pick.add(int(np.dot(base, strides)))
+    pick.update(int(i) for i in rng.integers(0, N, size=max(0, n - len(pick))))
+    return np.array(sorted(pick), dtype=np.int64)
+
+
+FULL_CONFIGS = {
+    # BASELINE configs 2-5 at full token-layout size, with batch/heads cut to keep the CPU oracle
+    # (a row sample of one batch entry) within seconds. dtype, then problem.
+    "c2_na1d": (torch.bfloat16, (32768,), 1, 2, (2048,), (1,), (1,), (True,), 0, 1.0),
+    "c3_na2d": (torch.bfloat16, (128, 128), 1, 2, (13, 13), (1, 1), (2, 2), (False, False), 0, 1.0),
+    "c4_na2d": (torch.float16, (256, 256), 1, 2, (32, 32), (16, 16), (1, 1), (False, False), 256, 0.5),
+    "c5_na3d": (torch.bfloat16, (32, 48, 80), 1, 1, (16, 24, 24), (1, 8, 8), (1, 1, 1),
+                (True, False, False), 0, 1.0),
+}
+
+
+@pytest.mark.parametrize("name", list(FULL_CONFIGS))
+def test_full_size_configs_row_sample_against_oracle(name):
+    dtype, shape, B, H, ks, st, di, ca, n_extra, mul = FULL_CONFIGS[name]
+    D = 128
+    torch.manual_seed(1000 + list(FULL_CONFIGS).index(name) + 1)
+    q, k, v = ((torch.randn(B, *shape, H, D) * mul).to(dtype) for _ in range(3))
+    ak = av = None
+    if n_extra:
+        ak, av = (torch.randn(B, n_extra, H, D).to(dtype) for _ in range(2))
+    out, lse = _na_fn(len(shape))(q.cuda(), k.cuda(), v.cuda(), kernel_size=ks, stride=st,
+                                  dilation=di, is_causal=ca,
+                                  additional_keys=ak.cuda() if n_extra else None,
+                                  additional_values=av.cuda() if n_extra else None,
+                                  return_lse=True)
+    assert L.device_status() == 0
+    assert torch.isfinite(out.float()).all() and torch.isfinite(lse).all()
+    rows = _sample_rows(shape, 192, seed=7)
+    want_o, want_l = oracle.na_forward(q.float().numpy(), k.float().numpy(), v.float().numpy(), ks,
+                                       st, di, ca, add_k=ak.float().numpy() if n_extra else None,
+                                       add_v=av.float().numpy() if n_extra else None, tok_idx=rows)
+    got_o = out.float().cpu().numpy().reshape(B, -1, H, D)[:, rows]
+    got_l = lse.cpu().numpy().reshape(B, -1, H)[:, rows]
+    assert np.abs(got_o - want_o).max() <= TOL_16
+    assert np.abs(got_l - want_l).max() <= TOL_16
+
+
+def test_tensor_core_kernel_agrees_with_cuda_core_kernel_on_every_row():
+    """Full-tensor cross-check of the two independent kernels at a mid-size 3-D problem with
+    causal, strided and ragged axes (every query row, not a sample)."""
+    torch.manual_seed(3)
+    shape, ks, st, di, ca = (10, 27, 45), (4, 9, 12), (1, 3, 4), (1, 1, 2), (True, False, False)
+    q, k, v = (torch.randn(1, *shape, 2, 128, device="cuda").bfloat16() for _ in range(3))
+    o_tc, l_tc = nb.na3d(q, k, v, ks, st, di, ca, return_lse=True)
+    o_cc, l_cc = nb.na3d(q.float(), k.float(), v.float(), ks, st, di, ca, return_lse=True)
+    assert L.device_status() == 0
+    assert (o_tc.float() - o_cc).abs().max().item() <= TOL_16
+    assert (l_tc - l_cc).abs().max().item() <= TOL_16
+
+
+def test_forward_is_deterministic():
+    torch.manual_seed(4)
+    q, k, v = (torch.randn(2, 40, 40, 2, 64, device="cuda").half() for _ in range(3))
+    a = nb.na2d(q, k, v, 7, 1, 2, return_lse=True)
+    b = nb.na2d(q, k, v, 7, 1, 2, return_lse=True)
+    assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+
+
+def test_unsupported_inputs_fail_loudly():
+    q = torch.randn(1, 64, 2, 64, device="cuda", dtype=torch.float64)
+    with pytest.raises(NotImplementedError):
+        nb.na1d(q, q, q, kernel_size=5)
+    q = torch.randn(1, 64, 2, 64, device="cuda").bfloat16()
+    with pytest.raises(ValueError):
+        nb.na1d(q, q, q, kernel_size=5, q_tile_shape=(128,))
+    with pytest.raises(NotImplementedError):
+        nb.attention(q, q, q, cumulative_seqlen_Q=torch.zeros(2, dtype=torch.int32, device="cuda"))

@@ -1,0 +1,116 @@
+"""Host-side logic that needs no GPU: argument rules (same exceptions as the reference),
+window arithmetic against the oracle's C restatement, tile-shape selection."""
+import itertools
+
+import numpy as np
+import pytest
+import torch
+
+import natten_b200 as nb
+from natten_b200 import functional as F
+from natten_b200.checks import check_all_args, is_self_attention
+
+
+def test_cpu_tensors_are_refused_loudly():
+    q = torch.randn(1, 16, 2, 8)
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        nb.na1d(q, q, q, kernel_size=3)
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        nb.attention(q, q, q)
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        nb.token_permute_operation(q, (4,))
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        nb.merge_attentions([q, q], [q[..., 0], q[..., 0]])
+
+
+def test_argument_rules_match_the_reference():
+    q = torch.randn(1, 16, 16, 2, 8)
+    with pytest.raises(ValueError):
+        nb.na2d(q, q, q, kernel_size=17)                 # k * d > X
+    with pytest.raises(ValueError):
+        nb.na2d(q, q, q, kernel_size=4, dilation=5)
+    with pytest.raises(ValueError):
+        nb.na2d(q, q, q, kernel_size=4, stride=5)        # s > k
+    with pytest.raises(ValueError):
+        nb.na2d(q, q, q, kernel_size=1)                  # k >= 2
+    with pytest.raises(ValueError):
+        nb.na2d(q, q, q, kernel_size=(3, 3, 3))
+    with pytest.raises(ValueError):
+        nb.na1d(q, q, q, kernel_size=3)                  # wrong rank for na1d
+    with pytest.raises(ValueError):
+        nb.na2d(q, q[:, :8], q, kernel_size=3)           # token layouts differ
+    with pytest.raises(ValueError):
+        nb.na2d(q, q.double(), q, kernel_size=3)         # dtypes differ
+    with pytest.raises(ValueError):
+        nb.na2d(q, q, q, kernel_size=3, additional_keys=q[:, 0])  # only one of the pair
+    with pytest.raises(ValueError):
+        nb.na2d(q, q[..., :1, :].expand(-1, -1, -1, 3, -1), q, kernel_size=3)  # 2 % 3 heads
+    with pytest.raises(NotImplementedError):
+        nb.na2d(q, q, q, kernel_size=3, backend="hopper-fna")
+    assert check_all_args(2, 3, None, None, None) == ((3, 3), (1, 1), (1, 1), (False, False))
+    assert check_all_args(2, (3, 5), 2, (1, 2), (True, False)) == ((3, 5), (2, 2), (1, 2), (True, False))
+
+
+def test_self_attention_detection():
+    q1 = torch.empty(1, 64, 1, 8)
+    assert is_self_attention(q1, (64,), (True,), False)       # 1-D causal full window
+    assert not is_self_attention(q1, (64,), (True,), True)    # ... unless extra KV is attached
+    q2 = torch.empty(1, 8, 8, 1, 8)
+    assert is_self_attention(q2, (8, 8), (False, False), True)
+    assert not is_self_attention(q2, (8, 8), (True, False), False)
+    assert not is_self_attention(q2, (8, 7), (False, False), False)
+
+
+def test_merge_attentions_argument_rules():
+    o = torch.randn(1, 4, 2, 8)
+    l = torch.randn(1, 4, 2)
+    with pytest.raises(ValueError):
+        nb.merge_attentions([o], [l])
+    with pytest.raises(ValueError):
+        nb.merge_attentions([o, o], [l])
+    with pytest.raises(ValueError):
+        nb.merge_attentions([o, o[:, :2]], [l, l])
+    with pytest.raises(ValueError):
+        nb.merge_attentions([o, o], [l, l[..., 0]])
+
+
+def test_window_arithmetic_matches_oracle_enumeration():
+    """Host window functions vs a brute-force use of the oracle: a one-hot value tensor makes the
+    attention output reveal exactly which keys each query attends."""
+    import oracle
+    for (L, k, s, d, causal) in [(23, 5, 1, 1, False), (23, 6, 3, 1, True), (29, 4, 2, 3, False),
+                                 (31, 7, 7, 2, True)]:
+        q = np.zeros((1, L, 1, 4), np.float32)
+        v = np.eye(L, dtype=np.float32).reshape(1, L, 1, L)
+        out, _ = oracle.na_forward(q, q, v, (k,), (s,), (d,), (causal,))
+        attended = out[0, :, 0, :] > 0
+        for x in range(L):
+            g, i = x % d, x // d
+            Lg = F.group_extent(L, d, g)
+            st = F.window_start(i, k, s, Lg, causal)
+            en = F.window_end(i, st, k, Lg, causal)
+            expect = np.zeros(L, bool)
+            expect[[j * d + g for j in range(st, en)]] = True
+            assert np.array_equal(attended[x], expect), (L, k, s, d, causal, x)
+
+
+def test_tile_shape_selection_is_valid_and_no_worse_than_reference_defaults():
+    cases = [((128, 128), (13, 13), (1, 1), (2, 2), (False, False)),
+             ((256, 256), (32, 32), (16, 16), (1, 1), (False, False)),
+             ((32, 48, 80), (16, 24, 24), (1, 8, 8), (1, 1, 1), (True, False, False)),
+             ((57, 20, 88), (3, 5, 7), (1, 2, 3), (2, 1, 1), (False, True, False))]
+    ref_default = {2: ((16, 16), (16, 8)), 3: ((8, 4, 8), (4, 4, 8))}
+    for shape, k, s, d, c in cases:
+        tq, tkv = nb.choose_tile_shapes(shape, k, s, d, c)
+        assert np.prod(tq) == 256 and np.prod(tkv) == 128
+        n = len(shape)
+
+        def cost(tq_, tkv_):
+            return np.prod([F._axis_tile_cost(shape[a], k[a], s[a], d[a], c[a], tq_[a], tkv_[a])
+                            for a in range(n)], dtype=np.float64)
+        # compare per query token (tiles may differ in count)
+        def per_token(tq_, tkv_):
+            return cost(tq_, tkv_) / np.prod([-(-F.group_extent(shape[a], d[a], 0) // tq_[a])
+                                              for a in range(n)])
+        assert cost(tq, tkv) <= cost(*ref_default[n])
+    assert nb.choose_tile_shapes((4096,), (64,), (1,), (1,), (False,)) == ((256,), (128,))
