@@ -209,7 +209,16 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   }
 }
 
-template <int D, bool kBf16>
+// Register budget: 384 threads are launched with kBaseRegs registers each; the four non-softmax
+// warps then release down to kOtherRegs and the eight softmax warps grow to kSoftmaxRegs. The
+// growth must fit in what was released or setmaxnreg.inc blocks forever.
+constexpr int kBaseRegs = 168;
+constexpr int kSoftmaxRegs = 216;
+constexpr int kOtherRegs = 72;
+static_assert(2 * (kSoftmaxRegs - kBaseRegs) <= (kBaseRegs - kOtherRegs),
+              "setmaxnreg.inc would wait for registers that are never released");
+
+template <int D, bool kBf16, bool kRegSplit>
 __global__ void __launch_bounds__(kThreads, 1)
 fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const FnaParams p) {
@@ -303,7 +312,7 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
   if (warp < 8) {
     // ======================= softmax + correction + epilogue ===============================
-    ptx::reg_alloc<216>();
+    if constexpr (kRegSplit) ptx::reg_alloc<kSoftmaxRegs>();
     const int half = warp >> 2;
     const int row = ((warp & 3) << 5) | lane;          // row inside the half = TMEM lane
     const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) << 5) << 16);
@@ -339,7 +348,9 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         int tc[B200NA_MAX_DIM];
         kv_tile_coord(p, it, iter, tc);
         const bool interior = kv_tile_interior(p, it, tc);
-        if (!wait_bar(bars.s_full + half, ph_s, abort_flag, p.status, (1 << 8) | kStSFull)) {
+        // warp-uniform outcome: the TMEM accesses below are warp-collective
+        if (!__all_sync(0xffffffffu, wait_bar(bars.s_full + half, ph_s, abort_flag, p.status,
+                                              (1 << 8) | kStSFull))) {
           alive = false;
           break;
         }
@@ -431,7 +442,9 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       }
       if (!alive) break;
       // ---- epilogue: O / sum -> global, LSE ----
-      if (!wait_bar(bars.o_full + half, ph_o, abort_flag, p.status, (1 << 8) | kStOFull)) break;
+      if (!__all_sync(0xffffffffu, wait_bar(bars.o_full + half, ph_o, abort_flag, p.status,
+                                            (1 << 8) | kStOFull)))
+        break;
       ph_o ^= 1;
       ptx::tc_fence_after_sync();
       const int q_row = it.qt * kQTile + half * kHalf + row;
@@ -460,9 +473,12 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       ptx::tc_fence_before_sync();
       ptx::mbar_arrive(bars.o_empty + half);
     }
-  } else if (warp == kMmaWarp) {
+  } else {
+    // Warps 8-11 form one warpgroup and must run the same register-release instruction.
+    if constexpr (kRegSplit) ptx::reg_dealloc<kOtherRegs>();
+  }
+  if (warp == kMmaWarp) {
     // =============================== MMA issue ==============================================
-    ptx::reg_dealloc<80>();
     if (lane == 0) {
       constexpr uint32_t idesc_qk = ptx::make_idesc(kBf16 ? 1 : 0, 0, 0, kHalf, kKVTile);
       constexpr uint32_t idesc_pv = ptx::make_idesc(kBf16 ? 1 : 0, 0, 1, kHalf, D);
@@ -554,10 +570,9 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
       }
     }
-  } else {
-    // ====================== TMA loads (warp 9); warps 10-11 only donate registers ===========
-    ptx::reg_dealloc<80>();
-    if (warp == kLoadWarp && lane == 0) {
+  } else if (warp == kLoadWarp) {
+    // ====================== TMA loads (warps 10-11 only donate registers) ===================
+    if (lane == 0) {
       uint32_t ph_qe = 1;
       uint32_t cnt = 0;
       bool alive = true;
@@ -655,8 +670,22 @@ int make_tensor_map(CUtensorMap* tm, const void* ptr, int dtype, int Bp, int S, 
   return B200NA_OK;
 }
 
+const void* kernel_variant(int D, bool bf16, bool reg_split) {
+  if (D == 128) {
+    if (bf16) return reg_split ? (const void*)fna_fwd_kernel<128, true, true>
+                               : (const void*)fna_fwd_kernel<128, true, false>;
+    return reg_split ? (const void*)fna_fwd_kernel<128, false, true>
+                     : (const void*)fna_fwd_kernel<128, false, false>;
+  }
+  if (bf16) return reg_split ? (const void*)fna_fwd_kernel<64, true, true>
+                             : (const void*)fna_fwd_kernel<64, true, false>;
+  return reg_split ? (const void*)fna_fwd_kernel<64, false, true>
+                   : (const void*)fna_fwd_kernel<64, false, false>;
+}
+
 struct DeviceState {
   bool ready = false;
+  bool reg_split_ok = true;
   int sms = 0;
   int* status_ptr = nullptr;
 };
@@ -675,14 +704,16 @@ int device_state(DeviceState** out) {
     B200NA_CUDA_TRY(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
     if (major != 10) return B200NA_ERR_DEVICE;
     B200NA_CUDA_TRY(cudaDeviceGetAttribute(&st.sms, cudaDevAttrMultiProcessorCount, dev));
-    B200NA_CUDA_TRY(cudaFuncSetAttribute(fna_fwd_kernel<128, true>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<128>::kBytes));
-    B200NA_CUDA_TRY(cudaFuncSetAttribute(fna_fwd_kernel<128, false>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<128>::kBytes));
-    B200NA_CUDA_TRY(cudaFuncSetAttribute(fna_fwd_kernel<64, true>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<64>::kBytes));
-    B200NA_CUDA_TRY(cudaFuncSetAttribute(fna_fwd_kernel<64, false>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<64>::kBytes));
+    for (int i = 0; i < 8; ++i) {
+      const void* fn = kernel_variant(i & 4 ? 128 : 64, (i & 2) != 0, (i & 1) != 0);
+      B200NA_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           i & 4 ? Smem<128>::kBytes : Smem<64>::kBytes));
+      cudaFuncAttributes fa;
+      B200NA_CUDA_TRY(cudaFuncGetAttributes(&fa, fn));
+      // the register re-partitioning is only safe when the launch allocation is what the
+      // static budget above assumes
+      if ((i & 1) && fa.numRegs != kBaseRegs) st.reg_split_ok = false;
+    }
     void* sp = nullptr;
     B200NA_CUDA_TRY(cudaGetSymbolAddress(&sp, g_status_word));
     st.status_ptr = reinterpret_cast<int*>(sp);
@@ -713,15 +744,11 @@ int launch_fna(const void* q, const void* k, const void* v, FnaParams& p, int D,
   p.total_work = (long long)p.n_qtiles * p.Hq * p.Bp;
   if (p.total_work == 0) return B200NA_OK;
   const int grid = (int)(p.total_work < st->sms ? p.total_work : st->sms);
-  const bool bf = dtype == B200NA_BF16;
-  if (D == 128) {
-    if (bf) fna_fwd_kernel<128, true><<<grid, kThreads, Smem<128>::kBytes, stream>>>(tq, tk, tv, p);
-    else fna_fwd_kernel<128, false><<<grid, kThreads, Smem<128>::kBytes, stream>>>(tq, tk, tv, p);
-  } else {
-    if (bf) fna_fwd_kernel<64, true><<<grid, kThreads, Smem<64>::kBytes, stream>>>(tq, tk, tv, p);
-    else fna_fwd_kernel<64, false><<<grid, kThreads, Smem<64>::kBytes, stream>>>(tq, tk, tv, p);
-  }
-  B200NA_CUDA_TRY(cudaGetLastError());
+  const bool reg_split = st->reg_split_ok && !(p.debug & 4);
+  const void* fn = kernel_variant(D, dtype == B200NA_BF16, reg_split);
+  void* args[] = {(void*)&tq, (void*)&tk, (void*)&tv, (void*)&p};
+  B200NA_CUDA_TRY(cudaLaunchKernel(fn, dim3(grid), dim3(kThreads),  args,
+                                   D == 128 ? Smem<128>::kBytes : Smem<64>::kBytes, stream));
   return B200NA_OK;
 }
 

@@ -108,8 +108,10 @@ def test_merge_matches_reference():
     for dtype, tol in ((torch.float32, 1e-6), (torch.bfloat16, 1e-2)):
         outs = [torch.from_numpy(z[f"merge/merge3/o{i}"]).cuda().to(dtype) for i in range(3)]
         lses = [torch.from_numpy(z[f"merge/merge3/l{i}"]).cuda() for i in range(3)]
-        o2, l2 = nb.merge_attentions(outs[:2], lses[:2])
         if dtype == torch.float32:
+            o2, l2 = nb.merge_attentions(
+                [torch.from_numpy(z[f"merge/merge2/o{i}"]).cuda() for i in range(2)],
+                [torch.from_numpy(z[f"merge/merge2/l{i}"]).cuda() for i in range(2)])
             assert np.abs(o2.cpu().numpy() - z["merge/merge2/out"]).max() <= tol
             assert np.abs(l2.cpu().numpy() - z["merge/merge2/lse"]).max() <= tol
         o3, l3 = nb.merge_attentions(outs, lses)
