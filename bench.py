@@ -237,17 +237,22 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--config", default="c2", choices=sorted(CONFIGS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--units", type=int, default=0,
+                    help="profiling aid: shrink the problem to this many (batch x head) units "
+                         "(batch 1); the printed line is then NOT a benchmark value")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
     cfg = CONFIGS[args.config]
+    if args.units:
+        cfg = cfg[:2] + (1, args.units) + cfg[4:]
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference_arm(args, cfg, rank)
         return
-    if args.warmup < 3:
+    if args.warmup < 3 and not args.units:
         args.warmup = 3
 
     import torch
@@ -369,7 +374,9 @@ def main():
         metric="FNA fwd effective TFLOPS (unmasked FLOPs)", value=value, unit="TFLOP/s",
         n_gpus=world, steps=args.steps, warmup=args.warmup, ms_per_step=ms_step,
         higher_is_better=True, scaling="strong", vs_baseline=None, dtype=dt, data="synthetic",
-        config=dict(workload=WORKLOAD_TEXT[args.config], partition="batch x heads",
+        config=dict(workload=WORKLOAD_TEXT[args.config] + (
+            f" [REDUCED to {args.units} (batch x head) units for profiling: not a benchmark value]"
+            if args.units else ""), partition="batch x heads",
                     units_per_gpu=b_local * h_local, l2="inputs larger than L2 (no flush needed)",
                     q_tile=list(q_tile), kv_tile=list(kv_tile)),
         clocks=clocks, gpu_launches=int(launches),

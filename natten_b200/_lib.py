@@ -9,7 +9,8 @@ import os
 from typing import Optional, Sequence
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "libnatten_b200.so")
+# NATTEN_B200_LIB overrides the library path (e.g. an instrumented build of the same sources).
+LIB_PATH = os.environ.get("NATTEN_B200_LIB") or os.path.join(_HERE, "lib", "libnatten_b200.so")
 
 OK = 0
 ERR_INVALID_ARGUMENT, ERR_UNSUPPORTED, ERR_ALIGNMENT, ERR_CUDA, ERR_DEVICE, ERR_KERNEL_TIMEOUT = (

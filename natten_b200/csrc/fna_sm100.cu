@@ -20,7 +20,6 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
-#include <cstdlib>
 #include <mutex>
 #include <type_traits>
 
@@ -39,6 +38,10 @@ constexpr int kLoadWarp = 9;
 constexpr int kTmemCols = 512;
 constexpr long long kWaitLimitCycles = 4000000000ll;  // ~2 s at 2 GHz
 constexpr float kRescaleThreshold = 8.0f;              // log2 units
+#ifndef B200NA_POLY_EVERY
+#define B200NA_POLY_EVERY 0
+#endif
+constexpr int kPolyEvery = B200NA_POLY_EVERY;  // every kPolyEvery-th pair of exponentials runs on the FMA pipes (0 = none)
 
 // status word: (role << 8) | barrier id, role 1 = softmax, 2 = mma, 3 = load, 4 = setup
 enum : int { kStSQFull = 1, kStSFull, kStPFull, kStOFull, kStOEmpty, kStKVFull, kStKVEmpty,
@@ -68,8 +71,38 @@ struct FnaParams {
   void* o;
   float* lse;
   int* status;
-  int debug;  // bring-up switches (0 in normal operation)
+#ifdef B200NA_PROFILE
+  long long* prof;  // [grid][4 roles][8] cycle counters (instrumented builds only)
+#endif
 };
+
+// Cycle-counter instrumentation, compiled only with -DB200NA_PROFILE (never in the product build).
+#ifdef B200NA_PROFILE
+#define TRACE(role, code) { if (blockIdx.x == 0 && trace_n_ < 1024) { p.prof[148 * 32 + (role) * 1024 + trace_n_] = (clock64() << 8) | (code); ++trace_n_; } }
+#define PROF_DECL int trace_n_ = 0; long long prof_[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long prof_t_ = clock64(); const long long prof_t0_ = prof_t_;
+#define PROF_MARK(i) { const long long n_ = clock64(); prof_[i] += n_ - prof_t_; prof_t_ = n_; }
+#define PROF_FLUSH(role) { prof_[7] = clock64() - prof_t0_; for (int i_ = 0; i_ < 8; ++i_) p.prof[((long long)blockIdx.x * 4 + (role)) * 8 + i_] = prof_[i_]; }
+#if B200NA_PROFILE >= 2
+#define TRACE2(role, code) TRACE(role, code)
+#define PROF2_DECL PROF_DECL
+#define PROF2_MARK(i) PROF_MARK(i)
+#define PROF2_FLUSH(role) PROF_FLUSH(role)
+#else
+#define TRACE2(role, code) {}
+#define PROF2_DECL
+#define PROF2_MARK(i) {}
+#define PROF2_FLUSH(role) {}
+#endif
+#else
+#define TRACE2(role, code) {}
+#define PROF2_DECL
+#define PROF2_MARK(i) {}
+#define PROF2_FLUSH(role) {}
+#define TRACE(role, code) {}
+#define PROF_DECL
+#define PROF_MARK(i) {}
+#define PROF_FLUSH(role) {}
+#endif
 
 struct Item {
   int bp, h, hk, qt;
@@ -171,6 +204,18 @@ struct Smem {
   static constexpr int kBytes = kMiscOff + 16;
 };
 
+// Position in the K/V ring: slot index and the phase parity of that slot's barriers.
+template <int kStages>
+struct RingPos {
+  uint32_t slot = 0, phase = 0;
+  __device__ __forceinline__ void advance() {
+    if (++slot == kStages) {
+      slot = 0;
+      phase ^= 1;
+    }
+  }
+};
+
 struct Bars {
   uint64_t* q_full;
   uint64_t* q_empty;
@@ -213,8 +258,12 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 // warps then release down to kOtherRegs and the eight softmax warps grow to kSoftmaxRegs. The
 // growth must fit in what was released or setmaxnreg.inc blocks forever.
 constexpr int kBaseRegs = 168;
-constexpr int kSoftmaxRegs = 216;
-constexpr int kOtherRegs = 72;
+#ifndef B200NA_SOFTMAX_REGS
+#define B200NA_SOFTMAX_REGS 216
+#define B200NA_OTHER_REGS 72
+#endif
+constexpr int kSoftmaxRegs = B200NA_SOFTMAX_REGS;
+constexpr int kOtherRegs = B200NA_OTHER_REGS;
 static_assert(2 * (kSoftmaxRegs - kBaseRegs) <= (kBaseRegs - kOtherRegs),
               "setmaxnreg.inc would wait for registers that are never released");
 
@@ -323,6 +372,7 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     typedef typename std::conditional<kBf16, __nv_bfloat16, __half>::type T;
     T* o_ptr = reinterpret_cast<T*>(p.o);
 
+    PROF_DECL
     for (long long w = blockIdx.x; w < p.total_work; w += gridDim.x) {
       Item it;
       decode_item(p, w, it);
@@ -355,11 +405,14 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           break;
         }
         ph_s ^= 1;
+        PROF_MARK(0)
+        if (row == 0) TRACE(half, 1)
         ptx::tc_fence_after_sync();
         uint32_t sr[4][32];
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) ptx::tmem_ld32(s_addr + q4 * 32, sr[q4]);
         ptx::tmem_ld_wait();
+        PROF_MARK(1)
         if (!interior) {
           uint4 mk = make_uint4(~0u, ~0u, ~0u, ~0u);
           int off = 0;
@@ -387,14 +440,14 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
               if (!((mw[q4] >> j) & 1u)) sr[q4][j] = 0xff800000u;  // -inf
           }
         }
-        // row maximum of the raw logits
+        // row maximum of the raw logits (3-input max, four independent chains)
         float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          mx0 = fmaxf(mx0, __uint_as_float(sr[0][j]));
-          mx1 = fmaxf(mx1, __uint_as_float(sr[1][j]));
-          mx2 = fmaxf(mx2, __uint_as_float(sr[2][j]));
-          mx3 = fmaxf(mx3, __uint_as_float(sr[3][j]));
+        for (int j = 0; j < 32; j += 2) {
+          mx0 = ptx::max3(mx0, __uint_as_float(sr[0][j]), __uint_as_float(sr[0][j + 1]));
+          mx1 = ptx::max3(mx1, __uint_as_float(sr[1][j]), __uint_as_float(sr[1][j + 1]));
+          mx2 = ptx::max3(mx2, __uint_as_float(sr[2][j]), __uint_as_float(sr[2][j + 1]));
+          mx3 = ptx::max3(mx3, __uint_as_float(sr[3][j]), __uint_as_float(sr[3][j + 1]));
         }
         const float m_new = fmaxf(fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)), m);
         // Lazy rescale: keep the stale maximum while the true one is at most 2^8 larger.
@@ -419,26 +472,52 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           }
         }
         const float neg_mc = (m == -INFINITY) ? 0.f : -m * c;
-        float sm0 = 0.f, sm1 = 0.f;
+        // p = 2^(s*c - m*c): packed fp32x2 multiply-add, then the exponential on the special
+        // function unit for one pair and on the FMA pipes for the next (kPolyEvery), so that
+        // neither pipe alone bounds the softmax.
+        const uint64_t c2 = ptx::pack_f2(c, c);
+        const uint64_t nmc2 = ptx::pack_f2(neg_mc, neg_mc);
+        uint64_t sum2a = ptx::pack_f2(0.f, 0.f), sum2b = sum2a;
         uint32_t pk[2][32];
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
 #pragma unroll
           for (int j = 0; j < 32; j += 2) {
-            const float p0 = ptx::ex2(fmaf(__uint_as_float(sr[q4][j]), c, neg_mc));
-            const float p1 = ptx::ex2(fmaf(__uint_as_float(sr[q4][j + 1]), c, neg_mc));
-            sm0 += p0;
-            sm1 += p1;
-            pk[q4 >> 1][((q4 & 1) << 4) + (j >> 1)] =
-                (p.debug & 2) ? pack2<kBf16>(p1, p0) : pack2<kBf16>(p0, p1);
+            const uint64_t t2 = ptx::fma2(
+                ptx::pack_f2(__uint_as_float(sr[q4][j]), __uint_as_float(sr[q4][j + 1])), c2, nmc2);
+            float p0, p1;
+            if (kPolyEvery > 0 && ((j >> 1) % (kPolyEvery > 0 ? kPolyEvery : 1)) == kPolyEvery - 1) {
+              ptx::ex2_poly2(t2, p0, p1);
+            } else {
+              float t0, t1;
+              ptx::unpack_f2(t2, t0, t1);
+#ifdef B200NA_EXPERIMENT_NO_EX2
+              p0 = t0 * 0.001f;
+              p1 = t1 * 0.001f;
+#else
+              p0 = ptx::ex2(t0);
+              p1 = ptx::ex2(t1);
+#endif
+            }
+            if ((j >> 1) & 1) sum2a = ptx::add2(sum2a, ptx::pack_f2(p0, p1));
+            else sum2b = ptx::add2(sum2b, ptx::pack_f2(p0, p1));
+            pk[q4 >> 1][((q4 & 1) << 4) + (j >> 1)] = pack2<kBf16>(p0, p1);
           }
         }
-        sum += sm0 + sm1;
+        {
+          float a0, a1, b0, b1;
+          ptx::unpack_f2(sum2a, a0, a1);
+          ptx::unpack_f2(sum2b, b0, b1);
+          sum += (a0 + a1) + (b0 + b1);
+        }
+        PROF_MARK(2)
         ptx::tmem_st32(s_addr, pk[0]);
         ptx::tmem_st32(s_addr + 32, pk[1]);
         ptx::tmem_st_wait();
         ptx::tc_fence_before_sync();
         ptx::mbar_arrive(bars.p_full + half);
+        PROF_MARK(3)
+        if (row == 0) TRACE(half, 2)
       }
       if (!alive) break;
       // ---- epilogue: O / sum -> global, LSE ----
@@ -446,6 +525,8 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                                             (1 << 8) | kStOFull)))
         break;
       ph_o ^= 1;
+      PROF_MARK(4)
+      if (row == 0) TRACE(half, 3)
       ptx::tc_fence_after_sync();
       const int q_row = it.qt * kQTile + half * kHalf + row;
       const bool valid = q_row < p.Sq;
@@ -472,7 +553,10 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         p.lse[((long long)it.bp * p.Sq + q_row) * p.Hq + it.h] = logf(sum) + m * p.scale;
       ptx::tc_fence_before_sync();
       ptx::mbar_arrive(bars.o_empty + half);
+      PROF_MARK(5)
+      if (row == 0) TRACE(half, 4)
     }
+    if (row == 0) { PROF_FLUSH(half) }
   } else {
     // Warps 8-11 form one warpgroup and must run the same register-release instruction.
     if constexpr (kRegSplit) ptx::reg_dealloc<kOtherRegs>();
@@ -483,43 +567,58 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       constexpr uint32_t idesc_qk = ptx::make_idesc(kBf16 ? 1 : 0, 0, 0, kHalf, kKVTile);
       constexpr uint32_t idesc_pv = ptx::make_idesc(kBf16 ? 1 : 0, 0, 1, kHalf, D);
       uint32_t ph_q = 0, ph_p[2] = {0, 0}, ph_oe[2] = {1, 1};
-      uint32_t cnt = 0;  // kv ring counter (K and V tiles in load order)
+      RingPos<kStages> ring;  // K and V tiles in load order
       const uint32_t q_base = ptx::smem_u32(q_sm);
       const uint32_t kv_base = ptx::smem_u32(kv_sm);
       bool alive = true;
 
+      // Descriptors are kept as (low, high) words: the high word is one constant, the low word
+      // of a tile is computed once and each K step adds a compile-time offset to it. The issuing
+      // thread runs alone in its warp, so every instruction here is on the critical path.
+      constexpr uint32_t desc_hi = ptx::smem_desc_hi_sw128();
+      const uint32_t q_lo[2] = {ptx::smem_desc_lo(q_base, 16),
+                                ptx::smem_desc_lo(q_base + kTileBytes, 16)};
+      const uint32_t s_tm[2] = {tmem_base + s_col(0), tmem_base + s_col(1)};
+      const uint32_t o_tm[2] = {tmem_base + o_col(0), tmem_base + o_col(1)};
+
       auto issue_qk = [&](int half, uint32_t k_addr) {
+        const uint32_t a_lo = half ? q_lo[1] : q_lo[0];
+        const uint32_t b_lo = ptx::smem_desc_lo(k_addr, 16);
+        const uint32_t d = half ? s_tm[1] : s_tm[0];
 #pragma unroll
         for (int kb = 0; kb < D / 16; ++kb) {
-          const uint32_t koff = (kb >> 2) * kBlockBytes + (kb & 3) * 32;
-          const uint64_t a = ptx::smem_desc_sw128(q_base + half * kTileBytes + koff, 16);
-          const uint64_t b = ptx::smem_desc_sw128(k_addr + koff, 16);
-          ptx::mma_ss(tmem_base + s_col(half), a, b, idesc_qk, kb > 0 ? 1u : 0u);
+          const uint32_t koff = ((kb >> 2) * kBlockBytes + (kb & 3) * 32) >> 4;
+          ptx::mma_ss_lohi(d, a_lo + koff, desc_hi, b_lo + koff, desc_hi, idesc_qk,
+                           kb > 0 ? 1u : 0u);
         }
       };
       auto issue_pv = [&](int half, uint32_t v_addr, bool first) {
+        const uint32_t b_lo = ptx::smem_desc_lo(v_addr, kBlockBytes);
+        const uint32_t d = half ? o_tm[1] : o_tm[0];
+        const uint32_t a = half ? s_tm[1] : s_tm[0];
+        ptx::mma_ts_lohi(d, a, b_lo, desc_hi, idesc_pv, first ? 0u : 1u);
 #pragma unroll
-        for (int ks = 0; ks < kKVTile / 16; ++ks) {
-          const uint64_t b = (p.debug & 1)
-                                 ? ptx::smem_desc_sw128(v_addr + ks * 2048, 1024u, kBlockBytes)
-                                 : ptx::smem_desc_sw128(v_addr + ks * 2048, kBlockBytes, 1024u);
-          ptx::mma_ts(tmem_base + o_col(half), tmem_base + s_col(half) + ks * 8, b, idesc_pv,
-                      (first && ks == 0) ? 0u : 1u);
-        }
+        for (int ks = 1; ks < kKVTile / 16; ++ks)
+          ptx::mma_ts_lohi(d, a + ks * 8, b_lo + ks * (2048 >> 4), desc_hi, idesc_pv, 1u);
       };
 
+      PROF2_DECL
       for (long long w = blockIdx.x; w < p.total_work && alive; w += gridDim.x) {
         Item it;
         decode_item(p, w, it);
         if (it.skip) continue;
         const int n = it.n_tiles;
+        PROF2_MARK(6)
         if (!wait_bar(bars.q_full, ph_q, abort_flag, p.status, (2 << 8) | kStSQFull)) break;
         ph_q ^= 1;
+        PROF2_MARK(0)
+        TRACE2(2, 10)
         // tile 0: S_h = Q_h K0^T for both halves
-        uint32_t slot_k = cnt % kStages;
-        if (!wait_bar(bars.kv_full + slot_k, (cnt / kStages) & 1, abort_flag, p.status,
+        const uint32_t slot_k = ring.slot;
+        if (!wait_bar(bars.kv_full + slot_k, ring.phase, abort_flag, p.status,
                       (2 << 8) | kStKVFull)) break;
-        ++cnt;
+        ring.advance();
+        PROF2_MARK(1)
         ptx::tc_fence_after_sync();
         for (int h = 0; h < 2; ++h) {
           issue_qk(h, kv_base + slot_k * kTileBytes);
@@ -528,10 +627,12 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         ptx::tc_commit(bars.kv_empty + slot_k);
         if (n == 1) ptx::tc_commit(bars.q_empty);
         for (int iter = 0; iter < n && alive; ++iter) {
-          const uint32_t slot_v = cnt % kStages;
-          if (!wait_bar(bars.kv_full + slot_v, (cnt / kStages) & 1, abort_flag, p.status,
+          const uint32_t slot_v = ring.slot;
+          if (!wait_bar(bars.kv_full + slot_v, ring.phase, abort_flag, p.status,
                         (2 << 8) | kStKVFull)) { alive = false; break; }
-          ++cnt;
+          ring.advance();
+          PROF2_MARK(1)
+          TRACE2(2, 11)
           const bool more = iter + 1 < n;
           uint32_t slot_kn = 0;
           for (int h = 0; h < 2; ++h) {
@@ -539,24 +640,31 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
               alive = false; break;
             }
             ph_p[h] ^= 1;
+            if (h == 0) { PROF2_MARK(2) } else { PROF2_MARK(3) }
+            TRACE2(2, 12 + h)
             if (iter == 0) {
               // the previous item's epilogue must have drained O_h before it is overwritten
               if (!wait_bar(bars.o_empty + h, ph_oe[h], abort_flag, p.status,
                             (2 << 8) | kStOEmpty)) { alive = false; break; }
               ph_oe[h] ^= 1;
+              PROF2_MARK(4)
             }
             ptx::tc_fence_after_sync();
             issue_pv(h, kv_base + slot_v * kTileBytes, iter == 0);
+            TRACE2(2, 14 + h)
             if (more) {
               if (h == 0) {
-                slot_kn = cnt % kStages;
-                if (!wait_bar(bars.kv_full + slot_kn, (cnt / kStages) & 1, abort_flag, p.status,
+                slot_kn = ring.slot;
+                if (!wait_bar(bars.kv_full + slot_kn, ring.phase, abort_flag, p.status,
                               (2 << 8) | kStKVFull)) { alive = false; break; }
-                ++cnt;
+                ring.advance();
+                PROF2_MARK(5)
+                TRACE2(2, 16)
                 ptx::tc_fence_after_sync();
               }
               issue_qk(h, kv_base + slot_kn * kTileBytes);
               ptx::tc_commit(bars.s_full + h);
+              TRACE2(2, 17 + h)
             } else {
               ptx::tc_commit(bars.o_full + h);
             }
@@ -567,21 +675,26 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             ptx::tc_commit(bars.kv_empty + slot_kn);
             if (iter + 2 == n) ptx::tc_commit(bars.q_empty);  // last Q.K^T has been issued
           }
+          PROF2_MARK(6)
         }
       }
+      PROF2_FLUSH(2)
     }
   } else if (warp == kLoadWarp) {
     // ====================== TMA loads (warps 10-11 only donate registers) ===================
     if (lane == 0) {
       uint32_t ph_qe = 1;
-      uint32_t cnt = 0;
+      RingPos<kStages> ring;
       bool alive = true;
+      PROF2_DECL
       for (long long w = blockIdx.x; w < p.total_work && alive; w += gridDim.x) {
         Item it;
         decode_item(p, w, it);
         if (it.skip) continue;
+        PROF2_MARK(6)
         if (!wait_bar(bars.q_empty, ph_qe, abort_flag, p.status, (3 << 8) | kStQEmpty)) break;
         ph_qe ^= 1;
+        PROF2_MARK(0)
         ptx::mbar_arrive_expect_tx(bars.q_full, 2 * kTileBytes);
         for (int h = 0; h < 2; ++h)
           for (int db = 0; db < kDBlocks; ++db)
@@ -592,17 +705,21 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           kv_tile_coord(p, it, iter, tc);
           const int row0 = kv_tile_row(p, tc);
           for (int kv = 0; kv < 2; ++kv) {
-            const uint32_t slot = cnt % kStages;
-            if (!wait_bar(bars.kv_empty + slot, ((cnt / kStages) & 1) ^ 1, abort_flag, p.status,
+            const uint32_t slot = ring.slot;
+            if (!wait_bar(bars.kv_empty + slot, ring.phase ^ 1, abort_flag, p.status,
                           (3 << 8) | kStKVEmpty)) { alive = false; break; }
-            ++cnt;
+            ring.advance();
+            PROF2_MARK(1)
+            TRACE2(3, 20 + kv)
             ptx::mbar_arrive_expect_tx(bars.kv_full + slot, kTileBytes);
             for (int db = 0; db < kDBlocks; ++db)
               ptx::tma_load_4d(kv_sm + slot * kTileBytes + db * kBlockBytes, kv == 0 ? &tm_k : &tm_v,
                                bars.kv_full + slot, db * 64, it.hk, row0, it.bp);
+            PROF2_MARK(6)
           }
         }
       }
+      PROF2_FLUSH(3)
     }
   }
 
@@ -724,6 +841,10 @@ int device_state(DeviceState** out) {
   return B200NA_OK;
 }
 
+#ifdef B200NA_PROFILE
+long long* g_prof_buffer = nullptr;
+#endif
+
 int launch_fna(const void* q, const void* k, const void* v, FnaParams& p, int D, int dtype,
                cudaStream_t stream) {
   DeviceState* st = nullptr;
@@ -736,15 +857,18 @@ int launch_fna(const void* q, const void* k, const void* v, FnaParams& p, int D,
   if ((rc = make_tensor_map(&tq, q, dtype, p.Bp, p.Sq, p.Hq, D)) != B200NA_OK) return rc;
   if ((rc = make_tensor_map(&tk, k, dtype, p.Bp, p.Skv, p.Hkv, D)) != B200NA_OK) return rc;
   if ((rc = make_tensor_map(&tv, v, dtype, p.Bp, p.Skv, p.Hkv, D)) != B200NA_OK) return rc;
-  {
-    const char* dbg = getenv("B200NA_DEBUG");
-    p.debug = dbg ? atoi(dbg) : 0;
-  }
   p.status = st->status_ptr;
+#ifdef B200NA_PROFILE
+  p.prof = g_prof_buffer;
+#endif
   p.total_work = (long long)p.n_qtiles * p.Hq * p.Bp;
   if (p.total_work == 0) return B200NA_OK;
   const int grid = (int)(p.total_work < st->sms ? p.total_work : st->sms);
-  const bool reg_split = st->reg_split_ok && !(p.debug & 4);
+#ifdef B200NA_EXPERIMENT_NO_SPLIT
+  const bool reg_split = false;
+#else
+  const bool reg_split = st->reg_split_ok;
+#endif
   const void* fn = kernel_variant(D, dtype == B200NA_BF16, reg_split);
   void* args[] = {(void*)&tq, (void*)&tk, (void*)&tv, (void*)&p};
   B200NA_CUDA_TRY(cudaLaunchKernel(fn, dim3(grid), dim3(kThreads),  args,
@@ -844,6 +968,13 @@ extern "C" B200NA_API int b200na_fmha_forward(const void* q, const void* k, cons
   p.lse = lse;
   return launch_fna(q, k, v, p, D, dtype, reinterpret_cast<cudaStream_t>(stream));
 }
+
+#ifdef B200NA_PROFILE
+// Instrumented builds only: device buffer of [grid][4][8] int64 cycle counters.
+extern "C" B200NA_API void b200na_debug_set_prof(void* buf) {
+  b200na::g_prof_buffer = reinterpret_cast<long long*>(buf);
+}
+#endif
 
 extern "C" B200NA_API int b200na_device_status(int* status) {
   using namespace b200na;

@@ -122,6 +122,40 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_
       : "memory");
 }
 
+// Same MMAs with the 64-bit descriptors passed as (lo, hi) halves: the issuing thread keeps the
+// constant high word in a register and only adds a small offset to the low word per K step.
+__device__ __forceinline__ void mma_ss_lohi(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi,
+                                            uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}\n"
+      ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_ts_lohi(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo,
+                                            uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}\n"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Low / high words of the 128-byte-swizzle descriptor below (low: address and leading offset;
+// high: stride offset 1024 B, version, layout). Addresses are < 256 KB, so adding a byte offset
+// >> 4 to the low word never carries into the leading-offset field.
+__device__ __forceinline__ uint32_t smem_desc_lo(uint32_t smem_addr, uint32_t lbo_bytes) {
+  return ((smem_addr & 0x3FFFFu) >> 4) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
+}
+__host__ __device__ constexpr uint32_t smem_desc_hi_sw128() {
+  return ((1024u >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
+}
+
 // Shared-memory matrix descriptor (64-bit) for a 128-byte-swizzled operand tile whose rows are
 // 128 bytes wide and packed back to back (what a TMA load with SWIZZLE_128B and a 64-element
 // 16-bit inner box produces): 8-row groups are 1024 bytes apart (stride byte offset), and
@@ -192,11 +226,62 @@ __device__ __forceinline__ void reg_dealloc() {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
 }
 
+// ---- packed fp32x2 arithmetic (two floats in one 64-bit register; one issue slot) -----------
+__device__ __forceinline__ uint64_t pack_f2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// 2^x for a pair of values on the FMA/ALU pipes instead of the special-function unit:
+// x = n + f with n = round(x), f in [-0.5, 0.5]; 2^f by a degree-3 polynomial (max relative
+// error 7.5e-5, far below the 16-bit precision P is rounded to), 2^n by adding n to the exponent
+// field. Inputs below -126 (including -inf for masked logits) clamp to 2^-126 ~ 1e-38.
+__device__ __forceinline__ void ex2_poly2(uint64_t x2, float& r0, float& r1) {
+  float x0, x1;
+  unpack_f2(x2, x0, x1);
+  x0 = fmaxf(x0, -126.f);
+  x1 = fmaxf(x1, -126.f);
+  x2 = pack_f2(x0, x1);
+  const uint64_t magic = pack_f2(12582912.f, 12582912.f);      // 1.5 * 2^23
+  const uint64_t neg_magic = pack_f2(-12582912.f, -12582912.f);
+  const uint64_t neg_one = pack_f2(-1.f, -1.f);
+  const uint64_t t2 = add2(x2, magic);                         // low mantissa bits = round(x)
+  const uint64_t n2 = add2(t2, neg_magic);                     // round(x) as float
+  const uint64_t f2 = fma2(n2, neg_one, x2);                   // x - round(x)
+  uint64_t p2 = fma2(pack_f2(0.0551716648f, 0.0551716648f), f2, pack_f2(0.2426111251f, 0.2426111251f));
+  p2 = fma2(p2, f2, pack_f2(0.6932609677f, 0.6932609677f));
+  p2 = fma2(p2, f2, pack_f2(0.9999280572f, 0.9999280572f));
+  float t0, t1, p0, p1;
+  unpack_f2(t2, t0, t1);
+  unpack_f2(p2, p0, p1);
+  r0 = __int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23));
+  r1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
+}
+
 __device__ __forceinline__ float lg2(float x) {
   float y;
   asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
