@@ -32,15 +32,23 @@ namespace {
 constexpr int kQTile = 256;      // query rows per CTA work item
 constexpr int kHalf = 128;       // rows per softmax warpgroup / per MMA (M)
 constexpr int kKVTile = 128;     // key/value rows per tile (N of QK^T, K of P.V)
-constexpr int kThreads = 384;    // 8 softmax warps + MMA warp + load warp + 2 idle warps
-constexpr int kMmaWarp = 8;
-constexpr int kLoadWarp = 9;
+constexpr int kSoftmaxWarps = 16; // 2 halves x 2 column parts x 4 warps (one thread per row and part)
+constexpr int kSoftmaxThreadsPerHalf = 256;
+constexpr int kMmaWarp = 16;
+constexpr int kLoadWarp = 17;
+constexpr int kThreads = 576;    // 16 softmax warps + MMA warp + load warp
+// Registers are allocated to warps in groups of four, so 18 warps cost as much as 20: the
+// per-thread ceiling is 65536 / 640 = 102 -> 96, which the streaming softmax loop fits into.
 constexpr int kTmemCols = 512;
 constexpr long long kWaitLimitCycles = 4000000000ll;  // ~2 s at 2 GHz
 constexpr float kRescaleThreshold = 8.0f;              // log2 units
 #ifndef B200NA_POLY_EVERY
 #define B200NA_POLY_EVERY 0
 #endif
+#ifndef B200NA_EXP_MIXED
+#define B200NA_EXP_MIXED 0
+#endif
+constexpr bool kExpMixed = B200NA_EXP_MIXED != 0;  // interleaved 50/50 special-function / polynomial exp2
 constexpr int kPolyEvery = B200NA_POLY_EVERY;  // every kPolyEvery-th pair of exponentials runs on the FMA pipes (0 = none)
 
 // status word: (role << 8) | barrier id, role 1 = softmax, 2 = mma, 3 = load, 4 = setup
@@ -127,6 +135,7 @@ __device__ __forceinline__ void axis_window(const FnaParams& p, int a, int i, in
   }
 }
 
+template <int NDIM>
 __device__ __forceinline__ void decode_item(const FnaParams& p, long long w, Item& it) {
   it.qt = (int)(w % p.n_qtiles);
   const long long rest = w / p.n_qtiles;
@@ -139,7 +148,7 @@ __device__ __forceinline__ void decode_item(const FnaParams& p, long long w, Ite
   it.skip = false;
 #pragma unroll
   for (int a = 0; a < B200NA_MAX_DIM; ++a) {
-    if (a < p.ndim) {
+    if (a < NDIM) {
       const int g = gl % p.dil[a];
       gl /= p.dil[a];
       it.L[a] = p.dense ? p.Skv : group_extent(p.X[a], p.dil[a], g);
@@ -163,25 +172,20 @@ __device__ __forceinline__ void decode_item(const FnaParams& p, long long w, Ite
   if (p.dense && it.qt * kQTile >= p.Sq) it.skip = true;
 }
 
-// Tile coordinates (tile units) of the `iter`-th kv tile of an item, colexicographic walk.
-__device__ __forceinline__ void kv_tile_coord(const FnaParams& p, const Item& it, int iter,
-                                              int (&c)[B200NA_MAX_DIM]) {
-#pragma unroll
-  for (int a = 0; a < B200NA_MAX_DIM; ++a) {
-    c[a] = it.kv_t0[a] + iter % it.kv_n[a];
-    iter /= it.kv_n[a];
-  }
-}
+template <int NDIM>
 __device__ __forceinline__ int kv_tile_row(const FnaParams& p, const int (&c)[B200NA_MAX_DIM]) {
+  if (NDIM == 1) return c[0] * kKVTile;
+  if (NDIM == 2) return (c[0] + p.Rkv[0] * c[1]) * kKVTile;
   return (c[0] + p.Rkv[0] * (c[1] + p.Rkv[1] * c[2])) * kKVTile;
 }
 // True when every key of the tile lies inside the window of every query of the item.
+template <int NDIM>
 __device__ __forceinline__ bool kv_tile_interior(const FnaParams& p, const Item& it,
                                                  const int (&c)[B200NA_MAX_DIM]) {
   bool in = true;
 #pragma unroll
   for (int a = 0; a < B200NA_MAX_DIM; ++a) {
-    if (a < p.ndim) {
+    if (a < NDIM) {
       const int lo = c[a] * p.Tkv[a];
       in = in && (lo >= it.ws_hi[a]) && (lo + p.Tkv[a] <= it.we_lo[a]);
     }
@@ -197,7 +201,9 @@ struct Smem {
   static constexpr int kKVOff = 2 * kTileBytes;
   static constexpr int kPrefOff = kKVOff + kStages * kTileBytes;
   static constexpr int kPrefEntries = 136;                  // sum(T_a + 1) <= 128 + 1 + 2 + 2
-  static constexpr int kBarOff = kPrefOff + kPrefEntries * 16;
+  static constexpr int kXchgOff = kPrefOff + kPrefEntries * 16;   // row max / row sum exchange
+  static constexpr int kXchgBytes = (2 * 2 * 2 + 2 * 2) * kHalf * 4;
+  static constexpr int kBarOff = kXchgOff + kXchgBytes;
   // barriers: q_full, q_empty, s_full[2], p_full[2], o_full[2], o_empty[2], kv_full[S], kv_empty[S]
   static constexpr int kNumBars = 10 + 2 * kStages;
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;
@@ -254,20 +260,29 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   }
 }
 
-// Register budget: 384 threads are launched with kBaseRegs registers each; the four non-softmax
-// warps then release down to kOtherRegs and the eight softmax warps grow to kSoftmaxRegs. The
-// growth must fit in what was released or setmaxnreg.inc blocks forever.
-constexpr int kBaseRegs = 168;
-#ifndef B200NA_SOFTMAX_REGS
-#define B200NA_SOFTMAX_REGS 216
-#define B200NA_OTHER_REGS 72
-#endif
-constexpr int kSoftmaxRegs = B200NA_SOFTMAX_REGS;
-constexpr int kOtherRegs = B200NA_OTHER_REGS;
-static_assert(2 * (kSoftmaxRegs - kBaseRegs) <= (kBaseRegs - kOtherRegs),
-              "setmaxnreg.inc would wait for registers that are never released");
+__device__ __forceinline__ void named_bar_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
 
-template <int D, bool kBf16, bool kRegSplit>
+// Advances the colexicographic kv-tile walk by one tile (no divisions on the per-tile path).
+template <int NDIM>
+__device__ __forceinline__ void kv_tile_next(const Item& it, int (&c)[B200NA_MAX_DIM]) {
+  if (NDIM == 1) {
+    ++c[0];
+    return;
+  }
+  if (++c[0] < it.kv_t0[0] + it.kv_n[0]) return;
+  c[0] = it.kv_t0[0];
+  if (NDIM == 2) {
+    ++c[1];
+    return;
+  }
+  if (++c[1] < it.kv_t0[1] + it.kv_n[1]) return;
+  c[1] = it.kv_t0[1];
+  ++c[2];
+}
+
+template <int D, bool kBf16, int NDIM>
 __global__ void __launch_bounds__(kThreads, 1)
 fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const FnaParams p) {
@@ -281,6 +296,8 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   uint8_t* q_sm = smem + SM::kQOff;
   uint8_t* kv_sm = smem + SM::kKVOff;
   uint4* pref = reinterpret_cast<uint4*>(smem + SM::kPrefOff);
+  float* xmax = reinterpret_cast<float*>(smem + SM::kXchgOff);        // [2 parity][2 half][2 part][128]
+  float* xsum = xmax + 2 * 2 * 2 * kHalf;                             // [2 half][2 part][128]
   uint64_t* bar_base = reinterpret_cast<uint64_t*>(smem + SM::kBarOff);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SM::kMiscOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM::kMiscOff + 4);
@@ -309,9 +326,9 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     ptx::mbar_init(bars.q_empty, 1);
     for (int h = 0; h < 2; ++h) {
       ptx::mbar_init(bars.s_full + h, 1);
-      ptx::mbar_init(bars.p_full + h, kHalf);
+      ptx::mbar_init(bars.p_full + h, kSoftmaxThreadsPerHalf);
       ptx::mbar_init(bars.o_full + h, 1);
-      ptx::mbar_init(bars.o_empty + h, kHalf);
+      ptx::mbar_init(bars.o_empty + h, kSoftmaxThreadsPerHalf);
     }
     for (int s = 0; s < kStages; ++s) {
       ptx::mbar_init(bars.kv_full + s, 1);
@@ -331,6 +348,7 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #pragma unroll
         for (int wd = 0; wd < 4; ++wd) {
           uint32_t bits = 0;
+#pragma unroll 1
           for (int j = 0; j < 32; ++j) {
             const int t = ((wd * 32 + j) / below) % p.Tkv[a];
             if (t < x) bits |= 1u << j;
@@ -359,45 +377,56 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   auto s_col = [](int half) -> uint32_t { return (uint32_t)half * 128u; };
   auto o_col = [](int half) -> uint32_t { return 256u + (uint32_t)half * 128u; };
 
-  if (warp < 8) {
+  if (warp < kSoftmaxWarps) {
     // ======================= softmax + correction + epilogue ===============================
-    if constexpr (kRegSplit) ptx::reg_alloc<kSoftmaxRegs>();
-    const int half = warp >> 2;
+    // Two threads share a query row: `part` 0 owns key columns [0, 64) of every tile and output
+    // columns [0, D/2), `part` 1 the other halves. A lone warp cannot keep a sub-partition's
+    // issue slots busy, so halving the per-thread work halves the softmax latency that sits
+    // between the two MMAs of a half.
+    const int half = warp >> 3;
+    const int part = (warp >> 2) & 1;
     const int row = ((warp & 3) << 5) | lane;          // row inside the half = TMEM lane
     const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) << 5) << 16);
     const uint32_t s_addr = lane_addr + s_col(half);
-    const uint32_t o_addr = lane_addr + o_col(half);
+    const uint32_t my_s = s_addr + part * 64;                 // my 64 fp32 logit columns
+    const uint32_t my_p = s_addr + part * 64;                 // my 32 packed P columns (in place)
+    const uint32_t my_o = lane_addr + o_col(half) + part * (D / 2);
+    const int bar_id = 1 + half;
     const float c = p.scale_log2;
     uint32_t ph_s = 0, ph_o = 0;
     typedef typename std::conditional<kBf16, __nv_bfloat16, __half>::type T;
     T* o_ptr = reinterpret_cast<T*>(p.o);
+    // in-tile coordinates of this thread's query row (fixed for the whole kernel)
+    int tq[B200NA_MAX_DIM];
+    {
+      int rl = half * kHalf + row;
+#pragma unroll
+      for (int a = 0; a < B200NA_MAX_DIM; ++a) {
+        tq[a] = (a < NDIM) ? rl % p.Tq[a] : 0;
+        rl /= (a < NDIM) ? p.Tq[a] : 1;
+      }
+    }
 
     PROF_DECL
     for (long long w = blockIdx.x; w < p.total_work; w += gridDim.x) {
       Item it;
-      decode_item(p, w, it);
+      decode_item<NDIM>(p, w, it);
       if (it.skip) continue;
       // window of this thread's query row
       int ws[B200NA_MAX_DIM], we[B200NA_MAX_DIM];
-      {
-        int rl = half * kHalf + row;
 #pragma unroll
-        for (int a = 0; a < B200NA_MAX_DIM; ++a) {
-          if (a < p.ndim) {
-            const int t = rl % p.Tq[a];
-            rl /= p.Tq[a];
-            axis_window(p, a, it.q_lo[a] + t, it.L[a], ws[a], we[a]);
-          } else {
-            ws[a] = 0; we[a] = 1;
-          }
+      for (int a = 0; a < B200NA_MAX_DIM; ++a) {
+        if (a < NDIM) {
+          axis_window(p, a, it.q_lo[a] + tq[a], it.L[a], ws[a], we[a]);
+        } else {
+          ws[a] = 0; we[a] = 1;
         }
       }
-      float m = -INFINITY, sum = 0.f;
+      float m = -INFINITY, sum = 0.f;   // sum covers this thread's columns only
       bool alive = true;
+      int tc[B200NA_MAX_DIM] = {it.kv_t0[0], it.kv_t0[1], it.kv_t0[2]};
       for (int iter = 0; iter < it.n_tiles; ++iter) {
-        int tc[B200NA_MAX_DIM];
-        kv_tile_coord(p, it, iter, tc);
-        const bool interior = kv_tile_interior(p, it, tc);
+        const bool interior = kv_tile_interior<NDIM>(p, it, tc);
         // warp-uniform outcome: the TMEM accesses below are warp-collective
         if (!__all_sync(0xffffffffu, wait_bar(bars.s_full + half, ph_s, abort_flag, p.status,
                                               (1 << 8) | kStSFull))) {
@@ -406,19 +435,16 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
         ph_s ^= 1;
         PROF_MARK(0)
-        if (row == 0) TRACE(half, 1)
+        if (row == 0 && part == 0) TRACE(half, 1)
         ptx::tc_fence_after_sync();
-        uint32_t sr[4][32];
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) ptx::tmem_ld32(s_addr + q4 * 32, sr[q4]);
-        ptx::tmem_ld_wait();
-        PROF_MARK(1)
+        // Mask words of this thread's two 32-column chunks (boundary tiles only).
+        uint32_t mw0 = ~0u, mw1 = ~0u;
         if (!interior) {
           uint4 mk = make_uint4(~0u, ~0u, ~0u, ~0u);
           int off = 0;
 #pragma unroll
           for (int a = 0; a < B200NA_MAX_DIM; ++a) {
-            if (a < p.ndim) {
+            if (a < NDIM) {
               const int base = tc[a] * p.Tkv[a];
               const int lo = imin(imax(ws[a] - base, 0), p.Tkv[a]);
               const int hi = imin(imax(we[a] - base, 0), p.Tkv[a]);
@@ -432,24 +458,44 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
               off += p.Tkv[a] + 1;
             }
           }
-          const uint32_t mw[4] = {mk.x, mk.y, mk.z, mk.w};
-#pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (!((mw[q4] >> j) & 1u)) sr[q4][j] = 0xff800000u;  // -inf
-          }
+          mw0 = part ? mk.z : mk.x;
+          mw1 = part ? mk.w : mk.y;
         }
-        // row maximum of the raw logits (3-input max, four independent chains)
+        kv_tile_next<NDIM>(it, tc);
+        // Pass 1: row maximum of the raw logits over this thread's 64 columns. Chunk 1 is read
+        // first and dropped, chunk 0 stays in registers for pass 2.
+        uint32_t sr[32];
         float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+        ptx::tmem_ld32(my_s + 32, sr);
+        ptx::tmem_ld_wait();
+        if (!interior) {
 #pragma unroll
-        for (int j = 0; j < 32; j += 2) {
-          mx0 = ptx::max3(mx0, __uint_as_float(sr[0][j]), __uint_as_float(sr[0][j + 1]));
-          mx1 = ptx::max3(mx1, __uint_as_float(sr[1][j]), __uint_as_float(sr[1][j + 1]));
-          mx2 = ptx::max3(mx2, __uint_as_float(sr[2][j]), __uint_as_float(sr[2][j + 1]));
-          mx3 = ptx::max3(mx3, __uint_as_float(sr[3][j]), __uint_as_float(sr[3][j + 1]));
+          for (int j = 0; j < 32; ++j)
+            if (!((mw1 >> j) & 1u)) sr[j] = 0xff800000u;  // -inf
         }
-        const float m_new = fmaxf(fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)), m);
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+          mx0 = ptx::max3(mx0, __uint_as_float(sr[j]), __uint_as_float(sr[j + 1]));
+          mx1 = ptx::max3(mx1, __uint_as_float(sr[j + 2]), __uint_as_float(sr[j + 3]));
+        }
+        ptx::tmem_ld32(my_s, sr);
+        ptx::tmem_ld_wait();
+        PROF_MARK(1)
+        if (!interior) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (!((mw0 >> j) & 1u)) sr[j] = 0xff800000u;
+        }
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+          mx2 = ptx::max3(mx2, __uint_as_float(sr[j]), __uint_as_float(sr[j + 1]));
+          mx3 = ptx::max3(mx3, __uint_as_float(sr[j + 2]), __uint_as_float(sr[j + 3]));
+        }
+        const float my_max = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+        float* xm = xmax + (((iter & 1) * 2 + half) * 2) * kHalf;
+        xm[part * kHalf + row] = my_max;
+        named_bar_sync(bar_id, kSoftmaxThreadsPerHalf);
+        const float m_new = ptx::max3(m, my_max, xm[(part ^ 1) * kHalf + row]);
         // Lazy rescale: keep the stale maximum while the true one is at most 2^8 larger.
         const bool grow = (m_new - m) * c > kRescaleThreshold;  // NaN (-inf - -inf) -> false
         if (__any_sync(0xffffffffu, grow)) {
@@ -462,62 +508,73 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             // O_half is quiescent here: P.V of the previous tile completed before s_full fired.
 #pragma unroll
             for (int ch = 0; ch < D / 32; ++ch) {
-              uint32_t orr[32];
-              ptx::tmem_ld32(o_addr + ch * 32, orr);
+              uint32_t orr[16];
+              ptx::tmem_ld16(my_o + ch * 16, orr);
               ptx::tmem_ld_wait();
 #pragma unroll
-              for (int j = 0; j < 32; ++j) orr[j] = __float_as_uint(__uint_as_float(orr[j]) * f);
-              ptx::tmem_st32(o_addr + ch * 32, orr);
+              for (int j = 0; j < 16; ++j) orr[j] = __float_as_uint(__uint_as_float(orr[j]) * f);
+              ptx::tmem_st16(my_o + ch * 16, orr);
             }
           }
         }
         const float neg_mc = (m == -INFINITY) ? 0.f : -m * c;
-        // p = 2^(s*c - m*c): packed fp32x2 multiply-add, then the exponential on the special
-        // function unit for one pair and on the FMA pipes for the next (kPolyEvery), so that
-        // neither pipe alone bounds the softmax.
-        const uint64_t c2 = ptx::pack_f2(c, c);
-        const uint64_t nmc2 = ptx::pack_f2(neg_mc, neg_mc);
-        uint64_t sum2a = ptx::pack_f2(0.f, 0.f), sum2b = sum2a;
-        uint32_t pk[2][32];
+        // Pass 2: p = 2^(s*c - m*c), 32 columns at a time; each packed chunk of P overwrites
+        // logit columns this same thread has already consumed, so no other thread is involved.
+        float sm0 = 0.f, sm1 = 0.f;
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
+        for (int ch = 0; ch < 2; ++ch) {
+          if (ch == 1) {
+            ptx::tmem_ld32(my_s + 32, sr);
+            ptx::tmem_ld_wait();
+            if (!interior) {
 #pragma unroll
-          for (int j = 0; j < 32; j += 2) {
-            const uint64_t t2 = ptx::fma2(
-                ptx::pack_f2(__uint_as_float(sr[q4][j]), __uint_as_float(sr[q4][j + 1])), c2, nmc2);
-            float p0, p1;
-            if (kPolyEvery > 0 && ((j >> 1) % (kPolyEvery > 0 ? kPolyEvery : 1)) == kPolyEvery - 1) {
-              ptx::ex2_poly2(t2, p0, p1);
-            } else {
-              float t0, t1;
-              ptx::unpack_f2(t2, t0, t1);
-#ifdef B200NA_EXPERIMENT_NO_EX2
-              p0 = t0 * 0.001f;
-              p1 = t1 * 0.001f;
-#else
-              p0 = ptx::ex2(t0);
-              p1 = ptx::ex2(t1);
-#endif
+              for (int j = 0; j < 32; ++j)
+                if (!((mw1 >> j) & 1u)) sr[j] = 0xff800000u;
             }
-            if ((j >> 1) & 1) sum2a = ptx::add2(sum2a, ptx::pack_f2(p0, p1));
-            else sum2b = ptx::add2(sum2b, ptx::pack_f2(p0, p1));
-            pk[q4 >> 1][((q4 & 1) << 4) + (j >> 1)] = pack2<kBf16>(p0, p1);
           }
+          uint32_t pk[16];
+          if (kExpMixed) {
+            // half of the exponentials on the special function unit, half on the FMA pipes,
+            // interleaved instruction by instruction
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              const float t0 = fmaf(__uint_as_float(sr[j]), c, neg_mc);
+              const float t1 = fmaf(__uint_as_float(sr[j + 1]), c, neg_mc);
+              const float t2 = fmaf(__uint_as_float(sr[j + 2]), c, neg_mc);
+              const float t3 = fmaf(__uint_as_float(sr[j + 3]), c, neg_mc);
+              float p0, p1, p2, p3;
+              ptx::ex2_mixed4(t0, t1, t2, t3, p0, p1, p2, p3);
+              sm0 += p0 + p2;
+              sm1 += p1 + p3;
+              pk[j >> 1] = pack2<kBf16>(p0, p1);
+              pk[(j >> 1) + 1] = pack2<kBf16>(p2, p3);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) {
+              const float t0 = fmaf(__uint_as_float(sr[j]), c, neg_mc);
+              const float t1 = fmaf(__uint_as_float(sr[j + 1]), c, neg_mc);
+              float p0, p1;
+              if (kPolyEvery > 0 && ((j >> 1) % (kPolyEvery > 0 ? kPolyEvery : 1)) == kPolyEvery - 1) {
+                ptx::ex2_poly2(ptx::pack_f2(t0, t1), p0, p1);
+              } else {
+                p0 = ptx::ex2(t0);
+                p1 = ptx::ex2(t1);
+              }
+              sm0 += p0;
+              sm1 += p1;
+              pk[j >> 1] = pack2<kBf16>(p0, p1);
+            }
+          }
+          ptx::tmem_st16(my_p + ch * 16, pk);
         }
-        {
-          float a0, a1, b0, b1;
-          ptx::unpack_f2(sum2a, a0, a1);
-          ptx::unpack_f2(sum2b, b0, b1);
-          sum += (a0 + a1) + (b0 + b1);
-        }
+        sum += sm0 + sm1;
         PROF_MARK(2)
-        ptx::tmem_st32(s_addr, pk[0]);
-        ptx::tmem_st32(s_addr + 32, pk[1]);
         ptx::tmem_st_wait();
         ptx::tc_fence_before_sync();
         ptx::mbar_arrive(bars.p_full + half);
         PROF_MARK(3)
-        if (row == 0) TRACE(half, 2)
+        if (row == 0 && part == 0) TRACE(half, 2)
       }
       if (!alive) break;
       // ---- epilogue: O / sum -> global, LSE ----
@@ -526,16 +583,19 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         break;
       ph_o ^= 1;
       PROF_MARK(4)
-      if (row == 0) TRACE(half, 3)
       ptx::tc_fence_after_sync();
+      float* xs = xsum + half * 2 * kHalf;
+      xs[part * kHalf + row] = sum;
+      named_bar_sync(bar_id, kSoftmaxThreadsPerHalf);
+      const float total = sum + xs[(part ^ 1) * kHalf + row];
       const int q_row = it.qt * kQTile + half * kHalf + row;
       const bool valid = q_row < p.Sq;
-      const float inv = sum > 0.f ? 1.f / sum : 0.f;
-      T* orow = o_ptr + (((long long)it.bp * p.Sq + q_row) * p.Hq + it.h) * D;
+      const float inv = total > 0.f ? 1.f / total : 0.f;
+      T* orow = o_ptr + (((long long)it.bp * p.Sq + q_row) * p.Hq + it.h) * D + part * (D / 2);
 #pragma unroll
-      for (int ch = 0; ch < D / 32; ++ch) {
+      for (int ch = 0; ch < D / 64; ++ch) {
         uint32_t orr[32];
-        ptx::tmem_ld32(o_addr + ch * 32, orr);
+        ptx::tmem_ld32(my_o + ch * 32, orr);
         ptx::tmem_ld_wait();
         if (valid) {
 #pragma unroll
@@ -549,19 +609,14 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           }
         }
       }
-      if (p.lse != nullptr && valid)
-        p.lse[((long long)it.bp * p.Sq + q_row) * p.Hq + it.h] = logf(sum) + m * p.scale;
+      if (p.lse != nullptr && valid && part == 0)
+        p.lse[((long long)it.bp * p.Sq + q_row) * p.Hq + it.h] = logf(total) + m * p.scale;
       ptx::tc_fence_before_sync();
       ptx::mbar_arrive(bars.o_empty + half);
       PROF_MARK(5)
-      if (row == 0) TRACE(half, 4)
     }
-    if (row == 0) { PROF_FLUSH(half) }
-  } else {
-    // Warps 8-11 form one warpgroup and must run the same register-release instruction.
-    if constexpr (kRegSplit) ptx::reg_dealloc<kOtherRegs>();
-  }
-  if (warp == kMmaWarp) {
+    if (row == 0 && part == 0) { PROF_FLUSH(half) }
+  } else if (warp == kMmaWarp) {
     // =============================== MMA issue ==============================================
     if (lane == 0) {
       constexpr uint32_t idesc_qk = ptx::make_idesc(kBf16 ? 1 : 0, 0, 0, kHalf, kKVTile);
@@ -592,20 +647,22 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                            kb > 0 ? 1u : 0u);
         }
       };
+      // P for keys [0,64) sits in S columns [0,32), for keys [64,128) in columns [64,96): each
+      // softmax thread writes its packed probabilities over its own logits.
       auto issue_pv = [&](int half, uint32_t v_addr, bool first) {
         const uint32_t b_lo = ptx::smem_desc_lo(v_addr, kBlockBytes);
         const uint32_t d = half ? o_tm[1] : o_tm[0];
         const uint32_t a = half ? s_tm[1] : s_tm[0];
-        ptx::mma_ts_lohi(d, a, b_lo, desc_hi, idesc_pv, first ? 0u : 1u);
 #pragma unroll
-        for (int ks = 1; ks < kKVTile / 16; ++ks)
-          ptx::mma_ts_lohi(d, a + ks * 8, b_lo + ks * (2048 >> 4), desc_hi, idesc_pv, 1u);
+        for (int ks = 0; ks < kKVTile / 16; ++ks)
+          ptx::mma_ts_lohi(d, a + (ks >> 2) * 64 + (ks & 3) * 8, b_lo + ks * (2048 >> 4), desc_hi,
+                           idesc_pv, (first && ks == 0) ? 0u : 1u);
       };
 
       PROF2_DECL
       for (long long w = blockIdx.x; w < p.total_work && alive; w += gridDim.x) {
         Item it;
-        decode_item(p, w, it);
+        decode_item<NDIM>(p, w, it);
         if (it.skip) continue;
         const int n = it.n_tiles;
         PROF2_MARK(6)
@@ -620,6 +677,7 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         ring.advance();
         PROF2_MARK(1)
         ptx::tc_fence_after_sync();
+#pragma unroll
         for (int h = 0; h < 2; ++h) {
           issue_qk(h, kv_base + slot_k * kTileBytes);
           ptx::tc_commit(bars.s_full + h);
@@ -635,6 +693,7 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           TRACE2(2, 11)
           const bool more = iter + 1 < n;
           uint32_t slot_kn = 0;
+#pragma unroll
           for (int h = 0; h < 2; ++h) {
             if (!wait_bar(bars.p_full + h, ph_p[h], abort_flag, p.status, (2 << 8) | kStPFull)) {
               alive = false; break;
@@ -689,7 +748,7 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       PROF2_DECL
       for (long long w = blockIdx.x; w < p.total_work && alive; w += gridDim.x) {
         Item it;
-        decode_item(p, w, it);
+        decode_item<NDIM>(p, w, it);
         if (it.skip) continue;
         PROF2_MARK(6)
         if (!wait_bar(bars.q_empty, ph_qe, abort_flag, p.status, (3 << 8) | kStQEmpty)) break;
@@ -700,10 +759,10 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           for (int db = 0; db < kDBlocks; ++db)
             ptx::tma_load_4d(q_sm + h * kTileBytes + db * kBlockBytes, &tm_q, bars.q_full, db * 64,
                              it.h, it.qt * kQTile + h * kHalf, it.bp);
+        int tc[B200NA_MAX_DIM] = {it.kv_t0[0], it.kv_t0[1], it.kv_t0[2]};
         for (int iter = 0; iter < it.n_tiles && alive; ++iter) {
-          int tc[B200NA_MAX_DIM];
-          kv_tile_coord(p, it, iter, tc);
-          const int row0 = kv_tile_row(p, tc);
+          const int row0 = kv_tile_row<NDIM>(p, tc);
+          kv_tile_next<NDIM>(it, tc);
           for (int kv = 0; kv < 2; ++kv) {
             const uint32_t slot = ring.slot;
             if (!wait_bar(bars.kv_empty + slot, ring.phase ^ 1, abort_flag, p.status,
@@ -787,22 +846,19 @@ int make_tensor_map(CUtensorMap* tm, const void* ptr, int dtype, int Bp, int S, 
   return B200NA_OK;
 }
 
-const void* kernel_variant(int D, bool bf16, bool reg_split) {
-  if (D == 128) {
-    if (bf16) return reg_split ? (const void*)fna_fwd_kernel<128, true, true>
-                               : (const void*)fna_fwd_kernel<128, true, false>;
-    return reg_split ? (const void*)fna_fwd_kernel<128, false, true>
-                     : (const void*)fna_fwd_kernel<128, false, false>;
-  }
-  if (bf16) return reg_split ? (const void*)fna_fwd_kernel<64, true, true>
-                             : (const void*)fna_fwd_kernel<64, true, false>;
-  return reg_split ? (const void*)fna_fwd_kernel<64, false, true>
-                   : (const void*)fna_fwd_kernel<64, false, false>;
+template <int D, bool kBf16>
+const void* kernel_for_ndim(int ndim) {
+  if (ndim == 1) return (const void*)fna_fwd_kernel<D, kBf16, 1>;
+  if (ndim == 2) return (const void*)fna_fwd_kernel<D, kBf16, 2>;
+  return (const void*)fna_fwd_kernel<D, kBf16, 3>;
+}
+const void* kernel_variant(int D, bool bf16, int ndim) {
+  if (D == 128) return bf16 ? kernel_for_ndim<128, true>(ndim) : kernel_for_ndim<128, false>(ndim);
+  return bf16 ? kernel_for_ndim<64, true>(ndim) : kernel_for_ndim<64, false>(ndim);
 }
 
 struct DeviceState {
   bool ready = false;
-  bool reg_split_ok = true;
   int sms = 0;
   int* status_ptr = nullptr;
 };
@@ -821,15 +877,14 @@ int device_state(DeviceState** out) {
     B200NA_CUDA_TRY(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
     if (major != 10) return B200NA_ERR_DEVICE;
     B200NA_CUDA_TRY(cudaDeviceGetAttribute(&st.sms, cudaDevAttrMultiProcessorCount, dev));
-    for (int i = 0; i < 8; ++i) {
-      const void* fn = kernel_variant(i & 4 ? 128 : 64, (i & 2) != 0, (i & 1) != 0);
+    for (int i = 0; i < 12; ++i) {
+      const void* fn = kernel_variant(i & 2 ? 128 : 64, (i & 1) != 0, 1 + (i >> 2));
       B200NA_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           i & 4 ? Smem<128>::kBytes : Smem<64>::kBytes));
+                                           i & 2 ? Smem<128>::kBytes : Smem<64>::kBytes));
       cudaFuncAttributes fa;
       B200NA_CUDA_TRY(cudaFuncGetAttributes(&fa, fn));
-      // the register re-partitioning is only safe when the launch allocation is what the
-      // static budget above assumes
-      if ((i & 1) && fa.numRegs != kBaseRegs) st.reg_split_ok = false;
+      // one CTA of kThreads threads must fit the register file
+      if (fa.numRegs * kThreads > 65536) return B200NA_ERR_UNSUPPORTED;
     }
     void* sp = nullptr;
     B200NA_CUDA_TRY(cudaGetSymbolAddress(&sp, g_status_word));
@@ -864,12 +919,7 @@ int launch_fna(const void* q, const void* k, const void* v, FnaParams& p, int D,
   p.total_work = (long long)p.n_qtiles * p.Hq * p.Bp;
   if (p.total_work == 0) return B200NA_OK;
   const int grid = (int)(p.total_work < st->sms ? p.total_work : st->sms);
-#ifdef B200NA_EXPERIMENT_NO_SPLIT
-  const bool reg_split = false;
-#else
-  const bool reg_split = st->reg_split_ok;
-#endif
-  const void* fn = kernel_variant(D, dtype == B200NA_BF16, reg_split);
+  const void* fn = kernel_variant(D, dtype == B200NA_BF16, p.ndim);
   void* args[] = {(void*)&tq, (void*)&tk, (void*)&tv, (void*)&p};
   B200NA_CUDA_TRY(cudaLaunchKernel(fn, dim3(grid), dim3(kThreads),  args,
                                    D == 128 ? Smem<128>::kBytes : Smem<64>::kBytes, stream));

@@ -209,6 +209,25 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
         "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
 }
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+        "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]),
+        "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
@@ -280,6 +299,47 @@ __device__ __forceinline__ void ex2_poly2(uint64_t x2, float& r0, float& r1) {
   unpack_f2(p2, p0, p1);
   r0 = __int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23));
   r1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
+}
+
+// Four exponentials with a fixed instruction order: 2^a0 and 2^a1 on the special function unit,
+// 2^b0 and 2^b1 by the polynomial above, the polynomial's FMA/ALU instructions placed between the
+// two special-function instructions so that a warp has independent work to issue while that unit
+// is busy (instruction issue is in order within a warp). Same numerics as ex2 / ex2_poly2.
+__device__ __forceinline__ void ex2_mixed4(float a0, float a1, float b0, float b1, float& ra0,
+                                           float& ra1, float& rb0, float& rb1) {
+  asm volatile(
+      "{\n\t"
+      ".reg .f32 x0, x1, t0, t1, n0, n1, f0, f1, q0, q1;\n\t"
+      ".reg .b32 i0, i1, s0, s1;\n\t"
+      "ex2.approx.ftz.f32 %0, %4;\n\t"
+      "max.f32 x0, %6, 0fC2FC0000;\n\t"          // -126
+      "max.f32 x1, %7, 0fC2FC0000;\n\t"
+      "add.rn.f32 t0, x0, 0f4B400000;\n\t"       // 1.5 * 2^23
+      "add.rn.f32 t1, x1, 0f4B400000;\n\t"
+      "add.rn.f32 n0, t0, 0fCB400000;\n\t"
+      "add.rn.f32 n1, t1, 0fCB400000;\n\t"
+      "sub.rn.f32 f0, x0, n0;\n\t"
+      "sub.rn.f32 f1, x1, n1;\n\t"
+      "ex2.approx.ftz.f32 %1, %5;\n\t"
+      "fma.rn.f32 q0, f0, 0f3D61FBAF, 0f3E786F0D;\n\t"   // 0.0551716648, 0.2426111251
+      "fma.rn.f32 q1, f1, 0f3D61FBAF, 0f3E786F0D;\n\t"
+      "fma.rn.f32 q0, q0, f0, 0f3F31798D;\n\t"           // 0.6932609677
+      "fma.rn.f32 q1, q1, f1, 0f3F31798D;\n\t"
+      "fma.rn.f32 q0, q0, f0, 0f3F7FFB49;\n\t"           // 0.9999280572
+      "fma.rn.f32 q1, q1, f1, 0f3F7FFB49;\n\t"
+      "mov.b32 i0, t0;\n\t"
+      "mov.b32 i1, t1;\n\t"
+      "shl.b32 i0, i0, 23;\n\t"
+      "shl.b32 i1, i1, 23;\n\t"
+      "mov.b32 s0, q0;\n\t"
+      "mov.b32 s1, q1;\n\t"
+      "add.s32 s0, s0, i0;\n\t"
+      "add.s32 s1, s1, i1;\n\t"
+      "mov.b32 %2, s0;\n\t"
+      "mov.b32 %3, s1;\n\t"
+      "}\n"
+      : "=f"(ra0), "=f"(ra1), "=f"(rb0), "=f"(rb1)
+      : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
 }
 
 __device__ __forceinline__ float lg2(float x) {
