@@ -98,6 +98,24 @@ B200NA_API int b200na_fna_forward(const void* q, const void* k, const void* v, v
                        int Hkv, int D, int dtype, float scale, b200na_stream_t stream);
 
 /*
+ * The same kernel on one rank's SLAB of a spatially sharded, undilated token layout. The
+ * reference has no counterpart (it has no multi-GPU code); window arithmetic follows
+ * csrc/include/natten/cuda/reference/mask.hpp:59-89 in layout ("global") coordinates.
+ *   qkv_shape: the WHOLE token layout; q holds query coordinates [q_origin, q_origin + q_extent)
+ *   per axis, padded to q_shape (tile multiples); k, v hold key coordinates
+ *   [kv_origin, kv_origin + kv_shape) (padding beyond the layout is never attended).
+ *   The key/value slab must contain every key the local queries' windows reach (own slab plus the
+ *   halo received from neighbouring ranks); otherwise B200NA_ERR_INVALID_ARGUMENT.
+ *   All dilations must be 1. Passing NULL for the three arrays is b200na_fna_forward.
+ */
+B200NA_API int b200na_fna_forward_sharded(
+    const void* q, const void* k, const void* v, void* o, float* lse, int ndim,
+    const int* qkv_shape, const int* q_shape, const int* kv_shape, const int* kernel,
+    const int* stride, const int* dilation, const int* causal, const int* q_tile,
+    const int* kv_tile, int Bp, int Hq, int Hkv, int D, int dtype, float scale,
+    const int* q_origin, const int* q_extent, const int* kv_origin, b200na_stream_t stream);
+
+/*
  * Dense attention forward: replaces natten::blackwell_fmha_forward for the non-varlen case
  * (reference: csrc/src/blackwell_fmha.cu:55-260; Python caller src/natten/functional.py:74-348),
  * used for the extra (cross-attention) KV tokens and the self-attention fast path.

@@ -20,7 +20,7 @@ F32, F16, BF16 = 0, 1, 2
 # Every symbol include/natten_b200.h declares.
 SYMBOLS = (
     "b200na_strerror", "b200na_version", "b200na_token_permute", "b200na_token_unpermute",
-    "b200na_fna_forward", "b200na_fmha_forward", "b200na_na_forward_simt", "b200na_merge",
+    "b200na_fna_forward", "b200na_fna_forward_sharded", "b200na_fmha_forward", "b200na_na_forward_simt", "b200na_merge",
     "b200na_device_status",
 )
 
@@ -37,7 +37,7 @@ def _load() -> ctypes.CDLL:
     if not os.path.exists(LIB_PATH):
         raise ImportError(
             f"{LIB_PATH} is missing. natten_b200 has no fallback path: build the CUDA library first "
-            "with `python -m natten_b200.build` (needs nvcc; targets sm_100a).")
+            "with `python natten_b200/build.py` (needs nvcc; targets sm_100a).")
     lib = ctypes.CDLL(LIB_PATH)
     c_int, c_void_p, c_float, c_i64 = ctypes.c_int, ctypes.c_void_p, ctypes.c_float, ctypes.c_int64
     ip = ctypes.POINTER(c_int)
@@ -54,6 +54,11 @@ def _load() -> ctypes.CDLL:
     lib.b200na_fna_forward.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                        ip, ip, ip, ip, ip, ip, ip, ip, ip,
                                        c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]
+    lib.b200na_fna_forward_sharded.restype = c_int
+    lib.b200na_fna_forward_sharded.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                               c_int, ip, ip, ip, ip, ip, ip, ip, ip, ip,
+                                               c_int, c_int, c_int, c_int, c_int, c_float,
+                                               ip, ip, ip, c_void_p]
     lib.b200na_fmha_forward.restype = c_int
     lib.b200na_fmha_forward.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                         c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,

@@ -1,6 +1,6 @@
 """Builds libnatten_b200.so (the C-ABI library) in-tree with nvcc for sm_100a.
 
-    python -m natten_b200.build [--force]
+    python natten_b200/build.py [--force]
 
 The library links the CUDA runtime statically and looks the driver entry point it needs
 (cuTensorMapEncodeTiled) up at run time, so it loads on machines without a GPU driver too.

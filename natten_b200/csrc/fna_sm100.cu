@@ -69,6 +69,9 @@ struct FnaParams {
   int Rq[B200NA_MAX_DIM];   // query tiles per axis per dilation group
   int Rkv[B200NA_MAX_DIM];  // kv tiles per axis per dilation group
   int G;                    // prod(dil)
+  int q_org[B200NA_MAX_DIM];   // layout coordinate of local query index 0 (spatial sharding; else 0)
+  int kv_org[B200NA_MAX_DIM];  // layout coordinate of local key/value index 0
+  int q_len[B200NA_MAX_DIM];   // number of real (non-padding) local query coordinates per axis
   int dense;                // dense attention: one axis, window = all keys (or causal prefix)
   int Bp, Hq, Hkv;
   int Sq, Skv;              // rows per batch' in the q / kv tensors
@@ -154,16 +157,17 @@ __device__ __forceinline__ void decode_item(const FnaParams& p, long long w, Ite
       it.L[a] = p.dense ? p.Skv : group_extent(p.X[a], p.dil[a], g);
       const int r = ql % p.Rq[a];
       ql /= p.Rq[a];
-      it.q_lo[a] = r * p.Tq[a];
+      if (!p.dense && r * p.Tq[a] >= p.q_len[a]) it.skip = true;  // tile holds padding rows only
+      it.q_lo[a] = p.q_org[a] + r * p.Tq[a];
       const int q_hi = it.q_lo[a] + p.Tq[a] - 1;
-      if (!p.dense && it.q_lo[a] >= it.L[a]) it.skip = true;  // tile holds padding rows only
       int s_lo, e_lo, s_hi, e_hi;
       axis_window(p, a, it.q_lo[a], it.L[a], s_lo, e_lo);
       axis_window(p, a, q_hi, it.L[a], s_hi, e_hi);
       it.ws_hi[a] = s_hi;
       it.we_lo[a] = e_lo;
-      it.kv_t0[a] = s_lo / p.Tkv[a];
-      it.kv_n[a] = (e_hi + p.Tkv[a] - 1) / p.Tkv[a] - it.kv_t0[a];
+      // windows are in layout coordinates, the key/value buffer starts at kv_org
+      it.kv_t0[a] = (s_lo - p.kv_org[a]) / p.Tkv[a];
+      it.kv_n[a] = (e_hi - p.kv_org[a] + p.Tkv[a] - 1) / p.Tkv[a] - it.kv_t0[a];
       it.n_tiles *= it.kv_n[a];
     } else {
       it.L[a] = 1; it.q_lo[a] = 0; it.kv_t0[a] = 0; it.kv_n[a] = 1; it.ws_hi[a] = 0; it.we_lo[a] = 1;
@@ -186,7 +190,7 @@ __device__ __forceinline__ bool kv_tile_interior(const FnaParams& p, const Item&
 #pragma unroll
   for (int a = 0; a < B200NA_MAX_DIM; ++a) {
     if (a < NDIM) {
-      const int lo = c[a] * p.Tkv[a];
+      const int lo = p.kv_org[a] + c[a] * p.Tkv[a];
       in = in && (lo >= it.ws_hi[a]) && (lo + p.Tkv[a] <= it.we_lo[a]);
     }
   }
@@ -445,7 +449,7 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #pragma unroll
           for (int a = 0; a < B200NA_MAX_DIM; ++a) {
             if (a < NDIM) {
-              const int base = tc[a] * p.Tkv[a];
+              const int base = p.kv_org[a] + tc[a] * p.Tkv[a];
               const int lo = imin(imax(ws[a] - base, 0), p.Tkv[a]);
               const int hi = imin(imax(we[a] - base, 0), p.Tkv[a]);
               const uint4 ph = pref[off + hi];
@@ -929,12 +933,12 @@ int launch_fna(const void* q, const void* k, const void* v, FnaParams& p, int D,
 }  // namespace
 }  // namespace b200na
 
-extern "C" B200NA_API int b200na_fna_forward(const void* q, const void* k, const void* v, void* o, float* lse,
-                                  int ndim, const int* qkv_shape, const int* q_shape,
-                                  const int* kv_shape, const int* kernel, const int* stride,
-                                  const int* dilation, const int* causal, const int* q_tile,
-                                  const int* kv_tile, int Bp, int Hq, int Hkv, int D, int dtype,
-                                  float scale, b200na_stream_t stream) {
+extern "C" B200NA_API int b200na_fna_forward_sharded(
+    const void* q, const void* k, const void* v, void* o, float* lse, int ndim,
+    const int* qkv_shape, const int* q_shape, const int* kv_shape, const int* kernel,
+    const int* stride, const int* dilation, const int* causal, const int* q_tile,
+    const int* kv_tile, int Bp, int Hq, int Hkv, int D, int dtype, float scale,
+    const int* q_origin, const int* q_extent, const int* kv_origin, b200na_stream_t stream) {
   using namespace b200na;
   if (!q || !k || !v || !o || !qkv_shape || !q_shape || !kv_shape || !kernel || !q_tile || !kv_tile)
     return B200NA_ERR_INVALID_ARGUMENT;
@@ -942,6 +946,8 @@ extern "C" B200NA_API int b200na_fna_forward(const void* q, const void* k, const
   if (dtype != B200NA_F16 && dtype != B200NA_BF16) return B200NA_ERR_UNSUPPORTED;
   if (D != 64 && D != 128) return B200NA_ERR_UNSUPPORTED;
   if (!(scale > 0.f)) return B200NA_ERR_INVALID_ARGUMENT;
+  const bool sharded = q_origin != nullptr || kv_origin != nullptr || q_extent != nullptr;
+  if (sharded && !(q_origin && kv_origin && q_extent)) return B200NA_ERR_INVALID_ARGUMENT;
   NaAxes ax;
   int rc = fill_axes(ax, ndim, qkv_shape, kernel, stride, dilation, causal);
   if (rc != B200NA_OK) return rc;
@@ -959,9 +965,29 @@ extern "C" B200NA_API int b200na_fna_forward(const void* q, const void* k, const
     const int qs = on ? q_shape[a] : 1, ks = on ? kv_shape[a] : 1;
     if (p.Tq[a] < 1 || p.Tkv[a] < 1 || qs < 1 || ks < 1) return B200NA_ERR_INVALID_ARGUMENT;
     if (qs % p.Tq[a] != 0 || ks % p.Tkv[a] != 0) return B200NA_ERR_INVALID_ARGUMENT;
-    // padded per-group extents must cover the largest dilation group
-    const int need = (p.X[a] + p.dil[a] - 1) / p.dil[a];
-    if (qs < need || ks < need) return B200NA_ERR_INVALID_ARGUMENT;
+    const int need = (p.X[a] + p.dil[a] - 1) / p.dil[a];  // largest dilation group
+    if (sharded) {
+      // a local slab of an undilated layout: [origin, origin + extent) must lie inside it
+      if (p.dil[a] != 1) return B200NA_ERR_UNSUPPORTED;
+      p.q_org[a] = on ? q_origin[a] : 0;
+      p.kv_org[a] = on ? kv_origin[a] : 0;
+      p.q_len[a] = on ? q_extent[a] : 1;
+      if (p.q_org[a] < 0 || p.kv_org[a] < 0 || p.q_len[a] < 1 || p.q_len[a] > qs ||
+          p.q_org[a] + p.q_len[a] > p.X[a] || p.kv_org[a] >= p.X[a])
+        return B200NA_ERR_INVALID_ARGUMENT;
+      // the key/value slab must hold every key the local queries' windows reach
+      const int first = p.q_org[a], last = p.q_org[a] + p.q_len[a] - 1;
+      const int lo = win_start(first, p.kernel[a], p.stride[a], p.X[a], p.causal[a]);
+      const int st_last = win_start(last, p.kernel[a], p.stride[a], p.X[a], p.causal[a]);
+      const int hi = win_end(last, st_last, p.kernel[a], p.X[a], p.causal[a]);
+      if (lo < p.kv_org[a] || hi > p.kv_org[a] + ks) return B200NA_ERR_INVALID_ARGUMENT;
+    } else {
+      // padded per-group extents must cover the largest dilation group
+      if (qs < need || ks < need) return B200NA_ERR_INVALID_ARGUMENT;
+      p.q_org[a] = 0;
+      p.kv_org[a] = 0;
+      p.q_len[a] = need;
+    }
     p.Rq[a] = qs / p.Tq[a];
     p.Rkv[a] = ks / p.Tkv[a];
     p.G *= p.dil[a];
@@ -979,6 +1005,19 @@ extern "C" B200NA_API int b200na_fna_forward(const void* q, const void* k, const
   p.o = o;
   p.lse = lse;
   return launch_fna(q, k, v, p, D, dtype, reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" B200NA_API int b200na_fna_forward(const void* q, const void* k, const void* v, void* o,
+                                             float* lse, int ndim, const int* qkv_shape,
+                                             const int* q_shape, const int* kv_shape,
+                                             const int* kernel, const int* stride,
+                                             const int* dilation, const int* causal,
+                                             const int* q_tile, const int* kv_tile, int Bp, int Hq,
+                                             int Hkv, int D, int dtype, float scale,
+                                             b200na_stream_t stream) {
+  return b200na_fna_forward_sharded(q, k, v, o, lse, ndim, qkv_shape, q_shape, kv_shape, kernel,
+                                    stride, dilation, causal, q_tile, kv_tile, Bp, Hq, Hkv, D,
+                                    dtype, scale, nullptr, nullptr, nullptr, stream);
 }
 
 extern "C" B200NA_API int b200na_fmha_forward(const void* q, const void* k, const void* v, void* o, float* lse,
@@ -1000,9 +1039,10 @@ extern "C" B200NA_API int b200na_fmha_forward(const void* q, const void* k, cons
   p.G = 1;
   for (int a = 0; a < B200NA_MAX_DIM; ++a) {
     p.X[a] = 1; p.kernel[a] = 1; p.stride[a] = 1; p.dil[a] = 1; p.causal[a] = 0;
-    p.Tq[a] = 1; p.Tkv[a] = 1; p.Rq[a] = 1; p.Rkv[a] = 1;
+    p.Tq[a] = 1; p.Tkv[a] = 1; p.Rq[a] = 1; p.Rkv[a] = 1; p.q_len[a] = 1;
   }
   p.X[0] = Nk;
+  p.q_len[0] = Nq;
   p.causal[0] = causal ? 1 : 0;
   p.Tq[0] = kQTile;
   p.Tkv[0] = kKVTile;

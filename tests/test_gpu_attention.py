@@ -197,6 +197,36 @@ def test_tensor_core_kernel_agrees_with_cuda_core_kernel_on_every_row():
     assert (l_tc - l_cc).abs().max().item() <= TOL_16
 
 
+@pytest.mark.parametrize("shape,ks,st,ca,world", [
+    ((32, 12, 20), (16, 6, 6), (1, 2, 2), (True, False, False), 8),   # config 5 scaled, T sharded
+    ((24, 16, 16), (7, 5, 5), (1, 1, 1), (False, False, False), 4),   # two-sided halo
+    ((4096,), (512,), (64,), (False,), 4),
+])
+def test_spatial_slabs_reproduce_the_unsharded_result(shape, ks, st, ca, world):
+    """Every rank's slab computed with b200na_fna_forward_sharded (ranks emulated one after the
+    other on this GPU; the halo is sliced from the global tensors) equals the unsharded rows."""
+    from natten_b200 import sharding
+    torch.manual_seed(11)
+    q, k, v = (torch.randn(1, *shape, 2, 128, device="cuda").bfloat16() for _ in range(3))
+    fn = _na_fn(len(shape))
+    full_o, full_l = fn(q, k, v, ks, st, 1, ca, return_lse=True)
+    plan = sharding.make_halo_plan(shape[0], world, ks[0], st[0], ca[0])
+    for r in range(world):
+        t0, t1 = plan.slabs[r]
+        lo, hi = plan.needs[r]
+        o, l = sharding.fna_forward_slab(q[:, t0:t1].contiguous(), k[:, lo:hi].contiguous(),
+                                         v[:, lo:hi].contiguous(), shape, t0, lo, ks, st, ca)
+        assert L.device_status() == 0
+        assert (o.float() - full_o[:, t0:t1].float()).abs().max().item() <= 4e-3, r
+        assert (l - full_l[:, t0:t1]).abs().max().item() <= 2e-3, r
+    # a slab that does not hold every needed key is refused, not silently wrong
+    t0, t1 = plan.slabs[world - 1]
+    lo, hi = plan.needs[world - 1]
+    with pytest.raises(L.NattenB200Error):
+        sharding.fna_forward_slab(q[:, t0:t1].contiguous(), k[:, lo + 1:hi].contiguous(),
+                                  v[:, lo + 1:hi].contiguous(), shape, t0, lo + 1, ks, st, ca)
+
+
 def test_forward_is_deterministic():
     torch.manual_seed(4)
     q, k, v = (torch.randn(2, 40, 40, 2, 64, device="cuda").half() for _ in range(3))
