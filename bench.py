@@ -80,6 +80,12 @@ def algorithmic_flops(cfg, units=None) -> float:
     return 4.0 * D * pairs * (B * H if units is None else units)
 
 
+# DRAM traffic of the attention kernel per (batch x head) unit, bytes, from the ncu capture of a
+# reduced case summarised in profiles/fna_fwd_kernel_c2.md (dram__bytes_read.sum +
+# dram__bytes_write.sum of one launch / units in that launch); scaled by the units of a launch.
+NCU_TRAFFIC_PER_UNIT = {"c2": (202.03e6 + 46.46e6) / 8}
+
+
 def read_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -146,19 +152,19 @@ class ClockSampler:
 
 def shard_units(B, H, world, rank):
     """(batch, heads) of this rank's slice when B*H independent units are split over `world`."""
-    units = B * H
-    if units % world != 0:
-        raise SystemExit(f"{units} (batch x heads) units do not divide over {world} ranks")
-    per = units // world
-    b_local = max(1, B // world)
-    h_local = per // b_local
-    assert b_local * h_local == per and h_local <= H
-    return b_local, h_local
+    from natten_b200.sharding import shard_batch_heads
+    try:
+        bs, hs = shard_batch_heads(B, H, world, rank)
+    except ValueError as e:
+        raise SystemExit(str(e))
+    return bs.stop - bs.start, hs.stop - hs.start
 
 
-def make_inputs(cfg, b_local, h_local, seed, device):
+def make_inputs(cfg, b_local, h_local, seed, device, slab=None):
     import torch
     _, dt, _, _, shape, D, _, _, _, _, n_extra, mul = cfg
+    if slab is not None:
+        shape = (slab[1] - slab[0],) + tuple(shape[1:])
     dtype = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[dt]
     g = torch.Generator(device="cpu").manual_seed(seed)
     host = []
@@ -174,36 +180,43 @@ def make_inputs(cfg, b_local, h_local, seed, device):
 
 
 def cpu_baseline(cfg, budget_s=12.0, acc64=False):
-    """Times the oracle (fp32-accumulating port of the reference's naive kernel) on a row sample
-    of one (batch, head) slice; returns effective TFLOP/s of the host cores."""
+    """Times the oracle (fp32-accumulating port of the reference's naive kernel, OpenMP on all host
+    cores) on a bounded sample of the workload: all query rows of `heads` (batch, head) slices, or
+    a row sample of one slice when even one slice exceeds the budget. Returns effective TFLOP/s."""
     import oracle
     _, _, _, _, shape, D, ks, st, di, ca, n_extra, mul = cfg
     rng = np.random.default_rng(0)
     N = math.prod(shape)
-    q = (rng.standard_normal((1, *shape, 1, D), dtype=np.float32) * mul)
-    k = (rng.standard_normal((1, *shape, 1, D), dtype=np.float32) * mul)
-    v = (rng.standard_normal((1, *shape, 1, D), dtype=np.float32) * mul)
-    ak = av = None
-    if n_extra:
-        ak = rng.standard_normal((1, n_extra, 1, D), dtype=np.float32)
-        av = rng.standard_normal((1, n_extra, 1, D), dtype=np.float32)
-    pairs_per_row = (attended_pairs(shape, ks, st, di, ca) + n_extra * N) / N
     cores = os.cpu_count() or 1
+    pairs_per_row = (attended_pairs(shape, ks, st, di, ca) + n_extra * N) / N
+
+    def run(heads, rows):
+        q = rng.standard_normal((1, *shape, heads, D), dtype=np.float32) * mul
+        k = rng.standard_normal((1, *shape, heads, D), dtype=np.float32) * mul
+        v = rng.standard_normal((1, *shape, heads, D), dtype=np.float32) * mul
+        ak = av = None
+        if n_extra:
+            ak = rng.standard_normal((1, n_extra, heads, D), dtype=np.float32)
+            av = rng.standard_normal((1, n_extra, heads, D), dtype=np.float32)
+        t0 = time.perf_counter()
+        oracle.na_forward(q, k, v, ks, st, di, ca, add_k=ak, add_v=av, tok_idx=rows, acc64=acc64)
+        return time.perf_counter() - t0
+
     n = min(N, 64 * cores)
     rows = np.sort(rng.choice(N, size=n, replace=False)).astype(np.int64)
-    t0 = time.perf_counter()
-    oracle.na_forward(q, k, v, ks, st, di, ca, add_k=ak, add_v=av, tok_idx=rows, acc64=acc64)
-    dt = time.perf_counter() - t0
-    # grow the sample towards the time budget
-    n2 = int(min(N, max(n, n * budget_s / max(dt, 1e-3))))
-    rows = np.sort(rng.choice(N, size=n2, replace=False)).astype(np.int64)
-    t0 = time.perf_counter()
-    oracle.na_forward(q, k, v, ks, st, di, ca, add_k=ak, add_v=av, tok_idx=rows, acc64=acc64)
-    dt = time.perf_counter() - t0
-    flops = 4.0 * D * pairs_per_row * n2
+    dt = run(1, rows)                      # calibration
+    per_row = max(dt, 1e-4) / n
+    want_rows = budget_s / per_row
+    if want_rows <= N:
+        heads, n2 = 1, int(max(n, min(N, want_rows)))
+    else:
+        heads, n2 = int(min(8, max(1, want_rows // N))), N
+    rows = None if n2 == N else np.sort(rng.choice(N, size=n2, replace=False)).astype(np.int64)
+    dt = run(heads, rows)
+    flops = 4.0 * D * pairs_per_row * n2 * heads
     return dict(value=flops / dt / 1e12, unit="TFLOP/s", cores=cores, kind="port",
-                sample=f"{n2} of {N} query rows of one (batch, head) slice, fp32 accumulation, "
-                       f"OpenMP on {cores} threads, {dt:.1f} s"), dt, n2
+                sample=f"{n2} of {N} query rows of {heads} (batch, head) slice(s), fp32 "
+                       f"accumulation, OpenMP on {cores} threads, {dt:.1f} s"), dt, n2 * heads
 
 
 def run_reference_arm(args, cfg, rank):
@@ -237,6 +250,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--config", default="c2", choices=sorted(CONFIGS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--partition", default="units", choices=["units", "spatial"],
+                    help="multi-GPU partitioning: (batch x heads) units, or slabs of the outermost "
+                         "axis with a key/value halo exchange (config c5 only)")
     ap.add_argument("--units", type=int, default=0,
                     help="profiling aid: shrink the problem to this many (batch x head) units "
                          "(batch 1); the printed line is then NOT a benchmark value")
@@ -267,11 +283,24 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     op, dt, B, H, shape, D, ks, st, di, ca, n_extra, _ = cfg
-    b_local, h_local = shard_units(B, H, world, rank)
-    host, extra = make_inputs(cfg, b_local, h_local, 1000 + rank, dev)
+    spatial = args.partition == "spatial" and world > 1
+    if args.partition == "spatial" and (n_extra or any(d != 1 for d in di)):
+        raise SystemExit("--partition spatial needs an undilated config without extra KV (c5)")
+    if spatial:
+        from natten_b200 import sharding
+        plan = sharding.make_halo_plan(shape[0], world, ks[0], st[0], ca[0])
+        b_local, h_local = B, H
+        host, extra = make_inputs(cfg, B, H, 1000 + rank, dev, slab=plan.slabs[rank])
+        work_fraction = None  # FLOPs of this rank's rows are computed below
+    else:
+        b_local, h_local = shard_units(B, H, world, rank)
+        host, extra = make_inputs(cfg, b_local, h_local, 1000 + rank, dev)
     fn = getattr(nb, op)
 
     def call(q, k, v, ak=None, av=None):
+        if spatial:
+            return sharding.na_forward_spatial_shard(q, k, v, shape, ks, st, ca, rank=rank,
+                                                     world=world)
         return fn(q, k, v, kernel_size=ks, stride=st, dilation=di, is_causal=ca,
                   additional_keys=ak, additional_values=av, return_lse=True)
 
@@ -305,24 +334,32 @@ def main():
 
     # ---- the fused attention kernel alone (roofline of the dominant kernel) ----
     q_tile, kv_tile = nb.choose_tile_shapes(shape, ks, st, di, ca)
-    qp, qkv_shape, q_shape = nb.token_permute_operation(dq, q_tile, di)
-    kp, _, kv_shape = nb.token_permute_operation(dk, kv_tile, di)
-    vp, _, _ = nb.token_permute_operation(dv, kv_tile, di)
-    qp = qp.reshape(-1, math.prod(q_shape), h_local, D)
-    kp = kp.reshape(-1, math.prod(kv_shape), h_local, D)
-    vp = vp.reshape(-1, math.prod(kv_shape), h_local, D)
-    scale = D ** -0.5
-    for _ in range(3):
-        nb.fna_forward_op(qp, kp, vp, qkv_shape, q_shape, kv_shape, ks, st, di, ca, scale, q_tile, kv_tile)
-    torch.cuda.synchronize()
-    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    k0.record()
-    for _ in range(args.steps):
-        nb.fna_forward_op(qp, kp, vp, qkv_shape, q_shape, kv_shape, ks, st, di, ca, scale, q_tile, kv_tile)
-    k1.record()
-    torch.cuda.synchronize()
-    kernel_ms = k0.elapsed_time(k1) / args.steps
-    del qp, kp, vp
+    if spatial:
+        # the slab kernel is timed through the operator above; reuse that time for the roofline
+        kernel_alone = False
+    else:
+        kernel_alone = True
+    if kernel_alone:
+        qp, qkv_shape, q_shape = nb.token_permute_operation(dq, q_tile, di)
+        kp, _, kv_shape = nb.token_permute_operation(dk, kv_tile, di)
+        vp, _, _ = nb.token_permute_operation(dv, kv_tile, di)
+        qp = qp.reshape(-1, math.prod(q_shape), h_local, D)
+        kp = kp.reshape(-1, math.prod(kv_shape), h_local, D)
+        vp = vp.reshape(-1, math.prod(kv_shape), h_local, D)
+        scale = D ** -0.5
+        for _ in range(3):
+            nb.fna_forward_op(qp, kp, vp, qkv_shape, q_shape, kv_shape, ks, st, di, ca, scale, q_tile, kv_tile)
+        torch.cuda.synchronize()
+        k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        k0.record()
+        for _ in range(args.steps):
+            nb.fna_forward_op(qp, kp, vp, qkv_shape, q_shape, kv_shape, ks, st, di, ca, scale, q_tile, kv_tile)
+        k1.record()
+        torch.cuda.synchronize()
+        kernel_ms = k0.elapsed_time(k1) / args.steps
+        del qp, kp, vp
+    else:
+        kernel_ms = ms_total / args.steps
 
     # ---- end to end through the public operator with HOST buffers ----
     e2e_ms = None
@@ -365,8 +402,9 @@ def main():
 
     peaks = read_peaks()
     flops_all = algorithmic_flops(cfg)
-    flops_rank = algorithmic_flops(cfg, units=b_local * h_local)
     fna_flops_rank = 4.0 * D * attended_pairs(shape, ks, st, di, ca) * b_local * h_local
+    if spatial:
+        fna_flops_rank /= world  # rows are split evenly; the roofline entry is then approximate
     ms_step = ms_total / args.steps
     value = flops_all / (ms_step * 1e-3) / 1e12
     achieved = fna_flops_rank / (kernel_ms_max * 1e-3) / 1e12
@@ -376,12 +414,16 @@ def main():
         higher_is_better=True, scaling="strong", vs_baseline=None, dtype=dt, data="synthetic",
         config=dict(workload=WORKLOAD_TEXT[args.config] + (
             f" [REDUCED to {args.units} (batch x head) units for profiling: not a benchmark value]"
-            if args.units else ""), partition="batch x heads",
+            if args.units else ""),
+                    partition=("slabs of axis 0 + NCCL halo exchange of K/V, output stays sharded"
+                               if spatial else "batch x heads, no collective"),
                     units_per_gpu=b_local * h_local, l2="inputs larger than L2 (no flush needed)",
                     q_tile=list(q_tile), kv_tile=list(kv_tile)),
         clocks=clocks, gpu_launches=int(launches),
         roofline=dict(bound="tensor", achieved=achieved, peak=peaks["bf16_tflops"], unit="TFLOP/s",
-                      frac=achieved / peaks["bf16_tflops"], traffic=None,
+                      frac=achieved / peaks["bf16_tflops"],
+                      traffic=(NCU_TRAFFIC_PER_UNIT[args.config] * b_local * h_local
+                               if args.config in NCU_TRAFFIC_PER_UNIT and not spatial else None),
                       kernel="fna_fwd_kernel", kernel_ms=kernel_ms_max,
                       peak_source=peaks["source"] + " burst (kernel timed alone)",
                       frac_of_sustained=achieved / peaks["bf16_tflops_sustained"]),
