@@ -94,10 +94,12 @@ struct FnaParams {
 #define PROF_MARK(i) { const long long n_ = clock64(); prof_[i] += n_ - prof_t_; prof_t_ = n_; }
 #define PROF_FLUSH(role) { prof_[7] = clock64() - prof_t0_; for (int i_ = 0; i_ < 8; ++i_) p.prof[((long long)blockIdx.x * 4 + (role)) * 8 + i_] = prof_[i_]; }
 #if B200NA_PROFILE >= 2
-#define TRACE2(role, code) TRACE(role, code)
-#define PROF2_DECL PROF_DECL
-#define PROF2_MARK(i) PROF_MARK(i)
-#define PROF2_FLUSH(role) PROF_FLUSH(role)
+// MMA / load threads: one 32-bit clock read and one shared-memory store per event (anything
+// heavier perturbs the single issuing thread); block 0 copies the ring to global at teardown.
+#define TRACE2(role, code) { if (trace2_n_ < 1024) { trace2_buf_[((role) - 2) * 1024 + trace2_n_] = ((uint32_t)clock() << 5) | (code); ++trace2_n_; } }
+#define PROF2_DECL int trace2_n_ = 0; uint32_t* trace2_buf_ = reinterpret_cast<uint32_t*>(smem + SM::kBytes);
+#define PROF2_MARK(i) {}
+#define PROF2_FLUSH(role) {}
 #else
 #define TRACE2(role, code) {}
 #define PROF2_DECL
@@ -324,6 +326,9 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     if (threadIdx.x == 0) atomicCAS(p.status, 0, (4 << 8) | kStSmemAlign);
     return;
   }
+#if defined(B200NA_PROFILE) && B200NA_PROFILE >= 2
+  for (int i = threadIdx.x; i < 2048; i += kThreads) reinterpret_cast<uint32_t*>(smem + SM::kBytes)[i] = 0;
+#endif
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     ptx::mbar_init(bars.q_full, 1);
@@ -689,43 +694,42 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         ptx::tc_commit(bars.kv_empty + slot_k);
         if (n == 1) ptx::tc_commit(bars.q_empty);
         for (int iter = 0; iter < n && alive; ++iter) {
+          // Both operands of this iteration (V of this tile, K of the next) are waited for up
+          // front, so that nothing but the softmax hand-off separates the MMA bursts below.
           const uint32_t slot_v = ring.slot;
           if (!wait_bar(bars.kv_full + slot_v, ring.phase, abort_flag, p.status,
                         (2 << 8) | kStKVFull)) { alive = false; break; }
           ring.advance();
-          PROF2_MARK(1)
           TRACE2(2, 11)
           const bool more = iter + 1 < n;
           uint32_t slot_kn = 0;
+          if (more) {
+            slot_kn = ring.slot;
+            if (!wait_bar(bars.kv_full + slot_kn, ring.phase, abort_flag, p.status,
+                          (2 << 8) | kStKVFull)) { alive = false; break; }
+            ring.advance();
+            TRACE2(2, 16)
+          }
+          const uint32_t v_addr = kv_base + slot_v * kTileBytes;
+          const uint32_t k_addr = kv_base + slot_kn * kTileBytes;
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             if (!wait_bar(bars.p_full + h, ph_p[h], abort_flag, p.status, (2 << 8) | kStPFull)) {
               alive = false; break;
             }
             ph_p[h] ^= 1;
-            if (h == 0) { PROF2_MARK(2) } else { PROF2_MARK(3) }
             TRACE2(2, 12 + h)
             if (iter == 0) {
               // the previous item's epilogue must have drained O_h before it is overwritten
               if (!wait_bar(bars.o_empty + h, ph_oe[h], abort_flag, p.status,
                             (2 << 8) | kStOEmpty)) { alive = false; break; }
               ph_oe[h] ^= 1;
-              PROF2_MARK(4)
             }
             ptx::tc_fence_after_sync();
-            issue_pv(h, kv_base + slot_v * kTileBytes, iter == 0);
+            issue_pv(h, v_addr, iter == 0);
             TRACE2(2, 14 + h)
             if (more) {
-              if (h == 0) {
-                slot_kn = ring.slot;
-                if (!wait_bar(bars.kv_full + slot_kn, ring.phase, abort_flag, p.status,
-                              (2 << 8) | kStKVFull)) { alive = false; break; }
-                ring.advance();
-                PROF2_MARK(5)
-                TRACE2(2, 16)
-                ptx::tc_fence_after_sync();
-              }
-              issue_qk(h, kv_base + slot_kn * kTileBytes);
+              issue_qk(h, k_addr);
               ptx::tc_commit(bars.s_full + h);
               TRACE2(2, 17 + h)
             } else {
@@ -738,7 +742,6 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             ptx::tc_commit(bars.kv_empty + slot_kn);
             if (iter + 2 == n) ptx::tc_commit(bars.q_empty);  // last Q.K^T has been issued
           }
-          PROF2_MARK(6)
         }
       }
       PROF2_FLUSH(2)
@@ -789,6 +792,12 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   // ---- teardown ----------------------------------------------------------------------------
   ptx::tc_fence_before_sync();
   __syncthreads();
+#if defined(B200NA_PROFILE) && B200NA_PROFILE >= 2
+  if (blockIdx.x == 0) {
+    const uint32_t* tb = reinterpret_cast<const uint32_t*>(smem + SM::kBytes);
+    for (int i = threadIdx.x; i < 2048; i += kThreads) p.prof[148 * 32 + 4096 + i] = tb[i];
+  }
+#endif
   if (*abort_flag) {
     // Draining after an expired wait: give loads that are still in flight time to land in this
     // CTA's shared memory before it is released.
@@ -884,7 +893,7 @@ int device_state(DeviceState** out) {
     for (int i = 0; i < 12; ++i) {
       const void* fn = kernel_variant(i & 2 ? 128 : 64, (i & 1) != 0, 1 + (i >> 2));
       B200NA_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           i & 2 ? Smem<128>::kBytes : Smem<64>::kBytes));
+                                           (i & 2 ? Smem<128>::kBytes : Smem<64>::kBytes) + 8192));
       cudaFuncAttributes fa;
       B200NA_CUDA_TRY(cudaFuncGetAttributes(&fa, fn));
       // one CTA of kThreads threads must fit the register file
@@ -925,8 +934,14 @@ int launch_fna(const void* q, const void* k, const void* v, FnaParams& p, int D,
   const int grid = (int)(p.total_work < st->sms ? p.total_work : st->sms);
   const void* fn = kernel_variant(D, dtype == B200NA_BF16, p.ndim);
   void* args[] = {(void*)&tq, (void*)&tk, (void*)&tv, (void*)&p};
-  B200NA_CUDA_TRY(cudaLaunchKernel(fn, dim3(grid), dim3(kThreads),  args,
-                                   D == 128 ? Smem<128>::kBytes : Smem<64>::kBytes, stream));
+#if defined(B200NA_PROFILE) && B200NA_PROFILE >= 2
+  constexpr int kExtraSmem = 8192;
+#else
+  constexpr int kExtraSmem = 0;
+#endif
+  B200NA_CUDA_TRY(cudaLaunchKernel(fn, dim3(grid), dim3(kThreads), args,
+                                   (D == 128 ? Smem<128>::kBytes : Smem<64>::kBytes) + kExtraSmem,
+                                   stream));
   return B200NA_OK;
 }
 
