@@ -116,6 +116,29 @@ B200NA_API int b200na_fna_forward_sharded(
     const int* q_origin, const int* q_extent, const int* kv_origin, b200na_stream_t stream);
 
 /*
+ * Whole operator in one call: token permute of Q, K, V -> fused attention -> unpermute of O and
+ * LSE, i.e. the forward of the reference's Python backend adapter
+ * (src/natten/backends/blackwell_fna.py:91-181) for hosts that bind this C ABI directly.
+ *   q: [B, *shape, Hq, D]; k, v: [B, *shape, Hkv, D]; o: [B, *shape, Hq, D]; lse: [B, *shape, Hq]
+ *   fp32 or NULL. dtype F16/BF16, D in {64, 128}, prod(q_tile) = 256, prod(kv_tile) = 128.
+ *   workspace: device scratch for the permuted copies, 256-byte aligned, at least
+ *   b200na_na_forward_workspace_bytes(...) bytes (0 for 1-D undilated tile-multiple layouts,
+ *   which need no permutation). Contents are unspecified afterwards; calls that share a
+ *   workspace must be ordered on one stream.
+ * b200na_na_forward_workspace_bytes returns the size, or a negative error code.
+ */
+B200NA_API int64_t b200na_na_forward_workspace_bytes(int ndim, const int* shape,
+                                                     const int* dilation, const int* q_tile,
+                                                     const int* kv_tile, int B, int Hq, int Hkv,
+                                                     int D, int want_lse);
+B200NA_API int b200na_na_forward(const void* q, const void* k, const void* v, void* o, float* lse,
+                                 int ndim, const int* shape, const int* kernel, const int* stride,
+                                 const int* dilation, const int* causal, const int* q_tile,
+                                 const int* kv_tile, int B, int Hq, int Hkv, int D, int dtype,
+                                 float scale, void* workspace, int64_t workspace_bytes,
+                                 b200na_stream_t stream);
+
+/*
  * Dense attention forward: replaces natten::blackwell_fmha_forward for the non-varlen case
  * (reference: csrc/src/blackwell_fmha.cu:55-260; Python caller src/natten/functional.py:74-348),
  * used for the extra (cross-attention) KV tokens and the self-attention fast path.

@@ -20,7 +20,8 @@ F32, F16, BF16 = 0, 1, 2
 # Every symbol include/natten_b200.h declares.
 SYMBOLS = (
     "b200na_strerror", "b200na_version", "b200na_token_permute", "b200na_token_unpermute",
-    "b200na_fna_forward", "b200na_fna_forward_sharded", "b200na_fmha_forward", "b200na_na_forward_simt", "b200na_merge",
+    "b200na_fna_forward", "b200na_fna_forward_sharded", "b200na_fmha_forward",
+    "b200na_na_forward", "b200na_na_forward_workspace_bytes", "b200na_na_forward_simt", "b200na_merge",
     "b200na_device_status",
 )
 
@@ -59,6 +60,13 @@ def _load() -> ctypes.CDLL:
                                                c_int, ip, ip, ip, ip, ip, ip, ip, ip, ip,
                                                c_int, c_int, c_int, c_int, c_int, c_float,
                                                ip, ip, ip, c_void_p]
+    lib.b200na_na_forward_workspace_bytes.restype = c_i64
+    lib.b200na_na_forward_workspace_bytes.argtypes = [c_int, ip, ip, ip, ip, c_int, c_int, c_int,
+                                                      c_int, c_int]
+    lib.b200na_na_forward.restype = c_int
+    lib.b200na_na_forward.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                      ip, ip, ip, ip, ip, ip, ip, c_int, c_int, c_int, c_int,
+                                      c_int, c_float, c_void_p, c_i64, c_void_p]
     lib.b200na_fmha_forward.restype = c_int
     lib.b200na_fmha_forward.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                         c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,

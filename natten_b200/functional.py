@@ -431,6 +431,62 @@ def fna_forward_op(q_perm: Tensor, k_perm: Tensor, v_perm: Tensor, qkv_shape: Di
     return out, lse
 
 
+def fused_workspace_bytes(shape: DimensionType, dilation: DimensionType, q_tile_shape: DimensionType,
+                          kv_tile_shape: DimensionType, batch: int, heads_q: int, heads_kv: int,
+                          head_dim: int, want_lse: bool = True) -> int:
+    """Scratch bytes `na_forward_fused` needs (0 when the layout needs no permutation)."""
+    n = _lib.lib.b200na_na_forward_workspace_bytes(
+        len(shape), _lib.ints(shape), _lib.ints(dilation), _lib.ints(q_tile_shape),
+        _lib.ints(kv_tile_shape), batch, heads_q, heads_kv, head_dim, 1 if want_lse else 0)
+    if n < 0:
+        _lib.check(int(n), "b200na_na_forward_workspace_bytes", kernel_launches=0)
+    return int(n)
+
+
+def na_forward_fused(query: Tensor, key: Tensor, value: Tensor, kernel_size, stride=1, dilation=1,
+                     is_causal=False, scale: Optional[float] = None, q_tile_shape=None,
+                     kv_tile_shape=None, workspace: Optional[Tensor] = None
+                     ) -> Tuple[Tensor, Tensor]:
+    """Neighborhood attention forward through the single-call C entry `b200na_na_forward`
+    (permute -> attention -> unpermute inside the library, permuted copies in `workspace`).
+    Same results as `na1d/na2d/na3d(..., return_lse=True)` for fp16/bf16 and head dim 64/128;
+    `workspace` is a uint8 CUDA tensor of at least `fused_workspace_bytes(...)` bytes (allocated
+    here when omitted)."""
+    na_tensor_checks(query, key, value)
+    na_dim = query.dim() - 3
+    kernel_size, stride, dilation, is_causal = check_all_args(na_dim, kernel_size, stride,
+                                                              dilation, is_causal)
+    check_args_against_input(query, kernel_size, stride, dilation, is_causal)
+    _require_cuda(query, key, value)
+    shape = tuple(query.shape[1:1 + na_dim])
+    B, Hq, D = query.shape[0], query.shape[-2], query.shape[-1]
+    Hkv = key.shape[-2]
+    if query.dtype not in (torch.float16, torch.bfloat16) or D not in TENSOR_CORE_HEAD_DIMS:
+        raise NotImplementedError("na_forward_fused needs fp16/bf16 operands and head dim 64 or 128.")
+    if q_tile_shape is None or kv_tile_shape is None:
+        auto_q, auto_kv = choose_tile_shapes(shape, kernel_size, stride, dilation, is_causal)
+        q_tile_shape = q_tile_shape or auto_q
+        kv_tile_shape = kv_tile_shape or auto_kv
+    q_tile_shape = check_tile_shape(na_dim, q_tile_shape, "q_tile_shape", Q_TILE_SIZE)
+    kv_tile_shape = check_tile_shape(na_dim, kv_tile_shape, "kv_tile_shape", KV_TILE_SIZE)
+    need = fused_workspace_bytes(shape, dilation, q_tile_shape, kv_tile_shape, B, Hq, Hkv, D)
+    if workspace is None and need > 0:
+        workspace = torch.empty(need, dtype=torch.uint8, device=query.device)
+    q, k, v = (t.detach().contiguous() for t in (query, key, value))
+    out = torch.empty_like(q)
+    lse = torch.empty(q.shape[:-1], dtype=torch.float32, device=q.device)
+    scale = scale or D ** -0.5
+    with torch.cuda.device(q.device):
+        _lib.check(_lib.lib.b200na_na_forward(
+            _ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(lse), na_dim, _lib.ints(shape),
+            _lib.ints(kernel_size), _lib.ints(stride), _lib.ints(dilation),
+            _lib.ints([1 if c else 0 for c in is_causal]), _lib.ints(q_tile_shape),
+            _lib.ints(kv_tile_shape), B, Hq, Hkv, D, _DTYPE_CODE[q.dtype], float(scale),
+            _ptr(workspace) if need > 0 else None, workspace.numel() if need > 0 else 0,
+            _stream(q)), "b200na_na_forward", kernel_launches=1 if need == 0 else 6)
+    return out, lse
+
+
 def _na(na_dim: int, query: Tensor, *args, **kwargs):
     if query.dim() != na_dim + 3:
         raise ValueError(f"NA{na_dim}D requires {na_dim + 3}-D input tensors, got {query.dim()=}.")

@@ -227,6 +227,31 @@ def test_spatial_slabs_reproduce_the_unsharded_result(shape, ks, st, ca, world):
                                   v[:, lo + 1:hi].contiguous(), shape, t0, lo + 1, ks, st, ca)
 
 
+@pytest.mark.parametrize("shape,ks,st,di,ca", [
+    ((40, 44), (7, 9), (1, 2), (2, 1), (False, True)),
+    ((6, 20, 24), (3, 5, 8), (1, 1, 4), (1, 1, 1), (True, False, False)),
+    ((1024,), (128,), (1,), (1,), (True,)),        # identity layout: no workspace needed
+    ((1000,), (33,), (1,), (3,), (False,)),
+])
+def test_single_call_c_entry_equals_the_operator(shape, ks, st, di, ca):
+    """b200na_na_forward (permute -> attention -> unpermute in one C call, caller workspace) gives
+    bit-identical results to na1d/na2d/na3d, also when the workspace is reused by a second call."""
+    torch.manual_seed(21)
+    q, k, v = (torch.randn(2, *shape, 2, 64, device="cuda").half() for _ in range(3))
+    want_o, want_l = _na_fn(len(shape))(q, k, v, ks, st, di, ca, return_lse=True)
+    tq, tkv = nb.choose_tile_shapes(shape, ks, st, di, ca)
+    need = nb.fused_workspace_bytes(shape, di, tq, tkv, 2, 2, 2, 64)
+    assert (need == 0) == (shape == (1024,))
+    ws = torch.full((max(need, 1),), 0xAB, dtype=torch.uint8, device="cuda")
+    for _ in range(2):
+        o, l = nb.na_forward_fused(q, k, v, ks, st, di, ca, workspace=ws)
+        assert L.device_status() == 0
+        assert torch.equal(o, want_o) and torch.equal(l, want_l)
+    if need:
+        with pytest.raises(L.NattenB200Error):
+            nb.na_forward_fused(q, k, v, ks, st, di, ca, workspace=ws[:need - 256])
+
+
 def test_forward_is_deterministic():
     torch.manual_seed(4)
     q, k, v = (torch.randn(2, 40, 40, 2, 64, device="cuda").half() for _ in range(3))
