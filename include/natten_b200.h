@@ -30,6 +30,7 @@ extern "C" {
 #define B200NA_ERR_CUDA (-4)             /* a CUDA runtime / driver call failed (see last error)  */
 #define B200NA_ERR_DEVICE (-5)           /* current device is not compute capability 10.x         */
 #define B200NA_ERR_KERNEL_TIMEOUT (-6)   /* a bounded device-side wait expired (see device_status) */
+#define B200NA_ERR_WORKSPACE_LIMIT (-7)  /* problem needs more scratch than the built-in array holds */
 
 /* Element types of Q/K/V/O. */
 #define B200NA_F32 0
@@ -137,6 +138,37 @@ B200NA_API int b200na_na_forward(const void* q, const void* k, const void* v, vo
                                  const int* kv_tile, int B, int Hq, int Hkv, int D, int dtype,
                                  float scale, void* workspace, int64_t workspace_bytes,
                                  b200na_stream_t stream);
+
+/*
+ * b200na_na_forward without a workspace argument and without any allocation. This entry has no
+ * counterpart in the reference.
+ *
+ * Who it is for: code that needs the operator at a point where it is not allowed to obtain device
+ * memory — a plug-in inside a host application that owns the whole device-memory budget and hands
+ * none out after start-up, a serving loop that must not hit the allocator (a cudaMalloc can stall
+ * the device and has unbounded latency), or a process that gave all of its memory to a pool when it
+ * started. Such callers still pass their own inputs and outputs; only the scratch for the permuted
+ * copies comes from the library: a fixed array of B200NA_STATIC_WORKSPACE_BYTES that is part of the
+ * loaded module (every GPU that loads the library holds it until the process exits).
+ *
+ * Same arguments, results and kernels as b200na_na_forward. Differences:
+ *   - returns B200NA_ERR_WORKSPACE_LIMIT when b200na_na_forward_workspace_bytes(...) for the
+ *     problem exceeds B200NA_STATIC_WORKSPACE_BYTES (use b200na_na_forward then);
+ *   - calls no cudaMalloc / cudaFree and no allocating library routine;
+ *   - the first call on each device looks up the array's device address (and does the library's
+ *     usual one-time per-device set-up); make that first call outside any stream capture;
+ *   - all calls on a device share the one array, which keeps whatever the previous call left in
+ *     it (nothing in it needs clearing between calls); two calls that can overlap on the GPU —
+ *     different streams, or the same stream from unsynchronised threads — race on it and corrupt
+ *     each other's results. Order them on one stream.
+ */
+#define B200NA_STATIC_WORKSPACE_BYTES (32u * 1024u * 1024u)
+B200NA_API int b200na_na_forward_static(const void* q, const void* k, const void* v, void* o,
+                                        float* lse, int ndim, const int* shape, const int* kernel,
+                                        const int* stride, const int* dilation, const int* causal,
+                                        const int* q_tile, const int* kv_tile, int B, int Hq,
+                                        int Hkv, int D, int dtype, float scale,
+                                        b200na_stream_t stream);
 
 /*
  * Dense attention forward: replaces natten::blackwell_fmha_forward for the non-varlen case

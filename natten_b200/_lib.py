@@ -15,13 +15,15 @@ LIB_PATH = os.environ.get("NATTEN_B200_LIB") or os.path.join(_HERE, "lib", "libn
 OK = 0
 ERR_INVALID_ARGUMENT, ERR_UNSUPPORTED, ERR_ALIGNMENT, ERR_CUDA, ERR_DEVICE, ERR_KERNEL_TIMEOUT = (
     -1, -2, -3, -4, -5, -6)
+ERR_WORKSPACE_LIMIT = -7
+STATIC_WORKSPACE_BYTES = 32 * 1024 * 1024
 F32, F16, BF16 = 0, 1, 2
 
 # Every symbol include/natten_b200.h declares.
 SYMBOLS = (
     "b200na_strerror", "b200na_version", "b200na_token_permute", "b200na_token_unpermute",
     "b200na_fna_forward", "b200na_fna_forward_sharded", "b200na_fmha_forward",
-    "b200na_na_forward", "b200na_na_forward_workspace_bytes", "b200na_na_forward_simt", "b200na_merge",
+    "b200na_na_forward", "b200na_na_forward_workspace_bytes", "b200na_na_forward_static", "b200na_na_forward_simt", "b200na_merge",
     "b200na_device_status",
 )
 
@@ -67,6 +69,10 @@ def _load() -> ctypes.CDLL:
     lib.b200na_na_forward.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                       ip, ip, ip, ip, ip, ip, ip, c_int, c_int, c_int, c_int,
                                       c_int, c_float, c_void_p, c_i64, c_void_p]
+    lib.b200na_na_forward_static.restype = c_int
+    lib.b200na_na_forward_static.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                             ip, ip, ip, ip, ip, ip, ip, c_int, c_int, c_int,
+                                             c_int, c_int, c_float, c_void_p]
     lib.b200na_fmha_forward.restype = c_int
     lib.b200na_fmha_forward.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                         c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,

@@ -29,6 +29,7 @@ extern "C" B200NA_API const char* b200na_strerror(int code) {
       return copy.c_str();
     }
     case B200NA_ERR_DEVICE: return "current device is not a compute capability 10.x (B200-class) GPU";
+    case B200NA_ERR_WORKSPACE_LIMIT: return "the problem needs more scratch than the 32 MiB built into the library; call b200na_na_forward with your own workspace";
     case B200NA_ERR_KERNEL_TIMEOUT: return "a bounded device-side wait expired; see b200na_device_status";
     default: return "unknown natten_b200 error code";
   }

@@ -2,6 +2,8 @@
 // behind ONE C call, for hosts that bind the C ABI directly (the reference runs the same three
 // stages from Python: src/natten/backends/blackwell_fna.py:91-181). The permuted copies of Q, K,
 // V, O and LSE live in a workspace the caller provides.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace b200na {
@@ -89,6 +91,58 @@ int na_forward_with_workspace(const void* q, const void* k, const void* v, void*
 }
 
 }  // namespace b200na
+
+namespace b200na {
+namespace {
+
+// Scratch of b200na_na_forward_static. It is part of the loaded module: every device that loads
+// this library holds these bytes from module load until the process exits.
+static __device__ __align__(256) unsigned char g_static_workspace[B200NA_STATIC_WORKSPACE_BYTES];
+
+// In host code `g_static_workspace` is only a handle for the runtime, not a device address; the
+// address a kernel can use comes from cudaGetSymbolAddress, looked up once per device while that
+// device is current.
+int static_workspace_address(void** out) {
+  static std::mutex mu;
+  static void* cached[64] = {nullptr};
+  int dev = 0;
+  B200NA_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return B200NA_ERR_DEVICE;
+  std::lock_guard<std::mutex> lk(mu);
+  if (!cached[dev]) {
+    void* ptr = nullptr;
+    B200NA_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_static_workspace));
+    if (!ptr) return B200NA_ERR_CUDA;
+    cached[dev] = ptr;
+  }
+  *out = cached[dev];
+  return B200NA_OK;
+}
+
+}  // namespace
+}  // namespace b200na
+
+extern "C" B200NA_API int b200na_na_forward_static(const void* q, const void* k, const void* v,
+                                                   void* o, float* lse, int ndim, const int* shape,
+                                                   const int* kernel, const int* stride,
+                                                   const int* dilation, const int* causal,
+                                                   const int* q_tile, const int* kv_tile, int B,
+                                                   int Hq, int Hkv, int D, int dtype, float scale,
+                                                   b200na_stream_t stream) {
+  using namespace b200na;
+  FusedPlan pl;
+  int rc = make_plan(pl, ndim, shape, dilation, q_tile, kv_tile, B, Hq, Hkv, D, 2, lse != nullptr);
+  if (rc != B200NA_OK) return rc;
+  if (pl.total > (int64_t)B200NA_STATIC_WORKSPACE_BYTES) return B200NA_ERR_WORKSPACE_LIMIT;
+  void* ws = nullptr;
+  if ((rc = static_workspace_address(&ws)) != B200NA_OK) return rc;
+  // Nothing in the workspace has to start at zero: the permute kernels overwrite every row they
+  // own (padding rows with zeros) and the unpermute kernels never read rows the attention kernel
+  // skipped, so whatever an earlier call left behind is never observed.
+  return na_forward_with_workspace(q, k, v, o, lse, ndim, shape, kernel, stride, dilation, causal,
+                                   q_tile, kv_tile, B, Hq, Hkv, D, dtype, scale, ws,
+                                   (int64_t)B200NA_STATIC_WORKSPACE_BYTES, stream);
+}
 
 extern "C" B200NA_API int64_t b200na_na_forward_workspace_bytes(int ndim, const int* shape,
                                                                 const int* dilation,
