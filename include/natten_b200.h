@@ -99,6 +99,23 @@ B200NA_API int b200na_fna_forward(const void* q, const void* k, const void* v, v
                        int Hkv, int D, int dtype, float scale, b200na_stream_t stream);
 
 /*
+ * b200na_fna_forward with extra key/value tokens that EVERY query attends in addition to its
+ * neighborhood (cross-attention context), fused into the same kernel and the same softmax. The
+ * reference runs a second attention over the extra tokens and merges the two results
+ * (src/natten/functional.py:524-559); the semantics are those of its reference mask
+ * (csrc/include/natten/cuda/reference/mask.hpp:314-318). The extra tiles ride the same K/V ring
+ * as the neighborhood tiles, so the dense-attention pass, the merge pass and their traffic vanish.
+ *   add_k, add_v: [Bp / prod(dilation), n_extra, Hkv, D] in the ORIGINAL batch order (not
+ *   permuted, shared by the dilation groups of a batch entry); n_extra need not be a tile multiple.
+ */
+B200NA_API int b200na_fna_forward_extra_kv(
+    const void* q, const void* k, const void* v, const void* add_k, const void* add_v,
+    int n_extra, void* o, float* lse, int ndim, const int* qkv_shape, const int* q_shape,
+    const int* kv_shape, const int* kernel, const int* stride, const int* dilation,
+    const int* causal, const int* q_tile, const int* kv_tile, int Bp, int Hq, int Hkv, int D,
+    int dtype, float scale, b200na_stream_t stream);
+
+/*
  * The same kernel on one rank's SLAB of a spatially sharded, undilated token layout. The
  * reference has no counterpart (it has no multi-GPU code); window arithmetic follows
  * csrc/include/natten/cuda/reference/mask.hpp:59-89 in layout ("global") coordinates.

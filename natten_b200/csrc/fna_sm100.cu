@@ -73,6 +73,8 @@ struct FnaParams {
   int kv_org[B200NA_MAX_DIM];  // layout coordinate of local key/value index 0
   int q_len[B200NA_MAX_DIM];   // number of real (non-padding) local query coordinates per axis
   int dense;                // dense attention: one axis, window = all keys (or causal prefix)
+  int n_extra;              // extra key/value tokens every query attends (0 = none)
+  int extra_tiles;          // ceil(n_extra / 128): KV tiles appended to every item's walk
   int Bp, Hq, Hkv;
   int Sq, Skv;              // rows per batch' in the q / kv tensors
   int n_qtiles;             // ceil(Sq / 256)
@@ -125,7 +127,8 @@ struct Item {
   int kv_n[B200NA_MAX_DIM];   // kv tiles per axis
   int ws_hi[B200NA_MAX_DIM];  // window start of the tile's last query
   int we_lo[B200NA_MAX_DIM];  // window end of the tile's first query
-  int n_tiles;
+  int n_tiles;   // neighborhood tiles + extra-KV tiles
+  int n_na;      // neighborhood tiles only
   bool skip;
 };
 
@@ -176,6 +179,8 @@ __device__ __forceinline__ void decode_item(const FnaParams& p, long long w, Ite
     }
   }
   if (p.dense && it.qt * kQTile >= p.Sq) it.skip = true;
+  it.n_na = it.n_tiles;
+  it.n_tiles += p.extra_tiles;
 }
 
 template <int NDIM>
@@ -291,7 +296,8 @@ __device__ __forceinline__ void kv_tile_next(const Item& it, int (&c)[B200NA_MAX
 template <int D, bool kBf16, int NDIM>
 __global__ void __launch_bounds__(kThreads, 1)
 fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-               const __grid_constant__ CUtensorMap tm_v, const FnaParams p) {
+               const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_ek,
+               const __grid_constant__ CUtensorMap tm_ev, const FnaParams p) {
   using SM = Smem<D>;
   constexpr int kStages = SM::kStages;
   constexpr int kTileBytes = SM::kTileBytes;
@@ -377,6 +383,10 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     ptx::prefetch_tensormap(&tm_q);
     ptx::prefetch_tensormap(&tm_k);
     ptx::prefetch_tensormap(&tm_v);
+    if (p.extra_tiles) {
+      ptx::prefetch_tensormap(&tm_ek);
+      ptx::prefetch_tensormap(&tm_ev);
+    }
   }
   ptx::tc_fence_before_sync();
   __syncthreads();
@@ -435,7 +445,11 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       bool alive = true;
       int tc[B200NA_MAX_DIM] = {it.kv_t0[0], it.kv_t0[1], it.kv_t0[2]};
       for (int iter = 0; iter < it.n_tiles; ++iter) {
-        const bool interior = kv_tile_interior<NDIM>(p, it, tc);
+        // Extra-KV tiles follow the neighborhood tiles: every query attends every extra token,
+        // only the ragged end of the last tile is masked.
+        const bool is_extra = iter >= it.n_na;
+        const int extra_valid = p.n_extra - (iter - it.n_na) * kKVTile;  // valid columns if extra
+        const bool interior = is_extra ? extra_valid >= kKVTile : kv_tile_interior<NDIM>(p, it, tc);
         // warp-uniform outcome: the TMEM accesses below are warp-collective
         if (!__all_sync(0xffffffffu, wait_bar(bars.s_full + half, ph_s, abort_flag, p.status,
                                               (1 << 8) | kStSFull))) {
@@ -448,7 +462,12 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         ptx::tc_fence_after_sync();
         // Mask words of this thread's two 32-column chunks (boundary tiles only).
         uint32_t mw0 = ~0u, mw1 = ~0u;
-        if (!interior) {
+        if (!interior && is_extra) {
+          const int v0 = imin(imax(extra_valid - (part * 64), 0), 32);
+          const int v1 = imin(imax(extra_valid - (part * 64 + 32), 0), 32);
+          mw0 = v0 >= 32 ? ~0u : ((1u << v0) - 1u);
+          mw1 = v1 >= 32 ? ~0u : ((1u << v1) - 1u);
+        } else if (!interior) {
           uint4 mk = make_uint4(~0u, ~0u, ~0u, ~0u);
           int off = 0;
 #pragma unroll
@@ -470,7 +489,7 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           mw0 = part ? mk.z : mk.x;
           mw1 = part ? mk.w : mk.y;
         }
-        kv_tile_next<NDIM>(it, tc);
+        if (!is_extra) kv_tile_next<NDIM>(it, tc);
         // Pass 1: row maximum of the raw logits over this thread's 64 columns. Chunk 1 is read
         // first and dropped, chunk 0 stays in registers for pass 2.
         uint32_t sr[32];
@@ -768,8 +787,11 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                              it.h, it.qt * kQTile + h * kHalf, it.bp);
         int tc[B200NA_MAX_DIM] = {it.kv_t0[0], it.kv_t0[1], it.kv_t0[2]};
         for (int iter = 0; iter < it.n_tiles && alive; ++iter) {
-          const int row0 = kv_tile_row<NDIM>(p, tc);
-          kv_tile_next<NDIM>(it, tc);
+          const bool is_extra = iter >= it.n_na;
+          const int row0 = is_extra ? (iter - it.n_na) * kKVTile : kv_tile_row<NDIM>(p, tc);
+          if (!is_extra) kv_tile_next<NDIM>(it, tc);
+          // extra tokens are shared by the dilation groups of a batch entry
+          const int b_src = is_extra ? it.bp / p.G : it.bp;
           for (int kv = 0; kv < 2; ++kv) {
             const uint32_t slot = ring.slot;
             if (!wait_bar(bars.kv_empty + slot, ring.phase ^ 1, abort_flag, p.status,
@@ -779,8 +801,9 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             TRACE2(3, 20 + kv)
             ptx::mbar_arrive_expect_tx(bars.kv_full + slot, kTileBytes);
             for (int db = 0; db < kDBlocks; ++db)
-              ptx::tma_load_4d(kv_sm + slot * kTileBytes + db * kBlockBytes, kv == 0 ? &tm_k : &tm_v,
-                               bars.kv_full + slot, db * 64, it.hk, row0, it.bp);
+              ptx::tma_load_4d(kv_sm + slot * kTileBytes + db * kBlockBytes,
+                               is_extra ? (kv == 0 ? &tm_ek : &tm_ev) : (kv == 0 ? &tm_k : &tm_v),
+                               bars.kv_full + slot, db * 64, it.hk, row0, b_src);
             PROF2_MARK(6)
           }
         }
@@ -914,7 +937,7 @@ long long* g_prof_buffer = nullptr;
 #endif
 
 int launch_fna(const void* q, const void* k, const void* v, FnaParams& p, int D, int dtype,
-               cudaStream_t stream) {
+               cudaStream_t stream, const void* add_k = nullptr, const void* add_v = nullptr) {
   DeviceState* st = nullptr;
   int rc = device_state(&st);
   if (rc != B200NA_OK) return rc;
@@ -925,6 +948,16 @@ int launch_fna(const void* q, const void* k, const void* v, FnaParams& p, int D,
   if ((rc = make_tensor_map(&tq, q, dtype, p.Bp, p.Sq, p.Hq, D)) != B200NA_OK) return rc;
   if ((rc = make_tensor_map(&tk, k, dtype, p.Bp, p.Skv, p.Hkv, D)) != B200NA_OK) return rc;
   if ((rc = make_tensor_map(&tv, v, dtype, p.Bp, p.Skv, p.Hkv, D)) != B200NA_OK) return rc;
+  // extra key/value tokens [B, n_extra, Hkv, D]; without them the maps alias K/V and are unused
+  CUtensorMap tek = tk, tev = tv;
+  if (p.n_extra > 0) {
+    if (!add_k || !add_v) return B200NA_ERR_INVALID_ARGUMENT;
+    if ((reinterpret_cast<uintptr_t>(add_k) | reinterpret_cast<uintptr_t>(add_v)) % 16 != 0)
+      return B200NA_ERR_ALIGNMENT;
+    if ((rc = make_tensor_map(&tek, add_k, dtype, p.Bp / p.G, p.n_extra, p.Hkv, D)) != B200NA_OK) return rc;
+    if ((rc = make_tensor_map(&tev, add_v, dtype, p.Bp / p.G, p.n_extra, p.Hkv, D)) != B200NA_OK) return rc;
+  }
+  p.extra_tiles = (p.n_extra + kKVTile - 1) / kKVTile;
   p.status = st->status_ptr;
 #ifdef B200NA_PROFILE
   p.prof = g_prof_buffer;
@@ -933,7 +966,7 @@ int launch_fna(const void* q, const void* k, const void* v, FnaParams& p, int D,
   if (p.total_work == 0) return B200NA_OK;
   const int grid = (int)(p.total_work < st->sms ? p.total_work : st->sms);
   const void* fn = kernel_variant(D, dtype == B200NA_BF16, p.ndim);
-  void* args[] = {(void*)&tq, (void*)&tk, (void*)&tv, (void*)&p};
+  void* args[] = {(void*)&tq, (void*)&tk, (void*)&tv, (void*)&tek, (void*)&tev, (void*)&p};
 #if defined(B200NA_PROFILE) && B200NA_PROFILE >= 2
   constexpr int kExtraSmem = 8192;
 #else
@@ -948,13 +981,16 @@ int launch_fna(const void* q, const void* k, const void* v, FnaParams& p, int D,
 }  // namespace
 }  // namespace b200na
 
-extern "C" B200NA_API int b200na_fna_forward_sharded(
+namespace b200na {
+namespace {
+int fna_forward_impl(
     const void* q, const void* k, const void* v, void* o, float* lse, int ndim,
     const int* qkv_shape, const int* q_shape, const int* kv_shape, const int* kernel,
     const int* stride, const int* dilation, const int* causal, const int* q_tile,
     const int* kv_tile, int Bp, int Hq, int Hkv, int D, int dtype, float scale,
-    const int* q_origin, const int* q_extent, const int* kv_origin, b200na_stream_t stream) {
-  using namespace b200na;
+    const int* q_origin, const int* q_extent, const int* kv_origin, const void* add_k,
+    const void* add_v, int n_extra, b200na_stream_t stream) {
+  if (n_extra < 0) return B200NA_ERR_INVALID_ARGUMENT;
   if (!q || !k || !v || !o || !qkv_shape || !q_shape || !kv_shape || !kernel || !q_tile || !kv_tile)
     return B200NA_ERR_INVALID_ARGUMENT;
   if (Bp < 1 || Hq < 1 || Hkv < 1 || Hq % Hkv != 0) return B200NA_ERR_INVALID_ARGUMENT;
@@ -1019,7 +1055,33 @@ extern "C" B200NA_API int b200na_fna_forward_sharded(
   p.scale_log2 = scale * 1.4426950408889634f;
   p.o = o;
   p.lse = lse;
-  return launch_fna(q, k, v, p, D, dtype, reinterpret_cast<cudaStream_t>(stream));
+  p.n_extra = n_extra;
+  return launch_fna(q, k, v, p, D, dtype, reinterpret_cast<cudaStream_t>(stream), add_k, add_v);
+}
+}  // namespace
+}  // namespace b200na
+
+extern "C" B200NA_API int b200na_fna_forward_sharded(
+    const void* q, const void* k, const void* v, void* o, float* lse, int ndim,
+    const int* qkv_shape, const int* q_shape, const int* kv_shape, const int* kernel,
+    const int* stride, const int* dilation, const int* causal, const int* q_tile,
+    const int* kv_tile, int Bp, int Hq, int Hkv, int D, int dtype, float scale,
+    const int* q_origin, const int* q_extent, const int* kv_origin, b200na_stream_t stream) {
+  return b200na::fna_forward_impl(q, k, v, o, lse, ndim, qkv_shape, q_shape, kv_shape, kernel,
+                                  stride, dilation, causal, q_tile, kv_tile, Bp, Hq, Hkv, D, dtype,
+                                  scale, q_origin, q_extent, kv_origin, nullptr, nullptr, 0, stream);
+}
+
+extern "C" B200NA_API int b200na_fna_forward_extra_kv(
+    const void* q, const void* k, const void* v, const void* add_k, const void* add_v,
+    int n_extra, void* o, float* lse, int ndim, const int* qkv_shape, const int* q_shape,
+    const int* kv_shape, const int* kernel, const int* stride, const int* dilation,
+    const int* causal, const int* q_tile, const int* kv_tile, int Bp, int Hq, int Hkv, int D,
+    int dtype, float scale, b200na_stream_t stream) {
+  if (n_extra > 0 && (!add_k || !add_v)) return B200NA_ERR_INVALID_ARGUMENT;
+  return b200na::fna_forward_impl(q, k, v, o, lse, ndim, qkv_shape, q_shape, kv_shape, kernel,
+                                  stride, dilation, causal, q_tile, kv_tile, Bp, Hq, Hkv, D, dtype,
+                                  scale, nullptr, nullptr, nullptr, add_k, add_v, n_extra, stream);
 }
 
 extern "C" B200NA_API int b200na_fna_forward(const void* q, const void* k, const void* v, void* o,
@@ -1030,9 +1092,9 @@ extern "C" B200NA_API int b200na_fna_forward(const void* q, const void* k, const
                                              const int* q_tile, const int* kv_tile, int Bp, int Hq,
                                              int Hkv, int D, int dtype, float scale,
                                              b200na_stream_t stream) {
-  return b200na_fna_forward_sharded(q, k, v, o, lse, ndim, qkv_shape, q_shape, kv_shape, kernel,
-                                    stride, dilation, causal, q_tile, kv_tile, Bp, Hq, Hkv, D,
-                                    dtype, scale, nullptr, nullptr, nullptr, stream);
+  return b200na::fna_forward_impl(q, k, v, o, lse, ndim, qkv_shape, q_shape, kv_shape, kernel,
+                                  stride, dilation, causal, q_tile, kv_tile, Bp, Hq, Hkv, D, dtype,
+                                  scale, nullptr, nullptr, nullptr, nullptr, nullptr, 0, stream);
 }
 
 extern "C" B200NA_API int b200na_fmha_forward(const void* q, const void* k, const void* v, void* o, float* lse,

@@ -372,11 +372,17 @@ def neighborhood_attention_generic(
     q_tile_shape = check_tile_shape(na_dim, q_tile_shape, "q_tile_shape", Q_TILE_SIZE)
     kv_tile_shape = check_tile_shape(na_dim, kv_tile_shape, "kv_tile_shape", KV_TILE_SIZE)
 
+    fuse_extra = has_extra and not (attention_kwargs or {}).get("unfused_extra_kv", False)
     output, lse = fna_forward_permuted(query.detach(), key.detach(), value.detach(), kernel_size,
                                        stride, dilation, is_causal, float(scale), q_tile_shape,
-                                       kv_tile_shape)
-    if has_extra:
+                                       kv_tile_shape,
+                                       additional_keys.detach() if fuse_extra else None,
+                                       additional_values.detach() if fuse_extra else None)
+    if has_extra and not fuse_extra:
+        # the reference's composition: a second (dense) attention over the extra tokens, then
+        # an LSE merge (src/natten/functional.py:524-559); kept for comparison
         kwargs = dict(attention_kwargs or {})
+        kwargs.pop("unfused_extra_kv", None)
         kwargs.pop("torch_compile", None)
         add_out, add_lse = attention(query.flatten(1, na_dim), additional_keys, additional_values,
                                      is_causal=False, scale=scale, return_lse=True, **kwargs)
@@ -389,10 +395,12 @@ def neighborhood_attention_generic(
 
 def fna_forward_permuted(query: Tensor, key: Tensor, value: Tensor, kernel_size: DimensionType,
                          stride: DimensionType, dilation: DimensionType, is_causal: CausalArgType,
-                         scale: float, q_tile_shape: DimensionType, kv_tile_shape: DimensionType
-                         ) -> Tuple[Tensor, Tensor]:
+                         scale: float, q_tile_shape: DimensionType, kv_tile_shape: DimensionType,
+                         additional_keys: Optional[Tensor] = None,
+                         additional_values: Optional[Tensor] = None) -> Tuple[Tensor, Tensor]:
     """permute Q/K/V -> fused kernel -> unpermute O/LSE, the flow of the reference's
-    src/natten/backends/blackwell_fna.py:91-181."""
+    src/natten/backends/blackwell_fna.py:91-181. Extra key/value tokens ``[B, M, Hkv, D]``, when
+    given, are attended by every query inside the same kernel (no second attention, no merge)."""
     na_dim = query.dim() - 3
     q_perm, qkv_shape, q_shape = token_permute_operation(query, q_tile_shape, dilation, True)
     k_perm, _, kv_shape = token_permute_operation(key, kv_tile_shape, dilation, True)
@@ -402,7 +410,8 @@ def fna_forward_permuted(query: Tensor, key: Tensor, value: Tensor, kernel_size:
     v_perm = v_perm.reshape(-1, math.prod(kv_shape), *v_perm.shape[-2:])
     o_perm, lse_perm = fna_forward_op(q_perm, k_perm, v_perm, qkv_shape, q_shape, kv_shape,
                                       kernel_size, stride, dilation, is_causal, scale,
-                                      q_tile_shape, kv_tile_shape)
+                                      q_tile_shape, kv_tile_shape, additional_keys,
+                                      additional_values)
     output = token_unpermute_operation(o_perm, qkv_shape, q_tile_shape, dilation, True)
     lse = token_unpermute_operation(lse_perm.unsqueeze(-1), qkv_shape, q_tile_shape, dilation,
                                     True).squeeze(-1)
@@ -412,22 +421,28 @@ def fna_forward_permuted(query: Tensor, key: Tensor, value: Tensor, kernel_size:
 def fna_forward_op(q_perm: Tensor, k_perm: Tensor, v_perm: Tensor, qkv_shape: DimensionType,
                    q_shape: DimensionType, kv_shape: DimensionType, kernel_size: DimensionType,
                    stride: DimensionType, dilation: DimensionType, is_causal: CausalArgType,
-                   scale: float, q_tile_shape: DimensionType, kv_tile_shape: DimensionType
-                   ) -> Tuple[Tensor, Tensor]:
+                   scale: float, q_tile_shape: DimensionType, kv_tile_shape: DimensionType,
+                   additional_keys: Optional[Tensor] = None,
+                   additional_values: Optional[Tensor] = None) -> Tuple[Tensor, Tensor]:
     """The fused kernel on token-permuted ``[B', S, H, D]`` operands; allocates O and LSE like the
-    reference's op wrapper (src/natten/_libnatten/torch_wrappers.py:670-714)."""
+    reference's op wrapper (src/natten/_libnatten/torch_wrappers.py:670-714). Extra key/value
+    tokens stay in the original ``[B, M, Hkv, D]`` layout."""
     na_dim = len(qkv_shape)
     bp, sq, hq, d = q_perm.shape
     hkv = k_perm.shape[2]
     out = torch.empty_like(q_perm)
     lse = torch.empty((bp, sq, hq), dtype=torch.float32, device=q_perm.device)
+    ak = additional_keys.contiguous() if additional_keys is not None else None
+    av = additional_values.contiguous() if additional_values is not None else None
     with torch.cuda.device(q_perm.device):
-        _lib.check(_lib.lib.b200na_fna_forward(
-            _ptr(q_perm), _ptr(k_perm), _ptr(v_perm), _ptr(out), _ptr(lse), na_dim,
+        _lib.check(_lib.lib.b200na_fna_forward_extra_kv(
+            _ptr(q_perm), _ptr(k_perm), _ptr(v_perm), _ptr(ak), _ptr(av),
+            ak.shape[1] if ak is not None else 0, _ptr(out), _ptr(lse), na_dim,
             _lib.ints(qkv_shape), _lib.ints(q_shape), _lib.ints(kv_shape), _lib.ints(kernel_size),
             _lib.ints(stride), _lib.ints(dilation), _lib.ints([1 if c else 0 for c in is_causal]),
             _lib.ints(q_tile_shape), _lib.ints(kv_tile_shape), bp, hq, hkv, d,
-            _DTYPE_CODE[q_perm.dtype], float(scale), _stream(q_perm)), "b200na_fna_forward")
+            _DTYPE_CODE[q_perm.dtype], float(scale), _stream(q_perm)),
+            "b200na_fna_forward_extra_kv")
     return out, lse
 
 

@@ -252,6 +252,33 @@ def test_single_call_c_entry_equals_the_operator(shape, ks, st, di, ca):
             nb.na_forward_fused(q, k, v, ks, st, di, ca, workspace=ws[:need - 256])
 
 
+@pytest.mark.parametrize("shape,ks,st,di,ca,n_extra,hq,hkv", [
+    ((32, 32), (8, 8), (4, 4), (1, 1), (False, False), 256, 2, 2),   # config 4 scaled
+    ((30, 26), (5, 7), (1, 1), (2, 3), (False, True), 77, 4, 2),     # dilation groups share the extra tokens; GQA
+    ((700,), (65,), (3,), (1,), (True,), 130, 2, 2),
+    ((6, 10, 12), (3, 4, 5), (1, 2, 1), (1, 1, 1), (True, False, False), 1, 1, 1),
+])
+def test_fused_extra_kv_equals_attention_plus_merge(shape, ks, st, di, ca, n_extra, hq, hkv):
+    """Extra KV tokens fused into the neighborhood kernel vs the reference's composition
+    (neighborhood attention, dense attention over the extra tokens, LSE merge) and vs the oracle."""
+    torch.manual_seed(17)
+    q = torch.randn(2, *shape, hq, 128).bfloat16()
+    k, v = (torch.randn(2, *shape, hkv, 128).bfloat16() for _ in range(2))
+    ak, av = (torch.randn(2, n_extra, hkv, 128).bfloat16() for _ in range(2))
+    fn = _na_fn(len(shape))
+    args = dict(kernel_size=ks, stride=st, dilation=di, is_causal=ca, return_lse=True,
+                additional_keys=ak.cuda(), additional_values=av.cuda())
+    o_f, l_f = fn(q.cuda(), k.cuda(), v.cuda(), **args)
+    o_u, l_u = fn(q.cuda(), k.cuda(), v.cuda(), attention_kwargs={"unfused_extra_kv": True}, **args)
+    assert L.device_status() == 0
+    want_o, want_l = oracle.na_forward(q.float().numpy(), k.float().numpy(), v.float().numpy(), ks,
+                                       st, di, ca, add_k=ak.float().numpy(), add_v=av.float().numpy())
+    assert np.abs(o_f.float().cpu().numpy() - want_o).max() <= TOL_16
+    assert np.abs(l_f.cpu().numpy() - want_l).max() <= TOL_16
+    assert (o_f.float() - o_u.float()).abs().max().item() <= TOL_16
+    assert (l_f - l_u).abs().max().item() <= TOL_16
+
+
 def test_forward_is_deterministic():
     torch.manual_seed(4)
     q, k, v = (torch.randn(2, 40, 40, 2, 64, device="cuda").half() for _ in range(3))
