@@ -256,6 +256,8 @@ def main():
     ap.add_argument("--units", type=int, default=0,
                     help="profiling aid: shrink the problem to this many (batch x head) units "
                          "(batch 1); the printed line is then NOT a benchmark value")
+    ap.add_argument("--eager", action="store_true",
+                    help="time eager operator calls instead of CUDA-graph replays of one call")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -315,7 +317,29 @@ def main():
 
     # ---- device-resident timing (inputs already in HBM; operands far exceed the 126 MB L2) ----
     for _ in range(args.warmup):
-        call(dq, dk, dv, dak, dav)
+        out, lse = call(dq, dk, dv, dak, dav)
+    # One operator call is captured into a CUDA graph and replayed per step, so that host-side
+    # launch latency and OS jitter (8 ranks share the host's cores) do not open gaps between the
+    # sub-millisecond steps of the multi-GPU runs. The graph holds exactly the kernels one call
+    # launches; spatial mode (NCCL point-to-point inside the step) stays eager.
+    graph = None
+    launches_per_step = None
+    if not spatial and not args.eager:
+        try:
+            torch.cuda.synchronize()
+            L.launches = 0
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                out, lse = call(dq, dk, dv, dak, dav)
+            launches_per_step = L.launches
+            for _ in range(2):
+                graph.replay()
+            torch.cuda.synchronize()
+        except Exception as e:  # capture not possible here: time eager calls instead
+            print(f"[bench] CUDA graph capture failed ({type(e).__name__}: {e}); eager steps",
+                  file=sys.stderr)
+            graph = None
+            torch.cuda.synchronize()
     barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -324,10 +348,13 @@ def main():
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record()
     for _ in range(args.steps):
-        out, lse = call(dq, dk, dv, dak, dav)
+        if graph is not None:
+            graph.replay()
+        else:
+            out, lse = call(dq, dk, dv, dak, dav)
     ev1.record()
     barrier()
-    launches = L.launches
+    launches = L.launches if graph is None else launches_per_step * args.steps
     clocks = sampler.stop() if rank == 0 else None
     ms_total = ev0.elapsed_time(ev1)
     status = L.device_status()
@@ -417,7 +444,9 @@ def main():
             if args.units else ""),
                     partition=("slabs of axis 0 + NCCL halo exchange of K/V, output stays sharded"
                                if spatial else "batch x heads, no collective"),
-                    units_per_gpu=b_local * h_local, l2="inputs larger than L2 (no flush needed)",
+                    units_per_gpu=b_local * h_local,
+                    launch="cuda-graph replay of one operator call" if graph is not None
+                    else "eager operator calls", l2="inputs larger than L2 (no flush needed)",
                     q_tile=list(q_tile), kv_tile=list(kv_tile)),
         clocks=clocks, gpu_launches=int(launches),
         roofline=dict(bound="tensor", achieved=achieved, peak=peaks["bf16_tflops"], unit="TFLOP/s",
