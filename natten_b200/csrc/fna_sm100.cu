@@ -42,14 +42,6 @@ constexpr int kThreads = 576;    // 16 softmax warps + MMA warp + load warp
 constexpr int kTmemCols = 512;
 constexpr long long kWaitLimitCycles = 4000000000ll;  // ~2 s at 2 GHz
 constexpr float kRescaleThreshold = 8.0f;              // log2 units
-#ifndef B200NA_POLY_EVERY
-#define B200NA_POLY_EVERY 0
-#endif
-#ifndef B200NA_EXP_MIXED
-#define B200NA_EXP_MIXED 0
-#endif
-constexpr bool kExpMixed = B200NA_EXP_MIXED != 0;  // interleaved 50/50 special-function / polynomial exp2
-constexpr int kPolyEvery = B200NA_POLY_EVERY;  // every kPolyEvery-th pair of exponentials runs on the FMA pipes (0 = none)
 
 // status word: (role << 8) | barrier id, role 1 = softmax, 2 = mma, 3 = load, 4 = setup
 enum : int { kStSQFull = 1, kStSFull, kStPFull, kStOFull, kStOEmpty, kStKVFull, kStKVEmpty,
@@ -561,38 +553,13 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             }
           }
           uint32_t pk[16];
-          if (kExpMixed) {
-            // half of the exponentials on the special function unit, half on the FMA pipes,
-            // interleaved instruction by instruction
 #pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              const float t0 = fmaf(__uint_as_float(sr[j]), c, neg_mc);
-              const float t1 = fmaf(__uint_as_float(sr[j + 1]), c, neg_mc);
-              const float t2 = fmaf(__uint_as_float(sr[j + 2]), c, neg_mc);
-              const float t3 = fmaf(__uint_as_float(sr[j + 3]), c, neg_mc);
-              float p0, p1, p2, p3;
-              ptx::ex2_mixed4(t0, t1, t2, t3, p0, p1, p2, p3);
-              sm0 += p0 + p2;
-              sm1 += p1 + p3;
-              pk[j >> 1] = pack2<kBf16>(p0, p1);
-              pk[(j >> 1) + 1] = pack2<kBf16>(p2, p3);
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; j += 2) {
-              const float t0 = fmaf(__uint_as_float(sr[j]), c, neg_mc);
-              const float t1 = fmaf(__uint_as_float(sr[j + 1]), c, neg_mc);
-              float p0, p1;
-              if (kPolyEvery > 0 && ((j >> 1) % (kPolyEvery > 0 ? kPolyEvery : 1)) == kPolyEvery - 1) {
-                ptx::ex2_poly2(ptx::pack_f2(t0, t1), p0, p1);
-              } else {
-                p0 = ptx::ex2(t0);
-                p1 = ptx::ex2(t1);
-              }
-              sm0 += p0;
-              sm1 += p1;
-              pk[j >> 1] = pack2<kBf16>(p0, p1);
-            }
+          for (int j = 0; j < 32; j += 2) {
+            const float p0 = ptx::ex2(fmaf(__uint_as_float(sr[j]), c, neg_mc));
+            const float p1 = ptx::ex2(fmaf(__uint_as_float(sr[j + 1]), c, neg_mc));
+            sm0 += p0;
+            sm1 += p1;
+            pk[j >> 1] = pack2<kBf16>(p0, p1);
           }
           ptx::tmem_st16(my_p + ch * 16, pk);
         }

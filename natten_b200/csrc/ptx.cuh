@@ -245,25 +245,6 @@ __device__ __forceinline__ void reg_dealloc() {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
 }
 
-// ---- packed fp32x2 arithmetic (two floats in one 64-bit register; one issue slot) -----------
-__device__ __forceinline__ uint64_t pack_f2(float lo, float hi) {
-  uint64_t r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-  return r;
-}
-__device__ __forceinline__ void unpack_f2(uint64_t v, float& lo, float& hi) {
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
-  uint64_t d;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-  return d;
-}
-__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
-  uint64_t d;
-  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-  return d;
-}
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
@@ -275,73 +256,6 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-// 2^x for a pair of values on the FMA/ALU pipes instead of the special-function unit:
-// x = n + f with n = round(x), f in [-0.5, 0.5]; 2^f by a degree-3 polynomial (max relative
-// error 7.5e-5, far below the 16-bit precision P is rounded to), 2^n by adding n to the exponent
-// field. Inputs below -126 (including -inf for masked logits) clamp to 2^-126 ~ 1e-38.
-__device__ __forceinline__ void ex2_poly2(uint64_t x2, float& r0, float& r1) {
-  float x0, x1;
-  unpack_f2(x2, x0, x1);
-  x0 = fmaxf(x0, -126.f);
-  x1 = fmaxf(x1, -126.f);
-  x2 = pack_f2(x0, x1);
-  const uint64_t magic = pack_f2(12582912.f, 12582912.f);      // 1.5 * 2^23
-  const uint64_t neg_magic = pack_f2(-12582912.f, -12582912.f);
-  const uint64_t neg_one = pack_f2(-1.f, -1.f);
-  const uint64_t t2 = add2(x2, magic);                         // low mantissa bits = round(x)
-  const uint64_t n2 = add2(t2, neg_magic);                     // round(x) as float
-  const uint64_t f2 = fma2(n2, neg_one, x2);                   // x - round(x)
-  uint64_t p2 = fma2(pack_f2(0.0551716648f, 0.0551716648f), f2, pack_f2(0.2426111251f, 0.2426111251f));
-  p2 = fma2(p2, f2, pack_f2(0.6932609677f, 0.6932609677f));
-  p2 = fma2(p2, f2, pack_f2(0.9999280572f, 0.9999280572f));
-  float t0, t1, p0, p1;
-  unpack_f2(t2, t0, t1);
-  unpack_f2(p2, p0, p1);
-  r0 = __int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23));
-  r1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
-}
-
-// Four exponentials with a fixed instruction order: 2^a0 and 2^a1 on the special function unit,
-// 2^b0 and 2^b1 by the polynomial above, the polynomial's FMA/ALU instructions placed between the
-// two special-function instructions so that a warp has independent work to issue while that unit
-// is busy (instruction issue is in order within a warp). Same numerics as ex2 / ex2_poly2.
-__device__ __forceinline__ void ex2_mixed4(float a0, float a1, float b0, float b1, float& ra0,
-                                           float& ra1, float& rb0, float& rb1) {
-  asm volatile(
-      "{\n\t"
-      ".reg .f32 x0, x1, t0, t1, n0, n1, f0, f1, q0, q1;\n\t"
-      ".reg .b32 i0, i1, s0, s1;\n\t"
-      "ex2.approx.ftz.f32 %0, %4;\n\t"
-      "max.f32 x0, %6, 0fC2FC0000;\n\t"          // -126
-      "max.f32 x1, %7, 0fC2FC0000;\n\t"
-      "add.rn.f32 t0, x0, 0f4B400000;\n\t"       // 1.5 * 2^23
-      "add.rn.f32 t1, x1, 0f4B400000;\n\t"
-      "add.rn.f32 n0, t0, 0fCB400000;\n\t"
-      "add.rn.f32 n1, t1, 0fCB400000;\n\t"
-      "sub.rn.f32 f0, x0, n0;\n\t"
-      "sub.rn.f32 f1, x1, n1;\n\t"
-      "ex2.approx.ftz.f32 %1, %5;\n\t"
-      "fma.rn.f32 q0, f0, 0f3D61FBAF, 0f3E786F0D;\n\t"   // 0.0551716648, 0.2426111251
-      "fma.rn.f32 q1, f1, 0f3D61FBAF, 0f3E786F0D;\n\t"
-      "fma.rn.f32 q0, q0, f0, 0f3F31798D;\n\t"           // 0.6932609677
-      "fma.rn.f32 q1, q1, f1, 0f3F31798D;\n\t"
-      "fma.rn.f32 q0, q0, f0, 0f3F7FFB49;\n\t"           // 0.9999280572
-      "fma.rn.f32 q1, q1, f1, 0f3F7FFB49;\n\t"
-      "mov.b32 i0, t0;\n\t"
-      "mov.b32 i1, t1;\n\t"
-      "shl.b32 i0, i0, 23;\n\t"
-      "shl.b32 i1, i1, 23;\n\t"
-      "mov.b32 s0, q0;\n\t"
-      "mov.b32 s1, q1;\n\t"
-      "add.s32 s0, s0, i0;\n\t"
-      "add.s32 s1, s1, i1;\n\t"
-      "mov.b32 %2, s0;\n\t"
-      "mov.b32 %3, s1;\n\t"
-      "}\n"
-      : "=f"(ra0), "=f"(ra1), "=f"(rb0), "=f"(rb1)
-      : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
-}
-
 __device__ __forceinline__ float lg2(float x) {
   float y;
   asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
