@@ -40,12 +40,15 @@ constexpr int kThreads = 576;    // 16 softmax warps + MMA warp + load warp
 // Registers are allocated to warps in groups of four, so 18 warps cost as much as 20: the
 // per-thread ceiling is 65536 / 640 = 102 -> 96, which the streaming softmax loop fits into.
 constexpr int kTmemCols = 512;
+constexpr int kDescSlots = 4;     // work-item descriptors the load warp may run ahead by
+constexpr int kDescBytes = 128;
+constexpr int kTileRecs = 8;      // per-tile records in flight (more than the K/V ring holds tiles)
 constexpr long long kWaitLimitCycles = 4000000000ll;  // ~2 s at 2 GHz
 constexpr float kRescaleThreshold = 8.0f;              // log2 units
 
 // status word: (role << 8) | barrier id, role 1 = softmax, 2 = mma, 3 = load, 4 = setup
 enum : int { kStSQFull = 1, kStSFull, kStPFull, kStOFull, kStOEmpty, kStKVFull, kStKVEmpty,
-             kStQEmpty, kStSmemAlign };
+             kStQEmpty, kStSmemAlign, kStDescFull, kStDescEmpty, kStRecFull };
 
 __device__ int g_status_word;
 
@@ -58,6 +61,7 @@ struct FnaParams {
   int causal[B200NA_MAX_DIM];
   int Tq[B200NA_MAX_DIM];
   int Tkv[B200NA_MAX_DIM];
+  int tkv_shift[B200NA_MAX_DIM];  // log2(Tkv) when Tkv is a power of two, else -1
   int Rq[B200NA_MAX_DIM];   // query tiles per axis per dilation group
   int Rkv[B200NA_MAX_DIM];  // kv tiles per axis per dilation group
   int G;                    // prod(dil)
@@ -121,40 +125,89 @@ struct Item {
   int we_lo[B200NA_MAX_DIM];  // window end of the tile's first query
   int n_tiles;   // neighborhood tiles + extra-KV tiles
   int n_na;      // neighborhood tiles only
-  bool skip;
+  int skip;
 };
+static_assert(sizeof(Item) <= kDescBytes, "descriptor slot too small");
 
 __device__ __forceinline__ void axis_window(const FnaParams& p, int a, int i, int L, int& st,
                                             int& en) {
   if (p.dense) {
     st = 0;
     en = p.causal[0] ? imin(i + 1, L) : L;
+  } else if (p.stride[a] == 1) {
+    // unit stride: the stride-group leader is the query itself, no division needed
+    const int k = p.kernel[a];
+    const int wl = k >> 1, wr = (k >> 1) + ((k & 1) - 1);
+    const int lead = imin(i, L - 1);
+    if (p.causal[a]) {
+      st = imax(lead - wl - wr, 0);
+      en = imin(i + 1, L);
+    } else {
+      st = imax(lead - wl, 0) + ((lead + wr >= L) ? (L - wr - lead - 1) : 0);
+      en = st + k;
+    }
   } else {
     st = win_start(i, p.kernel[a], p.stride[a], L, p.causal[a]);
     en = win_end(i, st, p.kernel[a], L, p.causal[a]);
   }
 }
 
+// Position of a CTA in its work list, advanced without divisions: item w = ((bp * Hq) + h) *
+// n_qtiles + qt, and consecutive items of a CTA are gridDim.x apart.
+struct WorkCursor {
+  long long w;
+  int qt, h, bp;
+  __device__ __forceinline__ void init(const FnaParams& p, long long w0) {
+    w = w0;
+    qt = (int)(w0 % p.n_qtiles);
+    const long long rest = w0 / p.n_qtiles;
+    h = (int)(rest % p.Hq);
+    bp = (int)(rest / p.Hq);
+  }
+  __device__ __forceinline__ void advance(const FnaParams& p, int step) {
+    w += step;
+    qt += step;
+    while (qt >= p.n_qtiles) {
+      qt -= p.n_qtiles;
+      if (++h == p.Hq) {
+        h = 0;
+        ++bp;
+      }
+    }
+  }
+};
+
+// x / d and x % d with a shift when d is a power of two (sh >= 0), else a real division.
+__device__ __forceinline__ int div_fast(int x, int d, int sh) { return sh >= 0 ? (x >> sh) : x / d; }
+
+// Geometry of one work item. Runs on the load warp's single thread, so integer divisions are
+// avoided wherever the launch parameters allow (no dilation, unit stride, power-of-two tiles).
 template <int NDIM>
-__device__ __forceinline__ void decode_item(const FnaParams& p, long long w, Item& it) {
-  it.qt = (int)(w % p.n_qtiles);
-  const long long rest = w / p.n_qtiles;
-  it.h = (int)(rest % p.Hq);
-  it.bp = (int)(rest / p.Hq);
-  it.hk = it.h / (p.Hq / p.Hkv);
-  int gl = it.bp % p.G;
-  int ql = it.qt;
+__device__ __forceinline__ void decode_item(const FnaParams& p, const WorkCursor& cur, Item& it) {
+  it.qt = cur.qt;
+  it.h = cur.h;
+  it.bp = cur.bp;
+  it.hk = (p.Hq == p.Hkv) ? cur.h : cur.h / (p.Hq / p.Hkv);
+  int gl = (p.G > 1) ? cur.bp % p.G : 0;
+  int ql = cur.qt;
   it.n_tiles = 1;
-  it.skip = false;
+  it.skip = 0;
 #pragma unroll
   for (int a = 0; a < B200NA_MAX_DIM; ++a) {
     if (a < NDIM) {
-      const int g = gl % p.dil[a];
-      gl /= p.dil[a];
-      it.L[a] = p.dense ? p.Skv : group_extent(p.X[a], p.dil[a], g);
-      const int r = ql % p.Rq[a];
-      ql /= p.Rq[a];
-      if (!p.dense && r * p.Tq[a] >= p.q_len[a]) it.skip = true;  // tile holds padding rows only
+      int g = 0;
+      if (p.G > 1) {
+        g = gl % p.dil[a];
+        gl /= p.dil[a];
+      }
+      it.L[a] = p.dense ? p.Skv : (p.dil[a] == 1 ? p.X[a] : group_extent(p.X[a], p.dil[a], g));
+      int r = ql;
+      if (a + 1 < NDIM) {  // the last axis takes what is left
+        const int qn = ql / p.Rq[a];
+        r = ql - qn * p.Rq[a];
+        ql = qn;
+      }
+      if (!p.dense && r * p.Tq[a] >= p.q_len[a]) it.skip = 1;  // tile holds padding rows only
       it.q_lo[a] = p.q_org[a] + r * p.Tq[a];
       const int q_hi = it.q_lo[a] + p.Tq[a] - 1;
       int s_lo, e_lo, s_hi, e_hi;
@@ -163,18 +216,17 @@ __device__ __forceinline__ void decode_item(const FnaParams& p, long long w, Ite
       it.ws_hi[a] = s_hi;
       it.we_lo[a] = e_lo;
       // windows are in layout coordinates, the key/value buffer starts at kv_org
-      it.kv_t0[a] = (s_lo - p.kv_org[a]) / p.Tkv[a];
-      it.kv_n[a] = (e_hi - p.kv_org[a] + p.Tkv[a] - 1) / p.Tkv[a] - it.kv_t0[a];
+      it.kv_t0[a] = div_fast(s_lo - p.kv_org[a], p.Tkv[a], p.tkv_shift[a]);
+      it.kv_n[a] = div_fast(e_hi - p.kv_org[a] + p.Tkv[a] - 1, p.Tkv[a], p.tkv_shift[a]) - it.kv_t0[a];
       it.n_tiles *= it.kv_n[a];
     } else {
       it.L[a] = 1; it.q_lo[a] = 0; it.kv_t0[a] = 0; it.kv_n[a] = 1; it.ws_hi[a] = 0; it.we_lo[a] = 1;
     }
   }
-  if (p.dense && it.qt * kQTile >= p.Sq) it.skip = true;
+  if (p.dense && it.qt * kQTile >= p.Sq) it.skip = 1;
   it.n_na = it.n_tiles;
   it.n_tiles += p.extra_tiles;
 }
-
 template <int NDIM>
 __device__ __forceinline__ int kv_tile_row(const FnaParams& p, const int (&c)[B200NA_MAX_DIM]) {
   if (NDIM == 1) return c[0] * kKVTile;
@@ -206,11 +258,17 @@ struct Smem {
   static constexpr int kPrefEntries = 136;                  // sum(T_a + 1) <= 128 + 1 + 2 + 2
   static constexpr int kXchgOff = kPrefOff + kPrefEntries * 16;   // row max / row sum exchange
   static constexpr int kXchgBytes = (2 * 2 * 2 + 2 * 2) * kHalf * 4;
-  static constexpr int kBarOff = kXchgOff + kXchgBytes;
-  // barriers: q_full, q_empty, s_full[2], p_full[2], o_full[2], o_empty[2], kv_full[S], kv_empty[S]
-  static constexpr int kNumBars = 10 + 2 * kStages;
+  static constexpr int kDescOff = kXchgOff + kXchgBytes;          // work-item descriptor ring
+  static constexpr int kRecOff = kDescOff + kDescSlots * kDescBytes;  // per-tile records
+  static constexpr int kBarOff = kRecOff + kTileRecs * 16;
+  // barriers: q_full, q_empty, s_full[2], p_full[2], o_full[2], o_empty[2], desc_full[4],
+  // desc_empty[4], rec_full[8], kv_full[S], kv_empty[S]
+  static constexpr int kNumBars = 10 + 2 * kDescSlots + kTileRecs + 2 * kStages;
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;
   static constexpr int kBytes = kMiscOff + 16;
+  // a record is overwritten kTileRecs tiles later; its readers lag the load warp by at most
+  // the tiles the K/V ring holds plus one
+  static_assert(kTileRecs >= kStages / 2 + 3, "per-tile record ring too short");
 };
 
 // Position in the K/V ring: slot index and the phase parity of that slot's barriers.
@@ -232,6 +290,9 @@ struct Bars {
   uint64_t* p_full;   // [2]
   uint64_t* o_full;   // [2]
   uint64_t* o_empty;  // [2]
+  uint64_t* desc_full;   // [kDescSlots] descriptor published by the load warp
+  uint64_t* desc_empty;  // [kDescSlots] every consumer has copied the descriptor
+  uint64_t* rec_full;    // [kTileRecs] per-tile record written by the load warp
   uint64_t* kv_full;  // [stages]
   uint64_t* kv_empty; // [stages]
 };
@@ -250,6 +311,24 @@ __device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, volatil
     }
   }
   return true;
+}
+
+// Consumer side of the work-item descriptor ring: waits for descriptor number `seq` and returns
+// it in place (nullptr when the CTA is draining). The slot stays valid until every consumer has
+// called release_item for it; the ring is deeper than the number of items in flight, so holding
+// a slot for a whole item costs nothing. The end of the work list is a descriptor with
+// n_tiles < 0.
+__device__ __forceinline__ const Item* fetch_item(const uint8_t* desc_sm, const Bars& bars,
+                                                  uint32_t seq, volatile int* abort_flag,
+                                                  int* status, int role) {
+  const uint32_t slot = seq % kDescSlots;
+  if (!wait_bar(bars.desc_full + slot, (seq / kDescSlots) & 1, abort_flag, status,
+                (role << 8) | kStDescFull))
+    return nullptr;
+  return reinterpret_cast<const Item*>(desc_sm + slot * kDescBytes);
+}
+__device__ __forceinline__ void release_item(const Bars& bars, uint32_t seq) {
+  ptx::mbar_arrive(bars.desc_empty + seq % kDescSlots);
 }
 
 template <bool kBf16>
@@ -302,6 +381,8 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   uint4* pref = reinterpret_cast<uint4*>(smem + SM::kPrefOff);
   float* xmax = reinterpret_cast<float*>(smem + SM::kXchgOff);        // [2 parity][2 half][2 part][128]
   float* xsum = xmax + 2 * 2 * 2 * kHalf;                             // [2 half][2 part][128]
+  uint8_t* desc_sm = smem + SM::kDescOff;
+  int4* tile_rec = reinterpret_cast<int4*>(smem + SM::kRecOff);
   uint64_t* bar_base = reinterpret_cast<uint64_t*>(smem + SM::kBarOff);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SM::kMiscOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM::kMiscOff + 4);
@@ -313,8 +394,11 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   bars.p_full = bar_base + 4;
   bars.o_full = bar_base + 6;
   bars.o_empty = bar_base + 8;
-  bars.kv_full = bar_base + 10;
-  bars.kv_empty = bar_base + 10 + kStages;
+  bars.desc_full = bar_base + 10;
+  bars.desc_empty = bar_base + 10 + kDescSlots;
+  bars.rec_full = bar_base + 10 + 2 * kDescSlots;
+  bars.kv_full = bar_base + 10 + 2 * kDescSlots + kTileRecs;
+  bars.kv_empty = bar_base + 10 + 2 * kDescSlots + kTileRecs + kStages;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -340,6 +424,11 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     for (int s = 0; s < kStages; ++s) {
       ptx::mbar_init(bars.kv_full + s, 1);
       ptx::mbar_init(bars.kv_empty + s, 1);
+    }
+    for (int s = 0; s < kTileRecs; ++s) ptx::mbar_init(bars.rec_full + s, 1);
+    for (int s = 0; s < kDescSlots; ++s) {
+      ptx::mbar_init(bars.desc_full + s, 1);
+      ptx::mbar_init(bars.desc_empty + s, kSoftmaxWarps * 32 + 1);  // softmax threads + MMA thread
     }
     ptx::fence_barrier_init();
   }
@@ -405,6 +494,7 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const int bar_id = 1 + half;
     const float c = p.scale_log2;
     uint32_t ph_s = 0, ph_o = 0;
+    uint32_t tseq = 0;  // tiles consumed so far, indexes the per-tile record ring
     typedef typename std::conditional<kBf16, __nv_bfloat16, __half>::type T;
     T* o_ptr = reinterpret_cast<T*>(p.o);
     // in-tile coordinates of this thread's query row (fixed for the whole kernel)
@@ -419,10 +509,12 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     }
 
     PROF_DECL
-    for (long long w = blockIdx.x; w < p.total_work; w += gridDim.x) {
-      Item it;
-      decode_item<NDIM>(p, w, it);
-      if (it.skip) continue;
+    for (uint32_t seq = 0;; ++seq) {
+      const Item* itp = fetch_item(desc_sm, bars, seq, abort_flag, p.status, 1);
+      if (!__all_sync(0xffffffffu, itp != nullptr)) break;
+      const Item& it = *itp;  // read in place: the fields do not occupy registers across a tile
+      const int n_tiles = it.n_tiles;
+      if (n_tiles < 0) break;  // end of this CTA's work list
       // window of this thread's query row
       int ws[B200NA_MAX_DIM], we[B200NA_MAX_DIM];
 #pragma unroll
@@ -435,37 +527,35 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       }
       float m = -INFINITY, sum = 0.f;   // sum covers this thread's columns only
       bool alive = true;
-      int tc[B200NA_MAX_DIM] = {it.kv_t0[0], it.kv_t0[1], it.kv_t0[2]};
-      for (int iter = 0; iter < it.n_tiles; ++iter) {
-        // Extra-KV tiles follow the neighborhood tiles: every query attends every extra token,
-        // only the ragged end of the last tile is masked.
-        const bool is_extra = iter >= it.n_na;
-        const int extra_valid = p.n_extra - (iter - it.n_na) * kKVTile;  // valid columns if extra
-        const bool interior = is_extra ? extra_valid >= kKVTile : kv_tile_interior<NDIM>(p, it, tc);
-        // warp-uniform outcome: the TMEM accesses below are warp-collective
-        if (!__all_sync(0xffffffffu, wait_bar(bars.s_full + half, ph_s, abort_flag, p.status,
-                                              (1 << 8) | kStSFull))) {
+      for (int iter = 0; iter < n_tiles; ++iter) {
+        // The load warp classified the tile when it fetched it: x = 0 nothing to mask, 1 window
+        // boundary (y, z, w = first key coordinate of the tile per axis), 2 ragged last tile of
+        // the extra tokens (y = valid columns). The record is there long before the logits are,
+        // so the masks are ready when the wait for the logits ends.
+        if (!__all_sync(0xffffffffu,
+                        wait_bar(bars.rec_full + tseq % kTileRecs, (tseq / kTileRecs) & 1,
+                                 abort_flag, p.status, (1 << 8) | kStRecFull))) {
           alive = false;
           break;
         }
-        ph_s ^= 1;
-        PROF_MARK(0)
-        if (row == 0 && part == 0) TRACE(half, 1)
-        ptx::tc_fence_after_sync();
+        const int4 rec = tile_rec[tseq % kTileRecs];
+        ++tseq;
+        const bool interior = rec.x == 0;
         // Mask words of this thread's two 32-column chunks (boundary tiles only).
         uint32_t mw0 = ~0u, mw1 = ~0u;
-        if (!interior && is_extra) {
-          const int v0 = imin(imax(extra_valid - (part * 64), 0), 32);
-          const int v1 = imin(imax(extra_valid - (part * 64 + 32), 0), 32);
+        if (rec.x == 2) {
+          const int v0 = imin(imax(rec.y - (part * 64), 0), 32);
+          const int v1 = imin(imax(rec.y - (part * 64 + 32), 0), 32);
           mw0 = v0 >= 32 ? ~0u : ((1u << v0) - 1u);
           mw1 = v1 >= 32 ? ~0u : ((1u << v1) - 1u);
         } else if (!interior) {
+          const int base3[B200NA_MAX_DIM] = {rec.y, rec.z, rec.w};
           uint4 mk = make_uint4(~0u, ~0u, ~0u, ~0u);
           int off = 0;
 #pragma unroll
           for (int a = 0; a < B200NA_MAX_DIM; ++a) {
             if (a < NDIM) {
-              const int base = p.kv_org[a] + tc[a] * p.Tkv[a];
+              const int base = base3[a];
               const int lo = imin(imax(ws[a] - base, 0), p.Tkv[a]);
               const int hi = imin(imax(we[a] - base, 0), p.Tkv[a]);
               const uint4 ph = pref[off + hi];
@@ -481,7 +571,16 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           mw0 = part ? mk.z : mk.x;
           mw1 = part ? mk.w : mk.y;
         }
-        if (!is_extra) kv_tile_next<NDIM>(it, tc);
+        // warp-uniform outcome: the TMEM accesses below are warp-collective
+        if (!__all_sync(0xffffffffu, wait_bar(bars.s_full + half, ph_s, abort_flag, p.status,
+                                              (1 << 8) | kStSFull))) {
+          alive = false;
+          break;
+        }
+        ph_s ^= 1;
+        PROF_MARK(0)
+        if (row == 0 && part == 0) TRACE(half, 1)
+        ptx::tc_fence_after_sync();
         // Pass 1: row maximum of the raw logits over this thread's 64 columns. Chunk 1 is read
         // first and dropped, chunk 0 stays in registers for pass 2.
         uint32_t sr[32];
@@ -608,6 +707,7 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         p.lse[((long long)it.bp * p.Sq + q_row) * p.Hq + it.h] = logf(total) + m * p.scale;
       ptx::tc_fence_before_sync();
       ptx::mbar_arrive(bars.o_empty + half);
+      release_item(bars, seq);
       PROF_MARK(5)
     }
     if (row == 0 && part == 0) { PROF_FLUSH(half) }
@@ -655,11 +755,12 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       };
 
       PROF2_DECL
-      for (long long w = blockIdx.x; w < p.total_work && alive; w += gridDim.x) {
-        Item it;
-        decode_item<NDIM>(p, w, it);
-        if (it.skip) continue;
-        const int n = it.n_tiles;
+      for (uint32_t seq = 0; alive; ++seq) {
+        const Item* itp = fetch_item(desc_sm, bars, seq, abort_flag, p.status, 2);
+        if (itp == nullptr) break;
+        const int n = itp->n_tiles;  // all this role needs
+        release_item(bars, seq);
+        if (n < 0) break;
         PROF2_MARK(6)
         if (!wait_bar(bars.q_full, ph_q, abort_flag, p.status, (2 << 8) | kStSQFull)) break;
         ph_q ^= 1;
@@ -739,41 +840,91 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       RingPos<kStages> ring;
       bool alive = true;
       PROF2_DECL
-      for (long long w = blockIdx.x; w < p.total_work && alive; w += gridDim.x) {
-        Item it;
-        decode_item<NDIM>(p, w, it);
-        if (it.skip) continue;
-        PROF2_MARK(6)
+      // The load warp decodes every work item once (integer divisions, window arithmetic) and
+      // publishes it through a small descriptor ring; it runs one item ahead of its own loads,
+      // so the other roles find the next item's geometry - and its Q tile - waiting for them.
+      // Descriptors are built in place in the ring and this thread reads its own copy back from
+      // there: only it ever writes a slot, and not before kDescSlots further items.
+      WorkCursor cur;
+      cur.init(p, blockIdx.x);
+      uint32_t published = 0;
+      uint32_t tseq = 0;  // tiles fetched so far, indexes the per-tile record ring
+      // Decodes the next item that is not all padding and publishes it; publishes the end marker
+      // (n_tiles < 0) when the list is exhausted. Returns the published descriptor (nullptr when
+      // the CTA is draining).
+      auto publish_next = [&]() -> const Item* {
+        const uint32_t slot = published % kDescSlots;
+        if (!wait_bar(bars.desc_empty + slot, ((published / kDescSlots) & 1) ^ 1, abort_flag,
+                      p.status, (3 << 8) | kStDescEmpty)) {
+          alive = false;
+          return nullptr;
+        }
+        Item* out = reinterpret_cast<Item*>(desc_sm + slot * kDescBytes);
+        bool found = false;
+        while (cur.w < p.total_work) {
+          decode_item<NDIM>(p, cur, *out);
+          cur.advance(p, (int)gridDim.x);
+          if (!out->skip) { found = true; break; }
+        }
+        if (!found) out->n_tiles = -1;
+        ptx::mbar_arrive(bars.desc_full + slot);  // release: the descriptor is visible to waiters
+        ++published;
+        return out;
+      };
+      const Item* itp = publish_next();
+      while (alive && itp != nullptr && itp->n_tiles >= 0) {
+        const Item& it = *itp;
+        const int n_tiles = it.n_tiles, n_na = it.n_na, bp = it.bp, hk = it.hk;
         if (!wait_bar(bars.q_empty, ph_qe, abort_flag, p.status, (3 << 8) | kStQEmpty)) break;
         ph_qe ^= 1;
-        PROF2_MARK(0)
         ptx::mbar_arrive_expect_tx(bars.q_full, 2 * kTileBytes);
         for (int h = 0; h < 2; ++h)
           for (int db = 0; db < kDBlocks; ++db)
             ptx::tma_load_4d(q_sm + h * kTileBytes + db * kBlockBytes, &tm_q, bars.q_full, db * 64,
-                             it.h, it.qt * kQTile + h * kHalf, it.bp);
+                             it.h, it.qt * kQTile + h * kHalf, bp);
         int tc[B200NA_MAX_DIM] = {it.kv_t0[0], it.kv_t0[1], it.kv_t0[2]};
-        for (int iter = 0; iter < it.n_tiles && alive; ++iter) {
-          const bool is_extra = iter >= it.n_na;
-          const int row0 = is_extra ? (iter - it.n_na) * kKVTile : kv_tile_row<NDIM>(p, tc);
-          if (!is_extra) kv_tile_next<NDIM>(it, tc);
+        const Item* next = nullptr;
+        const int publish_at = imin(kStages / 2 - 1, n_tiles - 1);
+        for (int iter = 0; iter < n_tiles && alive; ++iter) {
+          const bool is_extra = iter >= n_na;
+          const int row0 = is_extra ? (iter - n_na) * kKVTile : kv_tile_row<NDIM>(p, tc);
+          int4 rec;
+          if (is_extra) {
+            const int valid = p.n_extra - (iter - n_na) * kKVTile;
+            rec = make_int4(valid >= kKVTile ? 0 : 2, valid, 0, 0);
+          } else {
+            rec = make_int4(kv_tile_interior<NDIM>(p, it, tc) ? 0 : 1,
+                            p.kv_org[0] + tc[0] * p.Tkv[0],
+                            NDIM > 1 ? p.kv_org[1] + tc[1] * p.Tkv[1] : 0,
+                            NDIM > 2 ? p.kv_org[2] + tc[2] * p.Tkv[2] : 0);
+            kv_tile_next<NDIM>(it, tc);
+          }
           // extra tokens are shared by the dilation groups of a batch entry
-          const int b_src = is_extra ? it.bp / p.G : it.bp;
+          const int b_src = is_extra ? bp / p.G : bp;
           for (int kv = 0; kv < 2; ++kv) {
             const uint32_t slot = ring.slot;
             if (!wait_bar(bars.kv_empty + slot, ring.phase ^ 1, abort_flag, p.status,
                           (3 << 8) | kStKVEmpty)) { alive = false; break; }
             ring.advance();
-            PROF2_MARK(1)
             TRACE2(3, 20 + kv)
+            // The record goes out with its K tile. The K/V ring holds fewer tiles than
+            // kTileRecs, so the entry it replaces is long consumed.
+            if (kv == 0) {
+              tile_rec[tseq % kTileRecs] = rec;
+              ptx::mbar_arrive(bars.rec_full + tseq % kTileRecs);
+              ++tseq;
+            }
             ptx::mbar_arrive_expect_tx(bars.kv_full + slot, kTileBytes);
             for (int db = 0; db < kDBlocks; ++db)
               ptx::tma_load_4d(kv_sm + slot * kTileBytes + db * kBlockBytes,
                                is_extra ? (kv == 0 ? &tm_ek : &tm_ev) : (kv == 0 ? &tm_k : &tm_v),
-                               bars.kv_full + slot, db * 64, it.hk, row0, b_src);
-            PROF2_MARK(6)
+                               bars.kv_full + slot, db * 64, hk, row0, b_src);
           }
+          // Once this item's first tiles fill the ring the load thread would only wait for free
+          // slots: that is when it decodes and publishes the next item.
+          if (alive && iter == publish_at) next = publish_next();
         }
+        itp = next;
       }
       PROF2_FLUSH(3)
     }
@@ -980,6 +1131,9 @@ int fna_forward_impl(
     p.dil[a] = ax.dilation[a]; p.causal[a] = ax.causal[a];
     p.Tq[a] = on ? q_tile[a] : 1;
     p.Tkv[a] = on ? kv_tile[a] : 1;
+    p.tkv_shift[a] = -1;
+    for (int sh = 0; sh < 8; ++sh)
+      if (p.Tkv[a] == (1 << sh)) p.tkv_shift[a] = sh;
     const int qs = on ? q_shape[a] : 1, ks = on ? kv_shape[a] : 1;
     if (p.Tq[a] < 1 || p.Tkv[a] < 1 || qs < 1 || ks < 1) return B200NA_ERR_INVALID_ARGUMENT;
     if (qs % p.Tq[a] != 0 || ks % p.Tkv[a] != 0) return B200NA_ERR_INVALID_ARGUMENT;
@@ -1083,13 +1237,14 @@ extern "C" B200NA_API int b200na_fmha_forward(const void* q, const void* k, cons
   p.G = 1;
   for (int a = 0; a < B200NA_MAX_DIM; ++a) {
     p.X[a] = 1; p.kernel[a] = 1; p.stride[a] = 1; p.dil[a] = 1; p.causal[a] = 0;
-    p.Tq[a] = 1; p.Tkv[a] = 1; p.Rq[a] = 1; p.Rkv[a] = 1; p.q_len[a] = 1;
+    p.Tq[a] = 1; p.Tkv[a] = 1; p.Rq[a] = 1; p.Rkv[a] = 1; p.q_len[a] = 1; p.tkv_shift[a] = 0;
   }
   p.X[0] = Nk;
   p.q_len[0] = Nq;
   p.causal[0] = causal ? 1 : 0;
   p.Tq[0] = kQTile;
   p.Tkv[0] = kKVTile;
+  p.tkv_shift[0] = 7;
   p.n_qtiles = (Nq + kQTile - 1) / kQTile;
   p.Rq[0] = p.n_qtiles;
   p.Rkv[0] = (Nk + kKVTile - 1) / kKVTile;
