@@ -116,6 +116,28 @@ B200NA_API int b200na_fna_forward_extra_kv(
     int dtype, float scale, b200na_stream_t stream);
 
 /*
+ * Neighborhood attention forward on the caller's own tensors - q/o [B, *shape, Hq, D], k/v
+ * [B, *shape, Hkv, D], lse [B, *shape, Hq] fp32 (nullable), heads last, contiguous - in ONE
+ * kernel and with no scratch memory. It replaces the whole flow of the reference's backend
+ * (src/natten/backends/blackwell_fna.py:111-165: token_permute of Q, K, V -> FNA kernel ->
+ * token_unpermute of O and LSE): the tile gathers of the permutation
+ * (csrc/include/natten/cuda/tokperm/token_permute_kernel.cuh:159-378), dilation included, are
+ * done by the kernel's tensor-map loads, and every O / LSE row is stored at its final address.
+ * Results are those of b200na_token_permute + b200na_fna_forward_extra_kv +
+ * b200na_token_unpermute with the same tile shapes.
+ *   q_tile / kv_tile: prod = 256 / 128; tile[a] * dilation[a] <= 256 and dilation[a] <= 8 on
+ *   every axis, otherwise B200NA_ERR_UNSUPPORTED (use the permuted path then).
+ *   add_k / add_v [B, n_extra, Hkv, D]: optional extra tokens every query attends (n_extra = 0
+ *   and NULL for none).
+ */
+B200NA_API int b200na_na_forward_direct(
+    const void* q, const void* k, const void* v, const void* add_k, const void* add_v,
+    int n_extra, void* o, float* lse, int ndim, const int* shape, const int* kernel,
+    const int* stride, const int* dilation, const int* causal, const int* q_tile,
+    const int* kv_tile, int B, int Hq, int Hkv, int D, int dtype, float scale,
+    b200na_stream_t stream);
+
+/*
  * The same kernel on one rank's SLAB of a spatially sharded, undilated token layout. The
  * reference has no counterpart (it has no multi-GPU code); window arithmetic follows
  * csrc/include/natten/cuda/reference/mask.hpp:59-89 in layout ("global") coordinates.

@@ -69,6 +69,8 @@ struct FnaParams {
   int kv_org[B200NA_MAX_DIM];  // layout coordinate of local key/value index 0
   int q_len[B200NA_MAX_DIM];   // number of real (non-padding) local query coordinates per axis
   int dense;                // dense attention: one axis, window = all keys (or causal prefix)
+  int direct;               // Q/K/V/O/LSE are in the caller's [B, *X, H, D] layout (no permutation)
+  int half_axis;            // direct: axis along which the query tile splits into its two halves
   int n_extra;              // extra key/value tokens every query attends (0 = none)
   int extra_tiles;          // ceil(n_extra / 128): KV tiles appended to every item's walk
   int Bp, Hq, Hkv;
@@ -117,6 +119,8 @@ struct FnaParams {
 
 struct Item {
   int bp, h, hk, qt;
+  int b;                      // batch entry (bp / G)
+  int g[B200NA_MAX_DIM];      // dilation group offset per axis
   int L[B200NA_MAX_DIM];      // extent of this dilation group (dense: number of keys)
   int q_lo[B200NA_MAX_DIM];   // first query coordinate of the tile
   int kv_t0[B200NA_MAX_DIM];  // first kv tile (tile units) per axis
@@ -188,7 +192,8 @@ __device__ __forceinline__ void decode_item(const FnaParams& p, const WorkCursor
   it.h = cur.h;
   it.bp = cur.bp;
   it.hk = (p.Hq == p.Hkv) ? cur.h : cur.h / (p.Hq / p.Hkv);
-  int gl = (p.G > 1) ? cur.bp % p.G : 0;
+  it.b = (p.G > 1) ? cur.bp / p.G : cur.bp;
+  int gl = (p.G > 1) ? cur.bp - it.b * p.G : 0;
   int ql = cur.qt;
   it.n_tiles = 1;
   it.skip = 0;
@@ -200,6 +205,7 @@ __device__ __forceinline__ void decode_item(const FnaParams& p, const WorkCursor
         g = gl % p.dil[a];
         gl /= p.dil[a];
       }
+      it.g[a] = g;
       it.L[a] = p.dense ? p.Skv : (p.dil[a] == 1 ? p.X[a] : group_extent(p.X[a], p.dil[a], g));
       int r = ql;
       if (a + 1 < NDIM) {  // the last axis takes what is left
@@ -208,6 +214,7 @@ __device__ __forceinline__ void decode_item(const FnaParams& p, const WorkCursor
         ql = qn;
       }
       if (!p.dense && r * p.Tq[a] >= p.q_len[a]) it.skip = 1;  // tile holds padding rows only
+      if (p.direct && r * p.Tq[a] >= it.L[a]) it.skip = 1;     // beyond this dilation group
       it.q_lo[a] = p.q_org[a] + r * p.Tq[a];
       const int q_hi = it.q_lo[a] + p.Tq[a] - 1;
       int s_lo, e_lo, s_hi, e_hi;
@@ -221,6 +228,7 @@ __device__ __forceinline__ void decode_item(const FnaParams& p, const WorkCursor
       it.n_tiles *= it.kv_n[a];
     } else {
       it.L[a] = 1; it.q_lo[a] = 0; it.kv_t0[a] = 0; it.kv_n[a] = 1; it.ws_hi[a] = 0; it.we_lo[a] = 1;
+      it.g[a] = 0;
     }
   }
   if (p.dense && it.qt * kQTile >= p.Sq) it.skip = 1;
@@ -682,10 +690,29 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       xs[part * kHalf + row] = sum;
       named_bar_sync(bar_id, kSoftmaxThreadsPerHalf);
       const float total = sum + xs[(part ^ 1) * kHalf + row];
-      const int q_row = it.qt * kQTile + half * kHalf + row;
-      const bool valid = q_row < p.Sq;
+      // Row of O / LSE this thread writes: a row of the permuted [B', S, H, D] operand, or - in
+      // direct mode - the token of the caller's [B, *X, H, D] layout the query row stands for.
+      long long out_row;
+      bool valid;
+      if (p.direct) {
+        long long tok = it.b;
+        valid = true;
+#pragma unroll
+        for (int a = 0; a < B200NA_MAX_DIM; ++a) {
+          if (a < NDIM) {
+            const int qa = it.q_lo[a] + tq[a];
+            valid = valid && qa < it.L[a];
+            tok = tok * p.X[a] + (qa * p.dil[a] + it.g[a]);
+          }
+        }
+        out_row = tok * p.Hq + it.h;
+      } else {
+        const int q_row = it.qt * kQTile + half * kHalf + row;
+        valid = q_row < p.Sq;
+        out_row = ((long long)it.bp * p.Sq + q_row) * p.Hq + it.h;
+      }
       const float inv = total > 0.f ? 1.f / total : 0.f;
-      T* orow = o_ptr + (((long long)it.bp * p.Sq + q_row) * p.Hq + it.h) * D + part * (D / 2);
+      T* orow = o_ptr + out_row * D + part * (D / 2);
 #pragma unroll
       for (int ch = 0; ch < D / 64; ++ch) {
         uint32_t orr[32];
@@ -704,7 +731,7 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
       }
       if (p.lse != nullptr && valid && part == 0)
-        p.lse[((long long)it.bp * p.Sq + q_row) * p.Hq + it.h] = logf(total) + m * p.scale;
+        p.lse[out_row] = logf(total) + m * p.scale;
       ptx::tc_fence_before_sync();
       ptx::mbar_arrive(bars.o_empty + half);
       release_item(bars, seq);
@@ -879,9 +906,22 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         ph_qe ^= 1;
         ptx::mbar_arrive_expect_tx(bars.q_full, 2 * kTileBytes);
         for (int h = 0; h < 2; ++h)
-          for (int db = 0; db < kDBlocks; ++db)
-            ptx::tma_load_4d(q_sm + h * kTileBytes + db * kBlockBytes, &tm_q, bars.q_full, db * 64,
-                             it.h, it.qt * kQTile + h * kHalf, bp);
+          for (int db = 0; db < kDBlocks; ++db) {
+            if (p.direct) {
+              // box = half a query tile in the caller's layout; dilation is the box's element
+              // stride, rows past the extent come back as zeros
+              int x[B200NA_MAX_DIM];
+#pragma unroll
+              for (int a = 0; a < B200NA_MAX_DIM; ++a)
+                x[a] = (it.q_lo[a] + ((h && a == p.half_axis) ? (p.Tq[a] >> 1) : 0)) * p.dil[a] +
+                       it.g[a];
+              ptx::tma_load_5d(q_sm + h * kTileBytes + db * kBlockBytes, &tm_q, bars.q_full,
+                               it.h * D + db * 64, x[0], x[1], x[2], it.b);
+            } else {
+              ptx::tma_load_4d(q_sm + h * kTileBytes + db * kBlockBytes, &tm_q, bars.q_full,
+                               db * 64, it.h, it.qt * kQTile + h * kHalf, bp);
+            }
+          }
         int tc[B200NA_MAX_DIM] = {it.kv_t0[0], it.kv_t0[1], it.kv_t0[2]};
         const Item* next = nullptr;
         const int publish_at = imin(kStages / 2 - 1, n_tiles - 1);
@@ -897,10 +937,17 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                             p.kv_org[0] + tc[0] * p.Tkv[0],
                             NDIM > 1 ? p.kv_org[1] + tc[1] * p.Tkv[1] : 0,
                             NDIM > 2 ? p.kv_org[2] + tc[2] * p.Tkv[2] : 0);
-            kv_tile_next<NDIM>(it, tc);
           }
+          // direct mode: coordinates of the tile's first key in the caller's layout
+          int xk[B200NA_MAX_DIM] = {0, 0, 0};
+          if (p.direct && !is_extra) {
+#pragma unroll
+            for (int a = 0; a < B200NA_MAX_DIM; ++a)
+              xk[a] = (a < NDIM) ? tc[a] * p.Tkv[a] * p.dil[a] + it.g[a] : 0;
+          }
+          if (!is_extra) kv_tile_next<NDIM>(it, tc);
           // extra tokens are shared by the dilation groups of a batch entry
-          const int b_src = is_extra ? bp / p.G : bp;
+          const int b_src = is_extra ? it.b : bp;
           for (int kv = 0; kv < 2; ++kv) {
             const uint32_t slot = ring.slot;
             if (!wait_bar(bars.kv_empty + slot, ring.phase ^ 1, abort_flag, p.status,
@@ -915,10 +962,16 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
               ++tseq;
             }
             ptx::mbar_arrive_expect_tx(bars.kv_full + slot, kTileBytes);
-            for (int db = 0; db < kDBlocks; ++db)
-              ptx::tma_load_4d(kv_sm + slot * kTileBytes + db * kBlockBytes,
-                               is_extra ? (kv == 0 ? &tm_ek : &tm_ev) : (kv == 0 ? &tm_k : &tm_v),
-                               bars.kv_full + slot, db * 64, hk, row0, b_src);
+            for (int db = 0; db < kDBlocks; ++db) {
+              if (p.direct && !is_extra)
+                ptx::tma_load_5d(kv_sm + slot * kTileBytes + db * kBlockBytes,
+                                 kv == 0 ? &tm_k : &tm_v, bars.kv_full + slot, hk * D + db * 64,
+                                 xk[0], xk[1], xk[2], it.b);
+              else
+                ptx::tma_load_4d(kv_sm + slot * kTileBytes + db * kBlockBytes,
+                                 is_extra ? (kv == 0 ? &tm_ek : &tm_ev) : (kv == 0 ? &tm_k : &tm_v),
+                                 bars.kv_full + slot, db * 64, hk, row0, b_src);
+            }
           }
           // Once this item's first tiles fill the ring the load thread would only wait for free
           // slots: that is when it decodes and publishes the next item.
@@ -1000,6 +1053,39 @@ int make_tensor_map(CUtensorMap* tm, const void* ptr, int dtype, int Bp, int S, 
   return B200NA_OK;
 }
 
+// Tensor map over the caller's heads-last [B, X0, X1, X2, H, D] 16-bit tensor, seen as the 5-D
+// array (H*D, X0, X1, X2, B) - axis 0 right after the channel dimension, so that a box lands in
+// shared memory in the tile's own row order (axis 0 fastest). The box spans tile[a] * dil[a]
+// positions per axis and is traversed with element stride dil[a]: it picks the tile's tokens of
+// one dilation group; positions past an extent read as zeros.
+int make_tensor_map_direct(CUtensorMap* tm, const void* ptr, int dtype, int B, const int* X,
+                           int H, int D, const int* tile, const int* dil) {
+  EncodeTiledFn enc = nullptr;
+  int rc = get_encode_fn(&enc);
+  if (rc != B200NA_OK) return rc;
+  const cuuint64_t row = (cuuint64_t)H * D * 2;  // bytes per token
+  const cuuint64_t dims[5] = {(cuuint64_t)H * D, (cuuint64_t)X[0], (cuuint64_t)X[1],
+                              (cuuint64_t)X[2], (cuuint64_t)B};
+  const cuuint64_t strides[4] = {row * X[1] * X[2], row * X[2], row, row * X[0] * X[1] * X[2]};
+  cuuint32_t box[5] = {64, 1, 1, 1, 1};
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  for (int a = 0; a < B200NA_MAX_DIM; ++a) {
+    box[1 + a] = (cuuint32_t)(tile[a] * dil[a]);
+    estr[1 + a] = (cuuint32_t)dil[a];
+    if (box[1 + a] > 256 || estr[1 + a] > 8) return B200NA_ERR_UNSUPPORTED;
+  }
+  const CUresult r = enc(tm, dtype == B200NA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                  : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                         5, const_cast<void*>(ptr), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_last_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
+    return B200NA_ERR_CUDA;
+  }
+  return B200NA_OK;
+}
+
 template <int D, bool kBf16>
 const void* kernel_for_ndim(int ndim) {
   if (ndim == 1) return (const void*)fna_fwd_kernel<D, kBf16, 1>;
@@ -1063,9 +1149,19 @@ int launch_fna(const void* q, const void* k, const void* v, FnaParams& p, int D,
                        reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(p.o);
   if (al % 16 != 0) return B200NA_ERR_ALIGNMENT;
   CUtensorMap tq, tk, tv;
-  if ((rc = make_tensor_map(&tq, q, dtype, p.Bp, p.Sq, p.Hq, D)) != B200NA_OK) return rc;
-  if ((rc = make_tensor_map(&tk, k, dtype, p.Bp, p.Skv, p.Hkv, D)) != B200NA_OK) return rc;
-  if ((rc = make_tensor_map(&tv, v, dtype, p.Bp, p.Skv, p.Hkv, D)) != B200NA_OK) return rc;
+  if (p.direct) {
+    int half_tile[B200NA_MAX_DIM];
+    for (int a = 0; a < B200NA_MAX_DIM; ++a)
+      half_tile[a] = (a == p.half_axis) ? p.Tq[a] / 2 : p.Tq[a];
+    const int B = p.Bp / p.G;
+    if ((rc = make_tensor_map_direct(&tq, q, dtype, B, p.X, p.Hq, D, half_tile, p.dil)) != B200NA_OK) return rc;
+    if ((rc = make_tensor_map_direct(&tk, k, dtype, B, p.X, p.Hkv, D, p.Tkv, p.dil)) != B200NA_OK) return rc;
+    if ((rc = make_tensor_map_direct(&tv, v, dtype, B, p.X, p.Hkv, D, p.Tkv, p.dil)) != B200NA_OK) return rc;
+  } else {
+    if ((rc = make_tensor_map(&tq, q, dtype, p.Bp, p.Sq, p.Hq, D)) != B200NA_OK) return rc;
+    if ((rc = make_tensor_map(&tk, k, dtype, p.Bp, p.Skv, p.Hkv, D)) != B200NA_OK) return rc;
+    if ((rc = make_tensor_map(&tv, v, dtype, p.Bp, p.Skv, p.Hkv, D)) != B200NA_OK) return rc;
+  }
   // extra key/value tokens [B, n_extra, Hkv, D]; without them the maps alias K/V and are unused
   CUtensorMap tek = tk, tev = tv;
   if (p.n_extra > 0) {
@@ -1181,6 +1277,86 @@ int fna_forward_impl(
 }
 }  // namespace
 }  // namespace b200na
+
+namespace b200na {
+namespace {
+// Neighborhood attention straight on the caller's [B, *X, H, D] tensors: the tile gathers that
+// the token permutation would do are done by the tensor maps, and O / LSE rows are written to
+// their final place.
+int fna_direct_impl(const void* q, const void* k, const void* v, void* o, float* lse, int ndim,
+                    const int* shape, const int* kernel, const int* stride, const int* dilation,
+                    const int* causal, const int* q_tile, const int* kv_tile, int B, int Hq,
+                    int Hkv, int D, int dtype, float scale, const void* add_k, const void* add_v,
+                    int n_extra, b200na_stream_t stream) {
+  if (!q || !k || !v || !o || !shape || !kernel || !q_tile || !kv_tile)
+    return B200NA_ERR_INVALID_ARGUMENT;
+  if (n_extra < 0 || (n_extra > 0 && (!add_k || !add_v))) return B200NA_ERR_INVALID_ARGUMENT;
+  if (B < 1 || Hq < 1 || Hkv < 1 || Hq % Hkv != 0) return B200NA_ERR_INVALID_ARGUMENT;
+  if (dtype != B200NA_F16 && dtype != B200NA_BF16) return B200NA_ERR_UNSUPPORTED;
+  if (D != 64 && D != 128) return B200NA_ERR_UNSUPPORTED;
+  if (!(scale > 0.f)) return B200NA_ERR_INVALID_ARGUMENT;
+  NaAxes ax;
+  int rc = fill_axes(ax, ndim, shape, kernel, stride, dilation, causal);
+  if (rc != B200NA_OK) return rc;
+  FnaParams p;
+  memset(&p, 0, sizeof(p));
+  p.ndim = ndim;
+  p.G = 1;
+  p.direct = 1;
+  p.half_axis = 0;
+  long long sq = 1, skv = 1, tq = 1, tkv = 1, tokens = 1;
+  for (int a = 0; a < B200NA_MAX_DIM; ++a) {
+    const bool on = a < ndim;
+    p.X[a] = ax.shape[a]; p.kernel[a] = ax.kernel[a]; p.stride[a] = ax.stride[a];
+    p.dil[a] = ax.dilation[a]; p.causal[a] = ax.causal[a];
+    p.Tq[a] = on ? q_tile[a] : 1;
+    p.Tkv[a] = on ? kv_tile[a] : 1;
+    if (p.Tq[a] < 1 || p.Tkv[a] < 1) return B200NA_ERR_INVALID_ARGUMENT;
+    if (p.Tq[a] > 1) p.half_axis = a;  // the slowest-varying axis of the tile's row order
+    p.tkv_shift[a] = -1;
+    for (int sh = 0; sh < 8; ++sh)
+      if (p.Tkv[a] == (1 << sh)) p.tkv_shift[a] = sh;
+    const int need = (p.X[a] + p.dil[a] - 1) / p.dil[a];  // largest dilation group
+    p.q_org[a] = 0;
+    p.kv_org[a] = 0;
+    p.q_len[a] = need;
+    p.Rq[a] = (need + p.Tq[a] - 1) / p.Tq[a];
+    p.Rkv[a] = (need + p.Tkv[a] - 1) / p.Tkv[a];
+    p.G *= p.dil[a];
+    sq *= (long long)p.Rq[a] * p.Tq[a];
+    skv *= (long long)p.Rkv[a] * p.Tkv[a];
+    tq *= p.Tq[a]; tkv *= p.Tkv[a];
+    tokens *= p.X[a];
+  }
+  if (tq != kQTile || tkv != kKVTile) return B200NA_ERR_INVALID_ARGUMENT;
+  if (p.Tq[p.half_axis] % 2 != 0) return B200NA_ERR_UNSUPPORTED;
+  if (sq > 0x7fffffffLL || skv > 0x7fffffffLL || tokens * B > 0x7fffffffLL ||
+      (long long)Hq * D > 0x7fffffffLL)
+    return B200NA_ERR_UNSUPPORTED;
+  p.dense = 0;
+  p.Bp = B * p.G; p.Hq = Hq; p.Hkv = Hkv;
+  p.Sq = (int)sq; p.Skv = (int)skv;
+  p.n_qtiles = (int)(sq / kQTile);
+  p.scale = scale;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.o = o;
+  p.lse = lse;
+  p.n_extra = n_extra;
+  return launch_fna(q, k, v, p, D, dtype, reinterpret_cast<cudaStream_t>(stream), add_k, add_v);
+}
+}  // namespace
+}  // namespace b200na
+
+extern "C" B200NA_API int b200na_na_forward_direct(
+    const void* q, const void* k, const void* v, const void* add_k, const void* add_v,
+    int n_extra, void* o, float* lse, int ndim, const int* shape, const int* kernel,
+    const int* stride, const int* dilation, const int* causal, const int* q_tile,
+    const int* kv_tile, int B, int Hq, int Hkv, int D, int dtype, float scale,
+    b200na_stream_t stream) {
+  return b200na::fna_direct_impl(q, k, v, o, lse, ndim, shape, kernel, stride, dilation, causal,
+                                 q_tile, kv_tile, B, Hq, Hkv, D, dtype, scale, add_k, add_v,
+                                 n_extra, stream);
+}
 
 extern "C" B200NA_API int b200na_fna_forward_sharded(
     const void* q, const void* k, const void* v, void* o, float* lse, int ndim,

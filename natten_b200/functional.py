@@ -334,8 +334,10 @@ def neighborhood_attention_generic(
         if has_extra:
             k = torch.cat([k, additional_keys], dim=1)
             v = torch.cat([v, additional_values], dim=1)
+        fmha_kwargs = {kk: vv for kk, vv in (attention_kwargs or {}).items()
+                       if kk not in ("unfused_extra_kv", "permuted_layout")}
         out, lse = attention(q, k, v, is_causal=is_causal[0], scale=scale, return_lse=True,
-                             **(attention_kwargs or {}))
+                             **fmha_kwargs)
         out = out.reshape(*query_shape[:-1], value.shape[-1])
         lse = lse.reshape(*query_shape[:-1])
         return (out, lse) if return_lse else out
@@ -373,16 +375,26 @@ def neighborhood_attention_generic(
     kv_tile_shape = check_tile_shape(na_dim, kv_tile_shape, "kv_tile_shape", KV_TILE_SIZE)
 
     fuse_extra = has_extra and not (attention_kwargs or {}).get("unfused_extra_kv", False)
-    output, lse = fna_forward_permuted(query.detach(), key.detach(), value.detach(), kernel_size,
-                                       stride, dilation, is_causal, float(scale), q_tile_shape,
-                                       kv_tile_shape,
-                                       additional_keys.detach() if fuse_extra else None,
-                                       additional_values.detach() if fuse_extra else None)
+    want_permuted = (attention_kwargs or {}).get("permuted_layout", False)
+    if not want_permuted and direct_layout_supported(q_tile_shape, kv_tile_shape, dilation):
+        # one kernel on the caller's layout: no permuted copies of Q/K/V/O/LSE at all
+        output, lse = fna_forward_direct(query.detach(), key.detach(), value.detach(), kernel_size,
+                                         stride, dilation, is_causal, float(scale), q_tile_shape,
+                                         kv_tile_shape,
+                                         additional_keys.detach() if fuse_extra else None,
+                                         additional_values.detach() if fuse_extra else None)
+    else:
+        output, lse = fna_forward_permuted(query.detach(), key.detach(), value.detach(), kernel_size,
+                                           stride, dilation, is_causal, float(scale), q_tile_shape,
+                                           kv_tile_shape,
+                                           additional_keys.detach() if fuse_extra else None,
+                                           additional_values.detach() if fuse_extra else None)
     if has_extra and not fuse_extra:
         # the reference's composition: a second (dense) attention over the extra tokens, then
         # an LSE merge (src/natten/functional.py:524-559); kept for comparison
         kwargs = dict(attention_kwargs or {})
         kwargs.pop("unfused_extra_kv", None)
+        kwargs.pop("permuted_layout", None)
         kwargs.pop("torch_compile", None)
         add_out, add_lse = attention(query.flatten(1, na_dim), additional_keys, additional_values,
                                      is_causal=False, scale=scale, return_lse=True, **kwargs)
@@ -391,6 +403,49 @@ def neighborhood_attention_generic(
         output = m_out.reshape(output.shape)
         lse = m_lse.reshape(output.shape[:-1])
     return (output, lse) if return_lse else output
+
+
+MAX_TMA_BOX = 256      # positions a tensor-map box may span per axis
+MAX_TMA_ELEMENT_STRIDE = 8
+
+
+def direct_layout_supported(q_tile_shape: DimensionType, kv_tile_shape: DimensionType,
+                            dilation: DimensionType) -> bool:
+    """Whether the fused kernel can read the caller's ``[B, *X, H, D]`` layout directly: a tile of
+    one dilation group must fit a tensor-map box (tile * dilation <= 256 positions per axis,
+    dilation <= 8). The query tile is fetched as two halves split along its last non-unit axis."""
+    q_box = list(q_tile_shape)
+    split = max((a for a, t in enumerate(q_box) if t > 1), default=0)
+    if q_box[split] % 2:
+        return False
+    q_box[split] //= 2
+    return all(d <= MAX_TMA_ELEMENT_STRIDE and tq * d <= MAX_TMA_BOX and tkv * d <= MAX_TMA_BOX
+               for tq, tkv, d in zip(q_box, kv_tile_shape, dilation))
+
+
+def fna_forward_direct(query: Tensor, key: Tensor, value: Tensor, kernel_size: DimensionType,
+                       stride: DimensionType, dilation: DimensionType, is_causal: CausalArgType,
+                       scale: float, q_tile_shape: DimensionType, kv_tile_shape: DimensionType,
+                       additional_keys: Optional[Tensor] = None,
+                       additional_values: Optional[Tensor] = None) -> Tuple[Tensor, Tensor]:
+    """The fused kernel on the original heads-last layout: what the reference does as
+    permute -> kernel -> unpermute (src/natten/backends/blackwell_fna.py:111-165) in one launch,
+    the tile gathers (dilation included) done by the kernel's tensor-map loads."""
+    na_dim = query.dim() - 3
+    q, k, v = (t.contiguous() for t in (query, key, value))
+    ak = additional_keys.contiguous() if additional_keys is not None else None
+    av = additional_values.contiguous() if additional_values is not None else None
+    out = torch.empty_like(q)
+    lse = torch.empty(q.shape[:-1], dtype=torch.float32, device=q.device)
+    with torch.cuda.device(q.device):
+        _lib.check(_lib.lib.b200na_na_forward_direct(
+            _ptr(q), _ptr(k), _ptr(v), _ptr(ak), _ptr(av), ak.shape[1] if ak is not None else 0,
+            _ptr(out), _ptr(lse), na_dim, _lib.ints(q.shape[1:1 + na_dim]),
+            _lib.ints(kernel_size), _lib.ints(stride), _lib.ints(dilation),
+            _lib.ints([1 if c else 0 for c in is_causal]), _lib.ints(q_tile_shape),
+            _lib.ints(kv_tile_shape), q.shape[0], q.shape[-2], k.shape[-2], q.shape[-1],
+            _DTYPE_CODE[q.dtype], float(scale), _stream(q)), "b200na_na_forward_direct")
+    return out, lse
 
 
 def fna_forward_permuted(query: Tensor, key: Tensor, value: Tensor, kernel_size: DimensionType,

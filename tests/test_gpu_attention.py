@@ -46,12 +46,18 @@ def test_fp32_path_matches_reference(name):
     assert np.abs(lse - c.lse).max() <= TOL_F32
 
 
+LAYOUTS = {"direct": None, "permuted": {"permuted_layout": True}}
+
+
 @pytest.mark.parametrize("name", [n for n in na_case_names() if n != "c1_na2d_32x32_k7"])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-def test_16bit_path_matches_reference(name, dtype):
-    """bf16-exact operands: head dims 64/128 run on the tensor-core kernel, others on CUDA cores."""
+@pytest.mark.parametrize("layout", list(LAYOUTS))
+def test_16bit_path_matches_reference(name, dtype, layout):
+    """bf16-exact operands: head dims 64/128 run on the tensor-core kernel, others on CUDA cores.
+    The tensor-core kernel is run both on the caller's layout (tensor-map gathers, the default)
+    and on token-permuted copies (the reference's flow)."""
     c = na_cases()[name]
-    out, lse = _run(c, dtype)
+    out, lse = _run(c, dtype, attention_kwargs=LAYOUTS[layout])
     assert np.isfinite(out).all() and np.isfinite(lse).all()
     assert np.abs(out - c.out).max() <= TOL_16
     assert np.abs(lse - c.lse).max() <= TOL_16
@@ -69,9 +75,62 @@ def test_16bit_path_matches_reference(name, dtype):
 ])
 def test_tensor_core_kernel_with_explicit_tile_shapes(name, qt, kvt):
     c = na_cases()[name]
-    out, lse = _run(c, torch.bfloat16, q_tile_shape=qt, kv_tile_shape=kvt)
-    assert np.abs(out - c.out).max() <= TOL_16
-    assert np.abs(lse - c.lse).max() <= TOL_16
+    for layout, kwargs in LAYOUTS.items():
+        out, lse = _run(c, torch.bfloat16, q_tile_shape=qt, kv_tile_shape=kvt,
+                        attention_kwargs=kwargs)
+        assert np.abs(out - c.out).max() <= TOL_16, layout
+        assert np.abs(lse - c.lse).max() <= TOL_16, layout
+
+
+@pytest.mark.parametrize("shape,ks,st,di,ca,qt,kvt,n_extra,hq,hkv,D", [
+    ((1000,), (33,), (1,), (2,), (False,), (256,), (128,), 0, 2, 2, 64),       # ragged, dilated 1-D
+    ((777,), (100,), (7,), (1,), (True,), (256,), (128,), 50, 4, 2, 128),
+    ((40, 44), (7, 9), (1, 2), (2, 3), (False, True), (16, 16), (16, 8), 0, 2, 1, 128),
+    ((37, 51), (5, 5), (1, 1), (4, 8), (False, False), (8, 32), (4, 32), 130, 2, 2, 64),
+    ((64, 64), (16, 16), (8, 8), (1, 1), (False, False), (2, 128), (1, 128), 0, 1, 1, 128),
+    ((6, 20, 24), (3, 5, 8), (1, 1, 4), (1, 2, 1), (True, False, False), (2, 8, 16), (2, 8, 8), 0, 2, 2, 128),
+    ((9, 11, 13), (3, 3, 3), (1, 1, 1), (3, 2, 4), (False, True, False), (4, 8, 8), (4, 4, 8), 17, 2, 2, 64),
+    ((5, 7, 300), (2, 2, 31), (1, 1, 1), (1, 1, 2), (False, False, True), (1, 2, 128), (1, 1, 128), 0, 1, 1, 64),
+])
+def test_direct_layout_is_bit_identical_to_the_permuted_flow(shape, ks, st, di, ca, qt, kvt,
+                                                             n_extra, hq, hkv, D):
+    """The kernel reading the caller's layout through tensor maps (one launch, no scratch) against
+    permute -> kernel -> unpermute with the same tiles: same arithmetic in the same order, so
+    every bit of O and LSE agrees; ragged extents, dilation groups of unequal size, GQA and extra
+    tokens included. Also checked against the oracle."""
+    torch.manual_seed(33)
+    q = torch.randn(2, *shape, hq, D).bfloat16()
+    k, v = (torch.randn(2, *shape, hkv, D).bfloat16() for _ in range(2))
+    ak = av = None
+    if n_extra:
+        ak, av = (torch.randn(2, n_extra, hkv, D).bfloat16() for _ in range(2))
+    assert nb.direct_layout_supported(qt, kvt, di)
+    args = (q.cuda(), k.cuda(), v.cuda(), ks, st, di, ca, D ** -0.5, qt, kvt,
+            ak.cuda() if n_extra else None, av.cuda() if n_extra else None)
+    o_d, l_d = nb.fna_forward_direct(*args)
+    o_p, l_p = nb.fna_forward_permuted(*args)
+    assert L.device_status() == 0
+    assert torch.equal(o_d, o_p)
+    assert torch.equal(l_d, l_p)
+    want_o, want_l = oracle.na_forward(
+        q.float().numpy(), k.float().numpy(), v.float().numpy(), ks, st, di, ca,
+        add_k=ak.float().numpy() if n_extra else None, add_v=av.float().numpy() if n_extra else None)
+    assert np.abs(o_d.float().cpu().numpy() - want_o).max() <= TOL_16
+    assert np.abs(l_d.cpu().numpy() - want_l).max() <= TOL_16
+
+
+def test_direct_layout_limits():
+    """A tile of one dilation group must fit a tensor-map box; beyond that the C entry refuses and
+    the operator falls back to permuted copies."""
+    assert not nb.direct_layout_supported((256,), (128,), (3,))
+    assert nb.direct_layout_supported((256,), (128,), (2,))
+    assert not nb.direct_layout_supported((16, 16), (16, 8), (1, 9))
+    q = torch.randn(1, 1200, 2, 64, device="cuda").half()
+    with pytest.raises(L.NattenB200Error) as e:
+        nb.fna_forward_direct(q, q, q, (33,), (1,), (3,), (False,), 0.125, (256,), (128,))
+    assert e.value.code == L.ERR_UNSUPPORTED
+    out = nb.na1d(q, q, q, 33, dilation=3)     # permuted fallback
+    assert L.device_status() == 0 and torch.isfinite(out.float()).all()
 
 
 def test_dense_attention_matches_reference():
