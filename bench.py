@@ -3,9 +3,10 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--config c2|c3|c4|c5] [--impl b200|reference]
 
-One "step" is one forward call of the operator (token permute -> fused attention -> unpermute,
-plus dense attention over extra KV and the LSE merge when the config has them) on seeded
-synthetic inputs. The default workload is BASELINE config 2 (na1d bf16, B=4 H=16 L=32768 D=128,
+One "step" is one forward call of the operator na1d/na2d/na3d on seeded synthetic inputs: one
+launch of the fused attention kernel, which gathers its tiles from the caller's layout and
+attends the extra KV tokens of a config in the same softmax (token-permuted copies are only
+made for tile/dilation combinations a tensor-map box cannot express). The default workload is BASELINE config 2 (na1d bf16, B=4 H=16 L=32768 D=128,
 kernel 2048, causal). With N > 1 (launched by torchrun, one rank per GPU) the (batch x heads)
 units of the same fixed problem are partitioned across ranks with no collective ("strong").
 
@@ -367,24 +368,31 @@ def main():
     else:
         kernel_alone = True
     if kernel_alone:
-        qp, qkv_shape, q_shape = nb.token_permute_operation(dq, q_tile, di)
-        kp, _, kv_shape = nb.token_permute_operation(dk, kv_tile, di)
-        vp, _, _ = nb.token_permute_operation(dv, kv_tile, di)
-        qp = qp.reshape(-1, math.prod(q_shape), h_local, D)
-        kp = kp.reshape(-1, math.prod(kv_shape), h_local, D)
-        vp = vp.reshape(-1, math.prod(kv_shape), h_local, D)
         scale = D ** -0.5
+        if nb.direct_layout_supported(q_tile, kv_tile, di):
+            def kernel_call():
+                nb.fna_forward_direct(dq, dk, dv, ks, st, di, ca, scale, q_tile, kv_tile)
+        else:
+            qp, qkv_shape, q_shape = nb.token_permute_operation(dq, q_tile, di)
+            kp, _, kv_shape = nb.token_permute_operation(dk, kv_tile, di)
+            vp, _, _ = nb.token_permute_operation(dv, kv_tile, di)
+            qp = qp.reshape(-1, math.prod(q_shape), h_local, D)
+            kp = kp.reshape(-1, math.prod(kv_shape), h_local, D)
+            vp = vp.reshape(-1, math.prod(kv_shape), h_local, D)
+
+            def kernel_call():
+                nb.fna_forward_op(qp, kp, vp, qkv_shape, q_shape, kv_shape, ks, st, di, ca, scale,
+                                  q_tile, kv_tile)
         for _ in range(3):
-            nb.fna_forward_op(qp, kp, vp, qkv_shape, q_shape, kv_shape, ks, st, di, ca, scale, q_tile, kv_tile)
+            kernel_call()
         torch.cuda.synchronize()
         k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         k0.record()
         for _ in range(args.steps):
-            nb.fna_forward_op(qp, kp, vp, qkv_shape, q_shape, kv_shape, ks, st, di, ca, scale, q_tile, kv_tile)
+            kernel_call()
         k1.record()
         torch.cuda.synchronize()
         kernel_ms = k0.elapsed_time(k1) / args.steps
-        del qp, kp, vp
     else:
         kernel_ms = ms_total / args.steps
 
