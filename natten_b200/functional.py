@@ -18,7 +18,7 @@ from typing import Any, Dict, List, Optional, Sequence, Tuple, Union
 import torch
 from torch import Tensor
 
-from . import _lib
+from . import _lib, ops
 from .checks import (CausalArgType, DimensionType, additional_kv_tensor_checks, check_all_args,
                      check_args_against_input, check_tile_shape, fmha_tensor_checks,
                      is_self_attention, na_tensor_checks)
@@ -93,10 +93,19 @@ def _pow2_compositions(total_log2: int, n: int):
             yield (1 << e,) + rest
 
 
-@functools.lru_cache(maxsize=256)
 def choose_tile_shapes(shape: DimensionType, kernel_size: DimensionType, stride: DimensionType,
                        dilation: DimensionType, is_causal: CausalArgType
                        ) -> Tuple[DimensionType, DimensionType]:
+    """Cached front of :func:`_choose_tile_shapes` (normalises its arguments to hashable tuples)."""
+    return _choose_tile_shapes(tuple(int(x) for x in shape), tuple(int(x) for x in kernel_size),
+                               tuple(int(x) for x in stride), tuple(int(x) for x in dilation),
+                               tuple(bool(x) for x in is_causal))
+
+
+@functools.lru_cache(maxsize=256)
+def _choose_tile_shapes(shape: DimensionType, kernel_size: DimensionType, stride: DimensionType,
+                        dilation: DimensionType, is_causal: CausalArgType
+                        ) -> Tuple[DimensionType, DimensionType]:
     """Picks (q_tile_shape, kv_tile_shape), 256 and 128 tokens, that minimise the number of
     key/value tiles the kernel has to visit (the reference instead offers a fixed list:
     src/natten/backends/configs/cutlass_blackwell/__init__.py:45-64)."""
@@ -154,13 +163,8 @@ def token_permute_operation(tensor: Tensor, tile_shape: DimensionType,
     # 1-D, undilated, already a tile multiple: the permutation is the identity
     if na_dim == 1 and dil[0] == 1 and post[0] == layout[0]:
         return tensor, layout, post
-    out = torch.empty((batch * math.prod(dil), math.prod(post), heads, dim), dtype=tensor.dtype,
-                      device=tensor.device)
-    with torch.cuda.device(tensor.device):
-        _lib.check(_lib.lib.b200na_token_permute(
-            _ptr(tensor), _ptr(out), na_dim, _lib.ints(layout), _lib.ints(tile_shape),
-            _lib.ints(dil), batch, heads, dim, tensor.element_size(), 1 if flip_tiled_dims else 0,
-            _stream(tensor)), "b200na_token_permute")
+    out = ops.token_permute(tensor, list(layout), list(tile_shape), list(dil),
+                            bool(flip_tiled_dims))
     return out, layout, post
 
 
@@ -190,12 +194,8 @@ def token_unpermute_operation(tensor: Tensor, token_layout_shape: DimensionType,
     batch = bp // groups
     if na_dim == 1 and dil[0] == 1 and post[0] == layout[0]:
         return tensor.reshape(batch, *layout, heads, dim)
-    out = torch.empty((batch, *layout, heads, dim), dtype=tensor.dtype, device=tensor.device)
-    with torch.cuda.device(tensor.device):
-        _lib.check(_lib.lib.b200na_token_unpermute(
-            _ptr(tensor), _ptr(out), na_dim, _lib.ints(layout), _lib.ints(tile_shape),
-            _lib.ints(dil), batch, heads, dim, tensor.element_size(), 1 if flip_tiled_dims else 0,
-            _stream(tensor)), "b200na_token_unpermute")
+    out = ops.token_unpermute(tensor, list(layout), list(tile_shape), list(dil),
+                              bool(flip_tiled_dims))
     return out
 
 
@@ -234,19 +234,12 @@ def merge_attentions(outputs: List[Tensor], lse_tensors: List[Tensor], torch_com
     dtype = outputs[0].dtype
     if dtype not in _DTYPE_CODE:
         raise NotImplementedError(f"merge_attentions does not support dtype {dtype}.")
-    rows = shape[0] * shape[1] * shape[2]
     acc_o = outputs[0].detach().contiguous()
     acc_l = lse_tensors[0].detach().to(torch.float32).contiguous()
-    out = torch.empty_like(acc_o)
-    out_l = torch.empty_like(acc_l)
-    with torch.cuda.device(acc_o.device):
-        for i in range(1, len(outputs)):
-            o_i = outputs[i].detach().contiguous()
-            l_i = lse_tensors[i].detach().to(torch.float32).contiguous()
-            _lib.check(_lib.lib.b200na_merge(_ptr(acc_o), _ptr(acc_l), _ptr(o_i), _ptr(l_i),
-                                             _ptr(out), _ptr(out_l), rows, shape[3],
-                                             _DTYPE_CODE[dtype], _stream(acc_o)), "b200na_merge")
-            acc_o, acc_l = out, out_l  # later pairs merge in place (aliasing is allowed)
+    for i in range(1, len(outputs)):
+        acc_o, acc_l = ops.merge(acc_o, acc_l, outputs[i].detach().contiguous(),
+                                 lse_tensors[i].detach().to(torch.float32).contiguous())
+    out, out_l = acc_o, acc_l
     return out, out_l
 
 
@@ -283,18 +276,10 @@ def attention(query: Tensor, key: Tensor, value: Tensor, is_causal: bool = False
     Nk, Hkv = key.shape[1], key.shape[2]
     if is_causal and Nq != Nk:
         raise NotImplementedError("Causal attention needs equal query and key lengths here.")
+    if query.dtype not in _DTYPE_CODE:
+        raise NotImplementedError(f"natten_b200.attention does not support dtype {query.dtype}.")
     q, k, v = (t.detach().contiguous() for t in (query, key, value))
-    lse = torch.empty((B, Nq, Hq), dtype=torch.float32, device=q.device)
-    out = torch.empty_like(q)
-    if q.dtype not in _DTYPE_CODE:
-        raise NotImplementedError(f"natten_b200.attention does not support dtype {q.dtype}.")
-    with torch.cuda.device(q.device):
-        # fp16/bf16 with head dim 64/128 run on tensor cores, everything else on CUDA cores;
-        # the library picks the kernel.
-        _lib.check(_lib.lib.b200na_fmha_forward(
-            _ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(lse), B, Nq, Nk, Hq, Hkv, D,
-            _DTYPE_CODE[q.dtype], float(scale), 1 if is_causal else 0, _stream(q)),
-            "b200na_fmha_forward")
+    out, lse = ops.fmha_forward(q, k, v, bool(is_causal), float(scale))
     return (out, lse) if return_lse else out
 
 
@@ -343,52 +328,20 @@ def neighborhood_attention_generic(
         return (out, lse) if return_lse else out
 
     scale = scale or query.shape[-1] ** -0.5
-    shape = tuple(query.shape[1:1 + na_dim])
-    B, Hq, D = query.shape[0], query.shape[-2], query.shape[-1]
-    Hkv = key.shape[-2]
     if query.dtype not in _DTYPE_CODE:
         raise NotImplementedError(f"natten_b200 does not support dtype {query.dtype}.")
-
-    tensor_core = query.dtype in (torch.float16, torch.bfloat16) and D in TENSOR_CORE_HEAD_DIMS
-    if not tensor_core:
-        # fp32 operands (and other head dims): CUDA-core kernel on the original layout, extra KV
-        # tokens fused into the same softmax.
-        q, k, v = (t.detach().contiguous() for t in (query, key, value))
-        ak = additional_keys.detach().contiguous() if has_extra else None
-        av = additional_values.detach().contiguous() if has_extra else None
-        out = torch.empty_like(q)
-        lse = torch.empty(q.shape[:-1], dtype=torch.float32, device=q.device)
-        with torch.cuda.device(q.device):
-            _lib.check(_lib.lib.b200na_na_forward_simt(
-                _ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(lse), na_dim, _lib.ints(shape),
-                _lib.ints(kernel_size), _lib.ints(stride), _lib.ints(dilation),
-                _lib.ints([1 if c else 0 for c in is_causal]), B, Hq, Hkv, D,
-                _DTYPE_CODE[q.dtype], float(scale), _ptr(ak), _ptr(av),
-                ak.shape[1] if has_extra else 0, _stream(q)), "b200na_na_forward_simt")
-        return (out, lse) if return_lse else out
-
-    if q_tile_shape is None or kv_tile_shape is None:
-        auto_q, auto_kv = choose_tile_shapes(shape, kernel_size, stride, dilation, is_causal)
-        q_tile_shape = q_tile_shape or auto_q
-        kv_tile_shape = kv_tile_shape or auto_kv
-    q_tile_shape = check_tile_shape(na_dim, q_tile_shape, "q_tile_shape", Q_TILE_SIZE)
-    kv_tile_shape = check_tile_shape(na_dim, kv_tile_shape, "kv_tile_shape", KV_TILE_SIZE)
-
+    if q_tile_shape is not None:
+        q_tile_shape = check_tile_shape(na_dim, q_tile_shape, "q_tile_shape", Q_TILE_SIZE)
+    if kv_tile_shape is not None:
+        kv_tile_shape = check_tile_shape(na_dim, kv_tile_shape, "kv_tile_shape", KV_TILE_SIZE)
     fuse_extra = has_extra and not (attention_kwargs or {}).get("unfused_extra_kv", False)
-    want_permuted = (attention_kwargs or {}).get("permuted_layout", False)
-    if not want_permuted and direct_layout_supported(q_tile_shape, kv_tile_shape, dilation):
-        # one kernel on the caller's layout: no permuted copies of Q/K/V/O/LSE at all
-        output, lse = fna_forward_direct(query.detach(), key.detach(), value.detach(), kernel_size,
-                                         stride, dilation, is_causal, float(scale), q_tile_shape,
-                                         kv_tile_shape,
-                                         additional_keys.detach() if fuse_extra else None,
-                                         additional_values.detach() if fuse_extra else None)
-    else:
-        output, lse = fna_forward_permuted(query.detach(), key.detach(), value.detach(), kernel_size,
-                                           stride, dilation, is_causal, float(scale), q_tile_shape,
-                                           kv_tile_shape,
-                                           additional_keys.detach() if fuse_extra else None,
-                                           additional_values.detach() if fuse_extra else None)
+    want_permuted = bool((attention_kwargs or {}).get("permuted_layout", False))
+    q, k, v = (t.detach().contiguous() for t in (query, key, value))
+    ak = additional_keys.detach().contiguous() if fuse_extra else None
+    av = additional_values.detach().contiguous() if fuse_extra else None
+    output, lse = na_forward_op(q, k, v, ak, av, list(kernel_size), list(stride), list(dilation),
+                                [bool(c) for c in is_causal], float(scale),
+                                list(q_tile_shape or ()), list(kv_tile_shape or ()), want_permuted)
     if has_extra and not fuse_extra:
         # the reference's composition: a second (dense) attention over the extra tokens, then
         # an LSE merge (src/natten/functional.py:524-559); kept for comparison
@@ -405,6 +358,48 @@ def neighborhood_attention_generic(
     return (output, lse) if return_lse else output
 
 
+def _na_forward_fake(query, key, value, additional_keys, additional_values, kernel_size, stride,
+                     dilation, is_causal, scale, q_tile_shape, kv_tile_shape, permuted_layout):
+    return (torch.empty_like(query), query.new_empty(query.shape[:-1], dtype=torch.float32))
+
+
+@ops._op("na_forward", _na_forward_fake)
+def na_forward_op(query: Tensor, key: Tensor, value: Tensor, additional_keys: Optional[Tensor],
+                  additional_values: Optional[Tensor], kernel_size: List[int], stride: List[int],
+                  dilation: List[int], is_causal: List[bool], scale: float,
+                  q_tile_shape: List[int], kv_tile_shape: List[int],
+                  permuted_layout: bool) -> Tuple[Tensor, Tensor]:
+    """Neighborhood attention forward on validated, contiguous ``[B, *X, H, D]`` operands: the
+    one node `na1d/na2d/na3d` leave in a torch.compile graph. Everything that depends on concrete
+    sizes happens in here, at run time: kernel choice (tensor cores for fp16/bf16 with head dim
+    64/128, CUDA cores otherwise), tile shapes (empty lists = choose), and whether the kernel
+    can read this layout directly or needs token-permuted copies."""
+    na_dim = query.dim() - 3
+    shape = tuple(int(x) for x in query.shape[1:1 + na_dim])
+    kernel_size, stride, dilation = tuple(kernel_size), tuple(stride), tuple(dilation)
+    is_causal = tuple(bool(c) for c in is_causal)
+    tensor_core = (query.dtype in (torch.float16, torch.bfloat16)
+                   and query.shape[-1] in TENSOR_CORE_HEAD_DIMS)
+    if not tensor_core:
+        # fp32 operands (and other head dims): CUDA-core kernel on the original layout, extra KV
+        # tokens fused into the same softmax.
+        return ops.na_forward_simt(query, key, value, additional_keys, additional_values,
+                                   list(kernel_size), list(stride), list(dilation),
+                                   list(is_causal), scale)
+    if not q_tile_shape or not kv_tile_shape:
+        auto_q, auto_kv = choose_tile_shapes(shape, kernel_size, stride, dilation, is_causal)
+        q_tile_shape = tuple(q_tile_shape) or auto_q
+        kv_tile_shape = tuple(kv_tile_shape) or auto_kv
+    q_tile_shape, kv_tile_shape = tuple(q_tile_shape), tuple(kv_tile_shape)
+    if not permuted_layout and direct_layout_supported(q_tile_shape, kv_tile_shape, dilation):
+        # one kernel on the caller's layout: no permuted copies of Q/K/V/O/LSE at all
+        return fna_forward_direct(query, key, value, kernel_size, stride, dilation, is_causal,
+                                  scale, q_tile_shape, kv_tile_shape, additional_keys,
+                                  additional_values)
+    return fna_forward_permuted(query, key, value, kernel_size, stride, dilation, is_causal, scale,
+                                q_tile_shape, kv_tile_shape, additional_keys, additional_values)
+
+
 MAX_TMA_BOX = 256      # positions a tensor-map box may span per axis
 MAX_TMA_ELEMENT_STRIDE = 8
 
@@ -415,7 +410,10 @@ def direct_layout_supported(q_tile_shape: DimensionType, kv_tile_shape: Dimensio
     one dilation group must fit a tensor-map box (tile * dilation <= 256 positions per axis,
     dilation <= 8). The query tile is fetched as two halves split along its last non-unit axis."""
     q_box = list(q_tile_shape)
-    split = max((a for a, t in enumerate(q_box) if t > 1), default=0)
+    split = 0
+    for a, t in enumerate(q_box):
+        if t > 1:
+            split = a
     if q_box[split] % 2:
         return False
     q_box[split] //= 2
@@ -431,20 +429,12 @@ def fna_forward_direct(query: Tensor, key: Tensor, value: Tensor, kernel_size: D
     """The fused kernel on the original heads-last layout: what the reference does as
     permute -> kernel -> unpermute (src/natten/backends/blackwell_fna.py:111-165) in one launch,
     the tile gathers (dilation included) done by the kernel's tensor-map loads."""
-    na_dim = query.dim() - 3
     q, k, v = (t.contiguous() for t in (query, key, value))
     ak = additional_keys.contiguous() if additional_keys is not None else None
     av = additional_values.contiguous() if additional_values is not None else None
-    out = torch.empty_like(q)
-    lse = torch.empty(q.shape[:-1], dtype=torch.float32, device=q.device)
-    with torch.cuda.device(q.device):
-        _lib.check(_lib.lib.b200na_na_forward_direct(
-            _ptr(q), _ptr(k), _ptr(v), _ptr(ak), _ptr(av), ak.shape[1] if ak is not None else 0,
-            _ptr(out), _ptr(lse), na_dim, _lib.ints(q.shape[1:1 + na_dim]),
-            _lib.ints(kernel_size), _lib.ints(stride), _lib.ints(dilation),
-            _lib.ints([1 if c else 0 for c in is_causal]), _lib.ints(q_tile_shape),
-            _lib.ints(kv_tile_shape), q.shape[0], q.shape[-2], k.shape[-2], q.shape[-1],
-            _DTYPE_CODE[q.dtype], float(scale), _stream(q)), "b200na_na_forward_direct")
+    out, lse = ops.na_forward_direct(q, k, v, ak, av, list(kernel_size), list(stride),
+                                     list(dilation), [bool(c) for c in is_causal], float(scale),
+                                     list(q_tile_shape), list(kv_tile_shape))
     return out, lse
 
 
@@ -482,22 +472,12 @@ def fna_forward_op(q_perm: Tensor, k_perm: Tensor, v_perm: Tensor, qkv_shape: Di
     """The fused kernel on token-permuted ``[B', S, H, D]`` operands; allocates O and LSE like the
     reference's op wrapper (src/natten/_libnatten/torch_wrappers.py:670-714). Extra key/value
     tokens stay in the original ``[B, M, Hkv, D]`` layout."""
-    na_dim = len(qkv_shape)
-    bp, sq, hq, d = q_perm.shape
-    hkv = k_perm.shape[2]
-    out = torch.empty_like(q_perm)
-    lse = torch.empty((bp, sq, hq), dtype=torch.float32, device=q_perm.device)
     ak = additional_keys.contiguous() if additional_keys is not None else None
     av = additional_values.contiguous() if additional_values is not None else None
-    with torch.cuda.device(q_perm.device):
-        _lib.check(_lib.lib.b200na_fna_forward_extra_kv(
-            _ptr(q_perm), _ptr(k_perm), _ptr(v_perm), _ptr(ak), _ptr(av),
-            ak.shape[1] if ak is not None else 0, _ptr(out), _ptr(lse), na_dim,
-            _lib.ints(qkv_shape), _lib.ints(q_shape), _lib.ints(kv_shape), _lib.ints(kernel_size),
-            _lib.ints(stride), _lib.ints(dilation), _lib.ints([1 if c else 0 for c in is_causal]),
-            _lib.ints(q_tile_shape), _lib.ints(kv_tile_shape), bp, hq, hkv, d,
-            _DTYPE_CODE[q_perm.dtype], float(scale), _stream(q_perm)),
-            "b200na_fna_forward_extra_kv")
+    out, lse = ops.fna_forward_permuted(
+        q_perm.contiguous(), k_perm.contiguous(), v_perm.contiguous(), ak, av, list(qkv_shape),
+        list(q_shape), list(kv_shape), list(kernel_size), list(stride), list(dilation),
+        [bool(c) for c in is_causal], float(scale), list(q_tile_shape), list(kv_tile_shape))
     return out, lse
 
 

@@ -1,0 +1,82 @@
+"""torch op registration and layers on the GPU: opcheck, torch.compile without graph breaks,
+layer output against the oracle."""
+import numpy as np
+import pytest
+import torch
+
+import natten_b200 as nb
+import natten_b200._lib as L
+import oracle
+from natten_b200 import ops
+
+pytestmark = pytest.mark.gpu
+
+
+def test_opcheck_schema_and_fake_implementations():
+    torch.manual_seed(2)
+    q = torch.randn(1, 24, 20, 2, 64, device="cuda").bfloat16()
+    ak = torch.randn(1, 9, 2, 64, device="cuda").bfloat16()
+    tests = ("test_schema", "test_faketensor")
+    import natten_b200.functional as F
+    torch.library.opcheck(F.na_forward_op,
+                          (q, q, q, ak, ak, [5, 7], [1, 2], [2, 1], [False, True], 0.125, [], [],
+                           False), test_utils=tests)
+    torch.library.opcheck(ops.na_forward_direct,
+                          (q, q, q, ak, ak, [5, 7], [1, 2], [2, 1], [False, True], 0.125,
+                           [16, 16], [16, 8]), test_utils=tests)
+    torch.library.opcheck(ops.na_forward_simt,
+                          (q.float(), q.float(), q.float(), None, None, [5, 7], [1, 2], [2, 1],
+                           [False, True], 0.125), test_utils=tests)
+    torch.library.opcheck(ops.token_permute, (q, [24, 20], [8, 4], [2, 1], True), test_utils=tests)
+    a = q.flatten(1, 2)
+    torch.library.opcheck(ops.fmha_forward, (a, a, a, False, 0.125), test_utils=tests)
+    o, l = ops.fmha_forward(a, a, a, False, 0.125)
+    torch.library.opcheck(ops.merge, (o, l, o, l), test_utils=tests)
+    assert L.device_status() == 0
+
+
+def test_operator_compiles_without_graph_breaks():
+    torch.manual_seed(3)
+    q, k, v = (torch.randn(2, 32, 40, 2, 128, device="cuda").bfloat16() for _ in range(3))
+    ak, av = (torch.randn(2, 40, 2, 128, device="cuda").bfloat16() for _ in range(2))
+
+    def f(q, k, v, ak, av):
+        o, l = nb.na2d(q * 1.0, k, v, (7, 9), (1, 2), (2, 1), (False, True), additional_keys=ak,
+                       additional_values=av, return_lse=True)
+        return o.float() * 2.0, l + 1.0
+
+    want = f(q, k, v, ak, av)
+    got = torch.compile(f, fullgraph=True)(q, k, v, ak, av)
+    assert L.device_status() == 0
+    assert torch.equal(got[0], want[0]) and torch.equal(got[1], want[1])
+
+
+@pytest.mark.parametrize("cls,shape,ks,di,ca", [
+    (nb.NeighborhoodAttention1D, (300,), 33, 2, True),
+    (nb.NeighborhoodAttention2D, (24, 28), (5, 7), (1, 2), (False, False)),
+    (nb.NeighborhoodAttention3D, (6, 10, 12), (3, 4, 5), 1, (True, False, False)),
+])
+def test_layers_match_projections_around_the_oracle(cls, shape, ks, di, ca):
+    torch.manual_seed(5)
+    heads, dim = 2, 64
+    layer = cls(heads * dim, heads, ks, dilation=di, is_causal=ca).cuda().bfloat16().eval()
+    x = torch.randn(2, *shape, heads * dim, device="cuda").bfloat16()
+    with torch.no_grad():
+        got = layer(x)
+        compiled = torch.compile(layer, fullgraph=True)(x)
+        qkv = layer.qkv(x).unflatten(-1, (3, heads, dim))
+    assert L.device_status() == 0
+    assert torch.equal(got, compiled)
+    q, k, v = (qkv.select(-3, i).float().cpu().numpy() for i in range(3))
+    want_attn, _ = oracle.na_forward(q, k, v, layer.kernel_size, layer.stride, layer.dilation,
+                                     layer.is_causal)
+    with torch.no_grad():
+        want = layer.proj(torch.from_numpy(want_attn).cuda().bfloat16().reshape(x.shape))
+    # attention tolerance (2e-2) carried through the output projection of O(1) weights
+    assert np.abs(got.float().cpu().numpy() - want.float().cpu().numpy()).max() <= 2e-2
+
+
+def test_differentiating_through_the_operator_fails_loudly():
+    q = torch.randn(1, 64, 2, 64, device="cuda").bfloat16().requires_grad_()
+    out = nb.na1d(q, q.detach(), q.detach(), 9)
+    assert not out.requires_grad          # forward only: no autograd history is attached
