@@ -53,6 +53,7 @@ def _load():
         _lib.na_oracle_forward.restype = ctypes.c_int
         _lib.na_oracle_dense.restype = ctypes.c_int
         _lib.na_oracle_merge.restype = ctypes.c_int
+        _lib.na_oracle_backward.restype = ctypes.c_int
     return _lib
 
 
@@ -115,6 +116,39 @@ def na_forward(q, k, v, kernel_size, stride=1, dilation=1, is_causal=False, scal
     if rc != 0:
         raise ValueError(f"na_oracle_forward rejected its arguments (code {rc})")
     return out, lse
+
+
+def na_backward(q, k, v, d_out, kernel_size, stride=1, dilation=1, is_causal=False, scale=None,
+                add_k=None, add_v=None):
+    """Gradients of neighborhood attention w.r.t. q, k, v (and the extra tokens) for the output
+    gradient ``d_out [B, *shape, Hq, Dv]``; fp32 numpy in and out, double accumulation inside.
+
+    Returns ``(dq, dk, dv)`` or, with extra tokens, ``(dq, dk, dv, d_add_k, d_add_v)``."""
+    lib = _load()
+    q, k, v, d_out = _f32c(q), _f32c(k), _f32c(v), _f32c(d_out)
+    nd = q.ndim - 3
+    shape = q.shape[1:1 + nd]
+    B, Hq, D = q.shape[0], q.shape[-2], q.shape[-1]
+    Hkv, Dv = k.shape[-2], v.shape[-1]
+    ks, st, di = _tup(kernel_size, nd), _tup(stride, nd), _tup(dilation, nd)
+    ca = _tup(is_causal, nd, lambda c: 1 if c else 0)
+    scale = float(scale) if scale else float(D) ** -0.5
+    n_extra = 0
+    dak = dav = None
+    if add_k is not None:
+        add_k, add_v = _f32c(add_k), _f32c(add_v)
+        n_extra = add_k.shape[1]
+        dak, dav = np.empty_like(add_k), np.empty_like(add_v)
+    dq, dk, dv = np.empty_like(q), np.empty_like(k), np.empty_like(v)
+    rc = lib.na_oracle_backward(
+        _fptr(q), _fptr(k), _fptr(v), _fptr(d_out), _fptr(dq), _fptr(dk), _fptr(dv),
+        ctypes.c_int(nd), _ints(shape), ctypes.c_int(B), ctypes.c_int(Hq), ctypes.c_int(Hkv),
+        ctypes.c_int(D), ctypes.c_int(Dv), _ints(ks), _ints(st), _ints(di), _ints(ca),
+        ctypes.c_float(scale), _fptr(add_k), _fptr(add_v), _fptr(dak), _fptr(dav),
+        ctypes.c_int(n_extra))
+    if rc != 0:
+        raise ValueError(f"na_oracle_backward rejected its arguments (code {rc})")
+    return (dq, dk, dv, dak, dav) if n_extra else (dq, dk, dv)
 
 
 def dense_attention(q, k, v, scale=None, is_causal=False) -> Tuple[np.ndarray, np.ndarray]:

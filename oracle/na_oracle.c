@@ -194,3 +194,144 @@ int na_oracle_merge(const float* o0, const float* l0, const float* o1, const flo
   }
   return 0;
 }
+
+/*
+ * Backward of neighborhood attention, double accumulation (checker only). Restates
+ * csrc/include/natten/cuda/reference/fna_reference_backward.hpp:62-160 (dQ), :177-275 (dK),
+ * :293-385 (dV): with s_ij = scale q_i.k_j, P_ij = exp(s_ij - LSE_i), dP_ij = dO_i.v_j,
+ * delta_i = dO_i.O_i:
+ *   dS_ij = scale P_ij (dP_ij - delta_i);  dQ_i = sum_j dS_ij k_j;  dK_j = sum_i dS_ij q_i;
+ *   dV_j = sum_i P_ij dO_i,
+ * j running over the query's window and the extra tokens (which get d_add_k / d_add_v). The
+ * forward quantities are recomputed here in double from q, k, v, so the result does not depend on
+ * anybody's rounded O or LSE (delta_i = sum_j P_ij dP_ij). GQA: the gradients of a key/value head
+ * sum over the query heads that share it. All arrays fp32, layouts as in na_oracle_forward; the
+ * gradient buffers are overwritten.
+ */
+int na_oracle_backward(const float* q, const float* k, const float* v, const float* d_out,
+                       float* dq, float* dk, float* dv, int ndim, const int* shape, int B, int Hq,
+                       int Hkv, int D, int Dv, const int* kernel, const int* stride,
+                       const int* dilation, const int* causal, float scale, const float* add_k,
+                       const float* add_v, float* d_add_k, float* d_add_v, int n_extra) {
+  if (ndim < 1 || ndim > NA_MAX_DIM || Hkv <= 0 || Hq % Hkv != 0) return 1;
+  na_params p;
+  memset(&p, 0, sizeof(p));
+  p.ndim = ndim;
+  int64_t N = 1, win = 1;
+  for (int a = 0; a < ndim; ++a) {
+    p.shape[a] = shape[a];
+    p.kernel[a] = kernel[a];
+    p.stride[a] = stride ? stride[a] : 1;
+    p.dilation[a] = dilation ? dilation[a] : 1;
+    p.causal[a] = causal ? causal[a] : 0;
+    if (p.kernel[a] < 2 || p.stride[a] < 1 || p.dilation[a] < 1) return 2;
+    if (p.kernel[a] * p.dilation[a] > p.shape[a] || p.stride[a] > p.kernel[a]) return 3;
+    N *= shape[a];
+    win *= kernel[a];
+  }
+  if (n_extra > 0 && (!add_k || !add_v || !d_add_k || !d_add_v)) return 4;
+  win += n_extra;
+  const int rep = Hq / Hkv;
+  const int nd = ndim;
+
+  /* one (batch, key/value head) pair per task: it owns its slices of dK, dV and the extras */
+#pragma omp parallel
+  {
+    double* s = (double*)malloc(sizeof(double) * (size_t)win);
+    double* dp = (double*)malloc(sizeof(double) * (size_t)win);
+    int64_t* kidx = (int64_t*)malloc(sizeof(int64_t) * (size_t)win);
+    double* gk = (double*)malloc(sizeof(double) * (size_t)(N + n_extra) * D);
+    double* gv = (double*)malloc(sizeof(double) * (size_t)(N + n_extra) * Dv);
+    double* gq = (double*)malloc(sizeof(double) * (size_t)D);
+#pragma omp for collapse(2) schedule(dynamic, 1)
+    for (int b = 0; b < B; ++b)
+      for (int hk = 0; hk < Hkv; ++hk) {
+        memset(gk, 0, sizeof(double) * (size_t)(N + n_extra) * D);
+        memset(gv, 0, sizeof(double) * (size_t)(N + n_extra) * Dv);
+        for (int64_t tok = 0; tok < N; ++tok) {
+          int qc[NA_MAX_DIM] = {0, 0, 0}, g[NA_MAX_DIM], st[NA_MAX_DIM], en[NA_MAX_DIM];
+          int64_t r = tok;
+          for (int a = nd - 1; a >= 0; --a) {
+            qc[a] = (int)(r % p.shape[a]);
+            r /= p.shape[a];
+          }
+          query_window(&p, qc, g, st, en);
+          int64_t nk = 0;
+          int c[NA_MAX_DIM];
+          int lo[NA_MAX_DIM] = {0, 0, 0}, hi[NA_MAX_DIM] = {1, 1, 1};
+          for (int a = 0; a < nd; ++a) {
+            lo[a] = st[a];
+            hi[a] = en[a];
+          }
+          for (c[0] = lo[0]; c[0] < hi[0]; ++c[0])
+            for (c[1] = lo[1]; c[1] < hi[1]; ++c[1])
+              for (c[2] = lo[2]; c[2] < hi[2]; ++c[2]) {
+                int64_t lin = 0;
+                for (int a = 0; a < nd; ++a)
+                  lin = lin * p.shape[a] + ((int64_t)c[a] * p.dilation[a] + g[a]);
+                kidx[nk++] = lin;
+              }
+          const int64_t nall = nk + n_extra;
+          for (int h = hk * rep; h < (hk + 1) * rep; ++h) {
+            const float* qr = q + (((size_t)b * N + tok) * Hq + h) * D;
+            const float* gor = d_out + (((size_t)b * N + tok) * Hq + h) * Dv;
+            double m = -INFINITY;
+            for (int64_t j = 0; j < nall; ++j) {
+              const float* kr = (j < nk) ? k + (((size_t)b * N + kidx[j]) * Hkv + hk) * D
+                                         : add_k + (((size_t)b * n_extra + (j - nk)) * Hkv + hk) * D;
+              const float* vr = (j < nk) ? v + (((size_t)b * N + kidx[j]) * Hkv + hk) * Dv
+                                         : add_v + (((size_t)b * n_extra + (j - nk)) * Hkv + hk) * Dv;
+              double d = 0, e = 0;
+              for (int x = 0; x < D; ++x) d += (double)qr[x] * kr[x];
+              for (int x = 0; x < Dv; ++x) e += (double)gor[x] * vr[x];
+              s[j] = d * scale;
+              dp[j] = e;
+              if (s[j] > m) m = s[j];
+            }
+            double sum = 0, delta = 0;
+            for (int64_t j = 0; j < nall; ++j) {
+              s[j] = exp(s[j] - m);
+              sum += s[j];
+            }
+            for (int64_t j = 0; j < nall; ++j) {
+              s[j] /= sum; /* P_ij */
+              delta += s[j] * dp[j];
+            }
+            for (int x = 0; x < D; ++x) gq[x] = 0;
+            for (int64_t j = 0; j < nall; ++j) {
+              const int64_t row = (j < nk) ? kidx[j] : N + (j - nk);
+              const float* kr = (j < nk) ? k + (((size_t)b * N + kidx[j]) * Hkv + hk) * D
+                                         : add_k + (((size_t)b * n_extra + (j - nk)) * Hkv + hk) * D;
+              const double ds = (double)scale * s[j] * (dp[j] - delta);
+              for (int x = 0; x < D; ++x) {
+                gq[x] += ds * kr[x];
+                gk[row * D + x] += ds * qr[x];
+              }
+              for (int x = 0; x < Dv; ++x) gv[row * Dv + x] += s[j] * gor[x];
+            }
+            float* dqr = dq + (((size_t)b * N + tok) * Hq + h) * D;
+            for (int x = 0; x < D; ++x) dqr[x] = (float)gq[x];
+          }
+        }
+        for (int64_t t = 0; t < N; ++t) {
+          float* o1 = dk + (((size_t)b * N + t) * Hkv + hk) * D;
+          float* o2 = dv + (((size_t)b * N + t) * Hkv + hk) * Dv;
+          for (int x = 0; x < D; ++x) o1[x] = (float)gk[t * D + x];
+          for (int x = 0; x < Dv; ++x) o2[x] = (float)gv[t * Dv + x];
+        }
+        for (int64_t t = 0; t < n_extra; ++t) {
+          float* o1 = d_add_k + (((size_t)b * n_extra + t) * Hkv + hk) * D;
+          float* o2 = d_add_v + (((size_t)b * n_extra + t) * Hkv + hk) * Dv;
+          for (int x = 0; x < D; ++x) o1[x] = (float)gk[(N + t) * D + x];
+          for (int x = 0; x < Dv; ++x) o2[x] = (float)gv[(N + t) * Dv + x];
+        }
+      }
+    free(s);
+    free(dp);
+    free(kidx);
+    free(gk);
+    free(gv);
+    free(gq);
+  }
+  return 0;
+}

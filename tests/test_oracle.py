@@ -94,3 +94,64 @@ def test_tokperm_oracle_matches_reference(idx):
     back = oracle.token_unpermute(y, case["shape"], case["tile"], case["dilation"],
                                   flip=case["flip"])
     assert np.array_equal(back, x)
+
+
+# ---- backward -----------------------------------------------------------------------------------
+# The reference's CPU-capable path refuses to differentiate ("FlexAttention does not support
+# backward on CPU"), so no gradient fixtures can be generated from it. The backward oracle is tied
+# to the pinned forward instead: a dense masked attention in torch (float64) whose forward matches
+# the reference's own outputs in tests/golden/ is differentiated by torch.autograd, and the
+# oracle's gradients must agree with it.
+
+def _dense_twin(c):
+    """torch float64 restatement of one golden case as dense attention under an explicit mask."""
+    import torch
+    from natten_b200.functional import group_extent, window_end, window_start
+    shape = c.shape
+    n = int(np.prod(shape))
+    mask = torch.zeros(n, n + c.n_extra, dtype=torch.bool)
+    mask[:, n:] = True
+    coords = np.stack(np.unravel_index(np.arange(n), shape), axis=1)
+    for qi, qc in enumerate(coords):
+        axes = []
+        for x, k, s, d, ca, X in zip(qc, c.kernel_size, c.stride, c.dilation, c.is_causal, shape):
+            g, i = int(x) % d, int(x) // d
+            L = group_extent(X, d, g)
+            st = window_start(i, k, s, L, ca)
+            axes.append([j * d + g for j in range(st, window_end(i, st, k, L, ca))])
+        grid = np.stack(np.meshgrid(*axes, indexing="ij"), axis=-1).reshape(-1, len(shape))
+        mask[qi, np.ravel_multi_index(tuple(grid.T), shape)] = True
+    leaves = [torch.from_numpy(t).double().requires_grad_() for t in (c.q, c.k, c.v)]
+    if c.n_extra:
+        leaves += [torch.from_numpy(t).double().requires_grad_() for t in (c.add_k, c.add_v)]
+    q, k, v = (t.flatten(1, len(shape)) for t in leaves[:3])
+    if c.n_extra:
+        k, v = torch.cat([k, leaves[3]], 1), torch.cat([v, leaves[4]], 1)
+    rep = q.shape[2] // k.shape[2]
+    k, v = k.repeat_interleave(rep, dim=2), v.repeat_interleave(rep, dim=2)
+    s = torch.einsum("bqhd,bkhd->bhqk", q, k) * q.shape[-1] ** -0.5
+    s = s.masked_fill(~mask, float("-inf"))
+    out = torch.einsum("bhqk,bkhd->bqhd", s.softmax(-1), v).reshape(c.out.shape)
+    return leaves, out
+
+
+@pytest.mark.parametrize("name", [
+    "na1d_300_k33", "na1d_257_k9_s3_d4_causal", "na2d_33x30_k3x5_s1x2_d3x2_causal01",
+    "na2d_16x16_k5_gqa", "c5s_na3d_8x12x20_k4x6x6_s1x2x2_causalT",
+    "na3d_6x9x11_k3x3x5_s1x1x2_d2x1x1_causalW", "na1d_96_k17_causal_extra7"])
+def test_backward_oracle_is_the_derivative_of_the_pinned_forward(name):
+    import torch
+    c = na_cases()[name]
+    leaves, out = _dense_twin(c)
+    # the twin's forward is the reference's forward ...
+    assert np.abs(out.detach().numpy() - c.out).max() <= 4e-6
+    torch.manual_seed(7)
+    d_out = torch.randn(out.shape, dtype=torch.float64)
+    out.backward(d_out)
+    # ... so its autograd gradients are what the backward oracle must return
+    got = oracle.na_backward(c.q, c.k, c.v, d_out.float().numpy(), c.kernel_size, c.stride,
+                             c.dilation, c.is_causal, add_k=c.add_k, add_v=c.add_v)
+    assert len(got) == len(leaves)
+    for g, leaf in zip(got, leaves):
+        want = leaf.grad.numpy()
+        assert np.abs(g - want).max() <= 2e-5 * max(1.0, np.abs(want).max())
