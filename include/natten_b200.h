@@ -238,6 +238,25 @@ B200NA_API int b200na_na_forward_simt(const void* q, const void* k, const void* 
                            int n_extra, b200na_stream_t stream);
 
 /*
+ * Neighborhood attention BACKWARD on the original token layout with CUDA-core fp32 arithmetic:
+ * the gradients the reference's backward ops return (natten::blackwell_na{1,2,3}d_backward,
+ * csrc/include/natten/blackwell_fna.h:92-152, after natten::compute_delta,
+ * csrc/include/natten/compute_delta.h:35; arithmetic as in csrc/include/natten/cuda/reference/
+ * fna_reference_backward.hpp:62-385), on the caller's layout, any of F32 / F16 / BF16, D <= 256,
+ * extra key/value tokens included (their gradients go to d_add_k / d_add_v).
+ *   q, dq, o, d_out: [B, *shape, Hq, D]; k, v, dk, dv: [B, *shape, Hkv, D]; lse: [B, *shape, Hq]
+ *   fp32 as returned by the forward; add_k, add_v, d_add_k, d_add_v: [B, n_extra, Hkv, D] or NULL;
+ *   delta_scratch: B * prod(shape) * Hq floats of caller-owned scratch (overwritten).
+ * Three to four launches (delta, dQ, dK/dV, extra tokens), no atomics: results are deterministic.
+ */
+B200NA_API int b200na_na_backward_simt(
+    const void* q, const void* k, const void* v, const void* o, const void* d_out, const float* lse,
+    const void* add_k, const void* add_v, int n_extra, void* dq, void* dk, void* dv, void* d_add_k,
+    void* d_add_v, float* delta_scratch, int ndim, const int* shape, const int* kernel,
+    const int* stride, const int* dilation, const int* causal, int B, int Hq, int Hkv, int D,
+    int dtype, float scale, b200na_stream_t stream);
+
+/*
  * Two-way LSE merge: replaces the elementwise chain of natten.merge_attentions
  * (reference: src/natten/attn_merge.py:48-105; call site src/natten/functional.py:548-554).
  *   o = o0 - sigmoid(l1 - l0) * (o0 - o1);  l = l0 - logsigmoid(l0 - l1)   (fp32 arithmetic)

@@ -6,7 +6,9 @@ src/natten/token_permute/frontend.py:42-137) — and calls the CUDA kernels thro
 ``include/natten_b200.h``. PyTorch is used for device memory and streams only. There is no CPU or
 library fallback: tensors must live on a CUDA device of compute capability 10.x.
 
-Forward only: outputs never carry autograd history.
+Autograd: `na1d/na2d/na3d` (extra tokens fused) and self-attention `attention()` are
+differentiable - their backward runs the CUDA-core gradient kernels; `merge_attentions` and the
+unfused extra-token composition register no formula, so differentiating through them raises.
 """
 from __future__ import annotations
 
@@ -234,11 +236,11 @@ def merge_attentions(outputs: List[Tensor], lse_tensors: List[Tensor], torch_com
     dtype = outputs[0].dtype
     if dtype not in _DTYPE_CODE:
         raise NotImplementedError(f"merge_attentions does not support dtype {dtype}.")
-    acc_o = outputs[0].detach().contiguous()
-    acc_l = lse_tensors[0].detach().to(torch.float32).contiguous()
+    acc_o = outputs[0].contiguous()
+    acc_l = lse_tensors[0].to(torch.float32).contiguous()
     for i in range(1, len(outputs)):
-        acc_o, acc_l = ops.merge(acc_o, acc_l, outputs[i].detach().contiguous(),
-                                 lse_tensors[i].detach().to(torch.float32).contiguous())
+        acc_o, acc_l = ops.merge(acc_o, acc_l, outputs[i].contiguous(),
+                                 lse_tensors[i].to(torch.float32).contiguous())
     out, out_l = acc_o, acc_l
     return out, out_l
 
@@ -278,7 +280,7 @@ def attention(query: Tensor, key: Tensor, value: Tensor, is_causal: bool = False
         raise NotImplementedError("Causal attention needs equal query and key lengths here.")
     if query.dtype not in _DTYPE_CODE:
         raise NotImplementedError(f"natten_b200.attention does not support dtype {query.dtype}.")
-    q, k, v = (t.detach().contiguous() for t in (query, key, value))
+    q, k, v = (t.contiguous() for t in (query, key, value))
     out, lse = ops.fmha_forward(q, k, v, bool(is_causal), float(scale))
     return (out, lse) if return_lse else out
 
@@ -336,9 +338,9 @@ def neighborhood_attention_generic(
         kv_tile_shape = check_tile_shape(na_dim, kv_tile_shape, "kv_tile_shape", KV_TILE_SIZE)
     fuse_extra = has_extra and not (attention_kwargs or {}).get("unfused_extra_kv", False)
     want_permuted = bool((attention_kwargs or {}).get("permuted_layout", False))
-    q, k, v = (t.detach().contiguous() for t in (query, key, value))
-    ak = additional_keys.detach().contiguous() if fuse_extra else None
-    av = additional_values.detach().contiguous() if fuse_extra else None
+    q, k, v = (t.contiguous() for t in (query, key, value))
+    ak = additional_keys.contiguous() if fuse_extra else None
+    av = additional_values.contiguous() if fuse_extra else None
     output, lse = na_forward_op(q, k, v, ak, av, list(kernel_size), list(stride), list(dilation),
                                 [bool(c) for c in is_causal], float(scale),
                                 list(q_tile_shape or ()), list(kv_tile_shape or ()), want_permuted)
@@ -398,6 +400,34 @@ def na_forward_op(query: Tensor, key: Tensor, value: Tensor, additional_keys: Op
                                   additional_values)
     return fna_forward_permuted(query, key, value, kernel_size, stride, dilation, is_causal, scale,
                                 q_tile_shape, kv_tile_shape, additional_keys, additional_values)
+
+
+def _na_setup_context(ctx, inputs, output):
+    (query, key, value, additional_keys, additional_values, kernel_size, stride, dilation,
+     is_causal, scale, _q_tile, _kv_tile, _permuted) = inputs
+    out, lse = output
+    ctx.has_extra = additional_keys is not None
+    saved = [query, key, value, out, lse]
+    if ctx.has_extra:
+        saved += [additional_keys, additional_values]
+    ctx.save_for_backward(*saved)
+    ctx.na_args = (list(kernel_size), list(stride), list(dilation), list(is_causal), scale)
+
+
+def _na_backward(ctx, d_out, d_lse):
+    """Gradients of the output w.r.t. query, key, value and the fused extra tokens. d_lse is
+    ignored, as in the reference's backward (src/natten/backends/blackwell_fna.py:185-318)."""
+    query, key, value, out, lse = ctx.saved_tensors[:5]
+    ak, av = ctx.saved_tensors[5:] if ctx.has_extra else (None, None)
+    dq, dk, dv, dak, dav = ops.na_backward_simt(query, key, value, out, d_out.contiguous(), lse,
+                                                ak, av, *ctx.na_args)
+    if not ctx.has_extra:
+        dak = dav = None
+    return (dq, dk, dv, dak, dav) + (None,) * 8
+
+
+if ops.USE_TORCH_OPS:
+    na_forward_op.register_autograd(_na_backward, setup_context=_na_setup_context)
 
 
 MAX_TMA_BOX = 256      # positions a tensor-map box may span per axis

@@ -2,8 +2,8 @@
 
 Drop-in counterparts of the reference's ``NeighborhoodAttention1D/2D/3D``
 (src/natten/modules.py:42-122): same constructor arguments, same parameter names (``qkv``,
-``proj``), so a reference checkpoint loads unchanged. Inference only - the operators underneath
-are forward only.
+``proj``), so a reference checkpoint loads unchanged. Trainable: the operator underneath is
+differentiable.
 """
 from typing import Any, Optional
 

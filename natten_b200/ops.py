@@ -9,7 +9,8 @@ current stream and raises on a non-zero status. Argument validation lives in ``f
 
 ``NATTEN_B200_DISABLE_TORCH_OPS=1`` turns the registration off (the functions are then called
 directly), like the reference's ``NATTEN_DISABLE_TORCH_OPS`` (src/natten/utils/environment.py:67-69).
-Forward only: no autograd formula is registered, so differentiating through an op raises.
+Autograd formulas are registered for `na_forward` (functional.py) and `fmha_forward`; the other
+ops have none, so differentiating through them raises.
 """
 import ctypes
 import math
@@ -218,3 +219,63 @@ def na_forward_simt(query: Tensor, key: Tensor, value: Tensor, additional_keys: 
             _ptr(additional_keys), _ptr(additional_values), n_extra, _stream(query)),
             "b200na_na_forward_simt")
     return out, lse
+
+
+# ---- backward --------------------------------------------------------------------------------------
+
+def _na_backward_fake(query, key, value, out, d_out, lse, additional_keys, additional_values,
+                      kernel_size, stride, dilation, is_causal, scale):
+    extra = additional_keys if additional_keys is not None else key.new_empty((0,))
+    return (torch.empty_like(query), torch.empty_like(key), torch.empty_like(value),
+            torch.empty_like(extra), torch.empty_like(extra))
+
+
+@_op("na_backward_simt", _na_backward_fake)
+def na_backward_simt(query: Tensor, key: Tensor, value: Tensor, out: Tensor, d_out: Tensor,
+                     lse: Tensor, additional_keys: Optional[Tensor],
+                     additional_values: Optional[Tensor], kernel_size: List[int],
+                     stride: List[int], dilation: List[int], is_causal: List[bool],
+                     scale: float) -> Tuple[Tensor, Tensor, Tensor, Tensor, Tensor]:
+    """Gradients of neighborhood attention w.r.t. query, key, value and the extra tokens (empty
+    tensors when there are none) on the caller's layout, CUDA-core kernels, any supported dtype."""
+    dq, dk, dv, dak, dav = _na_backward_fake(query, key, value, out, d_out, lse, additional_keys,
+                                             additional_values, kernel_size, stride, dilation,
+                                             is_causal, scale)
+    na_dim = query.dim() - 3
+    n_extra = additional_keys.shape[1] if additional_keys is not None else 0
+    delta = torch.empty(query.shape[:-1], dtype=torch.float32, device=query.device)
+    with torch.cuda.device(query.device):
+        _lib.check(_lib.lib.b200na_na_backward_simt(
+            _ptr(query), _ptr(key), _ptr(value), _ptr(out), _ptr(d_out), _ptr(lse),
+            _ptr(additional_keys), _ptr(additional_values), n_extra, _ptr(dq), _ptr(dk), _ptr(dv),
+            _ptr(dak) if n_extra else None, _ptr(dav) if n_extra else None, _ptr(delta), na_dim,
+            _lib.ints(query.shape[1:1 + na_dim]), _lib.ints(kernel_size), _lib.ints(stride),
+            _lib.ints(dilation), _lib.ints(_flags(is_causal)), query.shape[0], query.shape[-2],
+            key.shape[-2], query.shape[-1], DTYPE_CODE[query.dtype], float(scale),
+            _stream(query)), "b200na_na_backward_simt", kernel_launches=4 if n_extra else 3)
+    return dq, dk, dv, dak, dav
+
+
+def _fmha_setup_context(ctx, inputs, output):
+    query, key, value, is_causal, scale = inputs
+    out, lse = output
+    ctx.save_for_backward(query, key, value, out, lse)
+    ctx.is_causal, ctx.scale = is_causal, scale
+
+
+def _fmha_backward(ctx, d_out, d_lse):
+    # Self attention is neighborhood attention whose window is the whole sequence, so its
+    # gradients come from the same kernels; d_lse is ignored like in the reference's backward
+    # (src/natten/backends/blackwell_fna.py:185-318 returns gradients of the output only).
+    query, key, value, out, lse = ctx.saved_tensors
+    if query.shape[1] != key.shape[1]:
+        raise NotImplementedError("natten_b200: backward of attention() needs equal query and "
+                                  "key/value lengths.")
+    n = query.shape[1]
+    dq, dk, dv, _, _ = na_backward_simt(query, key, value, out, d_out.contiguous(), lse, None,
+                                        None, [n], [1], [1], [bool(ctx.is_causal)], ctx.scale)
+    return dq, dk, dv, None, None
+
+
+if USE_TORCH_OPS:
+    fmha_forward.register_autograd(_fmha_backward, setup_context=_fmha_setup_context)

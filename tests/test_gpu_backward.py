@@ -1,0 +1,65 @@
+"""Backward of neighborhood attention through autograd, against the CPU oracle
+(oracle.na_backward: double accumulation, tied to the reference's forward by tests/test_oracle.py).
+
+Tolerances: fp32 operands 2e-4 relative to the largest gradient entry; fp16/bf16 operands 2e-2
+(the forward's tolerance) - gradients are rounded to the operand dtype."""
+import numpy as np
+import pytest
+import torch
+
+import natten_b200 as nb
+import natten_b200._lib as L
+import oracle
+from golden_io import na_cases
+
+pytestmark = pytest.mark.gpu
+
+CASES = ["na1d_300_k33", "na1d_257_k9_s3_d4_causal", "na2d_33x30_k3x5_s1x2_d3x2_causal01",
+         "na2d_16x16_k5_gqa", "c3s_na2d_32x32_k13_d2", "c4s_na2d_32x32_k8_s4_extra24",
+         "c5s_na3d_8x12x20_k4x6x6_s1x2x2_causalT", "na3d_6x9x11_k3x3x5_s1x1x2_d2x1x1_causalW",
+         "na1d_96_k17_causal_extra7", "na2d_8x8_k8_selfattn"]
+
+
+def _grads(c, dtype):
+    fn = {1: nb.na1d, 2: nb.na2d, 3: nb.na3d}[len(c.shape)]
+    leaves = [torch.from_numpy(t).cuda().to(dtype).requires_grad_() for t in (c.q, c.k, c.v)]
+    if c.n_extra:
+        leaves += [torch.from_numpy(t).cuda().to(dtype).requires_grad_() for t in (c.add_k, c.add_v)]
+    out = fn(leaves[0], leaves[1], leaves[2], kernel_size=c.kernel_size, stride=c.stride,
+             dilation=c.dilation, is_causal=c.is_causal,
+             additional_keys=leaves[3] if c.n_extra else None,
+             additional_values=leaves[4] if c.n_extra else None)
+    torch.manual_seed(11)
+    d_out = torch.randn(out.shape, device="cuda").to(dtype)
+    out.backward(d_out)
+    assert L.device_status() == 0
+    want = oracle.na_backward(c.q, c.k, c.v, d_out.float().cpu().numpy(), c.kernel_size, c.stride,
+                              c.dilation, c.is_causal, add_k=c.add_k, add_v=c.add_v)
+    return [t.grad for t in leaves], want
+
+
+@pytest.mark.parametrize("name", CASES)
+def test_fp32_gradients_match_the_oracle(name):
+    got, want = _grads(na_cases()[name], torch.float32)
+    for g, w in zip(got, want):
+        assert g.dtype == torch.float32 and tuple(g.shape) == w.shape
+        assert np.abs(g.cpu().numpy() - w).max() <= 2e-4 * max(1.0, np.abs(w).max())
+
+
+@pytest.mark.parametrize("name", CASES)
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_16bit_gradients_match_the_oracle(name, dtype):
+    got, want = _grads(na_cases()[name], dtype)
+    for g, w in zip(got, want):
+        assert g.dtype == dtype
+        assert np.abs(g.float().cpu().numpy() - w).max() <= 2e-2 * max(1.0, np.abs(w).max())
+
+
+def test_layer_trains():
+    torch.manual_seed(1)
+    layer = nb.NeighborhoodAttention2D(128, 2, (5, 5), dilation=(1, 2)).cuda()
+    x = torch.randn(2, 12, 14, 128, device="cuda", requires_grad=True)
+    layer(x).square().mean().backward()
+    assert L.device_status() == 0
+    for p in list(layer.parameters()) + [x]:
+        assert p.grad is not None and torch.isfinite(p.grad).all() and p.grad.abs().max() > 0
