@@ -257,6 +257,26 @@ B200NA_API int b200na_na_backward_simt(
     int dtype, float scale, b200na_stream_t stream);
 
 /*
+ * Neighborhood attention BACKWARD on tensor cores, on the caller's layout: replaces
+ * natten::blackwell_na{1,2,3}d_backward (csrc/include/natten/blackwell_fna.h:92-152) together with
+ * the token permutes / unpermutes around it (src/natten/backends/blackwell_fna.py:217-300) and
+ * natten::compute_delta (csrc/include/natten/compute_delta.h:35). Three launches: delta, one pass
+ * of the tcgen05 kernel for dQ (a CTA per 128-query tile streams key/value tiles), one pass of the
+ * same kernel for dK and dV (a CTA per 128-key tile streams the query tiles that attend it). No
+ * atomics: results are deterministic (the reference's Blackwell backward has no deterministic mode,
+ * src/natten/backends/blackwell_fna.py:209-215).
+ *   Tensors as in b200na_na_backward_simt; dtype F16 or BF16; D in {64, 128}; no extra tokens.
+ *   q_tile / kv_tile: prod = 128 each; tile[a] * dilation[a] <= 256 and dilation[a] <= 8,
+ *   otherwise B200NA_ERR_UNSUPPORTED (use b200na_na_backward_simt then).
+ */
+B200NA_API int b200na_na_backward_direct(
+    const void* q, const void* k, const void* v, const void* o, const void* d_out, const float* lse,
+    void* dq, void* dk, void* dv, float* delta_scratch, int ndim, const int* shape,
+    const int* kernel, const int* stride, const int* dilation, const int* causal,
+    const int* q_tile, const int* kv_tile, int B, int Hq, int Hkv, int D, int dtype, float scale,
+    b200na_stream_t stream);
+
+/*
  * Two-way LSE merge: replaces the elementwise chain of natten.merge_attentions
  * (reference: src/natten/attn_merge.py:48-105; call site src/natten/functional.py:548-554).
  *   o = o0 - sigmoid(l1 - l0) * (o0 - o1);  l = l0 - logsigmoid(l0 - l1)   (fp32 arithmetic)

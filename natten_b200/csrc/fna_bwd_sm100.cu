@@ -1,0 +1,928 @@
+// Fused neighborhood attention BACKWARD for sm_100a (B200) on tensor cores: TMA-fed tiles,
+// tcgen05 MMAs with TMEM accumulators, operands read straight from the caller's [B, *X, H, D]
+// layout through rank-5 tensor maps (same boxes as the forward kernel in fna_sm100.cu).
+//
+// Functional contract = the reference's Blackwell FNA backward
+// (natten::blackwell_na{1,2,3}d_backward, csrc/include/natten/blackwell_fna.h:92-152; arithmetic
+// csrc/include/natten/cuda/reference/fna_reference_backward.hpp:62-385): with
+// P = exp(scale q.k - LSE), dP = dO.v, delta = dO.O:  dS = P (dP - delta),
+//   dQ = scale dS K,   dK = scale dS^T Q,   dV = P^T dO,
+// P and dS rounded to the operand type before the second products. The design is this library's:
+// ONE kernel template serves both passes, because they are mirror images of each other.
+//   * A CTA owns a stationary 128-token ROW tile and streams 128-token COLUMN tiles past it:
+//       pass dQ   : rows = queries (R1 = Q, R2 = dO), columns = keys    (C1 = K, C2 = V)
+//       pass dKdV : rows = keys    (R1 = K, R2 = V),  columns = queries (C1 = Q, C2 = dO)
+//     In both, S = R1 C1^T and dP = R2 C2^T; then dQ += dS C1, resp. dK += dS C1 and dV += P C2.
+//     No atomics, no partial sums in memory: every gradient row is owned by exactly one CTA.
+//   * The columns a row tile needs form a box of tiles in both passes: a query's keys are its
+//     window, and a key's queries are the inverse window - an interval per axis, because window
+//     start and end never decrease with the query coordinate (found by bisection).
+//   * TMEM: S [0,128) dP [128,256) acc0 [256,256+D) acc1 [384,384+D). P and dS (16-bit) overwrite
+//     S and dP in place, privately per thread, and feed the second MMAs from TMEM.
+//   * Row statistics (LSE, delta) are per thread in pass dQ; in pass dKdV they belong to the
+//     columns and are staged through shared memory per column tile.
+//   * Warp roles: 8 softmax warps (two threads per row, 64 columns each), 1 MMA-issue warp, 1
+//     load warp that also decodes work items and classifies tiles (descriptor / record rings as in
+//     the forward kernel). Every mbarrier wait is bounded; on expiry the CTA records a status word
+//     (shared with the forward kernel) and drains.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <mutex>
+#include <type_traits>
+
+#include "common.cuh"
+#include "fna_host.cuh"
+#include "ptx.cuh"
+
+namespace b200na {
+namespace {
+
+constexpr int kTile = 128;          // tokens per row tile and per column tile
+constexpr int kSoftmaxWarps = 8;    // 2 column parts x 4 warps (one thread per row and part)
+constexpr int kSoftmaxThreads = 256;
+constexpr int kMmaWarp = 8;
+constexpr int kLoadWarp = 9;
+constexpr int kThreads = 320;
+constexpr int kTmemCols = 512;
+constexpr int kDescSlots = 4;
+constexpr int kDescBytes = 192;
+constexpr int kTileRecs = 8;
+constexpr long long kWaitLimitCycles = 4000000000ll;  // ~2 s at 2 GHz
+
+// status word: (role << 8) | barrier id; roles 5 = softmax, 6 = mma, 7 = load (backward kernel)
+enum : int { kStRFull = 1, kStREmpty, kStCFull, kStCEmpty, kStSdpFull, kStDsFull, kStAccFull,
+             kStAccEmpty, kStDescFull, kStDescEmpty, kStRecFull, kStRecEmpty, kStSmemAlign };
+
+struct BwdTcParams {
+  int ndim;
+  int X[B200NA_MAX_DIM];
+  int kernel[B200NA_MAX_DIM];
+  int stride[B200NA_MAX_DIM];
+  int dil[B200NA_MAX_DIM];
+  int causal[B200NA_MAX_DIM];
+  int Tr[B200NA_MAX_DIM];   // row tile shape
+  int Tc[B200NA_MAX_DIM];   // column tile shape
+  int Rr[B200NA_MAX_DIM];   // row tiles per axis per dilation group
+  int G;                    // prod(dil)
+  int B, Hq, Hkv, rep;
+  int n_rtiles;             // row tiles per (batch, group, head)
+  int row_heads;            // heads the row tiles carry: Hq (pass dQ) or Hkv (pass dKdV)
+  long long total_work;     // n_rtiles * row_heads * B * G
+  float scale;              // applied to dQ / dK in the epilogue
+  float scale_log2;         // scale * log2(e)
+  const float* lse;         // [B, *X, Hq]
+  const float* delta;       // [B, *X, Hq]
+  void* out0;               // dQ (pass dQ) or dK (pass dKdV)
+  void* out1;               // dV (pass dKdV)
+  int* status;
+};
+
+struct Item {
+  int b, h;                   // batch entry; head of the row tile (query head or kv head)
+  int g[B200NA_MAX_DIM];      // dilation group offset per axis
+  int L[B200NA_MAX_DIM];      // extent of this dilation group
+  int r_lo[B200NA_MAX_DIM];   // first row coordinate of the tile (group coordinates)
+  int c_t0[B200NA_MAX_DIM];   // first column tile per axis
+  int c_n[B200NA_MAX_DIM];    // column tiles per axis
+  // column tiles [int_lo, int_hi) of an axis lie inside the (inverse) window of every row
+  int int_lo[B200NA_MAX_DIM];
+  int int_hi[B200NA_MAX_DIM];
+  int n_tiles;                // column tiles to visit (times the heads of the group in pass dKdV)
+  int n_per_head;             // column tiles per head
+  int skip;
+};
+static_assert(sizeof(Item) <= kDescBytes, "descriptor slot too small");
+
+// Window of a query along one axis, group coordinates: [st, en).
+__device__ __forceinline__ void fwd_window(const BwdTcParams& p, int a, int i, int L, int& st,
+                                           int& en) {
+  st = win_start(i, p.kernel[a], p.stride[a], L, p.causal[a]);
+  en = win_end(i, st, p.kernel[a], L, p.causal[a]);
+}
+// Queries whose window holds key j (the inverse window): [lo, hi); empty for j outside [0, L).
+__device__ __forceinline__ void inv_window(const BwdTcParams& p, int a, int j, int L, int& lo,
+                                           int& hi) {
+  if (j >= L) {
+    lo = hi = L;
+    return;
+  }
+  int x = 0, y = L;
+  while (x < y) {  // first query whose window end is beyond j
+    const int mid = (x + y) >> 1;
+    int st, en;
+    fwd_window(p, a, mid, L, st, en);
+    if (en > j) y = mid; else x = mid + 1;
+  }
+  lo = x;
+  y = L;
+  while (x < y) {  // first query whose window start is beyond j
+    const int mid = (x + y) >> 1;
+    if (win_start(mid, p.kernel[a], p.stride[a], L, p.causal[a]) > j) y = mid; else x = mid + 1;
+  }
+  hi = x;
+}
+// Columns that interact with row coordinate i: the window (rows = queries) or the inverse window
+// (rows = keys).
+template <bool kKeyRows>
+__device__ __forceinline__ void row_span(const BwdTcParams& p, int a, int i, int L, int& lo,
+                                         int& hi) {
+  if (kKeyRows) inv_window(p, a, i, L, lo, hi); else fwd_window(p, a, i < L ? i : L - 1, L, lo, hi);
+}
+
+struct WorkCursor {
+  long long w;
+  int rt, h, bp;
+  __device__ __forceinline__ void init(const BwdTcParams& p, long long w0) {
+    w = w0;
+    rt = (int)(w0 % p.n_rtiles);
+    const long long rest = w0 / p.n_rtiles;
+    h = (int)(rest % p.row_heads);
+    bp = (int)(rest / p.row_heads);
+  }
+  __device__ __forceinline__ void advance(const BwdTcParams& p, int step) {
+    w += step;
+    rt += step;
+    while (rt >= p.n_rtiles) {
+      rt -= p.n_rtiles;
+      if (++h == p.row_heads) {
+        h = 0;
+        ++bp;
+      }
+    }
+  }
+};
+
+template <int NDIM, bool kKeyRows>
+__device__ __forceinline__ void decode_item(const BwdTcParams& p, const WorkCursor& cur, Item& it) {
+  it.h = cur.h;
+  it.b = (p.G > 1) ? cur.bp / p.G : cur.bp;
+  int gl = (p.G > 1) ? cur.bp - it.b * p.G : 0;
+  int rl = cur.rt;
+  it.n_per_head = 1;
+  it.skip = 0;
+#pragma unroll
+  for (int a = 0; a < B200NA_MAX_DIM; ++a) {
+    if (a < NDIM) {
+      int g = 0;
+      if (p.G > 1) {
+        g = gl % p.dil[a];
+        gl /= p.dil[a];
+      }
+      it.g[a] = g;
+      const int L = p.dil[a] == 1 ? p.X[a] : group_extent(p.X[a], p.dil[a], g);
+      it.L[a] = L;
+      int r = rl;
+      if (a + 1 < NDIM) {
+        const int rn = rl / p.Rr[a];
+        r = rl - rn * p.Rr[a];
+        rl = rn;
+      }
+      const int lo = r * p.Tr[a];
+      if (lo >= L) it.skip = 1;  // the tile lies beyond this dilation group
+      it.r_lo[a] = lo;
+      const int last = (lo + p.Tr[a] - 1 < L) ? lo + p.Tr[a] - 1 : L - 1;  // last real row
+      int s_lo, e_lo, s_hi, e_hi;
+      row_span<kKeyRows>(p, a, lo, L, s_lo, e_lo);
+      row_span<kKeyRows>(p, a, last, L, s_hi, e_hi);
+      const int Tc = p.Tc[a];
+      int t0 = s_lo / Tc;
+      int t1 = (e_hi + Tc - 1) / Tc;
+      if (t1 <= t0) t1 = t0 + 1;  // a key nobody attends: visit one (fully masked) tile
+      it.c_t0[a] = t0;
+      it.c_n[a] = t1 - t0;
+      it.int_lo[a] = (s_hi + Tc - 1) / Tc;
+      it.int_hi[a] = e_lo / Tc;
+      // rows past the extent (padding) interact with nothing: no tile is mask-free then
+      if (lo + p.Tr[a] > L) it.int_hi[a] = it.int_lo[a];
+      it.n_per_head *= it.c_n[a];
+    } else {
+      it.g[a] = 0; it.L[a] = 1; it.r_lo[a] = 0; it.c_t0[a] = 0; it.c_n[a] = 1;
+      it.int_lo[a] = 0; it.int_hi[a] = 1;
+    }
+  }
+  it.n_tiles = it.n_per_head * (kKeyRows ? p.rep : 1);
+}
+
+template <int D>
+struct Smem {
+  static constexpr int kTileBytes = kTile * D * 2;          // one 128-token operand tile
+  static constexpr int kStages = (D == 128) ? 2 : 3;        // (C1, C2) pairs in flight
+  static constexpr int kRowOff = 0;                         // R1, R2
+  static constexpr int kColOff = 2 * kTileBytes;
+  static constexpr int kPrefOff = kColOff + kStages * 2 * kTileBytes;
+  static constexpr int kPrefEntries = 136;
+  static constexpr int kStatOff = kPrefOff + kPrefEntries * 16;   // column stats [2][2][128] fp32
+  static constexpr int kDescOff = kStatOff + 2 * 2 * kTile * 4;
+  static constexpr int kRecOff = kDescOff + kDescSlots * kDescBytes;
+  static constexpr int kBarOff = kRecOff + kTileRecs * 16;
+  // r_full, r_empty, sdp_full, ds_full, acc_full, acc_empty, desc_full[4], desc_empty[4],
+  // rec_full[8], rec_empty[8], c_full[S], c_empty[S]
+  static constexpr int kNumBars = 6 + 2 * kDescSlots + 2 * kTileRecs + 2 * kStages;
+  static constexpr int kMiscOff = kBarOff + kNumBars * 8;
+  static constexpr int kBytes = kMiscOff + 16;
+};
+
+struct Bars {
+  uint64_t *r_full, *r_empty, *sdp_full, *ds_full, *acc_full, *acc_empty;
+  uint64_t *desc_full, *desc_empty, *rec_full, *rec_empty, *c_full, *c_empty;
+};
+
+__device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                         int* status, int code) {
+  if (ptx::mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!ptx::mbar_try_wait(bar, parity)) {
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitLimitCycles) {
+      *abort_flag = 1;
+      atomicCAS(status, 0, code);
+      return false;
+    }
+  }
+  return true;
+}
+
+template <bool kBf16>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  if (kBf16) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  } else {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+}
+
+__device__ __forceinline__ void named_bar_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+constexpr int kTileInterior = 1, kTileBoundary = 2;
+
+// Per-item constants of the column-tile walk and classification, held in registers by the load
+// thread (all its instructions are dependent, so shared-memory reads per tile would add latency).
+struct TileWalk {
+  int t0[B200NA_MAX_DIM], end[B200NA_MAX_DIM], int_lo[B200NA_MAX_DIM], int_hi[B200NA_MAX_DIM];
+  __device__ __forceinline__ void load(const Item& it) {
+#pragma unroll
+    for (int a = 0; a < B200NA_MAX_DIM; ++a) {
+      t0[a] = it.c_t0[a];
+      end[a] = it.c_t0[a] + it.c_n[a];
+      int_lo[a] = it.int_lo[a];
+      int_hi[a] = it.int_hi[a];
+    }
+  }
+  template <int NDIM>
+  __device__ __forceinline__ bool interior(const int (&c)[B200NA_MAX_DIM]) const {
+    bool in = true;
+#pragma unroll
+    for (int a = 0; a < B200NA_MAX_DIM; ++a)
+      if (a < NDIM) in = in && c[a] >= int_lo[a] && c[a] < int_hi[a];
+    return in;
+  }
+  // colexicographic walk, axis 0 fastest; wraps to the first tile after the last one
+  template <int NDIM>
+  __device__ __forceinline__ void next(int (&c)[B200NA_MAX_DIM]) const {
+    if (++c[0] < end[0]) return;
+    c[0] = t0[0];
+    if (NDIM == 1) return;
+    if (++c[1] < end[1]) return;
+    c[1] = t0[1];
+    if (NDIM == 2) return;
+    if (++c[2] < end[2]) return;
+    c[2] = t0[2];
+  }
+};
+
+template <int D, bool kBf16, int NDIM, bool kKeyRows>
+__global__ void __launch_bounds__(kThreads, 1)
+fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant__ CUtensorMap tm_r2,
+               const __grid_constant__ CUtensorMap tm_c1, const __grid_constant__ CUtensorMap tm_c2,
+               const BwdTcParams p) {
+  using SM = Smem<D>;
+  constexpr int kStages = SM::kStages;
+  constexpr int kTileBytes = SM::kTileBytes;
+  constexpr int kDBlocks = D / 64;
+  constexpr int kBlockBytes = kTile * 128;
+  typedef typename std::conditional<kBf16, __nv_bfloat16, __half>::type T;
+
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* row_sm = smem + SM::kRowOff;
+  uint8_t* col_sm = smem + SM::kColOff;
+  uint4* pref = reinterpret_cast<uint4*>(smem + SM::kPrefOff);
+  float* colstat = reinterpret_cast<float*>(smem + SM::kStatOff);  // [2 buf][lse | delta][128]
+  uint8_t* desc_sm = smem + SM::kDescOff;
+  int4* tile_rec = reinterpret_cast<int4*>(smem + SM::kRecOff);
+  uint64_t* bar_base = reinterpret_cast<uint64_t*>(smem + SM::kBarOff);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SM::kMiscOff);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM::kMiscOff + 4);
+
+  Bars bars;
+  bars.r_full = bar_base + 0;
+  bars.r_empty = bar_base + 1;
+  bars.sdp_full = bar_base + 2;
+  bars.ds_full = bar_base + 3;
+  bars.acc_full = bar_base + 4;
+  bars.acc_empty = bar_base + 5;
+  bars.desc_full = bar_base + 6;
+  bars.desc_empty = bars.desc_full + kDescSlots;
+  bars.rec_full = bars.desc_empty + kDescSlots;
+  bars.rec_empty = bars.rec_full + kTileRecs;
+  bars.c_full = bars.rec_empty + kTileRecs;
+  bars.c_empty = bars.c_full + kStages;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if ((ptx::smem_u32(smem) & 1023u) != 0) {
+    if (threadIdx.x == 0) atomicCAS(p.status, 0, (8 << 8) | kStSmemAlign);
+    return;
+  }
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    ptx::mbar_init(bars.r_full, 1);
+    ptx::mbar_init(bars.r_empty, 1);
+    ptx::mbar_init(bars.sdp_full, 1);
+    ptx::mbar_init(bars.ds_full, kSoftmaxWarps);
+    ptx::mbar_init(bars.acc_full, 1);
+    ptx::mbar_init(bars.acc_empty, kSoftmaxWarps);
+    for (int s = 0; s < kDescSlots; ++s) {
+      ptx::mbar_init(bars.desc_full + s, 1);
+      ptx::mbar_init(bars.desc_empty + s, kSoftmaxWarps + 1);  // softmax warps + MMA thread
+    }
+    for (int s = 0; s < kTileRecs; ++s) {
+      ptx::mbar_init(bars.rec_full + s, 1);
+      ptx::mbar_init(bars.rec_empty + s, kSoftmaxWarps);
+    }
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(bars.c_full + s, 1);
+      ptx::mbar_init(bars.c_empty + s, 1);
+    }
+    ptx::fence_barrier_init();
+  }
+  // Per-axis prefix bit tables over the COLUMN tile: pref[off_a + x] has bit j set iff the
+  // in-tile coordinate of column j along axis a is < x (columns ordered axis 0 fastest).
+  {
+    int off = 0;
+    for (int a = 0; a < p.ndim; ++a) {
+      int below = 1;
+      for (int b = 0; b < a; ++b) below *= p.Tc[b];
+      for (int x = threadIdx.x; x <= p.Tc[a]; x += kThreads) {
+        uint32_t wds[4];
+#pragma unroll
+        for (int wd = 0; wd < 4; ++wd) {
+          uint32_t bits = 0;
+#pragma unroll 1
+          for (int j = 0; j < 32; ++j) {
+            const int t = ((wd * 32 + j) / below) % p.Tc[a];
+            if (t < x) bits |= 1u << j;
+          }
+          wds[wd] = bits;
+        }
+        pref[off + x] = make_uint4(wds[0], wds[1], wds[2], wds[3]);
+      }
+      off += p.Tc[a] + 1;
+    }
+  }
+  if (warp == kMmaWarp) {
+    ptx::tmem_alloc(tmem_slot, kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  if (warp == kLoadWarp && lane == 0) {
+    ptx::prefetch_tensormap(&tm_r1);
+    ptx::prefetch_tensormap(&tm_r2);
+    ptx::prefetch_tensormap(&tm_c1);
+    ptx::prefetch_tensormap(&tm_c2);
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  constexpr uint32_t kSCol = 0, kDpCol = 128, kAcc0Col = 256, kAcc1Col = 384;
+
+  if (warp < kSoftmaxWarps) {
+    // ============ P / dS computation and the epilogue (two threads per row) ====================
+    const int part = warp >> 2;
+    const int row = ((warp & 3) << 5) | lane;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) << 5) << 16);
+    const uint32_t my_s = lane_addr + kSCol + part * 64;
+    const uint32_t my_dp = lane_addr + kDpCol + part * 64;
+    const float c = p.scale_log2;
+    constexpr float kLog2e = 1.4426950408889634f;
+    uint32_t ph_sdp = 0, ph_acc = 0, tseq = 0;
+    // in-tile coordinates of this thread's row, and of the column whose statistics it fetches
+    int tr[B200NA_MAX_DIM], tcol[B200NA_MAX_DIM];
+    {
+      int rl = row, cl = row;
+#pragma unroll
+      for (int a = 0; a < B200NA_MAX_DIM; ++a) {
+        tr[a] = (a < NDIM) ? rl % p.Tr[a] : 0;
+        rl /= (a < NDIM) ? p.Tr[a] : 1;
+        tcol[a] = (a < NDIM) ? cl % p.Tc[a] : 0;
+        cl /= (a < NDIM) ? p.Tc[a] : 1;
+      }
+    }
+    for (uint32_t seq = 0;; ++seq) {
+      const uint32_t dslot = seq % kDescSlots;
+      if (!__all_sync(0xffffffffu, wait_bar(bars.desc_full + dslot, (seq / kDescSlots) & 1,
+                                            abort_flag, p.status, (5 << 8) | kStDescFull)))
+        break;
+      const Item& it = *reinterpret_cast<const Item*>(desc_sm + dslot * kDescBytes);
+      const int n_tiles = it.n_tiles;
+      if (n_tiles < 0) break;
+      const int n_per_head = it.n_per_head;
+      // span of columns this thread's row interacts with, per axis; token index of the row
+      int lo_a[B200NA_MAX_DIM], hi_a[B200NA_MAX_DIM];
+      bool row_valid = true;
+      long long row_tok = it.b;
+#pragma unroll
+      for (int a = 0; a < B200NA_MAX_DIM; ++a) {
+        if (a < NDIM) {
+          const int i = it.r_lo[a] + tr[a];
+          row_valid = row_valid && i < it.L[a];
+          row_span<kKeyRows>(p, a, i, it.L[a], lo_a[a], hi_a[a]);
+          row_tok = row_tok * p.X[a] + (i * p.dil[a] + it.g[a]);
+        } else {
+          lo_a[a] = 0; hi_a[a] = 1;
+        }
+      }
+      // pass dQ: the statistics belong to this thread's row
+      float row_l = INFINITY, row_d = 0.f;
+      if (!kKeyRows && row_valid) {
+        row_l = p.lse[row_tok * p.Hq + it.h] * kLog2e;
+        row_d = p.delta[row_tok * p.Hq + it.h];
+      }
+      bool alive = true;
+      for (int iter = 0; iter < n_tiles; ++iter) {
+        if (!__all_sync(0xffffffffu,
+                        wait_bar(bars.rec_full + tseq % kTileRecs, (tseq / kTileRecs) & 1,
+                                 abort_flag, p.status, (5 << 8) | kStRecFull))) {
+          alive = false;
+          break;
+        }
+        const int4 rec = tile_rec[tseq % kTileRecs];  // x = code, y/z/w = first column coordinate
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(bars.rec_empty + tseq % kTileRecs);
+        ++tseq;
+        const bool interior = rec.x == kTileInterior;
+        const int base3[B200NA_MAX_DIM] = {rec.y, rec.z, rec.w};
+        // double-buffered by a count that runs across items, so that the buffer a thread fills
+        // is never one a slower thread may still be reading
+        float* stat = colstat + (tseq & 1) * 2 * kTile;
+        if (kKeyRows) {
+          // the statistics belong to the columns (queries): 128 threads fetch one column each
+          if (part == 0) {
+            const int hq = it.h * p.rep + iter / n_per_head;
+            bool ok = true;
+            long long tok = it.b;
+#pragma unroll
+            for (int a = 0; a < B200NA_MAX_DIM; ++a) {
+              if (a < NDIM) {
+                const int i = base3[a] + tcol[a];
+                ok = ok && i < it.L[a];
+                tok = tok * p.X[a] + (i * p.dil[a] + it.g[a]);
+              }
+            }
+            // a column past the extent gets LSE = +inf, i.e. P = 0
+            stat[row] = ok ? p.lse[tok * p.Hq + hq] * kLog2e : INFINITY;
+            stat[kTile + row] = ok ? p.delta[tok * p.Hq + hq] : 0.f;
+          }
+          named_bar_sync(1, kSoftmaxThreads);
+        }
+        uint32_t mw0 = ~0u, mw1 = ~0u;
+        if (!interior) {
+          uint4 mk = make_uint4(~0u, ~0u, ~0u, ~0u);
+          int off = 0;
+#pragma unroll
+          for (int a = 0; a < B200NA_MAX_DIM; ++a) {
+            if (a < NDIM) {
+              const int lo = imin(imax(lo_a[a] - base3[a], 0), p.Tc[a]);
+              const int hi = imin(imax(hi_a[a] - base3[a], 0), p.Tc[a]);
+              const uint4 ph = pref[off + hi];
+              const uint4 pl = pref[off + lo];
+              const bool none = hi <= lo;
+              mk.x &= none ? 0u : (ph.x & ~pl.x);
+              mk.y &= none ? 0u : (ph.y & ~pl.y);
+              mk.z &= none ? 0u : (ph.z & ~pl.z);
+              mk.w &= none ? 0u : (ph.w & ~pl.w);
+              off += p.Tc[a] + 1;
+            }
+          }
+          mw0 = part ? mk.z : mk.x;
+          mw1 = part ? mk.w : mk.y;
+        }
+        if (!__all_sync(0xffffffffu, wait_bar(bars.sdp_full, ph_sdp, abort_flag, p.status,
+                                              (5 << 8) | kStSdpFull))) {
+          alive = false;
+          break;
+        }
+        ph_sdp ^= 1;
+        ptx::tc_fence_after_sync();
+        // 32 columns at a time: p = 2^(s c - lse), ds = p (dp - delta); the packed results
+        // overwrite logit / dP columns this same thread has already consumed.
+#pragma unroll
+        for (int ch = 0; ch < 2; ++ch) {
+          uint32_t sr[32], dr[32];
+          ptx::tmem_ld32(my_s + ch * 32, sr);
+          ptx::tmem_ld32(my_dp + ch * 32, dr);
+          ptx::tmem_ld_wait();
+          const uint32_t mw = ch ? mw1 : mw0;
+          uint32_t pk[16], dk[16];
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            float l0 = row_l, l1 = row_l, d0 = row_d, d1 = row_d;
+            if (kKeyRows) {
+              const int col = part * 64 + ch * 32 + j;
+              const float2 lv = *reinterpret_cast<const float2*>(stat + col);
+              const float2 dv = *reinterpret_cast<const float2*>(stat + kTile + col);
+              l0 = lv.x; l1 = lv.y; d0 = dv.x; d1 = dv.y;
+            }
+            float p0 = ptx::ex2(fmaf(__uint_as_float(sr[j]), c, -l0));
+            float p1 = ptx::ex2(fmaf(__uint_as_float(sr[j + 1]), c, -l1));
+            if (!interior) {
+              p0 = ((mw >> j) & 1u) ? p0 : 0.f;
+              p1 = ((mw >> (j + 1)) & 1u) ? p1 : 0.f;
+            }
+            const float s0 = p0 * (__uint_as_float(dr[j]) - d0);
+            const float s1 = p1 * (__uint_as_float(dr[j + 1]) - d1);
+            pk[j >> 1] = pack2<kBf16>(p0, p1);
+            dk[j >> 1] = pack2<kBf16>(s0, s1);
+          }
+          if (kKeyRows) ptx::tmem_st16(my_s + ch * 16, pk);
+          ptx::tmem_st16(my_dp + ch * 16, dk);
+        }
+        ptx::tmem_st_wait();
+        ptx::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(bars.ds_full);
+      }
+      if (!alive) break;
+      // ---- epilogue: accumulators -> gradient rows ----
+      if (!__all_sync(0xffffffffu, wait_bar(bars.acc_full, ph_acc, abort_flag, p.status,
+                                            (5 << 8) | kStAccFull)))
+        break;
+      ph_acc ^= 1;
+      ptx::tc_fence_after_sync();
+      const long long out_row = row_tok * p.row_heads + it.h;
+#pragma unroll
+      for (int acc = 0; acc < (kKeyRows ? 2 : 1); ++acc) {
+        T* orow = reinterpret_cast<T*>(acc ? p.out1 : p.out0) + out_row * D + part * (D / 2);
+        const float mul = acc ? 1.f : p.scale;
+        const uint32_t src = lane_addr + (acc ? kAcc1Col : kAcc0Col) + part * (D / 2);
+#pragma unroll
+        for (int ch = 0; ch < D / 64; ++ch) {
+          uint32_t orr[32];
+          ptx::tmem_ld32(src + ch * 32, orr);
+          ptx::tmem_ld_wait();
+          if (row_valid) {
+#pragma unroll
+            for (int v4 = 0; v4 < 4; ++v4) {
+              uint4 o;
+              o.x = pack2<kBf16>(__uint_as_float(orr[v4 * 8 + 0]) * mul, __uint_as_float(orr[v4 * 8 + 1]) * mul);
+              o.y = pack2<kBf16>(__uint_as_float(orr[v4 * 8 + 2]) * mul, __uint_as_float(orr[v4 * 8 + 3]) * mul);
+              o.z = pack2<kBf16>(__uint_as_float(orr[v4 * 8 + 4]) * mul, __uint_as_float(orr[v4 * 8 + 5]) * mul);
+              o.w = pack2<kBf16>(__uint_as_float(orr[v4 * 8 + 6]) * mul, __uint_as_float(orr[v4 * 8 + 7]) * mul);
+              *reinterpret_cast<uint4*>(orow + ch * 32 + v4 * 8) = o;
+            }
+          }
+        }
+      }
+      ptx::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        ptx::mbar_arrive(bars.acc_empty);
+        ptx::mbar_arrive(bars.desc_empty + dslot);
+      }
+    }
+  } else if (warp == kMmaWarp) {
+    // =============================== MMA issue ==============================================
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = ptx::make_idesc(kBf16 ? 1 : 0, 0, 0, kTile, kTile);
+      constexpr uint32_t idesc_acc = ptx::make_idesc(kBf16 ? 1 : 0, 0, 1, kTile, D);
+      constexpr uint32_t desc_hi = ptx::smem_desc_hi_sw128();
+      const uint32_t row_base = ptx::smem_u32(row_sm);
+      const uint32_t col_base = ptx::smem_u32(col_sm);
+      const uint32_t r1_lo = ptx::smem_desc_lo(row_base, 16);
+      const uint32_t r2_lo = ptx::smem_desc_lo(row_base + kTileBytes, 16);
+      const uint32_t s_tm = tmem_base + kSCol, dp_tm = tmem_base + kDpCol;
+      const uint32_t acc0_tm = tmem_base + kAcc0Col, acc1_tm = tmem_base + kAcc1Col;
+      uint32_t ph_r = 0, ph_ds = 0, ph_ae = 1, slot = 0, ph_c = 0;
+      bool alive = true;
+      for (uint32_t seq = 0; alive; ++seq) {
+        const uint32_t dslot = seq % kDescSlots;
+        if (!wait_bar(bars.desc_full + dslot, (seq / kDescSlots) & 1, abort_flag, p.status,
+                      (6 << 8) | kStDescFull)) break;
+        const int n = reinterpret_cast<const Item*>(desc_sm + dslot * kDescBytes)->n_tiles;
+        ptx::mbar_arrive(bars.desc_empty + dslot);
+        if (n < 0) break;
+        if (!wait_bar(bars.r_full, ph_r, abort_flag, p.status, (6 << 8) | kStRFull)) break;
+        ph_r ^= 1;
+        for (int t = 0; t < n; ++t) {
+          if (!wait_bar(bars.c_full + slot, ph_c, abort_flag, p.status, (6 << 8) | kStCFull)) {
+            alive = false; break;
+          }
+          const uint32_t c1 = col_base + slot * 2 * kTileBytes, c2 = c1 + kTileBytes;
+          ptx::tc_fence_after_sync();
+          {
+            // S = R1 C1^T and dP = R2 C2^T: both operands K-major, contraction over the head dim
+            const uint32_t b1 = ptx::smem_desc_lo(c1, 16), b2 = ptx::smem_desc_lo(c2, 16);
+#pragma unroll
+            for (int kb = 0; kb < D / 16; ++kb) {
+              const uint32_t koff = ((kb >> 2) * kBlockBytes + (kb & 3) * 32) >> 4;
+              ptx::mma_ss_lohi(s_tm, r1_lo + koff, desc_hi, b1 + koff, desc_hi, idesc_s,
+                               kb > 0 ? 1u : 0u);
+            }
+#pragma unroll
+            for (int kb = 0; kb < D / 16; ++kb) {
+              const uint32_t koff = ((kb >> 2) * kBlockBytes + (kb & 3) * 32) >> 4;
+              ptx::mma_ss_lohi(dp_tm, r2_lo + koff, desc_hi, b2 + koff, desc_hi, idesc_s,
+                               kb > 0 ? 1u : 0u);
+            }
+          }
+          ptx::tc_commit(bars.sdp_full);
+          // the row tiles are read by these products only: after the item's last pair they may
+          // be replaced by the next item's
+          if (t == n - 1) ptx::tc_commit(bars.r_empty);
+          if (!wait_bar(bars.ds_full, ph_ds, abort_flag, p.status, (6 << 8) | kStDsFull)) {
+            alive = false; break;
+          }
+          ph_ds ^= 1;
+          if (t == 0) {
+            // the previous item's epilogue must have drained the accumulators
+            if (!wait_bar(bars.acc_empty, ph_ae, abort_flag, p.status, (6 << 8) | kStAccEmpty)) {
+              alive = false; break;
+            }
+            ph_ae ^= 1;
+          }
+          ptx::tc_fence_after_sync();
+          {
+            // acc0 += dS C1 (and acc1 += P C2): A from TMEM (16-bit values packed over the fp32
+            // columns their owner thread consumed), B = the column tile read MN-major,
+            // contraction over the 128 columns
+            const uint32_t b1 = ptx::smem_desc_lo(c1, kBlockBytes);
+            const uint32_t b2 = ptx::smem_desc_lo(c2, kBlockBytes);
+#pragma unroll
+            for (int ks = 0; ks < kTile / 16; ++ks)
+              ptx::mma_ts_lohi(acc0_tm, dp_tm + (ks >> 2) * 64 + (ks & 3) * 8, b1 + ks * (2048 >> 4),
+                               desc_hi, idesc_acc, (t == 0 && ks == 0) ? 0u : 1u);
+            if (kKeyRows) {
+#pragma unroll
+              for (int ks = 0; ks < kTile / 16; ++ks)
+                ptx::mma_ts_lohi(acc1_tm, s_tm + (ks >> 2) * 64 + (ks & 3) * 8,
+                                 b2 + ks * (2048 >> 4), desc_hi, idesc_acc,
+                                 (t == 0 && ks == 0) ? 0u : 1u);
+            }
+          }
+          ptx::tc_commit(bars.c_empty + slot);
+          if (t == n - 1) ptx::tc_commit(bars.acc_full);
+          if (++slot == kStages) {
+            slot = 0;
+            ph_c ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == kLoadWarp) {
+    // ============ TMA loads, work-item decode, tile classification ==========================
+    if (lane == 0) {
+      uint32_t ph_re = 1, slot = 0, ph_ce = 1, published = 0, tseq = 0;
+      bool alive = true;
+      WorkCursor cur;
+      cur.init(p, blockIdx.x);
+      auto publish_next = [&]() -> const Item* {
+        const uint32_t ds = published % kDescSlots;
+        if (!wait_bar(bars.desc_empty + ds, ((published / kDescSlots) & 1) ^ 1, abort_flag,
+                      p.status, (7 << 8) | kStDescEmpty)) {
+          alive = false;
+          return nullptr;
+        }
+        Item* out = reinterpret_cast<Item*>(desc_sm + ds * kDescBytes);
+        bool found = false;
+        while (cur.w < p.total_work) {
+          decode_item<NDIM, kKeyRows>(p, cur, *out);
+          cur.advance(p, (int)gridDim.x);
+          if (!out->skip) { found = true; break; }
+        }
+        if (!found) out->n_tiles = -1;
+        ptx::mbar_arrive(bars.desc_full + ds);
+        ++published;
+        return out;
+      };
+      const Item* itp = publish_next();
+      while (alive && itp != nullptr && itp->n_tiles >= 0) {
+        const Item& it = *itp;
+        const int n_tiles = it.n_tiles, n_per_head = it.n_per_head, b = it.b;
+        const int g0 = it.g[0], g1 = it.g[1], g2 = it.g[2];
+        // the stationary row tiles: R1, R2 of head it.h
+        if (!wait_bar(bars.r_empty, ph_re, abort_flag, p.status, (7 << 8) | kStREmpty)) break;
+        ph_re ^= 1;
+        ptx::mbar_arrive_expect_tx(bars.r_full, 2 * kTileBytes);
+        {
+          const int x0 = it.r_lo[0] * p.dil[0] + g0, x1 = it.r_lo[1] * p.dil[1] + g1,
+                    x2 = it.r_lo[2] * p.dil[2] + g2;
+          for (int db = 0; db < kDBlocks; ++db) {
+            ptx::tma_load_5d(row_sm + db * kBlockBytes, &tm_r1, bars.r_full, it.h * D + db * 64,
+                             x0, x1, x2, b);
+            ptx::tma_load_5d(row_sm + kTileBytes + db * kBlockBytes, &tm_r2, bars.r_full,
+                             it.h * D + db * 64, x0, x1, x2, b);
+          }
+        }
+        TileWalk tw;
+        tw.load(it);
+        int tc[B200NA_MAX_DIM] = {tw.t0[0], tw.t0[1], tw.t0[2]};
+        // head of the column tiles: the kv head of a query head, or the query heads of a kv head
+        int col_head = kKeyRows ? it.h * p.rep : it.h / p.rep;
+        int in_head = 0;
+        const Item* next = nullptr;
+        const int publish_at = imin(kStages - 1, n_tiles - 1);
+        for (int iter = 0; iter < n_tiles && alive; ++iter) {
+          const int k0 = tc[0] * p.Tc[0], k1 = NDIM > 1 ? tc[1] * p.Tc[1] : 0,
+                    k2 = NDIM > 2 ? tc[2] * p.Tc[2] : 0;
+          const int4 rec = make_int4(tw.template interior<NDIM>(tc) ? kTileInterior : kTileBoundary,
+                                     k0, k1, k2);
+          const int x0 = k0 * p.dil[0] + g0, x1 = k1 * p.dil[1] + g1, x2 = k2 * p.dil[2] + g2;
+          tw.template next<NDIM>(tc);
+          if (!wait_bar(bars.rec_empty + tseq % kTileRecs, ((tseq / kTileRecs) & 1) ^ 1, abort_flag,
+                        p.status, (7 << 8) | kStRecEmpty)) { alive = false; break; }
+          tile_rec[tseq % kTileRecs] = rec;
+          ptx::mbar_arrive(bars.rec_full + tseq % kTileRecs);
+          ++tseq;
+          if (!wait_bar(bars.c_empty + slot, ph_ce, abort_flag, p.status, (7 << 8) | kStCEmpty)) {
+            alive = false; break;
+          }
+          ptx::mbar_arrive_expect_tx(bars.c_full + slot, 2 * kTileBytes);
+          uint8_t* dst = col_sm + slot * 2 * kTileBytes;
+          for (int db = 0; db < kDBlocks; ++db) {
+            ptx::tma_load_5d(dst + db * kBlockBytes, &tm_c1, bars.c_full + slot,
+                             col_head * D + db * 64, x0, x1, x2, b);
+            ptx::tma_load_5d(dst + kTileBytes + db * kBlockBytes, &tm_c2, bars.c_full + slot,
+                             col_head * D + db * 64, x0, x1, x2, b);
+          }
+          if (++slot == kStages) {
+            slot = 0;
+            ph_ce ^= 1;
+          }
+          if (kKeyRows && ++in_head == n_per_head) {  // next query head of the group
+            in_head = 0;
+            ++col_head;
+          }
+          if (alive && iter == publish_at) next = publish_next();
+        }
+        itp = next;
+      }
+    }
+  }
+
+  // ---- teardown ----------------------------------------------------------------------------
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    // draining after an expired wait: let loads in flight land before shared memory is released
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000ll) {
+    }
+    __syncthreads();
+  }
+  if (warp == kMmaWarp) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---- host side -------------------------------------------------------------------------------
+
+template <int D, bool kBf16, bool kKeyRows>
+const void* bwd_kernel_for_ndim(int ndim) {
+  if (ndim == 1) return (const void*)fna_bwd_kernel<D, kBf16, 1, kKeyRows>;
+  if (ndim == 2) return (const void*)fna_bwd_kernel<D, kBf16, 2, kKeyRows>;
+  return (const void*)fna_bwd_kernel<D, kBf16, 3, kKeyRows>;
+}
+const void* bwd_kernel_variant(int D, bool bf16, int ndim, bool key_rows) {
+  if (D == 128) {
+    if (bf16) return key_rows ? bwd_kernel_for_ndim<128, true, true>(ndim)
+                              : bwd_kernel_for_ndim<128, true, false>(ndim);
+    return key_rows ? bwd_kernel_for_ndim<128, false, true>(ndim)
+                    : bwd_kernel_for_ndim<128, false, false>(ndim);
+  }
+  if (bf16) return key_rows ? bwd_kernel_for_ndim<64, true, true>(ndim)
+                            : bwd_kernel_for_ndim<64, true, false>(ndim);
+  return key_rows ? bwd_kernel_for_ndim<64, false, true>(ndim)
+                  : bwd_kernel_for_ndim<64, false, false>(ndim);
+}
+
+// Opt-in shared memory per kernel variant and device, set once.
+int ensure_smem_attribute(const void* fn, int D) {
+  static std::mutex mu;
+  static const void* done[64][24];
+  int dev = 0;
+  B200NA_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return B200NA_ERR_DEVICE;
+  std::lock_guard<std::mutex> lk(mu);
+  for (int i = 0; i < 24; ++i) {
+    if (done[dev][i] == fn) return B200NA_OK;
+    if (done[dev][i] == nullptr) {
+      B200NA_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           D == 128 ? Smem<128>::kBytes : Smem<64>::kBytes));
+      done[dev][i] = fn;
+      return B200NA_OK;
+    }
+  }
+  return B200NA_ERR_UNSUPPORTED;
+}
+
+}  // namespace
+}  // namespace b200na
+
+extern "C" B200NA_API int b200na_na_backward_direct(
+    const void* q, const void* k, const void* v, const void* o, const void* d_out, const float* lse,
+    void* dq, void* dk, void* dv, float* delta_scratch, int ndim, const int* shape,
+    const int* kernel, const int* stride, const int* dilation, const int* causal,
+    const int* q_tile, const int* kv_tile, int B, int Hq, int Hkv, int D, int dtype, float scale,
+    b200na_stream_t stream_) {
+  using namespace b200na;
+  if (!q || !k || !v || !o || !d_out || !lse || !dq || !dk || !dv || !delta_scratch || !shape ||
+      !kernel || !q_tile || !kv_tile)
+    return B200NA_ERR_INVALID_ARGUMENT;
+  if (B < 1 || Hq < 1 || Hkv < 1 || Hq % Hkv != 0) return B200NA_ERR_INVALID_ARGUMENT;
+  if (dtype != B200NA_F16 && dtype != B200NA_BF16) return B200NA_ERR_UNSUPPORTED;
+  if (D != 64 && D != 128) return B200NA_ERR_UNSUPPORTED;
+  if (!(scale > 0.f)) return B200NA_ERR_INVALID_ARGUMENT;
+  const uintptr_t al = reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) |
+                       reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(d_out) |
+                       reinterpret_cast<uintptr_t>(dq) | reinterpret_cast<uintptr_t>(dk) |
+                       reinterpret_cast<uintptr_t>(dv);
+  if (al % 16 != 0) return B200NA_ERR_ALIGNMENT;
+  NaAxes ax;
+  int rc = fill_axes(ax, ndim, shape, kernel, stride, dilation, causal);
+  if (rc != B200NA_OK) return rc;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  int sms = 0;
+  int* status_ptr = nullptr;
+  if ((rc = fna_device_info(&sms, &status_ptr)) != B200NA_OK) return rc;
+
+  BwdTcParams base;
+  memset(&base, 0, sizeof(base));
+  base.ndim = ndim;
+  base.G = 1;
+  int tq[B200NA_MAX_DIM], tkv[B200NA_MAX_DIM];
+  long long tokens = 1, nq = 1, nkv = 1;
+  for (int a = 0; a < B200NA_MAX_DIM; ++a) {
+    const bool on = a < ndim;
+    base.X[a] = ax.shape[a]; base.kernel[a] = ax.kernel[a]; base.stride[a] = ax.stride[a];
+    base.dil[a] = ax.dilation[a]; base.causal[a] = ax.causal[a];
+    tq[a] = on ? q_tile[a] : 1;
+    tkv[a] = on ? kv_tile[a] : 1;
+    if (tq[a] < 1 || tkv[a] < 1) return B200NA_ERR_INVALID_ARGUMENT;
+    base.G *= base.dil[a];
+    tokens *= base.X[a];
+    nq *= tq[a];
+    nkv *= tkv[a];
+  }
+  if (nq != kTile || nkv != kTile) return B200NA_ERR_INVALID_ARGUMENT;
+  if (tokens * B > 0x7fffffffLL || (long long)Hq * D > 0x7fffffffLL) return B200NA_ERR_UNSUPPORTED;
+  base.B = B; base.Hq = Hq; base.Hkv = Hkv; base.rep = Hq / Hkv;
+  base.scale = scale;
+  base.scale_log2 = scale * 1.4426950408889634f;
+  base.lse = lse;
+  base.delta = delta_scratch;
+  base.status = status_ptr;
+
+  CUtensorMap mq, mdo, mk, mv;
+  if ((rc = fna_make_tensor_map_direct(&mq, q, dtype, B, base.X, Hq, D, tq, base.dil)) != B200NA_OK) return rc;
+  if ((rc = fna_make_tensor_map_direct(&mdo, d_out, dtype, B, base.X, Hq, D, tq, base.dil)) != B200NA_OK) return rc;
+  if ((rc = fna_make_tensor_map_direct(&mk, k, dtype, B, base.X, Hkv, D, tkv, base.dil)) != B200NA_OK) return rc;
+  if ((rc = fna_make_tensor_map_direct(&mv, v, dtype, B, base.X, Hkv, D, tkv, base.dil)) != B200NA_OK) return rc;
+
+  if ((rc = launch_delta(o, d_out, delta_scratch, tokens * B * Hq, D, dtype, stream)) != B200NA_OK)
+    return rc;
+
+  for (int pass = 0; pass < 2; ++pass) {
+    const bool key_rows = pass == 1;
+    BwdTcParams p = base;
+    long long n_rtiles = 1;
+    for (int a = 0; a < B200NA_MAX_DIM; ++a) {
+      p.Tr[a] = key_rows ? tkv[a] : tq[a];
+      p.Tc[a] = key_rows ? tq[a] : tkv[a];
+      const int need = (p.X[a] + p.dil[a] - 1) / p.dil[a];  // largest dilation group
+      p.Rr[a] = (need + p.Tr[a] - 1) / p.Tr[a];
+      n_rtiles *= p.Rr[a];
+    }
+    if (n_rtiles > 0x7fffffffLL) return B200NA_ERR_UNSUPPORTED;
+    p.n_rtiles = (int)n_rtiles;
+    p.row_heads = key_rows ? Hkv : Hq;
+    p.total_work = n_rtiles * p.row_heads * B * p.G;
+    p.out0 = key_rows ? dk : dq;
+    p.out1 = key_rows ? dv : nullptr;
+    const void* fn = bwd_kernel_variant(D, dtype == B200NA_BF16, ndim, key_rows);
+    if ((rc = ensure_smem_attribute(fn, D)) != B200NA_OK) return rc;
+    const int grid = (int)(p.total_work < sms ? p.total_work : sms);
+    // pass dQ: rows Q, dO and columns K, V; pass dKdV: rows K, V and columns Q, dO
+    void* args_q[] = {(void*)&mq, (void*)&mdo, (void*)&mk, (void*)&mv, (void*)&p};
+    void* args_k[] = {(void*)&mk, (void*)&mv, (void*)&mq, (void*)&mdo, (void*)&p};
+    B200NA_CUDA_TRY(cudaLaunchKernel(fn, dim3(grid), dim3(kThreads), key_rows ? args_k : args_q,
+                                     D == 128 ? Smem<128>::kBytes : Smem<64>::kBytes, stream));
+  }
+  return B200NA_OK;
+}

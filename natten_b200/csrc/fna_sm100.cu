@@ -24,6 +24,7 @@
 #include <type_traits>
 
 #include "common.cuh"
+#include "fna_host.cuh"
 #include "ptx.cuh"
 
 namespace b200na {
@@ -1193,6 +1194,21 @@ int launch_fna(const void* q, const void* k, const void* v, FnaParams& p, int D,
 }
 
 }  // namespace
+}  // namespace b200na
+
+namespace b200na {
+int fna_make_tensor_map_direct(CUtensorMap* tm, const void* ptr, int dtype, int B, const int* X,
+                               int H, int D, const int* tile, const int* dil) {
+  return make_tensor_map_direct(tm, ptr, dtype, B, X, H, D, tile, dil);
+}
+int fna_device_info(int* sms, int** status_ptr) {
+  DeviceState* st = nullptr;
+  const int rc = device_state(&st);
+  if (rc != B200NA_OK) return rc;
+  *sms = st->sms;
+  *status_ptr = st->status_ptr;
+  return B200NA_OK;
+}
 }  // namespace b200na
 
 namespace b200na {

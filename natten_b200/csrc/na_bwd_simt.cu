@@ -20,6 +20,7 @@
 #include <math.h>
 
 #include "common.cuh"
+#include "fna_host.cuh"
 
 namespace b200na {
 namespace {
@@ -356,6 +357,28 @@ int launch_bwd(const void* q, const void* k, const void* v, const void* o, const
 }
 
 }  // namespace
+}  // namespace b200na
+
+namespace b200na {
+int launch_delta(const void* o, const void* d_out, float* delta, int64_t rows, int D, int dtype,
+                 cudaStream_t stream) {
+  int blocks = 0;
+  const int rc = grid_for(rows, &blocks);
+  if (rc != B200NA_OK) return rc;
+  if (dtype == B200NA_F32)
+    delta_kernel<float><<<blocks, kWarps * 32, 0, stream>>>((const float*)o, (const float*)d_out,
+                                                            delta, rows, D);
+  else if (dtype == B200NA_F16)
+    delta_kernel<__half><<<blocks, kWarps * 32, 0, stream>>>((const __half*)o, (const __half*)d_out,
+                                                             delta, rows, D);
+  else if (dtype == B200NA_BF16)
+    delta_kernel<__nv_bfloat16><<<blocks, kWarps * 32, 0, stream>>>(
+        (const __nv_bfloat16*)o, (const __nv_bfloat16*)d_out, delta, rows, D);
+  else
+    return B200NA_ERR_INVALID_ARGUMENT;
+  B200NA_CUDA_TRY(cudaGetLastError());
+  return B200NA_OK;
+}
 }  // namespace b200na
 
 extern "C" B200NA_API int b200na_na_backward_simt(

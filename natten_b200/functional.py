@@ -419,11 +419,80 @@ def _na_backward(ctx, d_out, d_lse):
     ignored, as in the reference's backward (src/natten/backends/blackwell_fna.py:185-318)."""
     query, key, value, out, lse = ctx.saved_tensors[:5]
     ak, av = ctx.saved_tensors[5:] if ctx.has_extra else (None, None)
+    kernel_size, stride, dilation, is_causal, scale = ctx.na_args
+    na_dim = query.dim() - 3
+    tensor_core = (not ctx.has_extra and query.dtype in (torch.float16, torch.bfloat16)
+                   and query.shape[-1] in TENSOR_CORE_HEAD_DIMS
+                   and not BACKWARD_ON_CUDA_CORES)
+    if tensor_core:
+        q_tile, kv_tile = choose_backward_tile_shapes(
+            tuple(int(x) for x in query.shape[1:1 + na_dim]), kernel_size, stride, dilation,
+            is_causal)
+        tensor_core = backward_layout_supported(q_tile, kv_tile, dilation)
+    if tensor_core:
+        dq, dk, dv = ops.na_backward_direct(query, key, value, out, d_out.contiguous(), lse,
+                                            kernel_size, stride, dilation, is_causal, scale,
+                                            list(q_tile), list(kv_tile))
+        return (dq, dk, dv, None, None) + (None,) * 8
+    # fp32 operands, other head dims, extra tokens, boxes a tensor map cannot express
     dq, dk, dv, dak, dav = ops.na_backward_simt(query, key, value, out, d_out.contiguous(), lse,
-                                                ak, av, *ctx.na_args)
+                                                ak, av, kernel_size, stride, dilation, is_causal,
+                                                scale)
     if not ctx.has_extra:
         dak = dav = None
     return (dq, dk, dv, dak, dav) + (None,) * 8
+
+
+BACKWARD_TILE_SIZE = 128
+# set True to force the CUDA-core gradient kernels (used by the tests to compare the two)
+BACKWARD_ON_CUDA_CORES = False
+
+
+def backward_layout_supported(q_tile_shape: DimensionType, kv_tile_shape: DimensionType,
+                              dilation: DimensionType) -> bool:
+    """Whether the tensor-core backward can address the caller's layout with these 128-token tiles
+    (a tile of one dilation group must fit a tensor-map box)."""
+    return all(d <= MAX_TMA_ELEMENT_STRIDE and tq * d <= MAX_TMA_BOX and tkv * d <= MAX_TMA_BOX
+               for tq, tkv, d in zip(q_tile_shape, kv_tile_shape, dilation))
+
+
+def choose_backward_tile_shapes(shape: DimensionType, kernel_size: DimensionType,
+                                stride: DimensionType, dilation: DimensionType,
+                                is_causal: CausalArgType) -> Tuple[DimensionType, DimensionType]:
+    """(q_tile_shape, kv_tile_shape), 128 tokens each, for the backward kernels: the pair that
+    minimises the key/value tiles visited per query tile (the mirrored pass visits the same
+    (query tile, key/value tile) pairs from the other side)."""
+    return _choose_backward_tile_shapes(
+        tuple(int(x) for x in shape), tuple(int(x) for x in kernel_size),
+        tuple(int(x) for x in stride), tuple(int(x) for x in dilation),
+        tuple(bool(x) for x in is_causal))
+
+
+@functools.lru_cache(maxsize=256)
+def _choose_backward_tile_shapes(shape, kernel_size, stride, dilation, is_causal):
+    n = len(shape)
+    if n == 1:
+        return (BACKWARD_TILE_SIZE,), (BACKWARD_TILE_SIZE,)
+    cost: Dict[Tuple[int, int, int], int] = {}
+    for a in range(n):
+        for eq in range(8):
+            for ek in range(8):
+                cost[(a, 1 << eq, 1 << ek)] = _axis_tile_cost(
+                    shape[a], kernel_size[a], stride[a], dilation[a], is_causal[a], 1 << eq, 1 << ek)
+    best = None
+    for tq in _pow2_compositions(7, n):
+        for tkv in _pow2_compositions(7, n):
+            if not backward_layout_supported(tq, tkv, dilation):
+                continue
+            c = 1
+            for a in range(n):
+                c *= cost[(a, tq[a], tkv[a])]
+            key = (c, -tq[-1], -tkv[-1])
+            if best is None or key < best[0]:
+                best = (key, tq, tkv)
+    if best is None:  # no 128-token box fits: the caller falls back to the CUDA-core kernels
+        return (BACKWARD_TILE_SIZE,) + (1,) * (n - 1), (BACKWARD_TILE_SIZE,) + (1,) * (n - 1)
+    return best[1], best[2]
 
 
 if ops.USE_TORCH_OPS:

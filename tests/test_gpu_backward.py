@@ -14,7 +14,7 @@ from golden_io import na_cases
 
 pytestmark = pytest.mark.gpu
 
-CASES = ["na1d_300_k33", "na1d_257_k9_s3_d4_causal", "na2d_33x30_k3x5_s1x2_d3x2_causal01",
+CASES = ["c2s_na1d_1024_k128_causal", "na1d_300_k33", "na1d_257_k9_s3_d4_causal", "na2d_33x30_k3x5_s1x2_d3x2_causal01",
          "na2d_16x16_k5_gqa", "c3s_na2d_32x32_k13_d2", "c4s_na2d_32x32_k8_s4_extra24",
          "c5s_na3d_8x12x20_k4x6x6_s1x2x2_causalT", "na3d_6x9x11_k3x3x5_s1x1x2_d2x1x1_causalW",
          "na1d_96_k17_causal_extra7", "na2d_8x8_k8_selfattn"]
@@ -63,3 +63,42 @@ def test_layer_trains():
     assert L.device_status() == 0
     for p in list(layer.parameters()) + [x]:
         assert p.grad is not None and torch.isfinite(p.grad).all() and p.grad.abs().max() > 0
+
+
+@pytest.mark.parametrize("shape,ks,st,di,ca,hq,hkv,D", [
+    ((700,), (65,), (3,), (1,), (True,), 2, 2, 128),
+    ((1000,), (33,), (1,), (2,), (False,), 4, 2, 64),            # dilation groups, GQA
+    ((40, 44), (7, 9), (1, 2), (2, 3), (False, True), 2, 1, 128),
+    ((64, 64), (16, 16), (8, 8), (1, 1), (False, False), 1, 1, 128),   # block-sparse windows
+    ((37, 51), (5, 5), (1, 1), (4, 8), (False, False), 2, 2, 64),
+    ((6, 20, 24), (3, 5, 8), (1, 1, 4), (1, 2, 1), (True, False, False), 2, 2, 128),
+    ((9, 11, 13), (3, 3, 3), (1, 1, 1), (3, 2, 4), (False, True, False), 4, 2, 64),
+])
+def test_tensor_core_backward_against_oracle_and_cuda_core_kernels(shape, ks, st, di, ca, hq, hkv, D):
+    """The tcgen05 backward (two passes of one kernel) against the oracle, and against the
+    CUDA-core gradient kernels on the same inputs (independent implementations)."""
+    import natten_b200.functional as F
+    torch.manual_seed(23)
+    fn = {1: nb.na1d, 2: nb.na2d, 3: nb.na3d}[len(shape)]
+    q = torch.randn(2, *shape, hq, D).bfloat16()
+    k, v = (torch.randn(2, *shape, hkv, D).bfloat16() for _ in range(2))
+    d_out = torch.randn(2, *shape, hq, D).bfloat16()
+    assert F.backward_layout_supported(*F.choose_backward_tile_shapes(shape, ks, st, di, ca), di)
+    grads = {}
+    for mode in (False, True):
+        F.BACKWARD_ON_CUDA_CORES = mode
+        try:
+            leaves = [t.cuda().requires_grad_() for t in (q, k, v)]
+            out = fn(*leaves, kernel_size=ks, stride=st, dilation=di, is_causal=ca)
+            out.backward(d_out.cuda())
+            assert L.device_status() == 0
+            grads[mode] = [t.grad.float().cpu().numpy() for t in leaves]
+        finally:
+            F.BACKWARD_ON_CUDA_CORES = False
+    want = oracle.na_backward(q.float().numpy(), k.float().numpy(), v.float().numpy(),
+                              d_out.float().numpy(), ks, st, di, ca)
+    for tc, cc, w in zip(grads[False], grads[True], want):
+        tol = 2e-2 * max(1.0, np.abs(w).max())
+        assert np.isfinite(tc).all()
+        assert np.abs(tc - w).max() <= tol
+        assert np.abs(cc - w).max() <= tol
