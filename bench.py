@@ -259,6 +259,9 @@ def main():
                          "(batch 1); the printed line is then NOT a benchmark value")
     ap.add_argument("--eager", action="store_true",
                     help="time eager operator calls instead of CUDA-graph replays of one call")
+    ap.add_argument("--pass", dest="pass_", default="forward", choices=["forward", "backward"],
+                    help="backward: time the gradient kernels (delta + dQ pass + dK/dV pass) "
+                         "instead of the forward call; an extra, not the BASELINE metric")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -315,6 +318,12 @@ def main():
     dq, dk, dv = (t.to(dev, non_blocking=True) for t in host)
     dak, dav = (t.to(dev, non_blocking=True) for t in extra) if n_extra else (None, None)
     torch.cuda.synchronize()
+
+    if args.pass_ == "backward":
+        run_backward(args, cfg, nb, L, dq, dk, dv, dak, dav, b_local, h_local, rank, world, barrier)
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     # ---- device-resident timing (inputs already in HBM; operands far exceed the 126 MB L2) ----
     for _ in range(args.warmup):
@@ -473,6 +482,78 @@ def main():
         info, _, _ = cpu_baseline(cfg)
         line["cpu_baseline"] = info
     print(json.dumps(line), flush=True)
+
+
+def run_backward(args, cfg, nb, L, q, k, v, ak, av, b_local, h_local, rank, world, barrier):
+    """Times the backward (delta + dQ pass + dK/dV pass, or the CUDA-core kernels when the config
+    has extra tokens) on device-resident operands and prints one JSON line of the same shape as
+    the forward's, without the end-to-end and CPU legs."""
+    import torch
+    import torch.distributed as dist
+    import natten_b200.functional as F
+    from natten_b200 import ops
+    op, dt, B, H, shape, D, ks, st, di, ca, n_extra, _ = cfg
+    fn = getattr(nb, op)
+    out, lse = fn(q, k, v, kernel_size=ks, stride=st, dilation=di, is_causal=ca,
+                  additional_keys=ak, additional_values=av, return_lse=True)
+    torch.manual_seed(77 + rank)
+    d_out = torch.randn(out.shape, device=out.device).to(out.dtype)
+    causal = [bool(c) for c in ca]
+    q_tile, kv_tile = F.choose_backward_tile_shapes(shape, ks, st, di, ca)
+    tensor_core = not n_extra and F.backward_layout_supported(q_tile, kv_tile, di)
+
+    def step():
+        if tensor_core:
+            return ops.na_backward_direct(q, k, v, out, d_out, lse, list(ks), list(st), list(di),
+                                          causal, D ** -0.5, list(q_tile), list(kv_tile))
+        return ops.na_backward_simt(q, k, v, out, d_out, lse, ak, av, list(ks), list(st), list(di),
+                                    causal, D ** -0.5)
+
+    for _ in range(max(1, args.warmup)):
+        step()
+    barrier()
+    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
+    if rank == 0:
+        sampler.start()
+    L.launches = 0
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    launches = L.launches
+    clocks = sampler.stop() if rank == 0 else None
+    status = L.device_status()
+    t = torch.tensor([e0.elapsed_time(e1), float(status)], device=q.device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total, status_max = (float(x) for x in t.tolist())
+    if rank != 0:
+        return
+    if status_max != 0:
+        raise SystemExit(f"device status word {int(status_max)}: a bounded wait expired in the kernel")
+    peaks = read_peaks()
+    flops = 2.5 * algorithmic_flops(cfg)       # 5 products in the backward for 2 in the forward
+    ms_step = ms_total / args.steps
+    value = flops / (ms_step * 1e-3) / 1e12
+    print(json.dumps(dict(
+        metric="FNA bwd effective TFLOPS (unmasked FLOPs, 2.5 x forward)", value=value,
+        unit="TFLOP/s", n_gpus=world, steps=args.steps, warmup=args.warmup, ms_per_step=ms_step,
+        higher_is_better=True, scaling="strong", vs_baseline=None, dtype=dt, data="synthetic",
+        config=dict(workload=WORKLOAD_TEXT[args.config] + " [backward pass]" + (
+            f" [REDUCED to {args.units} (batch x head) units for profiling: not a benchmark value]"
+            if args.units else ""),
+                    partition="batch x heads, no collective", units_per_gpu=b_local * h_local,
+                    launch="eager", l2="inputs larger than L2 (no flush needed)",
+                    kernels=("delta_kernel + fna_bwd_kernel (dQ pass) + fna_bwd_kernel (dK/dV pass)"
+                             if tensor_core else "CUDA-core gradient kernels"),
+                    q_tile=list(q_tile), kv_tile=list(kv_tile)),
+        clocks=clocks, gpu_launches=int(launches),
+        roofline=dict(bound="tensor", achieved=value / world, peak=peaks["bf16_tflops"],
+                      unit="TFLOP/s", frac=value / world / peaks["bf16_tflops"], traffic=None,
+                      kernel="fna_bwd_kernel", kernel_ms=ms_step,
+                      peak_source=peaks["source"] + " burst"))), flush=True)
 
 
 if __name__ == "__main__":
