@@ -21,7 +21,8 @@
 //     S and dP in place, privately per thread, and feed the second MMAs from TMEM.
 //   * Row statistics (LSE, delta) are per thread in pass dQ; in pass dKdV they belong to the
 //     columns and are staged through shared memory per column tile.
-//   * Warp roles: 8 softmax warps (two threads per row, 64 columns each), 1 MMA-issue warp, 1
+//   * Warp roles: 16 softmax warps (four threads per row, 32 columns each: the P / dS arithmetic
+//     is latency-bound, more warps per sub-partition hide it), 1 MMA-issue warp, 1
 //     load warp that also decodes work items and classifies tiles (descriptor / record rings as in
 //     the forward kernel). Every mbarrier wait is bounded; on expiry the CTA records a status word
 //     (shared with the forward kernel) and drains.
@@ -40,11 +41,14 @@ namespace b200na {
 namespace {
 
 constexpr int kTile = 128;          // tokens per row tile and per column tile
-constexpr int kSoftmaxWarps = 8;    // 2 column parts x 4 warps (one thread per row and part)
-constexpr int kSoftmaxThreads = 256;
-constexpr int kMmaWarp = 8;
-constexpr int kLoadWarp = 9;
-constexpr int kThreads = 320;
+constexpr int kParts = 4;           // threads per row: each owns 32 of a column tile's 128 columns
+constexpr int kSoftmaxWarps = 16;   // 4 column parts x 4 warps (one thread per row and part)
+constexpr int kSoftmaxThreads = 512;
+constexpr int kMmaWarp = 16;
+constexpr int kLoadWarp = 17;
+constexpr int kThreads = 576;
+// Registers are allocated to warps in groups of four, so 18 warps cost as much as 20: 96 per
+// thread; the 16-column chunks of the P / dS loop keep the live set well below that.
 constexpr int kTmemCols = 512;
 constexpr int kDescSlots = 4;
 constexpr int kDescBytes = 192;
@@ -404,11 +408,11 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
 
   if (warp < kSoftmaxWarps) {
     // ============ P / dS computation and the epilogue (two threads per row) ====================
-    const int part = warp >> 2;
+    const int part = warp >> 2;  // 0..3: columns [32 part, 32 part + 32) of every column tile
     const int row = ((warp & 3) << 5) | lane;
     const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) << 5) << 16);
-    const uint32_t my_s = lane_addr + kSCol + part * 64;
-    const uint32_t my_dp = lane_addr + kDpCol + part * 64;
+    const uint32_t my_s = lane_addr + kSCol + part * 32;
+    const uint32_t my_dp = lane_addr + kDpCol + part * 32;
     const float c = p.scale_log2;
     constexpr float kLog2e = 1.4426950408889634f;
     uint32_t ph_sdp = 0, ph_acc = 0, tseq = 0;
@@ -491,7 +495,7 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
           }
           named_bar_sync(1, kSoftmaxThreads);
         }
-        uint32_t mw0 = ~0u, mw1 = ~0u;
+        uint32_t mw = ~0u;  // mask bits of this thread's 32 columns (boundary tiles only)
         if (!interior) {
           uint4 mk = make_uint4(~0u, ~0u, ~0u, ~0u);
           int off = 0;
@@ -510,8 +514,7 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
               off += p.Tc[a] + 1;
             }
           }
-          mw0 = part ? mk.z : mk.x;
-          mw1 = part ? mk.w : mk.y;
+          mw = part == 0 ? mk.x : (part == 1 ? mk.y : (part == 2 ? mk.z : mk.w));
         }
         if (!__all_sync(0xffffffffu, wait_bar(bars.sdp_full, ph_sdp, abort_flag, p.status,
                                               (5 << 8) | kStSdpFull))) {
@@ -520,21 +523,20 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
         }
         ph_sdp ^= 1;
         ptx::tc_fence_after_sync();
-        // 32 columns at a time: p = 2^(s c - lse), ds = p (dp - delta); the packed results
+        // 16 columns at a time: p = 2^(s c - lse), ds = p (dp - delta); the packed results
         // overwrite logit / dP columns this same thread has already consumed.
 #pragma unroll
         for (int ch = 0; ch < 2; ++ch) {
-          uint32_t sr[32], dr[32];
-          ptx::tmem_ld32(my_s + ch * 32, sr);
-          ptx::tmem_ld32(my_dp + ch * 32, dr);
+          uint32_t sr[16], dr[16];
+          ptx::tmem_ld16(my_s + ch * 16, sr);
+          ptx::tmem_ld16(my_dp + ch * 16, dr);
           ptx::tmem_ld_wait();
-          const uint32_t mw = ch ? mw1 : mw0;
-          uint32_t pk[16], dk[16];
+          uint32_t pk[8], dk[8];
 #pragma unroll
-          for (int j = 0; j < 32; j += 2) {
+          for (int j = 0; j < 16; j += 2) {
             float l0 = row_l, l1 = row_l, d0 = row_d, d1 = row_d;
             if (kKeyRows) {
-              const int col = part * 64 + ch * 32 + j;
+              const int col = part * 32 + ch * 16 + j;
               const float2 lv = *reinterpret_cast<const float2*>(stat + col);
               const float2 dv = *reinterpret_cast<const float2*>(stat + kTile + col);
               l0 = lv.x; l1 = lv.y; d0 = dv.x; d1 = dv.y;
@@ -542,16 +544,16 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
             float p0 = ptx::ex2(fmaf(__uint_as_float(sr[j]), c, -l0));
             float p1 = ptx::ex2(fmaf(__uint_as_float(sr[j + 1]), c, -l1));
             if (!interior) {
-              p0 = ((mw >> j) & 1u) ? p0 : 0.f;
-              p1 = ((mw >> (j + 1)) & 1u) ? p1 : 0.f;
+              p0 = ((mw >> (ch * 16 + j)) & 1u) ? p0 : 0.f;
+              p1 = ((mw >> (ch * 16 + j + 1)) & 1u) ? p1 : 0.f;
             }
             const float s0 = p0 * (__uint_as_float(dr[j]) - d0);
             const float s1 = p1 * (__uint_as_float(dr[j + 1]) - d1);
             pk[j >> 1] = pack2<kBf16>(p0, p1);
             dk[j >> 1] = pack2<kBf16>(s0, s1);
           }
-          if (kKeyRows) ptx::tmem_st16(my_s + ch * 16, pk);
-          ptx::tmem_st16(my_dp + ch * 16, dk);
+          if (kKeyRows) ptx::tmem_st8(my_s + ch * 8, pk);
+          ptx::tmem_st8(my_dp + ch * 8, dk);
         }
         ptx::tmem_st_wait();
         ptx::tc_fence_before_sync();
@@ -568,24 +570,23 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
       const long long out_row = row_tok * p.row_heads + it.h;
 #pragma unroll
       for (int acc = 0; acc < (kKeyRows ? 2 : 1); ++acc) {
-        T* orow = reinterpret_cast<T*>(acc ? p.out1 : p.out0) + out_row * D + part * (D / 2);
+        constexpr int kCols = D / kParts;  // output columns per thread: 32 or 16
+        T* orow = reinterpret_cast<T*>(acc ? p.out1 : p.out0) + out_row * D + part * kCols;
         const float mul = acc ? 1.f : p.scale;
-        const uint32_t src = lane_addr + (acc ? kAcc1Col : kAcc0Col) + part * (D / 2);
+        const uint32_t src = lane_addr + (acc ? kAcc1Col : kAcc0Col) + part * kCols;
+        uint32_t orr[kCols];
+        if (kCols == 32) ptx::tmem_ld32(src, reinterpret_cast<uint32_t(&)[32]>(orr));
+        else ptx::tmem_ld16(src, reinterpret_cast<uint32_t(&)[16]>(orr));
+        ptx::tmem_ld_wait();
+        if (row_valid) {
 #pragma unroll
-        for (int ch = 0; ch < D / 64; ++ch) {
-          uint32_t orr[32];
-          ptx::tmem_ld32(src + ch * 32, orr);
-          ptx::tmem_ld_wait();
-          if (row_valid) {
-#pragma unroll
-            for (int v4 = 0; v4 < 4; ++v4) {
-              uint4 o;
-              o.x = pack2<kBf16>(__uint_as_float(orr[v4 * 8 + 0]) * mul, __uint_as_float(orr[v4 * 8 + 1]) * mul);
-              o.y = pack2<kBf16>(__uint_as_float(orr[v4 * 8 + 2]) * mul, __uint_as_float(orr[v4 * 8 + 3]) * mul);
-              o.z = pack2<kBf16>(__uint_as_float(orr[v4 * 8 + 4]) * mul, __uint_as_float(orr[v4 * 8 + 5]) * mul);
-              o.w = pack2<kBf16>(__uint_as_float(orr[v4 * 8 + 6]) * mul, __uint_as_float(orr[v4 * 8 + 7]) * mul);
-              *reinterpret_cast<uint4*>(orow + ch * 32 + v4 * 8) = o;
-            }
+          for (int v4 = 0; v4 < kCols / 8; ++v4) {
+            uint4 o;
+            o.x = pack2<kBf16>(__uint_as_float(orr[v4 * 8 + 0]) * mul, __uint_as_float(orr[v4 * 8 + 1]) * mul);
+            o.y = pack2<kBf16>(__uint_as_float(orr[v4 * 8 + 2]) * mul, __uint_as_float(orr[v4 * 8 + 3]) * mul);
+            o.z = pack2<kBf16>(__uint_as_float(orr[v4 * 8 + 4]) * mul, __uint_as_float(orr[v4 * 8 + 5]) * mul);
+            o.w = pack2<kBf16>(__uint_as_float(orr[v4 * 8 + 6]) * mul, __uint_as_float(orr[v4 * 8 + 7]) * mul);
+            *reinterpret_cast<uint4*>(orow + v4 * 8) = o;
           }
         }
       }
@@ -658,19 +659,20 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
           }
           ptx::tc_fence_after_sync();
           {
-            // acc0 += dS C1 (and acc1 += P C2): A from TMEM (16-bit values packed over the fp32
-            // columns their owner thread consumed), B = the column tile read MN-major,
-            // contraction over the 128 columns
+            // acc0 += dS C1 (and acc1 += P C2): A from TMEM (the 16-bit values of columns
+            // [32 q, 32 q + 32) sit packed in columns [32 q, 32 q + 16), over the fp32 columns
+            // their owner thread consumed), B = the column tile read MN-major, contraction over
+            // the 128 columns
             const uint32_t b1 = ptx::smem_desc_lo(c1, kBlockBytes);
             const uint32_t b2 = ptx::smem_desc_lo(c2, kBlockBytes);
 #pragma unroll
             for (int ks = 0; ks < kTile / 16; ++ks)
-              ptx::mma_ts_lohi(acc0_tm, dp_tm + (ks >> 2) * 64 + (ks & 3) * 8, b1 + ks * (2048 >> 4),
+              ptx::mma_ts_lohi(acc0_tm, dp_tm + (ks >> 1) * 32 + (ks & 1) * 8, b1 + ks * (2048 >> 4),
                                desc_hi, idesc_acc, (t == 0 && ks == 0) ? 0u : 1u);
             if (kKeyRows) {
 #pragma unroll
               for (int ks = 0; ks < kTile / 16; ++ks)
-                ptx::mma_ts_lohi(acc1_tm, s_tm + (ks >> 2) * 64 + (ks & 3) * 8,
+                ptx::mma_ts_lohi(acc1_tm, s_tm + (ks >> 1) * 32 + (ks & 1) * 8,
                                  b2 + ks * (2048 >> 4), desc_hi, idesc_acc,
                                  (t == 0 && ks == 0) ? 0u : 1u);
             }
