@@ -36,6 +36,8 @@ extern "C" {
 #define B200NA_F32 0
 #define B200NA_F16 1
 #define B200NA_BF16 2
+#define B200NA_E4M3 3 /* 8-bit float, 4 exponent bits (torch.float8_e4m3fn) */
+#define B200NA_E5M2 4 /* 8-bit float, 5 exponent bits (torch.float8_e5m2) */
 
 /* Exported-symbol marker (the library is built with hidden visibility by default). */
 #if defined(__GNUC__)
@@ -89,7 +91,10 @@ B200NA_API int b200na_token_unpermute(const void* in, void* out, int ndim, const
  *   qkv_shape: original token layout X; q_shape / kv_shape: padded per-group extents R_a*T_a
  *   (prod = Sq / Skv). prod(q_tile) must be 256 and prod(kv_tile) 128; tiles divide the shapes.
  *   kernel/stride/dilation/causal: the reference's kernel_size / stride / dilation / is_causal.
- *   dtype: B200NA_F16 or B200NA_BF16; D in {64, 128}; Hq % Hkv == 0. scale multiplies q.k.
+ *   dtype: B200NA_F16 or B200NA_BF16 with D in {64, 128}, or B200NA_E4M3 / B200NA_E5M2 with
+ *   D = 128 (the reference's 8-bit forward, csrc/src/blackwell_fna_forward.cu:178-191: fp32
+ *   accumulation and softmax, P rounded to e4m3 before P.V, O in the operand type);
+ *   Hq % Hkv == 0. scale multiplies q.k.
  * Rows of o/lse that correspond to padding tokens are left unspecified.
  */
 B200NA_API int b200na_fna_forward(const void* q, const void* k, const void* v, void* o, float* lse, int ndim,

@@ -17,7 +17,7 @@ ERR_INVALID_ARGUMENT, ERR_UNSUPPORTED, ERR_ALIGNMENT, ERR_CUDA, ERR_DEVICE, ERR_
     -1, -2, -3, -4, -5, -6)
 ERR_WORKSPACE_LIMIT = -7
 STATIC_WORKSPACE_BYTES = 32 * 1024 * 1024
-F32, F16, BF16 = 0, 1, 2
+F32, F16, BF16, E4M3, E5M2 = 0, 1, 2, 3, 4
 
 # Every symbol include/natten_b200.h declares.
 SYMBOLS = (

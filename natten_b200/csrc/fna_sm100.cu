@@ -257,10 +257,11 @@ __device__ __forceinline__ bool kv_tile_interior(const FnaParams& p, const Item&
   return in;
 }
 
-template <int D>
+// ES = bytes per operand element (2: fp16 / bf16, 1: 8-bit floats)
+template <int D, int ES>
 struct Smem {
-  static constexpr int kStages = (D == 128) ? 4 : 6;       // ring slots shared by K and V tiles
-  static constexpr int kTileBytes = kKVTile * D * 2;        // one K or V tile / one Q half
+  static constexpr int kTileBytes = kKVTile * D * ES;       // one K or V tile / one Q half
+  static constexpr int kStages = (kTileBytes >= 32768) ? 4 : 6;  // ring slots shared by K and V
   static constexpr int kQOff = 0;
   static constexpr int kKVOff = 2 * kTileBytes;
   static constexpr int kPrefOff = kKVOff + kStages * kTileBytes;
@@ -340,15 +341,39 @@ __device__ __forceinline__ void release_item(const Bars& bars, uint32_t seq) {
   ptx::mbar_arrive(bars.desc_empty + seq % kDescSlots);
 }
 
-template <bool kBf16>
+// Operand element types of the kernel template.
+enum : int { kTyF16 = 0, kTyBf16 = 1, kTyE4m3 = 2, kTyE5m2 = 3 };
+
+template <int kType>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
-  if (kBf16) {
+  if (kType == kTyBf16) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
   } else {
     __half2 v = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
   }
+}
+// 16 bytes of output elements from fp32 values scaled by `mul`: 8 (16-bit) or 16 (8-bit) values.
+template <int kType>
+__device__ __forceinline__ uint4 pack_out16(const uint32_t* f, float mul) {
+  uint4 o;
+  if (kType >= kTyE4m3) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float a = __uint_as_float(f[4 * i]) * mul, b = __uint_as_float(f[4 * i + 1]) * mul,
+                  c = __uint_as_float(f[4 * i + 2]) * mul, d = __uint_as_float(f[4 * i + 3]) * mul;
+      w[i] = kType == kTyE4m3 ? ptx::pack4_e4m3(a, b, c, d) : ptx::pack4_e5m2(a, b, c, d);
+    }
+    o = make_uint4(w[0], w[1], w[2], w[3]);
+  } else {
+    o.x = pack2<kType>(__uint_as_float(f[0]) * mul, __uint_as_float(f[1]) * mul);
+    o.y = pack2<kType>(__uint_as_float(f[2]) * mul, __uint_as_float(f[3]) * mul);
+    o.z = pack2<kType>(__uint_as_float(f[4]) * mul, __uint_as_float(f[5]) * mul);
+    o.w = pack2<kType>(__uint_as_float(f[6]) * mul, __uint_as_float(f[7]) * mul);
+  }
+  return o;
 }
 
 __device__ __forceinline__ void named_bar_sync(int id, int threads) {
@@ -373,16 +398,19 @@ __device__ __forceinline__ void kv_tile_next(const Item& it, int (&c)[B200NA_MAX
   ++c[2];
 }
 
-template <int D, bool kBf16, int NDIM>
+template <int D, int kType, int NDIM>
 __global__ void __launch_bounds__(kThreads, 1)
 fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_ek,
                const __grid_constant__ CUtensorMap tm_ev, const FnaParams p) {
-  using SM = Smem<D>;
+  constexpr int kES = kType >= kTyE4m3 ? 1 : 2;   // bytes per operand element
+  constexpr bool kF8 = kES == 1;
+  using SM = Smem<D, kES>;
   constexpr int kStages = SM::kStages;
   constexpr int kTileBytes = SM::kTileBytes;
-  constexpr int kDBlocks = D / 64;          // 64-element (128-byte) column blocks per row
-  constexpr int kBlockBytes = kKVTile * 128; // one column block of a 128-row tile
+  constexpr int kBlockElems = 128 / kES;           // elements of one 128-byte column block
+  constexpr int kDBlocks = D / kBlockElems;        // 128-byte column blocks per row
+  constexpr int kBlockBytes = kKVTile * 128;       // one column block of a 128-row tile
 
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* q_sm = smem + SM::kQOff;
@@ -504,8 +532,7 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const float c = p.scale_log2;
     uint32_t ph_s = 0, ph_o = 0;
     uint32_t tseq = 0;  // tiles consumed so far, indexes the per-tile record ring
-    typedef typename std::conditional<kBf16, __nv_bfloat16, __half>::type T;
-    T* o_ptr = reinterpret_cast<T*>(p.o);
+    uint8_t* o_ptr = reinterpret_cast<uint8_t*>(p.o);
     // in-tile coordinates of this thread's query row (fixed for the whole kernel)
     int tq[B200NA_MAX_DIM];
     {
@@ -660,16 +687,32 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 if (!((mw1 >> j) & 1u)) sr[j] = 0xff800000u;
             }
           }
-          uint32_t pk[16];
+          if (kF8) {
+            // 8-bit operands: P is rounded to e4m3, four probabilities per TMEM column
+            uint32_t pk[8];
 #pragma unroll
-          for (int j = 0; j < 32; j += 2) {
-            const float p0 = ptx::ex2(fmaf(__uint_as_float(sr[j]), c, neg_mc));
-            const float p1 = ptx::ex2(fmaf(__uint_as_float(sr[j + 1]), c, neg_mc));
-            sm0 += p0;
-            sm1 += p1;
-            pk[j >> 1] = pack2<kBf16>(p0, p1);
+            for (int j = 0; j < 32; j += 4) {
+              const float p0 = ptx::ex2(fmaf(__uint_as_float(sr[j]), c, neg_mc));
+              const float p1 = ptx::ex2(fmaf(__uint_as_float(sr[j + 1]), c, neg_mc));
+              const float p2 = ptx::ex2(fmaf(__uint_as_float(sr[j + 2]), c, neg_mc));
+              const float p3 = ptx::ex2(fmaf(__uint_as_float(sr[j + 3]), c, neg_mc));
+              sm0 += p0 + p2;
+              sm1 += p1 + p3;
+              pk[j >> 2] = ptx::pack4_e4m3(p0, p1, p2, p3);
+            }
+            ptx::tmem_st8(my_p + ch * 8, pk);
+          } else {
+            uint32_t pk[16];
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) {
+              const float p0 = ptx::ex2(fmaf(__uint_as_float(sr[j]), c, neg_mc));
+              const float p1 = ptx::ex2(fmaf(__uint_as_float(sr[j + 1]), c, neg_mc));
+              sm0 += p0;
+              sm1 += p1;
+              pk[j >> 1] = pack2<kType>(p0, p1);
+            }
+            ptx::tmem_st16(my_p + ch * 16, pk);
           }
-          ptx::tmem_st16(my_p + ch * 16, pk);
         }
         sum += sm0 + sm1;
         PROF_MARK(2)
@@ -713,22 +756,18 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         out_row = ((long long)it.bp * p.Sq + q_row) * p.Hq + it.h;
       }
       const float inv = total > 0.f ? 1.f / total : 0.f;
-      T* orow = o_ptr + out_row * D + part * (D / 2);
+      uint8_t* orow = o_ptr + (out_row * D + part * (D / 2)) * kES;
 #pragma unroll
       for (int ch = 0; ch < D / 64; ++ch) {
         uint32_t orr[32];
         ptx::tmem_ld32(my_o + ch * 32, orr);
         ptx::tmem_ld_wait();
         if (valid) {
+          constexpr int kPer = 16 / kES;  // output elements per 16-byte store
 #pragma unroll
-          for (int v4 = 0; v4 < 4; ++v4) {
-            uint4 out;
-            out.x = pack2<kBf16>(__uint_as_float(orr[v4 * 8 + 0]) * inv, __uint_as_float(orr[v4 * 8 + 1]) * inv);
-            out.y = pack2<kBf16>(__uint_as_float(orr[v4 * 8 + 2]) * inv, __uint_as_float(orr[v4 * 8 + 3]) * inv);
-            out.z = pack2<kBf16>(__uint_as_float(orr[v4 * 8 + 4]) * inv, __uint_as_float(orr[v4 * 8 + 5]) * inv);
-            out.w = pack2<kBf16>(__uint_as_float(orr[v4 * 8 + 6]) * inv, __uint_as_float(orr[v4 * 8 + 7]) * inv);
-            *reinterpret_cast<uint4*>(orow + ch * 32 + v4 * 8) = out;
-          }
+          for (int v4 = 0; v4 < 32 / kPer; ++v4)
+            *reinterpret_cast<uint4*>(orow + (ch * 32 + v4 * kPer) * kES) =
+                pack_out16<kType>(orr + v4 * kPer, inv);
         }
       }
       if (p.lse != nullptr && valid && part == 0)
@@ -742,8 +781,11 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   } else if (warp == kMmaWarp) {
     // =============================== MMA issue ==============================================
     if (lane == 0) {
-      constexpr uint32_t idesc_qk = ptx::make_idesc(kBf16 ? 1 : 0, 0, 0, kHalf, kKVTile);
-      constexpr uint32_t idesc_pv = ptx::make_idesc(kBf16 ? 1 : 0, 0, 1, kHalf, D);
+      // element format codes of the instruction descriptor: kind::f16 0 = fp16, 1 = bf16;
+      // kind::f8f6f4 0 = e4m3, 1 = e5m2 (P is always e4m3)
+      constexpr int kFmt = kF8 ? (kType == kTyE5m2 ? 1 : 0) : (kType == kTyBf16 ? 1 : 0);
+      constexpr uint32_t idesc_qk = ptx::make_idesc_ab(kFmt, kFmt, 0, 0, kHalf, kKVTile);
+      constexpr uint32_t idesc_pv = ptx::make_idesc_ab(kF8 ? 0 : kFmt, kFmt, 0, 1, kHalf, D);
       uint32_t ph_q = 0, ph_p[2] = {0, 0}, ph_oe[2] = {1, 1};
       RingPos<kStages> ring;  // K and V tiles in load order
       const uint32_t q_base = ptx::smem_u32(q_sm);
@@ -763,11 +805,16 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const uint32_t a_lo = half ? q_lo[1] : q_lo[0];
         const uint32_t b_lo = ptx::smem_desc_lo(k_addr, 16);
         const uint32_t d = half ? s_tm[1] : s_tm[0];
+        // one MMA consumes 32 bytes of the head dim per row: K = 16 (16-bit) or 32 (8-bit)
 #pragma unroll
-        for (int kb = 0; kb < D / 16; ++kb) {
+        for (int kb = 0; kb < D * kES / 32; ++kb) {
           const uint32_t koff = ((kb >> 2) * kBlockBytes + (kb & 3) * 32) >> 4;
-          ptx::mma_ss_lohi(d, a_lo + koff, desc_hi, b_lo + koff, desc_hi, idesc_qk,
-                           kb > 0 ? 1u : 0u);
+          if (kF8)
+            ptx::mma_ss_lohi_f8(d, a_lo + koff, desc_hi, b_lo + koff, desc_hi, idesc_qk,
+                                kb > 0 ? 1u : 0u);
+          else
+            ptx::mma_ss_lohi(d, a_lo + koff, desc_hi, b_lo + koff, desc_hi, idesc_qk,
+                             kb > 0 ? 1u : 0u);
         }
       };
       // P for keys [0,64) sits in S columns [0,32), for keys [64,128) in columns [64,96): each
@@ -776,10 +823,19 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const uint32_t b_lo = ptx::smem_desc_lo(v_addr, kBlockBytes);
         const uint32_t d = half ? o_tm[1] : o_tm[0];
         const uint32_t a = half ? s_tm[1] : s_tm[0];
+        if (kF8) {
+          // 8-bit: K = 32 keys per MMA = 8 packed columns; a thread's 64 probabilities take 16
+          // columns at [0,16) resp. [64,80); V rows are 128 bytes, 32 rows per step
 #pragma unroll
-        for (int ks = 0; ks < kKVTile / 16; ++ks)
-          ptx::mma_ts_lohi(d, a + (ks >> 2) * 64 + (ks & 3) * 8, b_lo + ks * (2048 >> 4), desc_hi,
-                           idesc_pv, (first && ks == 0) ? 0u : 1u);
+          for (int ks = 0; ks < kKVTile / 32; ++ks)
+            ptx::mma_ts_lohi_f8(d, a + (ks >> 1) * 64 + (ks & 1) * 8, b_lo + ks * (4096 >> 4),
+                                desc_hi, idesc_pv, (first && ks == 0) ? 0u : 1u);
+        } else {
+#pragma unroll
+          for (int ks = 0; ks < kKVTile / 16; ++ks)
+            ptx::mma_ts_lohi(d, a + (ks >> 2) * 64 + (ks & 3) * 8, b_lo + ks * (2048 >> 4),
+                             desc_hi, idesc_pv, (first && ks == 0) ? 0u : 1u);
+        }
       };
 
       PROF2_DECL
@@ -917,10 +973,10 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 x[a] = (it.q_lo[a] + ((h && a == p.half_axis) ? (p.Tq[a] >> 1) : 0)) * p.dil[a] +
                        it.g[a];
               ptx::tma_load_5d(q_sm + h * kTileBytes + db * kBlockBytes, &tm_q, bars.q_full,
-                               it.h * D + db * 64, x[0], x[1], x[2], it.b);
+                               it.h * D + db * kBlockElems, x[0], x[1], x[2], it.b);
             } else {
               ptx::tma_load_4d(q_sm + h * kTileBytes + db * kBlockBytes, &tm_q, bars.q_full,
-                               db * 64, it.h, it.qt * kQTile + h * kHalf, bp);
+                               db * kBlockElems, it.h, it.qt * kQTile + h * kHalf, bp);
             }
           }
         int tc[B200NA_MAX_DIM] = {it.kv_t0[0], it.kv_t0[1], it.kv_t0[2]};
@@ -966,12 +1022,12 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             for (int db = 0; db < kDBlocks; ++db) {
               if (p.direct && !is_extra)
                 ptx::tma_load_5d(kv_sm + slot * kTileBytes + db * kBlockBytes,
-                                 kv == 0 ? &tm_k : &tm_v, bars.kv_full + slot, hk * D + db * 64,
+                                 kv == 0 ? &tm_k : &tm_v, bars.kv_full + slot, hk * D + db * kBlockElems,
                                  xk[0], xk[1], xk[2], it.b);
               else
                 ptx::tma_load_4d(kv_sm + slot * kTileBytes + db * kBlockBytes,
                                  is_extra ? (kv == 0 ? &tm_ek : &tm_ev) : (kv == 0 ? &tm_k : &tm_v),
-                                 bars.kv_full + slot, db * 64, hk, row0, b_src);
+                                 bars.kv_full + slot, db * kBlockElems, hk, row0, b_src);
             }
           }
           // Once this item's first tiles fill the ring the load thread would only wait for free
@@ -1032,20 +1088,30 @@ int get_encode_fn(EncodeTiledFn* fn) {
   return B200NA_OK;
 }
 
-// Tensor map over a heads-last [Bp, S, H, D] 16-bit tensor; box = 64 (d) x 1 (h) x 128 (s) x 1.
+// Bytes per element and tensor-map data type of an operand dtype code (0 = not a tensor-core type).
+int elem_bytes_of(int dtype) {
+  return (dtype == B200NA_F16 || dtype == B200NA_BF16) ? 2
+         : (dtype == B200NA_E4M3 || dtype == B200NA_E5M2) ? 1 : 0;
+}
+CUtensorMapDataType tma_type_of(int dtype) {
+  return dtype == B200NA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+         : dtype == B200NA_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+}
+
+// Tensor map over a heads-last [Bp, S, H, D] tensor; box = 128 bytes of the head dim (64 16-bit or
+// 128 8-bit elements) x 1 (h) x 128 (s) x 1.
 int make_tensor_map(CUtensorMap* tm, const void* ptr, int dtype, int Bp, int S, int H, int D) {
   EncodeTiledFn enc = nullptr;
   int rc = get_encode_fn(&enc);
   if (rc != B200NA_OK) return rc;
+  const cuuint64_t es = (cuuint64_t)elem_bytes_of(dtype);
   const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)H, (cuuint64_t)S, (cuuint64_t)Bp};
-  const cuuint64_t strides[3] = {(cuuint64_t)D * 2, (cuuint64_t)H * D * 2,
-                                 (cuuint64_t)S * H * D * 2};
-  const cuuint32_t box[4] = {64, 1, (cuuint32_t)kKVTile, 1};
+  const cuuint64_t strides[3] = {(cuuint64_t)D * es, (cuuint64_t)H * D * es,
+                                 (cuuint64_t)S * H * D * es};
+  const cuuint32_t box[4] = {(cuuint32_t)(128 / es), 1, (cuuint32_t)kKVTile, 1};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
-  const CUresult r = enc(tm, dtype == B200NA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
-                                                  : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
-                         4, const_cast<void*>(ptr), dims, strides, box, estr,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+  const CUresult r = enc(tm, tma_type_of(dtype), 4, const_cast<void*>(ptr), dims, strides, box,
+                         estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     set_last_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
@@ -1054,31 +1120,30 @@ int make_tensor_map(CUtensorMap* tm, const void* ptr, int dtype, int Bp, int S, 
   return B200NA_OK;
 }
 
-// Tensor map over the caller's heads-last [B, X0, X1, X2, H, D] 16-bit tensor, seen as the 5-D
-// array (H*D, X0, X1, X2, B) - axis 0 right after the channel dimension, so that a box lands in
-// shared memory in the tile's own row order (axis 0 fastest). The box spans tile[a] * dil[a]
-// positions per axis and is traversed with element stride dil[a]: it picks the tile's tokens of
-// one dilation group; positions past an extent read as zeros.
+// Tensor map over the caller's heads-last [B, X0, X1, X2, H, D] tensor, seen as the 5-D array
+// (H*D, X0, X1, X2, B) - axis 0 right after the channel dimension, so that a box lands in
+// shared memory in the tile's own row order (axis 0 fastest). The box spans 128 bytes of one
+// head's channels and tile[a] * dil[a] positions per axis, traversed with element stride dil[a]:
+// it picks the tile's tokens of one dilation group; positions past an extent read as zeros.
 int make_tensor_map_direct(CUtensorMap* tm, const void* ptr, int dtype, int B, const int* X,
                            int H, int D, const int* tile, const int* dil) {
   EncodeTiledFn enc = nullptr;
   int rc = get_encode_fn(&enc);
   if (rc != B200NA_OK) return rc;
-  const cuuint64_t row = (cuuint64_t)H * D * 2;  // bytes per token
+  const cuuint64_t es = (cuuint64_t)elem_bytes_of(dtype);
+  const cuuint64_t row = (cuuint64_t)H * D * es;  // bytes per token
   const cuuint64_t dims[5] = {(cuuint64_t)H * D, (cuuint64_t)X[0], (cuuint64_t)X[1],
                               (cuuint64_t)X[2], (cuuint64_t)B};
   const cuuint64_t strides[4] = {row * X[1] * X[2], row * X[2], row, row * X[0] * X[1] * X[2]};
-  cuuint32_t box[5] = {64, 1, 1, 1, 1};
+  cuuint32_t box[5] = {(cuuint32_t)(128 / es), 1, 1, 1, 1};
   cuuint32_t estr[5] = {1, 1, 1, 1, 1};
   for (int a = 0; a < B200NA_MAX_DIM; ++a) {
     box[1 + a] = (cuuint32_t)(tile[a] * dil[a]);
     estr[1 + a] = (cuuint32_t)dil[a];
     if (box[1 + a] > 256 || estr[1 + a] > 8) return B200NA_ERR_UNSUPPORTED;
   }
-  const CUresult r = enc(tm, dtype == B200NA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
-                                                  : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
-                         5, const_cast<void*>(ptr), dims, strides, box, estr,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+  const CUresult r = enc(tm, tma_type_of(dtype), 5, const_cast<void*>(ptr), dims, strides, box,
+                         estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     set_last_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
@@ -1087,15 +1152,33 @@ int make_tensor_map_direct(CUtensorMap* tm, const void* ptr, int dtype, int B, c
   return B200NA_OK;
 }
 
-template <int D, bool kBf16>
+template <int D, int kType>
 const void* kernel_for_ndim(int ndim) {
-  if (ndim == 1) return (const void*)fna_fwd_kernel<D, kBf16, 1>;
-  if (ndim == 2) return (const void*)fna_fwd_kernel<D, kBf16, 2>;
-  return (const void*)fna_fwd_kernel<D, kBf16, 3>;
+  if (ndim == 1) return (const void*)fna_fwd_kernel<D, kType, 1>;
+  if (ndim == 2) return (const void*)fna_fwd_kernel<D, kType, 2>;
+  return (const void*)fna_fwd_kernel<D, kType, 3>;
 }
-const void* kernel_variant(int D, bool bf16, int ndim) {
-  if (D == 128) return bf16 ? kernel_for_ndim<128, true>(ndim) : kernel_for_ndim<128, false>(ndim);
-  return bf16 ? kernel_for_ndim<64, true>(ndim) : kernel_for_ndim<64, false>(ndim);
+// Supported (head dim, dtype) pairs: 16-bit floats with 64 / 128, 8-bit floats with 128.
+bool variant_supported(int D, int dtype) {
+  if (dtype == B200NA_F16 || dtype == B200NA_BF16) return D == 64 || D == 128;
+  if (dtype == B200NA_E4M3 || dtype == B200NA_E5M2) return D == 128;
+  return false;
+}
+const void* kernel_variant(int D, int dtype, int ndim) {
+  switch (dtype) {
+    case B200NA_F16:
+      return D == 128 ? kernel_for_ndim<128, kTyF16>(ndim) : kernel_for_ndim<64, kTyF16>(ndim);
+    case B200NA_BF16:
+      return D == 128 ? kernel_for_ndim<128, kTyBf16>(ndim) : kernel_for_ndim<64, kTyBf16>(ndim);
+    case B200NA_E4M3:
+      return kernel_for_ndim<128, kTyE4m3>(ndim);
+    default:
+      return kernel_for_ndim<128, kTyE5m2>(ndim);
+  }
+}
+int smem_bytes_of(int D, int dtype) {
+  if (elem_bytes_of(dtype) == 1) return Smem<128, 1>::kBytes;
+  return D == 128 ? Smem<128, 2>::kBytes : Smem<64, 2>::kBytes;
 }
 
 struct DeviceState {
@@ -1118,15 +1201,19 @@ int device_state(DeviceState** out) {
     B200NA_CUDA_TRY(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
     if (major != 10) return B200NA_ERR_DEVICE;
     B200NA_CUDA_TRY(cudaDeviceGetAttribute(&st.sms, cudaDevAttrMultiProcessorCount, dev));
-    for (int i = 0; i < 12; ++i) {
-      const void* fn = kernel_variant(i & 2 ? 128 : 64, (i & 1) != 0, 1 + (i >> 2));
-      B200NA_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           (i & 2 ? Smem<128>::kBytes : Smem<64>::kBytes) + 8192));
-      cudaFuncAttributes fa;
-      B200NA_CUDA_TRY(cudaFuncGetAttributes(&fa, fn));
-      // one CTA of kThreads threads must fit the register file
-      if (fa.numRegs * kThreads > 65536) return B200NA_ERR_UNSUPPORTED;
-    }
+    const int dtypes[4] = {B200NA_F16, B200NA_BF16, B200NA_E4M3, B200NA_E5M2};
+    for (int t = 0; t < 4; ++t)
+      for (int D = 64; D <= 128; D += 64)
+        for (int nd = 1; nd <= B200NA_MAX_DIM; ++nd) {
+          if (!variant_supported(D, dtypes[t])) continue;
+          const void* fn = kernel_variant(D, dtypes[t], nd);
+          B200NA_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               smem_bytes_of(D, dtypes[t]) + 8192));
+          cudaFuncAttributes fa;
+          B200NA_CUDA_TRY(cudaFuncGetAttributes(&fa, fn));
+          // one CTA of kThreads threads must fit the register file
+          if (fa.numRegs * kThreads > 65536) return B200NA_ERR_UNSUPPORTED;
+        }
     void* sp = nullptr;
     B200NA_CUDA_TRY(cudaGetSymbolAddress(&sp, g_status_word));
     st.status_ptr = reinterpret_cast<int*>(sp);
@@ -1180,7 +1267,7 @@ int launch_fna(const void* q, const void* k, const void* v, FnaParams& p, int D,
   p.total_work = (long long)p.n_qtiles * p.Hq * p.Bp;
   if (p.total_work == 0) return B200NA_OK;
   const int grid = (int)(p.total_work < st->sms ? p.total_work : st->sms);
-  const void* fn = kernel_variant(D, dtype == B200NA_BF16, p.ndim);
+  const void* fn = kernel_variant(D, dtype, p.ndim);
   void* args[] = {(void*)&tq, (void*)&tk, (void*)&tv, (void*)&tek, (void*)&tev, (void*)&p};
 #if defined(B200NA_PROFILE) && B200NA_PROFILE >= 2
   constexpr int kExtraSmem = 8192;
@@ -1188,7 +1275,7 @@ int launch_fna(const void* q, const void* k, const void* v, FnaParams& p, int D,
   constexpr int kExtraSmem = 0;
 #endif
   B200NA_CUDA_TRY(cudaLaunchKernel(fn, dim3(grid), dim3(kThreads), args,
-                                   (D == 128 ? Smem<128>::kBytes : Smem<64>::kBytes) + kExtraSmem,
+                                   smem_bytes_of(D, dtype) + kExtraSmem,
                                    stream));
   return B200NA_OK;
 }
@@ -1224,8 +1311,7 @@ int fna_forward_impl(
   if (!q || !k || !v || !o || !qkv_shape || !q_shape || !kv_shape || !kernel || !q_tile || !kv_tile)
     return B200NA_ERR_INVALID_ARGUMENT;
   if (Bp < 1 || Hq < 1 || Hkv < 1 || Hq % Hkv != 0) return B200NA_ERR_INVALID_ARGUMENT;
-  if (dtype != B200NA_F16 && dtype != B200NA_BF16) return B200NA_ERR_UNSUPPORTED;
-  if (D != 64 && D != 128) return B200NA_ERR_UNSUPPORTED;
+  if (!variant_supported(D, dtype)) return B200NA_ERR_UNSUPPORTED;
   if (!(scale > 0.f)) return B200NA_ERR_INVALID_ARGUMENT;
   const bool sharded = q_origin != nullptr || kv_origin != nullptr || q_extent != nullptr;
   if (sharded && !(q_origin && kv_origin && q_extent)) return B200NA_ERR_INVALID_ARGUMENT;
@@ -1308,8 +1394,7 @@ int fna_direct_impl(const void* q, const void* k, const void* v, void* o, float*
     return B200NA_ERR_INVALID_ARGUMENT;
   if (n_extra < 0 || (n_extra > 0 && (!add_k || !add_v))) return B200NA_ERR_INVALID_ARGUMENT;
   if (B < 1 || Hq < 1 || Hkv < 1 || Hq % Hkv != 0) return B200NA_ERR_INVALID_ARGUMENT;
-  if (dtype != B200NA_F16 && dtype != B200NA_BF16) return B200NA_ERR_UNSUPPORTED;
-  if (D != 64 && D != 128) return B200NA_ERR_UNSUPPORTED;
+  if (!variant_supported(D, dtype)) return B200NA_ERR_UNSUPPORTED;
   if (!(scale > 0.f)) return B200NA_ERR_INVALID_ARGUMENT;
   NaAxes ax;
   int rc = fill_axes(ax, ndim, shape, kernel, stride, dilation, causal);
@@ -1418,9 +1503,11 @@ extern "C" B200NA_API int b200na_fmha_forward(const void* q, const void* k, cons
   if (B < 1 || Nq < 1 || Nk < 1 || Hq < 1 || Hkv < 1 || Hq % Hkv != 0)
     return B200NA_ERR_INVALID_ARGUMENT;
   if (causal && Nq != Nk) return B200NA_ERR_INVALID_ARGUMENT;
-  if (dtype != B200NA_F32 && dtype != B200NA_F16 && dtype != B200NA_BF16)
+  if (dtype != B200NA_F32 && dtype != B200NA_F16 && dtype != B200NA_BF16 &&
+      dtype != B200NA_E4M3 && dtype != B200NA_E5M2)
     return B200NA_ERR_INVALID_ARGUMENT;
-  if (dtype == B200NA_F32 || (D != 64 && D != 128) || !(scale > 0.f))
+  if (elem_bytes_of(dtype) == 1 && !variant_supported(D, dtype)) return B200NA_ERR_UNSUPPORTED;
+  if (!variant_supported(D, dtype) || !(scale > 0.f))
     return simt_dense_forward(q, k, v, o, lse, B, Nq, Nk, Hq, Hkv, D, dtype, scale, causal,
                               reinterpret_cast<cudaStream_t>(stream));
   FnaParams p;

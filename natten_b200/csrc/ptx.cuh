@@ -156,6 +156,30 @@ __device__ __forceinline__ void mma_ts_lohi(uint32_t d_tmem, uint32_t a_tmem, ui
       ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// kind::f8f6f4 forms (8-bit operands, K = 32 per instruction, fp32 accumulate).
+__device__ __forceinline__ void mma_ss_lohi_f8(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi,
+                                               uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %5, p;\n\t}\n"
+      ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_ts_lohi_f8(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo,
+                                               uint32_t b_hi, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], db, %4, p;\n\t}\n"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // Low / high words of the 128-byte-swizzle descriptor below (low: address and leading offset;
 // high: stride offset 1024 B, version, layout). Addresses are < 256 KB, so adding a byte offset
 // >> 4 to the low word never carries into the leading-offset field.
@@ -191,6 +215,29 @@ __host__ __device__ constexpr uint32_t make_idesc(int ab_fmt, int a_mn_major, in
          | ((uint32_t)b_mn_major << 16)     // B major (0 = K, 1 = MN)
          | ((uint32_t)(N >> 3) << 17)       // N / 8
          | ((uint32_t)(M >> 4) << 24);      // M / 16
+}
+
+// Instruction descriptor with separate A / B element formats. kind::f16: 0 = fp16, 1 = bf16;
+// kind::f8f6f4: 0 = e4m3, 1 = e5m2.
+__host__ __device__ constexpr uint32_t make_idesc_ab(int a_fmt, int b_fmt, int a_mn_major,
+                                                     int b_mn_major, int M, int N) {
+  return (1u << 4) | ((uint32_t)a_fmt << 7) | ((uint32_t)b_fmt << 10) |
+         ((uint32_t)a_mn_major << 15) | ((uint32_t)b_mn_major << 16) |
+         ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+// Four fp32 values -> four 8-bit floats in one word, element 0 in the lowest byte.
+__device__ __forceinline__ uint32_t pack4_e4m3(float e0, float e1, float e2, float e3) {
+  uint16_t lo, hi;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(e1), "f"(e0));
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(e3), "f"(e2));
+  return (uint32_t)lo | ((uint32_t)hi << 16);
+}
+__device__ __forceinline__ uint32_t pack4_e5m2(float e0, float e1, float e2, float e3) {
+  uint16_t lo, hi;
+  asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(e1), "f"(e0));
+  asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(e3), "f"(e2));
+  return (uint32_t)lo | ((uint32_t)hi << 16);
 }
 
 // ---- tcgen05: TMEM <-> registers (32 lanes x 32-bit, one row per thread) ------------------

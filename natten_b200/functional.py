@@ -31,7 +31,17 @@ Q_TILE_SIZE = 256
 KV_TILE_SIZE = 128
 TENSOR_CORE_HEAD_DIMS = (64, 128)
 
-_DTYPE_CODE = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.bfloat16: _lib.BF16}
+_DTYPE_CODE = ops.DTYPE_CODE
+FP8_DTYPES = (torch.float8_e4m3fn, torch.float8_e5m2)
+FP8_HEAD_DIM = 128
+
+
+def _tensor_core_supported(dtype: torch.dtype, head_dim: int) -> bool:
+    """Operand types of the tcgen05 kernels: fp16 / bf16 with head dim 64 or 128, 8-bit floats
+    (forward only) with head dim 128."""
+    if dtype in (torch.float16, torch.bfloat16):
+        return head_dim in TENSOR_CORE_HEAD_DIMS
+    return dtype in FP8_DTYPES and head_dim == FP8_HEAD_DIM
 
 
 def _ptr(t: Optional[Tensor]):
@@ -234,7 +244,7 @@ def merge_attentions(outputs: List[Tensor], lse_tensors: List[Tensor], torch_com
             raise ValueError("Output tensors must share one dtype.")
     _require_cuda(*outputs, *lse_tensors)
     dtype = outputs[0].dtype
-    if dtype not in _DTYPE_CODE:
+    if dtype not in _DTYPE_CODE or dtype in FP8_DTYPES:
         raise NotImplementedError(f"merge_attentions does not support dtype {dtype}.")
     acc_o = outputs[0].contiguous()
     acc_l = lse_tensors[0].to(torch.float32).contiguous()
@@ -380,8 +390,10 @@ def na_forward_op(query: Tensor, key: Tensor, value: Tensor, additional_keys: Op
     shape = tuple(int(x) for x in query.shape[1:1 + na_dim])
     kernel_size, stride, dilation = tuple(kernel_size), tuple(stride), tuple(dilation)
     is_causal = tuple(bool(c) for c in is_causal)
-    tensor_core = (query.dtype in (torch.float16, torch.bfloat16)
-                   and query.shape[-1] in TENSOR_CORE_HEAD_DIMS)
+    tensor_core = _tensor_core_supported(query.dtype, query.shape[-1])
+    if not tensor_core and query.dtype in FP8_DTYPES:
+        raise NotImplementedError(f"natten_b200: 8-bit operands need head dim {FP8_HEAD_DIM}, got "
+                                  f"{query.shape[-1]}.")
     if not tensor_core:
         # fp32 operands (and other head dims): CUDA-core kernel on the original layout, extra KV
         # tokens fused into the same softmax.

@@ -24,7 +24,8 @@ from . import _lib
 
 USE_TORCH_OPS = os.environ.get("NATTEN_B200_DISABLE_TORCH_OPS", "0") != "1"
 NAMESPACE = "natten_b200"
-DTYPE_CODE = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.bfloat16: _lib.BF16}
+DTYPE_CODE = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.bfloat16: _lib.BF16,
+              torch.float8_e4m3fn: _lib.E4M3, torch.float8_e5m2: _lib.E5M2}
 
 
 def _ptr(t: Optional[Tensor]):
