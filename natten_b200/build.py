@@ -17,7 +17,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libnatten_b200.so")
 SOURCES = ["capi.cu", "tokperm.cu", "merge.cu", "na_simt.cu", "na_bwd_simt.cu", "fna_sm100.cu", "fna_bwd_sm100.cu", "na_fused.cu"]
-HEADERS = ["common.cuh", "ptx.cuh", "fna_host.cuh", os.path.join("..", "..", "include", "natten_b200.h")]
+HEADERS = ["common.cuh", "ptx.cuh", "fna_host.cuh", "fna_device.cuh", os.path.join("..", "..", "include", "natten_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
 

@@ -34,6 +34,7 @@
 #include <type_traits>
 
 #include "common.cuh"
+#include "fna_device.cuh"
 #include "fna_host.cuh"
 #include "ptx.cuh"
 
@@ -53,7 +54,6 @@ constexpr int kTmemCols = 512;
 constexpr int kDescSlots = 4;
 constexpr int kDescBytes = 192;
 constexpr int kTileRecs = 8;
-constexpr long long kWaitLimitCycles = 4000000000ll;  // ~2 s at 2 GHz
 
 // status word: (role << 8) | barrier id; roles 5 = softmax, 6 = mma, 7 = load (backward kernel)
 enum : int { kStRFull = 1, kStREmpty, kStCFull, kStCEmpty, kStSdpFull, kStDsFull, kStAccFull,
@@ -233,36 +233,6 @@ struct Bars {
   uint64_t *desc_full, *desc_empty, *rec_full, *rec_empty, *c_full, *c_empty;
 };
 
-__device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                         int* status, int code) {
-  if (ptx::mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  while (!ptx::mbar_try_wait(bar, parity)) {
-    if (*abort_flag) return false;
-    if (clock64() - t0 > kWaitLimitCycles) {
-      *abort_flag = 1;
-      atomicCAS(status, 0, code);
-      return false;
-    }
-  }
-  return true;
-}
-
-template <bool kBf16>
-__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
-  if (kBf16) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&v);
-  } else {
-    __half2 v = __floats2half2_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&v);
-  }
-}
-
-__device__ __forceinline__ void named_bar_sync(int id, int threads) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
-}
-
 constexpr int kTileInterior = 1, kTileBoundary = 2;
 
 // Per-item constants of the column-tile walk and classification, held in registers by the load
@@ -300,7 +270,7 @@ struct TileWalk {
   }
 };
 
-template <int D, bool kBf16, int NDIM, bool kKeyRows>
+template <int D, int kType, int NDIM, bool kKeyRows>
 __global__ void __launch_bounds__(kThreads, 1)
 fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant__ CUtensorMap tm_r2,
                const __grid_constant__ CUtensorMap tm_c1, const __grid_constant__ CUtensorMap tm_c2,
@@ -310,7 +280,7 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
   constexpr int kTileBytes = SM::kTileBytes;
   constexpr int kDBlocks = D / 64;
   constexpr int kBlockBytes = kTile * 128;
-  typedef typename std::conditional<kBf16, __nv_bfloat16, __half>::type T;
+  typedef typename std::conditional<kType == kTyBf16, __nv_bfloat16, __half>::type T;
 
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* row_sm = smem + SM::kRowOff;
@@ -366,30 +336,8 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
     }
     ptx::fence_barrier_init();
   }
-  // Per-axis prefix bit tables over the COLUMN tile: pref[off_a + x] has bit j set iff the
-  // in-tile coordinate of column j along axis a is < x (columns ordered axis 0 fastest).
-  {
-    int off = 0;
-    for (int a = 0; a < p.ndim; ++a) {
-      int below = 1;
-      for (int b = 0; b < a; ++b) below *= p.Tc[b];
-      for (int x = threadIdx.x; x <= p.Tc[a]; x += kThreads) {
-        uint32_t wds[4];
-#pragma unroll
-        for (int wd = 0; wd < 4; ++wd) {
-          uint32_t bits = 0;
-#pragma unroll 1
-          for (int j = 0; j < 32; ++j) {
-            const int t = ((wd * 32 + j) / below) % p.Tc[a];
-            if (t < x) bits |= 1u << j;
-          }
-          wds[wd] = bits;
-        }
-        pref[off + x] = make_uint4(wds[0], wds[1], wds[2], wds[3]);
-      }
-      off += p.Tc[a] + 1;
-    }
-  }
+  // per-axis prefix bit tables over the COLUMN tile, for the masks of boundary tiles
+  build_prefix_tables(pref, p.ndim, p.Tc, threadIdx.x, kThreads);
   if (warp == kMmaWarp) {
     ptx::tmem_alloc(tmem_slot, kTmemCols);
     ptx::tmem_relinquish();
@@ -497,23 +445,7 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
         }
         uint32_t mw = ~0u;  // mask bits of this thread's 32 columns (boundary tiles only)
         if (!interior) {
-          uint4 mk = make_uint4(~0u, ~0u, ~0u, ~0u);
-          int off = 0;
-#pragma unroll
-          for (int a = 0; a < B200NA_MAX_DIM; ++a) {
-            if (a < NDIM) {
-              const int lo = imin(imax(lo_a[a] - base3[a], 0), p.Tc[a]);
-              const int hi = imin(imax(hi_a[a] - base3[a], 0), p.Tc[a]);
-              const uint4 ph = pref[off + hi];
-              const uint4 pl = pref[off + lo];
-              const bool none = hi <= lo;
-              mk.x &= none ? 0u : (ph.x & ~pl.x);
-              mk.y &= none ? 0u : (ph.y & ~pl.y);
-              mk.z &= none ? 0u : (ph.z & ~pl.z);
-              mk.w &= none ? 0u : (ph.w & ~pl.w);
-              off += p.Tc[a] + 1;
-            }
-          }
+          const uint4 mk = tile_mask<NDIM>(pref, p.Tc, lo_a, hi_a, base3);
           mw = part == 0 ? mk.x : (part == 1 ? mk.y : (part == 2 ? mk.z : mk.w));
         }
         if (!__all_sync(0xffffffffu, wait_bar(bars.sdp_full, ph_sdp, abort_flag, p.status,
@@ -549,8 +481,8 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
             }
             const float s0 = p0 * (__uint_as_float(dr[j]) - d0);
             const float s1 = p1 * (__uint_as_float(dr[j + 1]) - d1);
-            pk[j >> 1] = pack2<kBf16>(p0, p1);
-            dk[j >> 1] = pack2<kBf16>(s0, s1);
+            pk[j >> 1] = pack2<kType>(p0, p1);
+            dk[j >> 1] = pack2<kType>(s0, s1);
           }
           if (kKeyRows) ptx::tmem_st8(my_s + ch * 8, pk);
           ptx::tmem_st8(my_dp + ch * 8, dk);
@@ -582,10 +514,10 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
 #pragma unroll
           for (int v4 = 0; v4 < kCols / 8; ++v4) {
             uint4 o;
-            o.x = pack2<kBf16>(__uint_as_float(orr[v4 * 8 + 0]) * mul, __uint_as_float(orr[v4 * 8 + 1]) * mul);
-            o.y = pack2<kBf16>(__uint_as_float(orr[v4 * 8 + 2]) * mul, __uint_as_float(orr[v4 * 8 + 3]) * mul);
-            o.z = pack2<kBf16>(__uint_as_float(orr[v4 * 8 + 4]) * mul, __uint_as_float(orr[v4 * 8 + 5]) * mul);
-            o.w = pack2<kBf16>(__uint_as_float(orr[v4 * 8 + 6]) * mul, __uint_as_float(orr[v4 * 8 + 7]) * mul);
+            o.x = pack2<kType>(__uint_as_float(orr[v4 * 8 + 0]) * mul, __uint_as_float(orr[v4 * 8 + 1]) * mul);
+            o.y = pack2<kType>(__uint_as_float(orr[v4 * 8 + 2]) * mul, __uint_as_float(orr[v4 * 8 + 3]) * mul);
+            o.z = pack2<kType>(__uint_as_float(orr[v4 * 8 + 4]) * mul, __uint_as_float(orr[v4 * 8 + 5]) * mul);
+            o.w = pack2<kType>(__uint_as_float(orr[v4 * 8 + 6]) * mul, __uint_as_float(orr[v4 * 8 + 7]) * mul);
             *reinterpret_cast<uint4*>(orow + v4 * 8) = o;
           }
         }
@@ -600,8 +532,8 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
   } else if (warp == kMmaWarp) {
     // =============================== MMA issue ==============================================
     if (lane == 0) {
-      constexpr uint32_t idesc_s = ptx::make_idesc(kBf16 ? 1 : 0, 0, 0, kTile, kTile);
-      constexpr uint32_t idesc_acc = ptx::make_idesc(kBf16 ? 1 : 0, 0, 1, kTile, D);
+      constexpr uint32_t idesc_s = ptx::make_idesc(kType == kTyBf16 ? 1 : 0, 0, 0, kTile, kTile);
+      constexpr uint32_t idesc_acc = ptx::make_idesc(kType == kTyBf16 ? 1 : 0, 0, 1, kTile, D);
       constexpr uint32_t desc_hi = ptx::smem_desc_hi_sw128();
       const uint32_t row_base = ptx::smem_u32(row_sm);
       const uint32_t col_base = ptx::smem_u32(col_sm);
@@ -797,9 +729,10 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
 
 template <int D, bool kBf16, bool kKeyRows>
 const void* bwd_kernel_for_ndim(int ndim) {
-  if (ndim == 1) return (const void*)fna_bwd_kernel<D, kBf16, 1, kKeyRows>;
-  if (ndim == 2) return (const void*)fna_bwd_kernel<D, kBf16, 2, kKeyRows>;
-  return (const void*)fna_bwd_kernel<D, kBf16, 3, kKeyRows>;
+  constexpr int kType = kBf16 ? kTyBf16 : kTyF16;
+  if (ndim == 1) return (const void*)fna_bwd_kernel<D, kType, 1, kKeyRows>;
+  if (ndim == 2) return (const void*)fna_bwd_kernel<D, kType, 2, kKeyRows>;
+  return (const void*)fna_bwd_kernel<D, kType, 3, kKeyRows>;
 }
 const void* bwd_kernel_variant(int D, bool bf16, int ndim, bool key_rows) {
   if (D == 128) {

@@ -24,6 +24,7 @@
 #include <type_traits>
 
 #include "common.cuh"
+#include "fna_device.cuh"
 #include "fna_host.cuh"
 #include "ptx.cuh"
 
@@ -44,7 +45,6 @@ constexpr int kTmemCols = 512;
 constexpr int kDescSlots = 4;     // work-item descriptors the load warp may run ahead by
 constexpr int kDescBytes = 128;
 constexpr int kTileRecs = 8;      // per-tile records in flight (more than the K/V ring holds tiles)
-constexpr long long kWaitLimitCycles = 4000000000ll;  // ~2 s at 2 GHz
 constexpr float kRescaleThreshold = 8.0f;              // log2 units
 
 // status word: (role << 8) | barrier id, role 1 = softmax, 2 = mma, 3 = load, 4 = setup
@@ -307,22 +307,6 @@ struct Bars {
   uint64_t* kv_empty; // [stages]
 };
 
-// Bounded mbarrier wait. Returns false when the CTA is draining (this or another wait expired).
-__device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                         int* status, int code) {
-  if (ptx::mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  while (!ptx::mbar_try_wait(bar, parity)) {
-    if (*abort_flag) return false;
-    if (clock64() - t0 > kWaitLimitCycles) {
-      *abort_flag = 1;
-      atomicCAS(status, 0, code);
-      return false;
-    }
-  }
-  return true;
-}
-
 // Consumer side of the work-item descriptor ring: waits for descriptor number `seq` and returns
 // it in place (nullptr when the CTA is draining). The slot stays valid until every consumer has
 // called release_item for it; the ring is deeper than the number of items in flight, so holding
@@ -339,45 +323,6 @@ __device__ __forceinline__ const Item* fetch_item(const uint8_t* desc_sm, const 
 }
 __device__ __forceinline__ void release_item(const Bars& bars, uint32_t seq) {
   ptx::mbar_arrive(bars.desc_empty + seq % kDescSlots);
-}
-
-// Operand element types of the kernel template.
-enum : int { kTyF16 = 0, kTyBf16 = 1, kTyE4m3 = 2, kTyE5m2 = 3 };
-
-template <int kType>
-__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
-  if (kType == kTyBf16) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&v);
-  } else {
-    __half2 v = __floats2half2_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&v);
-  }
-}
-// 16 bytes of output elements from fp32 values scaled by `mul`: 8 (16-bit) or 16 (8-bit) values.
-template <int kType>
-__device__ __forceinline__ uint4 pack_out16(const uint32_t* f, float mul) {
-  uint4 o;
-  if (kType >= kTyE4m3) {
-    uint32_t w[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float a = __uint_as_float(f[4 * i]) * mul, b = __uint_as_float(f[4 * i + 1]) * mul,
-                  c = __uint_as_float(f[4 * i + 2]) * mul, d = __uint_as_float(f[4 * i + 3]) * mul;
-      w[i] = kType == kTyE4m3 ? ptx::pack4_e4m3(a, b, c, d) : ptx::pack4_e5m2(a, b, c, d);
-    }
-    o = make_uint4(w[0], w[1], w[2], w[3]);
-  } else {
-    o.x = pack2<kType>(__uint_as_float(f[0]) * mul, __uint_as_float(f[1]) * mul);
-    o.y = pack2<kType>(__uint_as_float(f[2]) * mul, __uint_as_float(f[3]) * mul);
-    o.z = pack2<kType>(__uint_as_float(f[4]) * mul, __uint_as_float(f[5]) * mul);
-    o.w = pack2<kType>(__uint_as_float(f[6]) * mul, __uint_as_float(f[7]) * mul);
-  }
-  return o;
-}
-
-__device__ __forceinline__ void named_bar_sync(int id, int threads) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
 // Advances the colexicographic kv-tile walk by one tile (no divisions on the per-tile path).
@@ -469,30 +414,8 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     }
     ptx::fence_barrier_init();
   }
-  // Per-axis prefix bit tables: pref[off_a + x] has bit j set iff the in-tile coordinate of
-  // column j along axis a is < x (columns are ordered colexicographically over Tkv).
-  {
-    int off = 0;
-    for (int a = 0; a < p.ndim; ++a) {
-      int below = 1;
-      for (int b = 0; b < a; ++b) below *= p.Tkv[b];
-      for (int x = threadIdx.x; x <= p.Tkv[a]; x += kThreads) {
-        uint32_t wds[4];
-#pragma unroll
-        for (int wd = 0; wd < 4; ++wd) {
-          uint32_t bits = 0;
-#pragma unroll 1
-          for (int j = 0; j < 32; ++j) {
-            const int t = ((wd * 32 + j) / below) % p.Tkv[a];
-            if (t < x) bits |= 1u << j;
-          }
-          wds[wd] = bits;
-        }
-        pref[off + x] = make_uint4(wds[0], wds[1], wds[2], wds[3]);
-      }
-      off += p.Tkv[a] + 1;
-    }
-  }
+  // per-axis prefix bit tables over the key/value tile, for the masks of boundary tiles
+  build_prefix_tables(pref, p.ndim, p.Tkv, threadIdx.x, kThreads);
   if (warp == kMmaWarp) {
     ptx::tmem_alloc(tmem_slot, kTmemCols);
     ptx::tmem_relinquish();
@@ -586,24 +509,7 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           mw1 = v1 >= 32 ? ~0u : ((1u << v1) - 1u);
         } else if (!interior) {
           const int base3[B200NA_MAX_DIM] = {rec.y, rec.z, rec.w};
-          uint4 mk = make_uint4(~0u, ~0u, ~0u, ~0u);
-          int off = 0;
-#pragma unroll
-          for (int a = 0; a < B200NA_MAX_DIM; ++a) {
-            if (a < NDIM) {
-              const int base = base3[a];
-              const int lo = imin(imax(ws[a] - base, 0), p.Tkv[a]);
-              const int hi = imin(imax(we[a] - base, 0), p.Tkv[a]);
-              const uint4 ph = pref[off + hi];
-              const uint4 pl = pref[off + lo];
-              const bool none = hi <= lo;
-              mk.x &= none ? 0u : (ph.x & ~pl.x);
-              mk.y &= none ? 0u : (ph.y & ~pl.y);
-              mk.z &= none ? 0u : (ph.z & ~pl.z);
-              mk.w &= none ? 0u : (ph.w & ~pl.w);
-              off += p.Tkv[a] + 1;
-            }
-          }
+          const uint4 mk = tile_mask<NDIM>(pref, p.Tkv, ws, we, base3);
           mw0 = part ? mk.z : mk.x;
           mw1 = part ? mk.w : mk.y;
         }
