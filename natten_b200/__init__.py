@@ -11,6 +11,7 @@ from .functional import (BACKEND_NAME, FMHA_BACKEND_NAME, attention, choose_tile
                          neighborhood_attention_generic, token_permute_operation,
                          token_unpermute_operation)
 
+from .host_io import na_forward_from_host  # noqa: E402
 from .modules import (NeighborhoodAttention1D, NeighborhoodAttention2D,  # noqa: E402
                       NeighborhoodAttention3D)
 
@@ -18,6 +19,7 @@ __version__ = "0.1.0"
 __all__ = [
     "na1d", "na2d", "na3d", "attention", "merge_attentions", "neighborhood_attention_generic",
     "NeighborhoodAttention1D", "NeighborhoodAttention2D", "NeighborhoodAttention3D",
+    "na_forward_from_host",
     "token_permute_operation", "token_unpermute_operation", "fna_forward_op",
     "fna_forward_permuted", "fna_forward_direct", "direct_layout_supported", "na_forward_fused", "fused_workspace_bytes", "choose_tile_shapes", "BACKEND_NAME", "FMHA_BACKEND_NAME",
 ]

@@ -82,3 +82,21 @@ def test_ops_without_a_formula_refuse_to_differentiate():
     m, _ = nb.merge_attentions([o, o], [l, l])
     with pytest.raises(RuntimeError):
         m.float().sum().backward()
+
+
+def test_host_operand_entry_point_matches_the_device_call():
+    torch.manual_seed(9)
+    q, k, v = (torch.randn(5, 20, 24, 2, 64).bfloat16().pin_memory() for _ in range(3))
+    ak, av = (torch.randn(5, 33, 2, 64).bfloat16().pin_memory() for _ in range(2))
+    args = dict(kernel_size=(5, 7), stride=(1, 2), dilation=(2, 1), is_causal=(False, True))
+    want_o, want_l = nb.na2d(q.cuda(), k.cuda(), v.cuda(), additional_keys=ak.cuda(),
+                             additional_values=av.cuda(), return_lse=True, **args)
+    for chunk in (1, 2, 8):
+        out, lse = nb.na_forward_from_host(q, k, v, additional_keys=ak, additional_values=av,
+                                           batch_chunk=chunk, **args)
+        torch.cuda.current_stream().synchronize()
+        assert L.device_status() == 0
+        assert out.is_pinned() and not out.is_cuda
+        assert torch.equal(out, want_o.cpu()) and torch.equal(lse, want_l.cpu())
+    with pytest.raises(ValueError):
+        nb.na_forward_from_host(q.cuda(), k, v, **args)
