@@ -508,12 +508,12 @@ def run_backward(args, cfg, nb, L, q, k, v, ak, av, b_local, h_local, rank, worl
     d_out = torch.randn(out.shape, device=out.device).to(out.dtype)
     causal = [bool(c) for c in ca]
     q_tile, kv_tile = F.choose_backward_tile_shapes(shape, ks, st, di, ca)
-    tensor_core = not n_extra and F.backward_layout_supported(q_tile, kv_tile, di)
+    tensor_core = F.backward_layout_supported(q_tile, kv_tile, di)
 
     def step():
         if tensor_core:
-            return ops.na_backward_direct(q, k, v, out, d_out, lse, list(ks), list(st), list(di),
-                                          causal, D ** -0.5, list(q_tile), list(kv_tile))
+            return ops.na_backward_direct(q, k, v, out, d_out, lse, ak, av, list(ks), list(st),
+                                          list(di), causal, D ** -0.5, list(q_tile), list(kv_tile))
         return ops.na_backward_simt(q, k, v, out, d_out, lse, ak, av, list(ks), list(st), list(di),
                                     causal, D ** -0.5)
 

@@ -270,15 +270,18 @@ B200NA_API int b200na_na_backward_simt(
  * same kernel for dK and dV (a CTA per 128-key tile streams the query tiles that attend it). No
  * atomics: results are deterministic (the reference's Blackwell backward has no deterministic mode,
  * src/natten/backends/blackwell_fna.py:209-215).
- *   Tensors as in b200na_na_backward_simt; dtype F16 or BF16; D in {64, 128}; no extra tokens.
+ *   Tensors as in b200na_na_backward_simt (extra tokens and their gradients included: they are
+ *   appended to every query's columns in the dQ pass and get a third pass of the same kernel,
+ *   rows = the extra tokens, columns = all queries); dtype F16 or BF16; D in {64, 128}.
  *   q_tile / kv_tile: prod = 128 each; tile[a] * dilation[a] <= 256 and dilation[a] <= 8,
  *   otherwise B200NA_ERR_UNSUPPORTED (use b200na_na_backward_simt then).
  */
 B200NA_API int b200na_na_backward_direct(
     const void* q, const void* k, const void* v, const void* o, const void* d_out, const float* lse,
-    void* dq, void* dk, void* dv, float* delta_scratch, int ndim, const int* shape,
-    const int* kernel, const int* stride, const int* dilation, const int* causal,
-    const int* q_tile, const int* kv_tile, int B, int Hq, int Hkv, int D, int dtype, float scale,
+    const void* add_k, const void* add_v, int n_extra, void* dq, void* dk, void* dv, void* d_add_k,
+    void* d_add_v, float* delta_scratch, int ndim, const int* shape, const int* kernel,
+    const int* stride, const int* dilation, const int* causal, const int* q_tile,
+    const int* kv_tile, int B, int Hq, int Hkv, int D, int dtype, float scale,
     b200na_stream_t stream);
 
 /*

@@ -71,7 +71,7 @@ def _load() -> ctypes.CDLL:
     lib.b200na_na_backward_simt.argtypes = [c_void_p] * 8 + [c_int] + [c_void_p] * 6 + [
         c_int, ip, ip, ip, ip, ip, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]
     lib.b200na_na_backward_direct.restype = c_int
-    lib.b200na_na_backward_direct.argtypes = [c_void_p] * 10 + [
+    lib.b200na_na_backward_direct.argtypes = [c_void_p] * 8 + [c_int] + [c_void_p] * 6 + [
         c_int, ip, ip, ip, ip, ip, ip, ip, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]
     lib.b200na_fna_forward_sharded.restype = c_int
     lib.b200na_fna_forward_sharded.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,

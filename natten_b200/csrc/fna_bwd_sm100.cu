@@ -71,6 +71,12 @@ struct BwdTcParams {
   int Rr[B200NA_MAX_DIM];   // row tiles per axis per dilation group
   int G;                    // prod(dil)
   int B, Hq, Hkv, rep;
+  int n_extra;              // pass dQ: extra key/value tokens appended to every query's columns
+  int extra_tiles;          // ceil(n_extra / 128)
+  int dense_rows;           // pass over the extra tokens: rows = the n_extra tokens of a batch
+                            // entry (one axis), columns = all its queries, every valid row
+                            // interacts with every column; X[0] is then the COLUMN extent
+  int row_extent;           // dense_rows: number of rows (n_extra)
   int n_rtiles;             // row tiles per (batch, group, head)
   int row_heads;            // heads the row tiles carry: Hq (pass dQ) or Hkv (pass dKdV)
   long long total_work;     // n_rtiles * row_heads * B * G
@@ -93,7 +99,9 @@ struct Item {
   // column tiles [int_lo, int_hi) of an axis lie inside the (inverse) window of every row
   int int_lo[B200NA_MAX_DIM];
   int int_hi[B200NA_MAX_DIM];
-  int n_tiles;                // column tiles to visit (times the heads of the group in pass dKdV)
+  int n_tiles;                // column tiles to visit (times the heads of the group in pass dKdV),
+                              // extra-token tiles included
+  int n_na;                   // neighborhood column tiles (without the extra-token tiles)
   int n_per_head;             // column tiles per head
   int skip;
 };
@@ -132,7 +140,14 @@ __device__ __forceinline__ void inv_window(const BwdTcParams& p, int a, int j, i
 template <bool kKeyRows>
 __device__ __forceinline__ void row_span(const BwdTcParams& p, int a, int i, int L, int& lo,
                                          int& hi) {
-  if (kKeyRows) inv_window(p, a, i, L, lo, hi); else fwd_window(p, a, i < L ? i : L - 1, L, lo, hi);
+  if (kKeyRows && p.dense_rows) {  // an extra token: every query attends it
+    lo = 0;
+    hi = i < p.row_extent ? L : 0;
+  } else if (kKeyRows) {
+    inv_window(p, a, i, L, lo, hi);
+  } else {
+    fwd_window(p, a, i < L ? i : L - 1, L, lo, hi);
+  }
 }
 
 struct WorkCursor {
@@ -183,10 +198,11 @@ __device__ __forceinline__ void decode_item(const BwdTcParams& p, const WorkCurs
         r = rl - rn * p.Rr[a];
         rl = rn;
       }
+      const int Lr = (kKeyRows && p.dense_rows) ? p.row_extent : L;  // extent of the rows
       const int lo = r * p.Tr[a];
-      if (lo >= L) it.skip = 1;  // the tile lies beyond this dilation group
+      if (lo >= Lr) it.skip = 1;  // the tile lies beyond this dilation group
       it.r_lo[a] = lo;
-      const int last = (lo + p.Tr[a] - 1 < L) ? lo + p.Tr[a] - 1 : L - 1;  // last real row
+      const int last = (lo + p.Tr[a] - 1 < Lr) ? lo + p.Tr[a] - 1 : Lr - 1;  // last real row
       int s_lo, e_lo, s_hi, e_hi;
       row_span<kKeyRows>(p, a, lo, L, s_lo, e_lo);
       row_span<kKeyRows>(p, a, last, L, s_hi, e_hi);
@@ -199,14 +215,15 @@ __device__ __forceinline__ void decode_item(const BwdTcParams& p, const WorkCurs
       it.int_lo[a] = (s_hi + Tc - 1) / Tc;
       it.int_hi[a] = e_lo / Tc;
       // rows past the extent (padding) interact with nothing: no tile is mask-free then
-      if (lo + p.Tr[a] > L) it.int_hi[a] = it.int_lo[a];
+      if (lo + p.Tr[a] > Lr) it.int_hi[a] = it.int_lo[a];
       it.n_per_head *= it.c_n[a];
     } else {
       it.g[a] = 0; it.L[a] = 1; it.r_lo[a] = 0; it.c_t0[a] = 0; it.c_n[a] = 1;
       it.int_lo[a] = 0; it.int_hi[a] = 1;
     }
   }
-  it.n_tiles = it.n_per_head * (kKeyRows ? p.rep : 1);
+  it.n_na = it.n_per_head * (kKeyRows ? p.rep : 1);
+  it.n_tiles = it.n_na + (kKeyRows ? 0 : p.extra_tiles);
 }
 
 template <int D>
@@ -233,7 +250,7 @@ struct Bars {
   uint64_t *desc_full, *desc_empty, *rec_full, *rec_empty, *c_full, *c_empty;
 };
 
-constexpr int kTileInterior = 1, kTileBoundary = 2;
+constexpr int kTileInterior = 1, kTileBoundary = 2, kTileRagged = 3;
 
 // Per-item constants of the column-tile walk and classification, held in registers by the load
 // thread (all its instructions are dependent, so shared-memory reads per tile would add latency).
@@ -274,6 +291,7 @@ template <int D, int kType, int NDIM, bool kKeyRows>
 __global__ void __launch_bounds__(kThreads, 1)
 fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant__ CUtensorMap tm_r2,
                const __grid_constant__ CUtensorMap tm_c1, const __grid_constant__ CUtensorMap tm_c2,
+               const __grid_constant__ CUtensorMap tm_e1, const __grid_constant__ CUtensorMap tm_e2,
                const BwdTcParams p) {
   using SM = Smem<D>;
   constexpr int kStages = SM::kStages;
@@ -347,6 +365,10 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
     ptx::prefetch_tensormap(&tm_r2);
     ptx::prefetch_tensormap(&tm_c1);
     ptx::prefetch_tensormap(&tm_c2);
+    if (p.extra_tiles) {
+      ptx::prefetch_tensormap(&tm_e1);
+      ptx::prefetch_tensormap(&tm_e2);
+    }
   }
   ptx::tc_fence_before_sync();
   __syncthreads();
@@ -393,9 +415,10 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
       for (int a = 0; a < B200NA_MAX_DIM; ++a) {
         if (a < NDIM) {
           const int i = it.r_lo[a] + tr[a];
-          row_valid = row_valid && i < it.L[a];
+          const bool dense = kKeyRows && p.dense_rows;
+          row_valid = row_valid && i < (dense ? p.row_extent : it.L[a]);
           row_span<kKeyRows>(p, a, i, it.L[a], lo_a[a], hi_a[a]);
-          row_tok = row_tok * p.X[a] + (i * p.dil[a] + it.g[a]);
+          row_tok = row_tok * (dense ? p.row_extent : p.X[a]) + (i * p.dil[a] + it.g[a]);
         } else {
           lo_a[a] = 0; hi_a[a] = 1;
         }
@@ -444,7 +467,11 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
           named_bar_sync(1, kSoftmaxThreads);
         }
         uint32_t mw = ~0u;  // mask bits of this thread's 32 columns (boundary tiles only)
-        if (!interior) {
+        if (rec.x == kTileRagged) {
+          // last tile of the extra tokens: rec.y of its columns exist
+          const int vcols = imin(imax(rec.y - part * 32, 0), 32);
+          mw = vcols >= 32 ? ~0u : ((1u << vcols) - 1u);
+        } else if (!interior) {
           const uint4 mk = tile_mask<NDIM>(pref, p.Tc, lo_a, hi_a, base3);
           mw = part == 0 ? mk.x : (part == 1 ? mk.y : (part == 2 ? mk.z : mk.w));
         }
@@ -671,13 +698,24 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
         int in_head = 0;
         const Item* next = nullptr;
         const int publish_at = imin(kStages - 1, n_tiles - 1);
+        const int n_na = it.n_na;
         for (int iter = 0; iter < n_tiles && alive; ++iter) {
-          const int k0 = tc[0] * p.Tc[0], k1 = NDIM > 1 ? tc[1] * p.Tc[1] : 0,
-                    k2 = NDIM > 2 ? tc[2] * p.Tc[2] : 0;
-          const int4 rec = make_int4(tw.template interior<NDIM>(tc) ? kTileInterior : kTileBoundary,
-                                     k0, k1, k2);
-          const int x0 = k0 * p.dil[0] + g0, x1 = k1 * p.dil[1] + g1, x2 = k2 * p.dil[2] + g2;
-          tw.template next<NDIM>(tc);
+          // pass dQ: the extra tokens follow the neighborhood tiles; every query attends them
+          const bool is_extra = iter >= n_na;
+          int4 rec;
+          int x0, x1, x2;
+          if (is_extra) {
+            const int e0 = (iter - n_na) * kTile, valid = p.n_extra - e0;
+            rec = make_int4(valid >= kTile ? kTileInterior : kTileRagged, valid, 0, 0);
+            x0 = e0; x1 = 0; x2 = 0;
+          } else {
+            const int k0 = tc[0] * p.Tc[0], k1 = NDIM > 1 ? tc[1] * p.Tc[1] : 0,
+                      k2 = NDIM > 2 ? tc[2] * p.Tc[2] : 0;
+            rec = make_int4(tw.template interior<NDIM>(tc) ? kTileInterior : kTileBoundary, k0, k1,
+                            k2);
+            x0 = k0 * p.dil[0] + g0; x1 = k1 * p.dil[1] + g1; x2 = k2 * p.dil[2] + g2;
+            tw.template next<NDIM>(tc);
+          }
           if (!wait_bar(bars.rec_empty + tseq % kTileRecs, ((tseq / kTileRecs) & 1) ^ 1, abort_flag,
                         p.status, (7 << 8) | kStRecEmpty)) { alive = false; break; }
           tile_rec[tseq % kTileRecs] = rec;
@@ -689,10 +727,10 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
           ptx::mbar_arrive_expect_tx(bars.c_full + slot, 2 * kTileBytes);
           uint8_t* dst = col_sm + slot * 2 * kTileBytes;
           for (int db = 0; db < kDBlocks; ++db) {
-            ptx::tma_load_5d(dst + db * kBlockBytes, &tm_c1, bars.c_full + slot,
-                             col_head * D + db * 64, x0, x1, x2, b);
-            ptx::tma_load_5d(dst + kTileBytes + db * kBlockBytes, &tm_c2, bars.c_full + slot,
-                             col_head * D + db * 64, x0, x1, x2, b);
+            ptx::tma_load_5d(dst + db * kBlockBytes, is_extra ? &tm_e1 : &tm_c1,
+                             bars.c_full + slot, col_head * D + db * 64, x0, x1, x2, b);
+            ptx::tma_load_5d(dst + kTileBytes + db * kBlockBytes, is_extra ? &tm_e2 : &tm_c2,
+                             bars.c_full + slot, col_head * D + db * 64, x0, x1, x2, b);
           }
           if (++slot == kStages) {
             slot = 0;
@@ -772,22 +810,28 @@ int ensure_smem_attribute(const void* fn, int D) {
 
 extern "C" B200NA_API int b200na_na_backward_direct(
     const void* q, const void* k, const void* v, const void* o, const void* d_out, const float* lse,
-    void* dq, void* dk, void* dv, float* delta_scratch, int ndim, const int* shape,
-    const int* kernel, const int* stride, const int* dilation, const int* causal,
-    const int* q_tile, const int* kv_tile, int B, int Hq, int Hkv, int D, int dtype, float scale,
+    const void* add_k, const void* add_v, int n_extra, void* dq, void* dk, void* dv, void* d_add_k,
+    void* d_add_v, float* delta_scratch, int ndim, const int* shape, const int* kernel,
+    const int* stride, const int* dilation, const int* causal, const int* q_tile,
+    const int* kv_tile, int B, int Hq, int Hkv, int D, int dtype, float scale,
     b200na_stream_t stream_) {
   using namespace b200na;
   if (!q || !k || !v || !o || !d_out || !lse || !dq || !dk || !dv || !delta_scratch || !shape ||
       !kernel || !q_tile || !kv_tile)
     return B200NA_ERR_INVALID_ARGUMENT;
+  if (n_extra < 0 || (n_extra > 0 && (!add_k || !add_v || !d_add_k || !d_add_v)))
+    return B200NA_ERR_INVALID_ARGUMENT;
   if (B < 1 || Hq < 1 || Hkv < 1 || Hq % Hkv != 0) return B200NA_ERR_INVALID_ARGUMENT;
   if (dtype != B200NA_F16 && dtype != B200NA_BF16) return B200NA_ERR_UNSUPPORTED;
   if (D != 64 && D != 128) return B200NA_ERR_UNSUPPORTED;
   if (!(scale > 0.f)) return B200NA_ERR_INVALID_ARGUMENT;
-  const uintptr_t al = reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) |
-                       reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(d_out) |
-                       reinterpret_cast<uintptr_t>(dq) | reinterpret_cast<uintptr_t>(dk) |
-                       reinterpret_cast<uintptr_t>(dv);
+  uintptr_t al = reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) |
+                 reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(d_out) |
+                 reinterpret_cast<uintptr_t>(dq) | reinterpret_cast<uintptr_t>(dk) |
+                 reinterpret_cast<uintptr_t>(dv);
+  if (n_extra > 0)
+    al |= reinterpret_cast<uintptr_t>(add_k) | reinterpret_cast<uintptr_t>(add_v) |
+          reinterpret_cast<uintptr_t>(d_add_k) | reinterpret_cast<uintptr_t>(d_add_v);
   if (al % 16 != 0) return B200NA_ERR_ALIGNMENT;
   NaAxes ax;
   int rc = fill_axes(ax, ndim, shape, kernel, stride, dilation, causal);
@@ -829,18 +873,51 @@ extern "C" B200NA_API int b200na_na_backward_direct(
   if ((rc = fna_make_tensor_map_direct(&mdo, d_out, dtype, B, base.X, Hq, D, tq, base.dil)) != B200NA_OK) return rc;
   if ((rc = fna_make_tensor_map_direct(&mk, k, dtype, B, base.X, Hkv, D, tkv, base.dil)) != B200NA_OK) return rc;
   if ((rc = fna_make_tensor_map_direct(&mv, v, dtype, B, base.X, Hkv, D, tkv, base.dil)) != B200NA_OK) return rc;
+  // extra tokens [B, n_extra, Hkv, D] are a one-axis layout of their own; flat views of Q / dO
+  // ([B, N, Hq, D]) serve the pass that computes their gradients
+  const int flat_tile[B200NA_MAX_DIM] = {kTile, 1, 1}, ones[B200NA_MAX_DIM] = {1, 1, 1};
+  const int x_extra[B200NA_MAX_DIM] = {n_extra > 0 ? n_extra : 1, 1, 1};
+  const int x_flat[B200NA_MAX_DIM] = {(int)tokens, 1, 1};
+  CUtensorMap mek = mk, mev = mv, mqf = mq, mdof = mdo;
+  if (n_extra > 0) {
+    if ((rc = fna_make_tensor_map_direct(&mek, add_k, dtype, B, x_extra, Hkv, D, flat_tile, ones)) != B200NA_OK) return rc;
+    if ((rc = fna_make_tensor_map_direct(&mev, add_v, dtype, B, x_extra, Hkv, D, flat_tile, ones)) != B200NA_OK) return rc;
+    if ((rc = fna_make_tensor_map_direct(&mqf, q, dtype, B, x_flat, Hq, D, flat_tile, ones)) != B200NA_OK) return rc;
+    if ((rc = fna_make_tensor_map_direct(&mdof, d_out, dtype, B, x_flat, Hq, D, flat_tile, ones)) != B200NA_OK) return rc;
+  }
 
   if ((rc = launch_delta(o, d_out, delta_scratch, tokens * B * Hq, D, dtype, stream)) != B200NA_OK)
     return rc;
 
-  for (int pass = 0; pass < 2; ++pass) {
-    const bool key_rows = pass == 1;
+  // pass 0: dQ (rows Q, dO; columns K, V, then the extra tokens); pass 1: dK, dV (rows K, V;
+  // columns Q, dO); pass 2, with extra tokens only: their gradients (rows = the extra tokens,
+  // columns = all queries of the batch entry, flat)
+  for (int pass = 0; pass < (n_extra > 0 ? 3 : 2); ++pass) {
+    const bool key_rows = pass >= 1;
+    const bool dense = pass == 2;
     BwdTcParams p = base;
+    int kernel_ndim = ndim;
+    if (dense) {
+      kernel_ndim = 1;
+      p.ndim = 1;
+      p.G = 1;
+      p.dense_rows = 1;
+      p.row_extent = n_extra;
+      for (int a = 0; a < B200NA_MAX_DIM; ++a) {
+        p.X[a] = a == 0 ? (int)tokens : 1;
+        p.kernel[a] = 1; p.stride[a] = 1; p.dil[a] = 1; p.causal[a] = 0;
+      }
+    }
+    if (pass == 0) {
+      p.n_extra = n_extra;
+      p.extra_tiles = (n_extra + kTile - 1) / kTile;
+    }
     long long n_rtiles = 1;
     for (int a = 0; a < B200NA_MAX_DIM; ++a) {
-      p.Tr[a] = key_rows ? tkv[a] : tq[a];
-      p.Tc[a] = key_rows ? tq[a] : tkv[a];
-      const int need = (p.X[a] + p.dil[a] - 1) / p.dil[a];  // largest dilation group
+      p.Tr[a] = dense ? flat_tile[a] : (key_rows ? tkv[a] : tq[a]);
+      p.Tc[a] = dense ? flat_tile[a] : (key_rows ? tq[a] : tkv[a]);
+      // rows per axis: the largest dilation group, or the extra tokens
+      const int need = dense ? (a == 0 ? n_extra : 1) : (p.X[a] + p.dil[a] - 1) / p.dil[a];
       p.Rr[a] = (need + p.Tr[a] - 1) / p.Tr[a];
       n_rtiles *= p.Rr[a];
     }
@@ -848,15 +925,16 @@ extern "C" B200NA_API int b200na_na_backward_direct(
     p.n_rtiles = (int)n_rtiles;
     p.row_heads = key_rows ? Hkv : Hq;
     p.total_work = n_rtiles * p.row_heads * B * p.G;
-    p.out0 = key_rows ? dk : dq;
-    p.out1 = key_rows ? dv : nullptr;
-    const void* fn = bwd_kernel_variant(D, dtype == B200NA_BF16, ndim, key_rows);
+    p.out0 = dense ? d_add_k : (key_rows ? dk : dq);
+    p.out1 = dense ? d_add_v : (key_rows ? dv : nullptr);
+    const void* fn = bwd_kernel_variant(D, dtype == B200NA_BF16, kernel_ndim, key_rows);
     if ((rc = ensure_smem_attribute(fn, D)) != B200NA_OK) return rc;
     const int grid = (int)(p.total_work < sms ? p.total_work : sms);
-    // pass dQ: rows Q, dO and columns K, V; pass dKdV: rows K, V and columns Q, dO
-    void* args_q[] = {(void*)&mq, (void*)&mdo, (void*)&mk, (void*)&mv, (void*)&p};
-    void* args_k[] = {(void*)&mk, (void*)&mv, (void*)&mq, (void*)&mdo, (void*)&p};
-    B200NA_CUDA_TRY(cudaLaunchKernel(fn, dim3(grid), dim3(kThreads), key_rows ? args_k : args_q,
+    void* args_q[] = {(void*)&mq, (void*)&mdo, (void*)&mk, (void*)&mv, (void*)&mek, (void*)&mev, (void*)&p};
+    void* args_k[] = {(void*)&mk, (void*)&mv, (void*)&mq, (void*)&mdo, (void*)&mek, (void*)&mev, (void*)&p};
+    void* args_e[] = {(void*)&mek, (void*)&mev, (void*)&mqf, (void*)&mdof, (void*)&mek, (void*)&mev, (void*)&p};
+    B200NA_CUDA_TRY(cudaLaunchKernel(fn, dim3(grid), dim3(kThreads),
+                                     dense ? args_e : (key_rows ? args_k : args_q),
                                      D == 128 ? Smem<128>::kBytes : Smem<64>::kBytes, stream));
   }
   return B200NA_OK;

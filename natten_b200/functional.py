@@ -433,7 +433,7 @@ def _na_backward(ctx, d_out, d_lse):
     ak, av = ctx.saved_tensors[5:] if ctx.has_extra else (None, None)
     kernel_size, stride, dilation, is_causal, scale = ctx.na_args
     na_dim = query.dim() - 3
-    tensor_core = (not ctx.has_extra and query.dtype in (torch.float16, torch.bfloat16)
+    tensor_core = (query.dtype in (torch.float16, torch.bfloat16)
                    and query.shape[-1] in TENSOR_CORE_HEAD_DIMS
                    and not BACKWARD_ON_CUDA_CORES)
     if tensor_core:
@@ -442,11 +442,13 @@ def _na_backward(ctx, d_out, d_lse):
             is_causal)
         tensor_core = backward_layout_supported(q_tile, kv_tile, dilation)
     if tensor_core:
-        dq, dk, dv = ops.na_backward_direct(query, key, value, out, d_out.contiguous(), lse,
-                                            kernel_size, stride, dilation, is_causal, scale,
-                                            list(q_tile), list(kv_tile))
-        return (dq, dk, dv, None, None) + (None,) * 8
-    # fp32 operands, other head dims, extra tokens, boxes a tensor map cannot express
+        dq, dk, dv, dak, dav = ops.na_backward_direct(
+            query, key, value, out, d_out.contiguous(), lse, ak, av, kernel_size, stride, dilation,
+            is_causal, scale, list(q_tile), list(kv_tile))
+        if not ctx.has_extra:
+            dak = dav = None
+        return (dq, dk, dv, dak, dav) + (None,) * 8
+    # fp32 operands, other head dims, boxes a tensor map cannot express
     dq, dk, dv, dak, dav = ops.na_backward_simt(query, key, value, out, d_out.contiguous(), lse,
                                                 ak, av, kernel_size, stride, dilation, is_causal,
                                                 scale)

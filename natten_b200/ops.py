@@ -257,31 +257,40 @@ def na_backward_simt(query: Tensor, key: Tensor, value: Tensor, out: Tensor, d_o
     return dq, dk, dv, dak, dav
 
 
-def _na_backward_direct_fake(query, key, value, out, d_out, lse, kernel_size, stride, dilation,
-                             is_causal, scale, q_tile_shape, kv_tile_shape):
-    return torch.empty_like(query), torch.empty_like(key), torch.empty_like(value)
+def _na_backward_direct_fake(query, key, value, out, d_out, lse, additional_keys,
+                             additional_values, kernel_size, stride, dilation, is_causal, scale,
+                             q_tile_shape, kv_tile_shape):
+    extra = additional_keys if additional_keys is not None else key.new_empty((0,))
+    return (torch.empty_like(query), torch.empty_like(key), torch.empty_like(value),
+            torch.empty_like(extra), torch.empty_like(extra))
 
 
 @_op("na_backward_direct", _na_backward_direct_fake)
 def na_backward_direct(query: Tensor, key: Tensor, value: Tensor, out: Tensor, d_out: Tensor,
-                       lse: Tensor, kernel_size: List[int], stride: List[int], dilation: List[int],
-                       is_causal: List[bool], scale: float, q_tile_shape: List[int],
-                       kv_tile_shape: List[int]) -> Tuple[Tensor, Tensor, Tensor]:
-    """dQ, dK, dV on tensor cores (fp16/bf16, head dim 64/128, no extra tokens), caller's layout."""
-    dq, dk, dv = _na_backward_direct_fake(query, key, value, out, d_out, lse, kernel_size, stride,
-                                          dilation, is_causal, scale, q_tile_shape, kv_tile_shape)
+                       lse: Tensor, additional_keys: Optional[Tensor],
+                       additional_values: Optional[Tensor], kernel_size: List[int],
+                       stride: List[int], dilation: List[int], is_causal: List[bool], scale: float,
+                       q_tile_shape: List[int], kv_tile_shape: List[int]
+                       ) -> Tuple[Tensor, Tensor, Tensor, Tensor, Tensor]:
+    """dQ, dK, dV and the extra tokens' gradients (empty tensors when there are none) on tensor
+    cores (fp16/bf16, head dim 64/128), caller's layout."""
+    dq, dk, dv, dak, dav = _na_backward_direct_fake(
+        query, key, value, out, d_out, lse, additional_keys, additional_values, kernel_size,
+        stride, dilation, is_causal, scale, q_tile_shape, kv_tile_shape)
     na_dim = query.dim() - 3
+    n_extra = additional_keys.shape[1] if additional_keys is not None else 0
     delta = torch.empty(query.shape[:-1], dtype=torch.float32, device=query.device)
     with torch.cuda.device(query.device):
         _lib.check(_lib.lib.b200na_na_backward_direct(
-            _ptr(query), _ptr(key), _ptr(value), _ptr(out), _ptr(d_out), _ptr(lse), _ptr(dq),
-            _ptr(dk), _ptr(dv), _ptr(delta), na_dim, _lib.ints(query.shape[1:1 + na_dim]),
-            _lib.ints(kernel_size), _lib.ints(stride), _lib.ints(dilation),
-            _lib.ints(_flags(is_causal)), _lib.ints(q_tile_shape), _lib.ints(kv_tile_shape),
-            query.shape[0], query.shape[-2], key.shape[-2], query.shape[-1],
-            DTYPE_CODE[query.dtype], float(scale), _stream(query)), "b200na_na_backward_direct",
-            kernel_launches=3)
-    return dq, dk, dv
+            _ptr(query), _ptr(key), _ptr(value), _ptr(out), _ptr(d_out), _ptr(lse),
+            _ptr(additional_keys), _ptr(additional_values), n_extra, _ptr(dq), _ptr(dk), _ptr(dv),
+            _ptr(dak) if n_extra else None, _ptr(dav) if n_extra else None, _ptr(delta), na_dim,
+            _lib.ints(query.shape[1:1 + na_dim]), _lib.ints(kernel_size), _lib.ints(stride),
+            _lib.ints(dilation), _lib.ints(_flags(is_causal)), _lib.ints(q_tile_shape),
+            _lib.ints(kv_tile_shape), query.shape[0], query.shape[-2], key.shape[-2],
+            query.shape[-1], DTYPE_CODE[query.dtype], float(scale), _stream(query)),
+            "b200na_na_backward_direct", kernel_launches=4 if n_extra else 3)
+    return dq, dk, dv, dak, dav
 
 
 def _fmha_setup_context(ctx, inputs, output):

@@ -65,16 +65,21 @@ def test_layer_trains():
         assert p.grad is not None and torch.isfinite(p.grad).all() and p.grad.abs().max() > 0
 
 
-@pytest.mark.parametrize("shape,ks,st,di,ca,hq,hkv,D", [
-    ((700,), (65,), (3,), (1,), (True,), 2, 2, 128),
-    ((1000,), (33,), (1,), (2,), (False,), 4, 2, 64),            # dilation groups, GQA
-    ((40, 44), (7, 9), (1, 2), (2, 3), (False, True), 2, 1, 128),
-    ((64, 64), (16, 16), (8, 8), (1, 1), (False, False), 1, 1, 128),   # block-sparse windows
-    ((37, 51), (5, 5), (1, 1), (4, 8), (False, False), 2, 2, 64),
-    ((6, 20, 24), (3, 5, 8), (1, 1, 4), (1, 2, 1), (True, False, False), 2, 2, 128),
-    ((9, 11, 13), (3, 3, 3), (1, 1, 1), (3, 2, 4), (False, True, False), 4, 2, 64),
+@pytest.mark.parametrize("shape,ks,st,di,ca,hq,hkv,D,n_extra", [
+    ((700,), (65,), (3,), (1,), (True,), 2, 2, 128, 0),
+    ((1000,), (33,), (1,), (2,), (False,), 4, 2, 64, 0),            # dilation groups, GQA
+    ((40, 44), (7, 9), (1, 2), (2, 3), (False, True), 2, 1, 128, 0),
+    ((64, 64), (16, 16), (8, 8), (1, 1), (False, False), 1, 1, 128, 0),   # block-sparse windows
+    ((37, 51), (5, 5), (1, 1), (4, 8), (False, False), 2, 2, 64, 0),
+    ((6, 20, 24), (3, 5, 8), (1, 1, 4), (1, 2, 1), (True, False, False), 2, 2, 128, 0),
+    ((9, 11, 13), (3, 3, 3), (1, 1, 1), (3, 2, 4), (False, True, False), 4, 2, 64, 0),
+    ((32, 32), (8, 8), (4, 4), (1, 1), (False, False), 2, 2, 128, 256),   # config 4 scaled
+    ((30, 26), (5, 7), (1, 1), (2, 3), (False, True), 4, 2, 64, 130),     # ragged extras, GQA
+    ((700,), (65,), (3,), (1,), (True,), 2, 1, 128, 7),
+    ((6, 10, 12), (3, 4, 5), (1, 2, 1), (1, 1, 1), (True, False, False), 1, 1, 64, 300),
 ])
-def test_tensor_core_backward_against_oracle_and_cuda_core_kernels(shape, ks, st, di, ca, hq, hkv, D):
+def test_tensor_core_backward_against_oracle_and_cuda_core_kernels(shape, ks, st, di, ca, hq, hkv,
+                                                                   D, n_extra):
     """The tcgen05 backward (two passes of one kernel) against the oracle, and against the
     CUDA-core gradient kernels on the same inputs (independent implementations)."""
     import natten_b200.functional as F
@@ -83,20 +88,26 @@ def test_tensor_core_backward_against_oracle_and_cuda_core_kernels(shape, ks, st
     q = torch.randn(2, *shape, hq, D).bfloat16()
     k, v = (torch.randn(2, *shape, hkv, D).bfloat16() for _ in range(2))
     d_out = torch.randn(2, *shape, hq, D).bfloat16()
+    extras = [torch.randn(2, n_extra, hkv, D).bfloat16() for _ in range(2)] if n_extra else []
     assert F.backward_layout_supported(*F.choose_backward_tile_shapes(shape, ks, st, di, ca), di)
     grads = {}
     for mode in (False, True):
         F.BACKWARD_ON_CUDA_CORES = mode
         try:
-            leaves = [t.cuda().requires_grad_() for t in (q, k, v)]
-            out = fn(*leaves, kernel_size=ks, stride=st, dilation=di, is_causal=ca)
+            leaves = [t.cuda().requires_grad_() for t in [q, k, v] + extras]
+            out = fn(leaves[0], leaves[1], leaves[2], kernel_size=ks, stride=st, dilation=di,
+                     is_causal=ca, additional_keys=leaves[3] if n_extra else None,
+                     additional_values=leaves[4] if n_extra else None)
             out.backward(d_out.cuda())
             assert L.device_status() == 0
             grads[mode] = [t.grad.float().cpu().numpy() for t in leaves]
         finally:
             F.BACKWARD_ON_CUDA_CORES = False
     want = oracle.na_backward(q.float().numpy(), k.float().numpy(), v.float().numpy(),
-                              d_out.float().numpy(), ks, st, di, ca)
+                              d_out.float().numpy(), ks, st, di, ca,
+                              add_k=extras[0].float().numpy() if n_extra else None,
+                              add_v=extras[1].float().numpy() if n_extra else None)
+    assert len(want) == len(grads[False]) == (5 if n_extra else 3)
     for tc, cc, w in zip(grads[False], grads[True], want):
         tol = 2e-2 * max(1.0, np.abs(w).max())
         assert np.isfinite(tc).all()
