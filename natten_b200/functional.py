@@ -27,6 +27,10 @@ from .checks import (CausalArgType, DimensionType, additional_kv_tensor_checks, 
 
 BACKEND_NAME = "b200-fna"
 FMHA_BACKEND_NAME = "b200-fmha"
+# The reference's names for the backends this library replaces are accepted as aliases, so that
+# code written against it (backend="blackwell-fna") runs unchanged.
+BACKEND_ALIASES = (None, BACKEND_NAME, "blackwell-fna")
+FMHA_BACKEND_ALIASES = (None, FMHA_BACKEND_NAME, "blackwell-fmha")
 Q_TILE_SIZE = 256
 KV_TILE_SIZE = 128
 TENSOR_CORE_HEAD_DIMS = (64, 128)
@@ -277,7 +281,7 @@ def attention(query: Tensor, key: Tensor, value: Tensor, is_causal: bool = False
                                    cumulative_seqlen_KV, max_seqlen_Q, max_seqlen_KV)):
         raise NotImplementedError("natten_b200.attention does not implement variable-length "
                                   "(varlen) attention.")
-    if backend not in (None, FMHA_BACKEND_NAME):
+    if backend not in FMHA_BACKEND_ALIASES:
         raise NotImplementedError(f"Unrecognized NATTEN FMHA backend {backend}; natten_b200 "
                                   f"provides '{FMHA_BACKEND_NAME}' only.")
     if q_tile_size not in (None, Q_TILE_SIZE) or kv_tile_size not in (None, KV_TILE_SIZE):
@@ -317,7 +321,7 @@ def neighborhood_attention_generic(
     kernel_size, stride, dilation, is_causal = check_all_args(na_dim, kernel_size, stride,
                                                               dilation, is_causal)
     check_args_against_input(query, kernel_size, stride, dilation, is_causal)
-    if backend not in (None, BACKEND_NAME):
+    if backend not in BACKEND_ALIASES:
         raise NotImplementedError(f"Unrecognized NATTEN backend {backend}; natten_b200 provides "
                                   f"'{BACKEND_NAME}' only.")
     _require_cuda(query, key, value, additional_keys, additional_values)
@@ -351,9 +355,17 @@ def neighborhood_attention_generic(
     q, k, v = (t.contiguous() for t in (query, key, value))
     ak = additional_keys.contiguous() if fuse_extra else None
     av = additional_values.contiguous() if fuse_extra else None
+    if backward_q_tile_shape is not None:
+        backward_q_tile_shape = check_tile_shape(na_dim, backward_q_tile_shape,
+                                                 "backward_q_tile_shape", BACKWARD_TILE_SIZE)
+    if backward_kv_tile_shape is not None:
+        backward_kv_tile_shape = check_tile_shape(na_dim, backward_kv_tile_shape,
+                                                  "backward_kv_tile_shape", BACKWARD_TILE_SIZE)
     output, lse = na_forward_op(q, k, v, ak, av, list(kernel_size), list(stride), list(dilation),
                                 [bool(c) for c in is_causal], float(scale),
-                                list(q_tile_shape or ()), list(kv_tile_shape or ()), want_permuted)
+                                list(q_tile_shape or ()), list(kv_tile_shape or ()), want_permuted,
+                                list(backward_q_tile_shape or ()),
+                                list(backward_kv_tile_shape or ()))
     if has_extra and not fuse_extra:
         # the reference's composition: a second (dense) attention over the extra tokens, then
         # an LSE merge (src/natten/functional.py:524-559); kept for comparison
@@ -371,7 +383,8 @@ def neighborhood_attention_generic(
 
 
 def _na_forward_fake(query, key, value, additional_keys, additional_values, kernel_size, stride,
-                     dilation, is_causal, scale, q_tile_shape, kv_tile_shape, permuted_layout):
+                     dilation, is_causal, scale, q_tile_shape, kv_tile_shape, permuted_layout,
+                     backward_q_tile_shape, backward_kv_tile_shape):
     return (torch.empty_like(query), query.new_empty(query.shape[:-1], dtype=torch.float32))
 
 
@@ -379,13 +392,15 @@ def _na_forward_fake(query, key, value, additional_keys, additional_values, kern
 def na_forward_op(query: Tensor, key: Tensor, value: Tensor, additional_keys: Optional[Tensor],
                   additional_values: Optional[Tensor], kernel_size: List[int], stride: List[int],
                   dilation: List[int], is_causal: List[bool], scale: float,
-                  q_tile_shape: List[int], kv_tile_shape: List[int],
-                  permuted_layout: bool) -> Tuple[Tensor, Tensor]:
+                  q_tile_shape: List[int], kv_tile_shape: List[int], permuted_layout: bool,
+                  backward_q_tile_shape: List[int],
+                  backward_kv_tile_shape: List[int]) -> Tuple[Tensor, Tensor]:
     """Neighborhood attention forward on validated, contiguous ``[B, *X, H, D]`` operands: the
     one node `na1d/na2d/na3d` leave in a torch.compile graph. Everything that depends on concrete
     sizes happens in here, at run time: kernel choice (tensor cores for fp16/bf16 with head dim
     64/128, CUDA cores otherwise), tile shapes (empty lists = choose), and whether the kernel
-    can read this layout directly or needs token-permuted copies."""
+    can read this layout directly or needs token-permuted copies. The backward tile shapes
+    (128 tokens each, empty = choose) only matter when the result is differentiated."""
     na_dim = query.dim() - 3
     shape = tuple(int(x) for x in query.shape[1:1 + na_dim])
     kernel_size, stride, dilation = tuple(kernel_size), tuple(stride), tuple(dilation)
@@ -416,7 +431,8 @@ def na_forward_op(query: Tensor, key: Tensor, value: Tensor, additional_keys: Op
 
 def _na_setup_context(ctx, inputs, output):
     (query, key, value, additional_keys, additional_values, kernel_size, stride, dilation,
-     is_causal, scale, _q_tile, _kv_tile, _permuted) = inputs
+     is_causal, scale, _q_tile, _kv_tile, _permuted, bwd_q_tile, bwd_kv_tile) = inputs
+    ctx.bwd_tiles = (tuple(bwd_q_tile), tuple(bwd_kv_tile))
     out, lse = output
     ctx.has_extra = additional_keys is not None
     saved = [query, key, value, out, lse]
@@ -440,6 +456,8 @@ def _na_backward(ctx, d_out, d_lse):
         q_tile, kv_tile = choose_backward_tile_shapes(
             tuple(int(x) for x in query.shape[1:1 + na_dim]), kernel_size, stride, dilation,
             is_causal)
+        q_tile = ctx.bwd_tiles[0] or q_tile      # the caller's choice wins
+        kv_tile = ctx.bwd_tiles[1] or kv_tile
         tensor_core = backward_layout_supported(q_tile, kv_tile, dilation)
     if tensor_core:
         dq, dk, dv, dak, dav = ops.na_backward_direct(
@@ -447,14 +465,14 @@ def _na_backward(ctx, d_out, d_lse):
             is_causal, scale, list(q_tile), list(kv_tile))
         if not ctx.has_extra:
             dak = dav = None
-        return (dq, dk, dv, dak, dav) + (None,) * 8
+        return (dq, dk, dv, dak, dav) + (None,) * 10
     # fp32 operands, other head dims, boxes a tensor map cannot express
     dq, dk, dv, dak, dav = ops.na_backward_simt(query, key, value, out, d_out.contiguous(), lse,
                                                 ak, av, kernel_size, stride, dilation, is_causal,
                                                 scale)
     if not ctx.has_extra:
         dak = dav = None
-    return (dq, dk, dv, dak, dav) + (None,) * 8
+    return (dq, dk, dv, dak, dav) + (None,) * 10
 
 
 BACKWARD_TILE_SIZE = 128
@@ -511,6 +529,48 @@ def _choose_backward_tile_shapes(shape, kernel_size, stride, dilation, is_causal
 
 if ops.USE_TORCH_OPS:
     na_forward_op.register_autograd(_na_backward, setup_context=_na_setup_context)
+
+
+def can_run_b200_fna(query: Tensor, key: Tensor, value: Tensor, raise_error: bool = False) -> bool:
+    """Whether the tensor-core kernels take these operands (the reference's per-backend predicate,
+    src/natten/backends/configs/checks.py:143-248): CUDA tensors on a compute-capability-10 GPU,
+    fp16 / bf16 with head dim 64 or 128, or 8-bit floats with head dim 128."""
+    def fail(msg: str) -> bool:
+        if raise_error:
+            raise ValueError(msg)
+        return False
+    if not (query.is_cuda and key.is_cuda and value.is_cuda):
+        return fail("natten_b200 needs CUDA tensors.")
+    if torch.cuda.get_device_capability(query.device)[0] != 10:
+        return fail("natten_b200's tensor-core kernels need compute capability 10.x (B200).")
+    if not _tensor_core_supported(query.dtype, query.shape[-1]):
+        return fail(f"Unsupported dtype / head dim for the tensor-core kernels: {query.dtype}, "
+                    f"{query.shape[-1]}.")
+    return True
+
+
+def _all_tile_shapes(na_dim: int, q_log2: int, kv_log2: int):
+    return [(tq, tkv) for tq in _pow2_compositions(q_log2, na_dim)
+            for tkv in _pow2_compositions(kv_log2, na_dim)]
+
+
+def get_configs_for_b200_fna(query: Tensor, key: Tensor, value: Tensor):
+    """Forward tile-shape pairs `(q_tile_shape, kv_tile_shape)` the kernel accepts for these
+    operands - every power-of-two factorisation of 256 / 128 tokens (any factorisation works; the
+    list is what `choose_tile_shapes` searches). Counterpart of the reference's
+    `get_configs_for_cutlass_blackwell_fna` (src/natten/backends/configs/__init__.py:159-188)."""
+    if not can_run_b200_fna(query, key, value):
+        return []
+    return _all_tile_shapes(query.dim() - 3, 8, 7)
+
+
+def get_bwd_configs_for_b200_fna(query: Tensor, key: Tensor, value: Tensor):
+    """Backward tile-shape pairs (128 tokens each) for the tensor-core backward; empty for 8-bit
+    operands (no backward). Counterpart of `get_bwd_configs_for_cutlass_blackwell_fna`
+    (src/natten/backends/configs/__init__.py:191-220)."""
+    if not can_run_b200_fna(query, key, value) or query.dtype in FP8_DTYPES:
+        return []
+    return _all_tile_shapes(query.dim() - 3, 7, 7)
 
 
 MAX_TMA_BOX = 256      # positions a tensor-map box may span per axis

@@ -20,7 +20,7 @@ def test_opcheck_schema_and_fake_implementations():
     import natten_b200.functional as F
     torch.library.opcheck(F.na_forward_op,
                           (q, q, q, ak, ak, [5, 7], [1, 2], [2, 1], [False, True], 0.125, [], [],
-                           False), test_utils=tests)
+                           False, [], []), test_utils=tests)
     torch.library.opcheck(ops.na_forward_direct,
                           (q, q, q, ak, ak, [5, 7], [1, 2], [2, 1], [False, True], 0.125,
                            [16, 16], [16, 8]), test_utils=tests)
@@ -100,3 +100,37 @@ def test_host_operand_entry_point_matches_the_device_call():
         assert torch.equal(out, want_o.cpu()) and torch.equal(lse, want_l.cpu())
     with pytest.raises(ValueError):
         nb.na_forward_from_host(q.cuda(), k, v, **args)
+
+
+def test_reference_backend_names_and_config_listing():
+    q = torch.randn(1, 20, 24, 2, 64, device="cuda").half()
+    a = nb.na2d(q, q, q, 5, backend="blackwell-fna")          # the reference's name is an alias
+    b = nb.na2d(q, q, q, 5, backend="b200-fna")
+    assert torch.equal(a, b)
+    with pytest.raises(NotImplementedError):
+        nb.na2d(q, q, q, 5, backend="hopper-fna")
+    assert nb.can_run_b200_fna(q, q, q)
+    cfgs = nb.get_configs_for_b200_fna(q, q, q)
+    assert ((16, 16), (16, 8)) in cfgs and all(
+        qt[0] * qt[1] == 256 and kt[0] * kt[1] == 128 for qt, kt in cfgs)
+    bwd = nb.get_bwd_configs_for_b200_fna(q, q, q)
+    assert ((8, 16), (16, 8)) in bwd
+    assert not nb.can_run_b200_fna(q.float(), q.float(), q.float())
+    assert nb.get_configs_for_b200_fna(q.float(), q.float(), q.float()) == []
+    with pytest.raises(ValueError):
+        nb.can_run_b200_fna(q.cpu(), q.cpu(), q.cpu(), raise_error=True)
+    # every listed forward pair gives the same result up to rounding; so does a caller-chosen
+    # backward pair
+    want = nb.na2d(q, q, q, 5).float()
+    for qt, kt in cfgs[::7]:
+        got = nb.na2d(q, q, q, 5, q_tile_shape=qt, kv_tile_shape=kt).float()
+        assert (got - want).abs().max().item() <= 2e-2
+    grads = []
+    for bq, bk in (None, None), ((4, 32), (32, 4)):
+        x = q.clone().requires_grad_()
+        nb.na2d(x, q, q, 5, backward_q_tile_shape=bq, backward_kv_tile_shape=bk).float().sum().backward()
+        grads.append(x.grad.float())
+    assert L.device_status() == 0
+    assert (grads[0] - grads[1]).abs().max().item() <= 2e-2 * max(1.0, grads[0].abs().max().item())
+    with pytest.raises(ValueError):
+        nb.na2d(q, q, q, 5, backward_q_tile_shape=(16, 16))
