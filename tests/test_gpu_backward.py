@@ -113,3 +113,20 @@ def test_tensor_core_backward_against_oracle_and_cuda_core_kernels(shape, ks, st
         assert np.isfinite(tc).all()
         assert np.abs(tc - w).max() <= tol
         assert np.abs(cc - w).max() <= tol
+
+
+def test_compiled_training_step_matches_eager():
+    """torch.compile (AOT autograd) traces the registered backward too: gradients of a compiled
+    layer equal the eager ones."""
+    torch.manual_seed(3)
+    layer = nb.NeighborhoodAttention2D(128, 2, (7, 5), stride=(1, 2), is_causal=(False, True)).cuda().bfloat16()
+    x = torch.randn(2, 20, 24, 128, device="cuda").bfloat16()
+    grads = []
+    for fn in (layer, torch.compile(layer, fullgraph=True)):
+        layer.zero_grad()
+        xi = x.clone().requires_grad_()
+        fn(xi).float().square().mean().backward()
+        grads.append([xi.grad.float()] + [p.grad.float().clone() for p in layer.parameters()])
+    assert L.device_status() == 0
+    for a, b in zip(*grads):
+        assert torch.allclose(a, b, rtol=1e-2, atol=1e-3 * max(1.0, a.abs().max().item()))
