@@ -20,6 +20,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <atomic>
 #include <mutex>
 #include <type_traits>
 
@@ -52,6 +53,10 @@ enum : int { kStSQFull = 1, kStSFull, kStPFull, kStOFull, kStOEmpty, kStKVFull, 
              kStQEmpty, kStSmemAlign, kStDescFull, kStDescEmpty, kStRecFull };
 
 __device__ int g_status_word;
+// Work counters of the dynamic item scheduler: [slot][0] = next item, [slot][1] = CTAs finished.
+// A launch takes the next slot in turn; the last CTA to finish zeroes its pair again.
+constexpr int kCounterSlots = 64;
+__device__ unsigned long long g_work_counters[kCounterSlots][2];
 
 struct FnaParams {
   int ndim;
@@ -83,6 +88,7 @@ struct FnaParams {
   void* o;
   float* lse;
   int* status;
+  unsigned long long* work;  // [0] next work item, [1] CTAs done (see g_work_counters)
 #ifdef B200NA_PROFILE
   long long* prof;  // [grid][4 roles][8] cycle counters (instrumented builds only)
 #endif
@@ -835,8 +841,9 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       // so the other roles find the next item's geometry - and its Q tile - waiting for them.
       // Descriptors are built in place in the ring and this thread reads its own copy back from
       // there: only it ever writes a slot, and not before kDescSlots further items.
+      // Items are handed out by an atomic counter, in order: a CTA that drew short items (the
+      // first query tiles of a causal axis, tiles at the borders) simply draws more of them.
       WorkCursor cur;
-      cur.init(p, blockIdx.x);
       uint32_t published = 0;
       uint32_t tseq = 0;  // tiles fetched so far, indexes the per-tile record ring
       // Decodes the next item that is not all padding and publishes it; publishes the end marker
@@ -851,9 +858,11 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
         Item* out = reinterpret_cast<Item*>(desc_sm + slot * kDescBytes);
         bool found = false;
-        while (cur.w < p.total_work) {
+        while (true) {
+          const long long w = (long long)atomicAdd(p.work, 1ull);
+          if (w >= p.total_work) break;
+          cur.init(p, w);
           decode_item<NDIM>(p, cur, *out);
-          cur.advance(p, (int)gridDim.x);
           if (!out->skip) { found = true; break; }
         }
         if (!found) out->n_tiles = -1;
@@ -949,6 +958,15 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   // ---- teardown ----------------------------------------------------------------------------
   ptx::tc_fence_before_sync();
   __syncthreads();
+  if (threadIdx.x == 0) {
+    // the last CTA to get here re-arms the work counters for the next launch that uses them
+    __threadfence();
+    if (atomicAdd(p.work + 1, 1ull) == (unsigned long long)gridDim.x - 1) {
+      p.work[0] = 0;
+      p.work[1] = 0;
+      __threadfence();
+    }
+  }
 #if defined(B200NA_PROFILE) && B200NA_PROFILE >= 2
   if (blockIdx.x == 0) {
     const uint32_t* tb = reinterpret_cast<const uint32_t*>(smem + SM::kBytes);
@@ -1091,6 +1109,8 @@ struct DeviceState {
   bool ready = false;
   int sms = 0;
   int* status_ptr = nullptr;
+  unsigned long long* counters = nullptr;  // g_work_counters on this device
+  std::atomic<unsigned> next_slot{0};      // launches take the counter pairs in turn
 };
 
 // Per-device one-time setup: capability check, opt-in shared memory, status word address.
@@ -1124,6 +1144,9 @@ int device_state(DeviceState** out) {
     B200NA_CUDA_TRY(cudaGetSymbolAddress(&sp, g_status_word));
     st.status_ptr = reinterpret_cast<int*>(sp);
     B200NA_CUDA_TRY(cudaMemset(st.status_ptr, 0, sizeof(int)));
+    B200NA_CUDA_TRY(cudaGetSymbolAddress(&sp, g_work_counters));
+    st.counters = reinterpret_cast<unsigned long long*>(sp);
+    B200NA_CUDA_TRY(cudaMemset(st.counters, 0, sizeof(unsigned long long) * kCounterSlots * 2));
     st.ready = true;
   }
   *out = &st;
@@ -1167,6 +1190,9 @@ int launch_fna(const void* q, const void* k, const void* v, FnaParams& p, int D,
   }
   p.extra_tiles = (p.n_extra + kKVTile - 1) / kKVTile;
   p.status = st->status_ptr;
+  // A launch captured into a CUDA graph keeps its pair for every replay; replays of one graph are
+  // ordered, and 64 other launches lie between two uses of a pair otherwise.
+  p.work = st->counters + 2 * (st->next_slot.fetch_add(1) % kCounterSlots);
 #ifdef B200NA_PROFILE
   p.prof = g_prof_buffer;
 #endif
