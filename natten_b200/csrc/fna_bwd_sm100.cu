@@ -87,6 +87,7 @@ struct BwdTcParams {
   void* out0;               // dQ (pass dQ) or dK (pass dKdV)
   void* out1;               // dV (pass dKdV)
   int* status;
+  unsigned long long* work;  // [0] next work item, [1] CTAs done (dynamic item scheduler)
 };
 
 struct Item {
@@ -650,8 +651,9 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
     if (lane == 0) {
       uint32_t ph_re = 1, slot = 0, ph_ce = 1, published = 0, tseq = 0;
       bool alive = true;
+      // items are drawn in order from an atomic counter (row tiles differ a lot in how many
+      // column tiles they need: borders, the first rows of a causal axis)
       WorkCursor cur;
-      cur.init(p, blockIdx.x);
       auto publish_next = [&]() -> const Item* {
         const uint32_t ds = published % kDescSlots;
         if (!wait_bar(bars.desc_empty + ds, ((published / kDescSlots) & 1) ^ 1, abort_flag,
@@ -661,9 +663,11 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
         }
         Item* out = reinterpret_cast<Item*>(desc_sm + ds * kDescBytes);
         bool found = false;
-        while (cur.w < p.total_work) {
+        while (true) {
+          const long long w = (long long)atomicAdd(p.work, 1ull);
+          if (w >= p.total_work) break;
+          cur.init(p, w);
           decode_item<NDIM, kKeyRows>(p, cur, *out);
-          cur.advance(p, (int)gridDim.x);
           if (!out->skip) { found = true; break; }
         }
         if (!found) out->n_tiles = -1;
@@ -750,6 +754,15 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
   // ---- teardown ----------------------------------------------------------------------------
   ptx::tc_fence_before_sync();
   __syncthreads();
+  if (threadIdx.x == 0) {
+    // the last CTA to get here re-arms the work counters for the next launch that uses them
+    __threadfence();
+    if (atomicAdd(p.work + 1, 1ull) == (unsigned long long)gridDim.x - 1) {
+      p.work[0] = 0;
+      p.work[1] = 0;
+      __threadfence();
+    }
+  }
   if (*abort_flag) {
     // draining after an expired wait: let loads in flight land before shared memory is released
     const long long t0 = clock64();
@@ -927,6 +940,7 @@ extern "C" B200NA_API int b200na_na_backward_direct(
     p.total_work = n_rtiles * p.row_heads * B * p.G;
     p.out0 = dense ? d_add_k : (key_rows ? dk : dq);
     p.out1 = dense ? d_add_v : (key_rows ? dv : nullptr);
+    if ((rc = fna_work_counters(&p.work)) != B200NA_OK) return rc;
     const void* fn = bwd_kernel_variant(D, dtype == B200NA_BF16, kernel_ndim, key_rows);
     if ((rc = ensure_smem_attribute(fn, D)) != B200NA_OK) return rc;
     const int grid = (int)(p.total_work < sms ? p.total_work : sms);

@@ -1192,7 +1192,7 @@ int launch_fna(const void* q, const void* k, const void* v, FnaParams& p, int D,
   p.status = st->status_ptr;
   // A launch captured into a CUDA graph keeps its pair for every replay; replays of one graph are
   // ordered, and 64 other launches lie between two uses of a pair otherwise.
-  p.work = st->counters + 2 * (st->next_slot.fetch_add(1) % kCounterSlots);
+  if ((rc = fna_work_counters(&p.work)) != B200NA_OK) return rc;
 #ifdef B200NA_PROFILE
   p.prof = g_prof_buffer;
 #endif
@@ -1219,6 +1219,13 @@ namespace b200na {
 int fna_make_tensor_map_direct(CUtensorMap* tm, const void* ptr, int dtype, int B, const int* X,
                                int H, int D, const int* tile, const int* dil) {
   return make_tensor_map_direct(tm, ptr, dtype, B, X, H, D, tile, dil);
+}
+int fna_work_counters(unsigned long long** pair) {
+  DeviceState* st = nullptr;
+  const int rc = device_state(&st);
+  if (rc != B200NA_OK) return rc;
+  *pair = st->counters + 2 * (st->next_slot.fetch_add(1) % kCounterSlots);
+  return B200NA_OK;
 }
 int fna_device_info(int* sms, int** status_ptr) {
   DeviceState* st = nullptr;
