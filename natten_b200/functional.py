@@ -15,7 +15,7 @@ from __future__ import annotations
 import ctypes
 import functools
 import math
-from typing import Any, Dict, List, Optional, Sequence, Tuple, Union
+from typing import Any, Dict, List, Optional, Tuple, Union
 
 import torch
 from torch import Tensor

@@ -2,8 +2,6 @@
 (tests/golden/) and the CPU oracle.
 
 Tolerances (max-abs, on output and logsumexp): 1e-4 for fp32 operands, 2e-2 for fp16/bf16."""
-import math
-
 import numpy as np
 import pytest
 import torch

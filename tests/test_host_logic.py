@@ -1,6 +1,5 @@
 """Host-side logic that needs no GPU: argument rules (same exceptions as the reference),
 window arithmetic against the oracle's C restatement, tile-shape selection."""
-import itertools
 
 import numpy as np
 import pytest
