@@ -161,17 +161,6 @@ struct WorkCursor {
     h = (int)(rest % p.row_heads);
     bp = (int)(rest / p.row_heads);
   }
-  __device__ __forceinline__ void advance(const BwdTcParams& p, int step) {
-    w += step;
-    rt += step;
-    while (rt >= p.n_rtiles) {
-      rt -= p.n_rtiles;
-      if (++h == p.row_heads) {
-        h = 0;
-        ++bp;
-      }
-    }
-  }
 };
 
 template <int NDIM, bool kKeyRows>

@@ -163,8 +163,7 @@ __device__ __forceinline__ void axis_window(const FnaParams& p, int a, int i, in
   }
 }
 
-// Position of a CTA in its work list, advanced without divisions: item w = ((bp * Hq) + h) *
-// n_qtiles + qt, and consecutive items of a CTA are gridDim.x apart.
+// Coordinates of work item w = ((bp * Hq) + h) * n_qtiles + qt.
 struct WorkCursor {
   long long w;
   int qt, h, bp;
@@ -174,17 +173,6 @@ struct WorkCursor {
     const long long rest = w0 / p.n_qtiles;
     h = (int)(rest % p.Hq);
     bp = (int)(rest / p.Hq);
-  }
-  __device__ __forceinline__ void advance(const FnaParams& p, int step) {
-    w += step;
-    qt += step;
-    while (qt >= p.n_qtiles) {
-      qt -= p.n_qtiles;
-      if (++h == p.Hq) {
-        h = 0;
-        ++bp;
-      }
-    }
   }
 };
 
@@ -281,7 +269,11 @@ struct Smem {
   // desc_empty[4], rec_full[8], kv_full[S], kv_empty[S]
   static constexpr int kNumBars = 10 + 2 * kDescSlots + kTileRecs + 2 * kStages;
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;
-  static constexpr int kBytes = kMiscOff + 16;
+  // 1 KB per softmax warp: output rows are regrouped there so that stores cover whole rows
+  static constexpr int kStageOff = (kMiscOff + 16 + 127) / 128 * 128;
+  static constexpr int kStageBytes = 1024;
+  static constexpr int kBytes = kStageOff + kSoftmaxWarps * kStageBytes;
+  static_assert(kBytes <= 227 * 1024, "shared memory budget");
   // a record is overwritten kTileRecs tiles later; its readers lag the load warp by at most
   // the tiles the K/V ring holds plus one
   static_assert(kTileRecs >= kStages / 2 + 3, "per-tile record ring too short");
@@ -668,18 +660,46 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         out_row = ((long long)it.bp * p.Sq + q_row) * p.Hq + it.h;
       }
       const float inv = total > 0.f ? 1.f / total : 0.f;
-      uint8_t* orow = o_ptr + (out_row * D + part * (D / 2)) * kES;
+      // This thread's share of its output row: D/2 elements = kChunks 16-byte chunks. A store of
+      // one chunk per lane would touch 32 rows (32 separate lines) per instruction, and the
+      // load/store unit would spend more time on the epilogue than the arithmetic does. The
+      // chunks go through a 1 KB warp-private staging buffer instead, kRowsPerRound rows at a
+      // time, and come back out with consecutive lanes holding consecutive chunks of one row:
+      // every store instruction then writes whole rows.
+      constexpr int kChunks = (D / 2) * kES / 16;       // 8 (128 bytes) or 4 (64 bytes)
+      constexpr int kRowsPerRound = 64 / kChunks;       // rows whose chunks fill the 1 KB buffer
+      constexpr int kPer = 16 / kES;                    // output elements per chunk
+      uint4 pk[kChunks];
 #pragma unroll
       for (int ch = 0; ch < D / 64; ++ch) {
         uint32_t orr[32];
         ptx::tmem_ld32(my_o + ch * 32, orr);
         ptx::tmem_ld_wait();
-        if (valid) {
-          constexpr int kPer = 16 / kES;  // output elements per 16-byte store
 #pragma unroll
-          for (int v4 = 0; v4 < 32 / kPer; ++v4)
-            *reinterpret_cast<uint4*>(orow + (ch * 32 + v4 * kPer) * kES) =
-                pack_out16<kType>(orr + v4 * kPer, inv);
+        for (int v4 = 0; v4 < 32 / kPer; ++v4)
+          pk[ch * (32 / kPer) + v4] = pack_out16<kType>(orr + v4 * kPer, inv);
+      }
+      uint8_t* const orow = valid ? o_ptr + (out_row * D + part * (D / 2)) * kES : nullptr;
+      uint4* const stage = reinterpret_cast<uint4*>(smem + SM::kStageOff + warp * SM::kStageBytes);
+#pragma unroll
+      for (int rd = 0; rd < 32 / kRowsPerRound; ++rd) {
+        __syncwarp();
+        if (lane / kRowsPerRound == rd) {
+          const int lr = lane % kRowsPerRound;
+#pragma unroll
+          for (int cidx = 0; cidx < kChunks; ++cidx)  // XOR placement: conflict-free both ways
+            stage[lr * kChunks + (cidx ^ (lr % kChunks))] = pk[cidx];
+        }
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const int idx = i * 32 + lane;
+          const int lr = idx / kChunks, cidx = (idx % kChunks) ^ (lr % kChunks);
+          const uint4 val = stage[idx];
+          // the row's address lives in the lane that owns the row (null: padding row)
+          const unsigned long long rp = __shfl_sync(
+              0xffffffffu, (unsigned long long)(uintptr_t)orow, rd * kRowsPerRound + lr);
+          if (rp != 0ull) *reinterpret_cast<uint4*>((uint8_t*)(uintptr_t)rp + cidx * 16) = val;
         }
       }
       if (p.lse != nullptr && valid && part == 0)
