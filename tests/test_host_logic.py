@@ -113,3 +113,37 @@ def test_tile_shape_selection_is_valid_and_no_worse_than_reference_defaults():
                                               for a in range(n)])
         assert cost(tq, tkv) <= cost(*ref_default[n])
     assert nb.choose_tile_shapes((4096,), (64,), (1,), (1,), (False,)) == ((256,), (128,))
+
+
+def test_layout_predicates_and_backward_tile_choice():
+    # a tile of one dilation group must fit a tensor-map box (256 positions, element stride <= 8);
+    # the 256-token query tile is fetched as two halves split along its last non-unit axis
+    assert nb.direct_layout_supported((256,), (128,), (1,))
+    assert nb.direct_layout_supported((256,), (128,), (2,))           # halves of 128 * 2 = 256
+    assert not nb.direct_layout_supported((256,), (128,), (3,))
+    assert nb.direct_layout_supported((16, 16), (16, 8), (8, 8))
+    assert not nb.direct_layout_supported((16, 16), (16, 8), (9, 1))  # stride > 8
+    assert not nb.direct_layout_supported((4, 64), (2, 64), (1, 5))   # 32 * 5 fits, 64 * 5 does not
+    assert F.backward_layout_supported((128,), (128,), (2,))
+    assert not F.backward_layout_supported((128,), (128,), (3,))
+    for shape, k, s, d, c in [((128, 128), (13, 13), (1, 1), (2, 2), (False, False)),
+                              ((32, 48, 80), (16, 24, 24), (1, 8, 8), (1, 1, 1), (True, False, False)),
+                              ((57, 20, 88), (3, 5, 7), (1, 2, 3), (2, 1, 4), (False, True, False))]:
+        tq, tkv = F.choose_backward_tile_shapes(shape, k, s, d, c)
+        assert np.prod(tq) == 128 and np.prod(tkv) == 128
+        assert F.backward_layout_supported(tq, tkv, d)
+    assert F.choose_backward_tile_shapes((5000,), (33,), (1,), (1,), (True,)) == ((128,), (128,))
+    # nothing fits a box at dilation 9: the caller then uses the CUDA-core kernels
+    tq, tkv = F.choose_backward_tile_shapes((90, 90), (3, 3), (1, 1), (9, 9), (False, False))
+    assert not F.backward_layout_supported(tq, tkv, (9, 9))
+
+
+def test_backend_names():
+    assert "blackwell-fna" in F.BACKEND_ALIASES and "b200-fna" in F.BACKEND_ALIASES
+    q = torch.zeros(1, 16, 2, 64)
+    with pytest.raises(NotImplementedError):
+        nb.na1d(q, q, q, 3, backend="hopper-fna")
+    with pytest.raises(NotImplementedError):
+        nb.attention(q, q, q, backend="cutlass-fmha")
+    with pytest.raises(RuntimeError):             # accepted name, but CPU tensors
+        nb.na1d(q, q, q, 3, backend="blackwell-fna")
