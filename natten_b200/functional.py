@@ -40,6 +40,14 @@ FP8_DTYPES = (torch.float8_e4m3fn, torch.float8_e5m2)
 FP8_HEAD_DIM = 128
 
 
+def _padded_head_dim(dtype: torch.dtype, head_dim: int) -> int:
+    """Head dim the operands are zero-padded to so that the tensor-core kernels take them:
+    fp16 / bf16 below 128 go to 64 or 128; everything else is left alone."""
+    if dtype in (torch.float16, torch.bfloat16) and head_dim < 128 and head_dim not in (64,):
+        return 64 if head_dim < 64 else 128
+    return head_dim
+
+
 def _tensor_core_supported(dtype: torch.dtype, head_dim: int) -> bool:
     """Operand types of the tcgen05 kernels: fp16 / bf16 with head dim 64 or 128, 8-bit floats
     (forward only) with head dim 128."""
@@ -295,7 +303,12 @@ def attention(query: Tensor, key: Tensor, value: Tensor, is_causal: bool = False
     if query.dtype not in _DTYPE_CODE:
         raise NotImplementedError(f"natten_b200.attention does not support dtype {query.dtype}.")
     q, k, v = (t.contiguous() for t in (query, key, value))
+    padded_dim = _padded_head_dim(query.dtype, D)   # see neighborhood_attention_generic
+    if padded_dim != D:
+        q, k, v = (torch.nn.functional.pad(t, (0, padded_dim - D)) for t in (q, k, v))
     out, lse = ops.fmha_forward(q, k, v, bool(is_causal), float(scale))
+    if padded_dim != D:
+        out = out[..., :D].contiguous()
     return (out, lse) if return_lse else out
 
 
@@ -355,6 +368,18 @@ def neighborhood_attention_generic(
     q, k, v = (t.contiguous() for t in (query, key, value))
     ak = additional_keys.contiguous() if fuse_extra else None
     av = additional_values.contiguous() if fuse_extra else None
+    # fp16 / bf16 with a head dim below 128 that the tensor-core kernels do not take as is (the
+    # reference's Blackwell kernels accept every multiple of 8, blackwell_fna_forward.cu:123-138;
+    # e.g. 32 in NAT-style models): zero-pad the head dim to 64 or 128. Zeros change neither q.k
+    # nor the real columns of P.V, the scale is already fixed, and autograd differentiates through
+    # the pad and the slice - far faster than the CUDA-core kernel despite the wasted columns.
+    head_dim = query.shape[-1]
+    padded_dim = _padded_head_dim(query.dtype, head_dim)
+    if padded_dim != head_dim:
+        grow = (0, padded_dim - head_dim)
+        q, k, v = (torch.nn.functional.pad(t, grow) for t in (q, k, v))
+        if fuse_extra:
+            ak, av = torch.nn.functional.pad(ak, grow), torch.nn.functional.pad(av, grow)
     if backward_q_tile_shape is not None:
         backward_q_tile_shape = check_tile_shape(na_dim, backward_q_tile_shape,
                                                  "backward_q_tile_shape", BACKWARD_TILE_SIZE)
@@ -366,6 +391,8 @@ def neighborhood_attention_generic(
                                 list(q_tile_shape or ()), list(kv_tile_shape or ()), want_permuted,
                                 list(backward_q_tile_shape or ()),
                                 list(backward_kv_tile_shape or ()))
+    if padded_dim != head_dim:
+        output = output[..., :head_dim].contiguous()
     if has_extra and not fuse_extra:
         # the reference's composition: a second (dense) attention over the extra tokens, then
         # an LSE merge (src/natten/functional.py:524-559); kept for comparison

@@ -51,7 +51,7 @@ LAYOUTS = {"direct": None, "permuted": {"permuted_layout": True}}
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("layout", list(LAYOUTS))
 def test_16bit_path_matches_reference(name, dtype, layout):
-    """bf16-exact operands: head dims 64/128 run on the tensor-core kernel, others on CUDA cores.
+    """bf16-exact operands on the tensor-core kernel (head dims other than 64/128 zero-padded).
     The tensor-core kernel is run both on the caller's layout (tensor-map gathers, the default)
     and on token-permuted copies (the reference's flow)."""
     c = na_cases()[name]
@@ -353,3 +353,24 @@ def test_unsupported_inputs_fail_loudly():
         nb.na1d(q, q, q, kernel_size=5, q_tile_shape=(128,))
     with pytest.raises(NotImplementedError):
         nb.attention(q, q, q, cumulative_seqlen_Q=torch.zeros(2, dtype=torch.int32, device="cuda"))
+
+
+@pytest.mark.parametrize("D", [8, 32, 48, 80, 96])
+def test_odd_head_dims_run_padded_on_tensor_cores(D):
+    """fp16/bf16 head dims below 128 other than 64 are zero-padded to 64 / 128 for the tensor-core
+    kernel; results match the oracle like any other, for neighborhood and dense attention."""
+    torch.manual_seed(D)
+    q, k, v = (torch.randn(2, 20, 28, 2, D).bfloat16() for _ in range(3))
+    ks, st, di, ca = (5, 7), (1, 2), (2, 1), (False, True)
+    out, lse = nb.na2d(q.cuda(), k.cuda(), v.cuda(), ks, st, di, ca, return_lse=True)
+    assert out.shape == q.shape and out.is_contiguous()
+    want_o, want_l = oracle.na_forward(q.float().numpy(), k.float().numpy(), v.float().numpy(),
+                                       ks, st, di, ca)
+    assert np.abs(out.float().cpu().numpy() - want_o).max() <= TOL_16
+    assert np.abs(lse.cpu().numpy() - want_l).max() <= TOL_16
+    a, b, c = (t.flatten(1, 2)[:, :300] for t in (q, k, v))
+    o2, l2 = nb.attention(a.cuda(), b.cuda(), c.cuda(), return_lse=True)
+    w2, wl2 = oracle.dense_attention(a.float().numpy(), b.float().numpy(), c.float().numpy())
+    assert L.device_status() == 0
+    assert np.abs(o2.float().cpu().numpy() - w2).max() <= TOL_16
+    assert np.abs(l2.cpu().numpy() - wl2).max() <= TOL_16

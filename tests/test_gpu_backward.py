@@ -77,6 +77,8 @@ def test_layer_trains():
     ((30, 26), (5, 7), (1, 1), (2, 3), (False, True), 4, 2, 64, 130),     # ragged extras, GQA
     ((700,), (65,), (3,), (1,), (True,), 2, 1, 128, 7),
     ((6, 10, 12), (3, 4, 5), (1, 2, 1), (1, 1, 1), (True, False, False), 1, 1, 64, 300),
+    ((33, 30), (3, 5), (1, 2), (3, 2), (False, True), 4, 2, 32, 0),       # head dim 32: zero-padded
+    ((500,), (21,), (1,), (1,), (True,), 2, 2, 96, 19),                   # head dim 96 -> 128
 ])
 def test_tensor_core_backward_against_oracle_and_cuda_core_kernels(shape, ks, st, di, ca, hq, hkv,
                                                                    D, n_extra):
