@@ -143,6 +143,22 @@ B200NA_API int b200na_na_forward_direct(
     b200na_stream_t stream);
 
 /*
+ * b200na_na_forward_direct for q, k, v that are VIEWS into wider token rows - typically the three
+ * slices of a fused projection output [B, *shape, 3, H, D], which the reference's layers separate
+ * with a permute + copy (src/natten/modules.py:104-113). `*_token_stride` is the distance between
+ * consecutive tokens in elements (>= H * D, a multiple of 16 bytes; 0 = contiguous); batch entries
+ * are prod(shape) tokens apart. The tensor maps absorb the stride, nothing is copied. o and lse
+ * are contiguous as always.
+ */
+B200NA_API int b200na_na_forward_direct_strided(
+    const void* q, const void* k, const void* v, const void* add_k, const void* add_v,
+    int n_extra, void* o, float* lse, int ndim, const int* shape, const int* kernel,
+    const int* stride, const int* dilation, const int* causal, const int* q_tile,
+    const int* kv_tile, int B, int Hq, int Hkv, int D, int dtype, float scale,
+    long long q_token_stride, long long k_token_stride, long long v_token_stride,
+    b200na_stream_t stream);
+
+/*
  * The same kernel on one rank's SLAB of a spatially sharded, undilated token layout. The
  * reference has no counterpart (it has no multi-GPU code); window arithmetic follows
  * csrc/include/natten/cuda/reference/mask.hpp:59-89 in layout ("global") coordinates.

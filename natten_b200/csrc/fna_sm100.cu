@@ -76,6 +76,7 @@ struct FnaParams {
   int q_len[B200NA_MAX_DIM];   // number of real (non-padding) local query coordinates per axis
   int dense;                // dense attention: one axis, window = all keys (or causal prefix)
   int direct;               // Q/K/V/O/LSE are in the caller's [B, *X, H, D] layout (no permutation)
+  long long tok_stride[3];  // direct: elements between consecutive tokens of q, k, v (0 = H * D)
   int half_axis;            // direct: axis along which the query tile splits into its two halves
   int n_extra;              // extra key/value tokens every query attends (0 = none)
   int extra_tiles;          // ceil(n_extra / 128): KV tiles appended to every item's walk
@@ -1070,12 +1071,16 @@ int make_tensor_map(CUtensorMap* tm, const void* ptr, int dtype, int Bp, int S, 
 // head's channels and tile[a] * dil[a] positions per axis, traversed with element stride dil[a]:
 // it picks the tile's tokens of one dilation group; positions past an extent read as zeros.
 int make_tensor_map_direct(CUtensorMap* tm, const void* ptr, int dtype, int B, const int* X,
-                           int H, int D, const int* tile, const int* dil) {
+                           int H, int D, const int* tile, const int* dil,
+                           long long token_stride = 0) {
   EncodeTiledFn enc = nullptr;
   int rc = get_encode_fn(&enc);
   if (rc != B200NA_OK) return rc;
   const cuuint64_t es = (cuuint64_t)elem_bytes_of(dtype);
-  const cuuint64_t row = (cuuint64_t)H * D * es;  // bytes per token
+  // bytes from one token to the next: H * D elements when the tensor is contiguous, more when it
+  // is a view into a wider row (q, k or v inside a fused [.., 3, H, D] projection output)
+  const cuuint64_t row = (cuuint64_t)(token_stride > 0 ? token_stride : (long long)H * D) * es;
+  if (row % 16 != 0 || row < (cuuint64_t)H * D * es) return B200NA_ERR_ALIGNMENT;
   const cuuint64_t dims[5] = {(cuuint64_t)H * D, (cuuint64_t)X[0], (cuuint64_t)X[1],
                               (cuuint64_t)X[2], (cuuint64_t)B};
   const cuuint64_t strides[4] = {row * X[1] * X[2], row * X[2], row, row * X[0] * X[1] * X[2]};
@@ -1191,9 +1196,9 @@ int launch_fna(const void* q, const void* k, const void* v, FnaParams& p, int D,
     for (int a = 0; a < B200NA_MAX_DIM; ++a)
       half_tile[a] = (a == p.half_axis) ? p.Tq[a] / 2 : p.Tq[a];
     const int B = p.Bp / p.G;
-    if ((rc = make_tensor_map_direct(&tq, q, dtype, B, p.X, p.Hq, D, half_tile, p.dil)) != B200NA_OK) return rc;
-    if ((rc = make_tensor_map_direct(&tk, k, dtype, B, p.X, p.Hkv, D, p.Tkv, p.dil)) != B200NA_OK) return rc;
-    if ((rc = make_tensor_map_direct(&tv, v, dtype, B, p.X, p.Hkv, D, p.Tkv, p.dil)) != B200NA_OK) return rc;
+    if ((rc = make_tensor_map_direct(&tq, q, dtype, B, p.X, p.Hq, D, half_tile, p.dil, p.tok_stride[0])) != B200NA_OK) return rc;
+    if ((rc = make_tensor_map_direct(&tk, k, dtype, B, p.X, p.Hkv, D, p.Tkv, p.dil, p.tok_stride[1])) != B200NA_OK) return rc;
+    if ((rc = make_tensor_map_direct(&tv, v, dtype, B, p.X, p.Hkv, D, p.Tkv, p.dil, p.tok_stride[2])) != B200NA_OK) return rc;
   } else {
     if ((rc = make_tensor_map(&tq, q, dtype, p.Bp, p.Sq, p.Hq, D)) != B200NA_OK) return rc;
     if ((rc = make_tensor_map(&tk, k, dtype, p.Bp, p.Skv, p.Hkv, D)) != B200NA_OK) return rc;
@@ -1348,7 +1353,7 @@ int fna_direct_impl(const void* q, const void* k, const void* v, void* o, float*
                     const int* shape, const int* kernel, const int* stride, const int* dilation,
                     const int* causal, const int* q_tile, const int* kv_tile, int B, int Hq,
                     int Hkv, int D, int dtype, float scale, const void* add_k, const void* add_v,
-                    int n_extra, b200na_stream_t stream) {
+                    int n_extra, const long long* token_strides, b200na_stream_t stream) {
   if (!q || !k || !v || !o || !shape || !kernel || !q_tile || !kv_tile)
     return B200NA_ERR_INVALID_ARGUMENT;
   if (n_extra < 0 || (n_extra > 0 && (!add_k || !add_v))) return B200NA_ERR_INVALID_ARGUMENT;
@@ -1364,6 +1369,7 @@ int fna_direct_impl(const void* q, const void* k, const void* v, void* o, float*
   p.G = 1;
   p.direct = 1;
   p.half_axis = 0;
+  for (int i = 0; i < 3; ++i) p.tok_stride[i] = token_strides ? token_strides[i] : 0;
   long long sq = 1, skv = 1, tq = 1, tkv = 1, tokens = 1;
   for (int a = 0; a < B200NA_MAX_DIM; ++a) {
     const bool on = a < ndim;
@@ -1415,7 +1421,20 @@ extern "C" B200NA_API int b200na_na_forward_direct(
     b200na_stream_t stream) {
   return b200na::fna_direct_impl(q, k, v, o, lse, ndim, shape, kernel, stride, dilation, causal,
                                  q_tile, kv_tile, B, Hq, Hkv, D, dtype, scale, add_k, add_v,
-                                 n_extra, stream);
+                                 n_extra, nullptr, stream);
+}
+
+extern "C" B200NA_API int b200na_na_forward_direct_strided(
+    const void* q, const void* k, const void* v, const void* add_k, const void* add_v,
+    int n_extra, void* o, float* lse, int ndim, const int* shape, const int* kernel,
+    const int* stride, const int* dilation, const int* causal, const int* q_tile,
+    const int* kv_tile, int B, int Hq, int Hkv, int D, int dtype, float scale,
+    long long q_token_stride, long long k_token_stride, long long v_token_stride,
+    b200na_stream_t stream) {
+  const long long ts[3] = {q_token_stride, k_token_stride, v_token_stride};
+  return b200na::fna_direct_impl(q, k, v, o, lse, ndim, shape, kernel, stride, dilation, causal,
+                                 q_tile, kv_tile, B, Hq, Hkv, D, dtype, scale, add_k, add_v,
+                                 n_extra, ts, stream);
 }
 
 extern "C" B200NA_API int b200na_fna_forward_sharded(

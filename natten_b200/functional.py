@@ -365,7 +365,10 @@ def neighborhood_attention_generic(
         kv_tile_shape = check_tile_shape(na_dim, kv_tile_shape, "kv_tile_shape", KV_TILE_SIZE)
     fuse_extra = has_extra and not (attention_kwargs or {}).get("unfused_extra_kv", False)
     want_permuted = bool((attention_kwargs or {}).get("permuted_layout", False))
-    q, k, v = (t.contiguous() for t in (query, key, value))
+    # no .contiguous() here: evenly token-strided views (q / k / v sliced out of a fused
+    # projection) reach the kernel as they are - its tensor maps absorb the stride; the op makes
+    # anything else contiguous itself
+    q, k, v = query, key, value
     ak = additional_keys.contiguous() if fuse_extra else None
     av = additional_values.contiguous() if fuse_extra else None
     # fp16 / bf16 with a head dim below 128 that the tensor-core kernels do not take as is (the
@@ -439,6 +442,7 @@ def na_forward_op(query: Tensor, key: Tensor, value: Tensor, additional_keys: Op
     if not tensor_core:
         # fp32 operands (and other head dims): CUDA-core kernel on the original layout, extra KV
         # tokens fused into the same softmax.
+        query, key, value = query.contiguous(), key.contiguous(), value.contiguous()
         return ops.na_forward_simt(query, key, value, additional_keys, additional_values,
                                    list(kernel_size), list(stride), list(dilation),
                                    list(is_causal), scale)
@@ -452,8 +456,9 @@ def na_forward_op(query: Tensor, key: Tensor, value: Tensor, additional_keys: Op
         return fna_forward_direct(query, key, value, kernel_size, stride, dilation, is_causal,
                                   scale, q_tile_shape, kv_tile_shape, additional_keys,
                                   additional_values)
-    return fna_forward_permuted(query, key, value, kernel_size, stride, dilation, is_causal, scale,
-                                q_tile_shape, kv_tile_shape, additional_keys, additional_values)
+    return fna_forward_permuted(query.contiguous(), key.contiguous(), value.contiguous(),
+                                kernel_size, stride, dilation, is_causal, scale, q_tile_shape,
+                                kv_tile_shape, additional_keys, additional_values)
 
 
 def _na_setup_context(ctx, inputs, output):
@@ -473,6 +478,7 @@ def _na_backward(ctx, d_out, d_lse):
     """Gradients of the output w.r.t. query, key, value and the fused extra tokens. d_lse is
     ignored, as in the reference's backward (src/natten/backends/blackwell_fna.py:185-318)."""
     query, key, value, out, lse = ctx.saved_tensors[:5]
+    query, key, value = query.contiguous(), key.contiguous(), value.contiguous()
     ak, av = ctx.saved_tensors[5:] if ctx.has_extra else (None, None)
     kernel_size, stride, dilation, is_causal, scale = ctx.na_args
     na_dim = query.dim() - 3
@@ -629,7 +635,7 @@ def fna_forward_direct(query: Tensor, key: Tensor, value: Tensor, kernel_size: D
     """The fused kernel on the original heads-last layout: what the reference does as
     permute -> kernel -> unpermute (src/natten/backends/blackwell_fna.py:111-165) in one launch,
     the tile gathers (dilation included) done by the kernel's tensor-map loads."""
-    q, k, v = (t.contiguous() for t in (query, key, value))
+    q, k, v = query, key, value   # token-strided views are fine, see ops.na_forward_direct
     ak = additional_keys.contiguous() if additional_keys is not None else None
     av = additional_values.contiguous() if additional_values is not None else None
     out, lse = ops.na_forward_direct(q, k, v, ak, av, list(kernel_size), list(stride),

@@ -118,8 +118,27 @@ def merge(out0: Tensor, lse0: Tensor, out1: Tensor, lse1: Tensor) -> Tuple[Tenso
 # ---- attention kernels ---------------------------------------------------------------------------
 
 def _attn_fake(query, *_args):
-    return (torch.empty_like(query),
+    return (query.new_empty(query.shape),   # contiguous, also for a strided query view
             query.new_empty(query.shape[:-1], dtype=torch.float32))
+
+
+def token_stride(t: Tensor) -> int:
+    """Elements between consecutive tokens of a heads-last ``[B, *X, H, D]`` tensor whose tokens
+    (batch entries included) are evenly spaced and whose ``[H, D]`` block is contiguous - true for
+    contiguous tensors and for q / k / v sliced out of a fused ``[B, *X, 3, H, D]`` projection.
+    -1 when the tensor is not of that form (or not aligned for a tensor map)."""
+    H, D = t.shape[-2], t.shape[-1]
+    if t.stride(-1) != 1 or t.stride(-2) != D:
+        return -1
+    ts = t.stride(-3)
+    expected = ts
+    for i in range(t.dim() - 3, -1, -1):
+        if t.shape[i] != 1 and t.stride(i) != expected:
+            return -1
+        expected *= t.shape[i]
+    if ts < H * D or (ts * t.element_size()) % 16 != 0 or t.data_ptr() % 16 != 0:
+        return -1
+    return int(ts)
 
 
 def _fmha_fake(query, key, value, is_causal, scale):
@@ -152,18 +171,26 @@ def na_forward_direct(query: Tensor, key: Tensor, value: Tensor,
                       kernel_size: List[int], stride: List[int], dilation: List[int],
                       is_causal: List[bool], scale: float, q_tile_shape: List[int],
                       kv_tile_shape: List[int]) -> Tuple[Tensor, Tensor]:
-    """The fused tensor-core kernel on the caller's ``[B, *X, H, D]`` layout (one launch)."""
+    """The fused tensor-core kernel on the caller's ``[B, *X, H, D]`` layout (one launch).
+    query / key / value may be evenly token-strided views (see `token_stride`): the kernel's
+    tensor maps absorb the stride, nothing is copied."""
+    strides = [token_stride(t) for t in (query, key, value)]
+    if min(strides) < 0:
+        query, key, value = (t if s >= 0 else t.contiguous()
+                             for t, s in zip((query, key, value), strides))
+        strides = [token_stride(t) for t in (query, key, value)]
     out, lse = _attn_fake(query)
     na_dim = query.dim() - 3
     n_extra = additional_keys.shape[1] if additional_keys is not None else 0
     with torch.cuda.device(query.device):
-        _lib.check(_lib.lib.b200na_na_forward_direct(
+        _lib.check(_lib.lib.b200na_na_forward_direct_strided(
             _ptr(query), _ptr(key), _ptr(value), _ptr(additional_keys), _ptr(additional_values),
             n_extra, _ptr(out), _ptr(lse), na_dim, _lib.ints(query.shape[1:1 + na_dim]),
             _lib.ints(kernel_size), _lib.ints(stride), _lib.ints(dilation),
             _lib.ints(_flags(is_causal)), _lib.ints(q_tile_shape), _lib.ints(kv_tile_shape),
             query.shape[0], query.shape[-2], key.shape[-2], query.shape[-1],
-            DTYPE_CODE[query.dtype], float(scale), _stream(query)), "b200na_na_forward_direct")
+            DTYPE_CODE[query.dtype], float(scale), strides[0], strides[1], strides[2],
+            _stream(query)), "b200na_na_forward_direct_strided")
     return out, lse
 
 

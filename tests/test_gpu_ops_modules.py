@@ -134,3 +134,28 @@ def test_reference_backend_names_and_config_listing():
     assert (grads[0] - grads[1]).abs().max().item() <= 2e-2 * max(1.0, grads[0].abs().max().item())
     with pytest.raises(ValueError):
         nb.na2d(q, q, q, 5, backward_q_tile_shape=(16, 16))
+
+
+def test_fused_projection_views_are_read_in_place():
+    """q, k, v sliced out of a fused [B, *X, 3, H, D] projection go to the kernel without copies
+    (the tensor maps absorb the token stride) and give the bits of the contiguous call."""
+    torch.manual_seed(12)
+    qkv = torch.randn(2, 24, 28, 3, 2, 128, device="cuda").bfloat16()
+    q, k, v = qkv.unbind(-3)
+    assert not q.is_contiguous() and ops.token_stride(q) == 3 * 2 * 128
+    args = dict(kernel_size=(7, 5), stride=(1, 2), dilation=(2, 1), is_causal=(False, True),
+                return_lse=True)
+    o_v, l_v = nb.na2d(q, k, v, **args)
+    o_c, l_c = nb.na2d(q.contiguous(), k.contiguous(), v.contiguous(), **args)
+    assert L.device_status() == 0
+    assert o_v.is_contiguous() and torch.equal(o_v, o_c) and torch.equal(l_v, l_c)
+    # a view the maps cannot express (transposed heads) is copied by the op, not refused
+    qt = torch.randn(2, 24, 28, 128, 2, device="cuda").bfloat16().transpose(-1, -2)
+    assert ops.token_stride(qt) < 0
+    o_t = nb.na2d(qt, qt, qt, kernel_size=5)
+    assert torch.equal(o_t, nb.na2d(qt.contiguous(), qt.contiguous(), qt.contiguous(), kernel_size=5))
+    # gradients flow back into the fused tensor
+    qkv2 = qkv.clone().requires_grad_()
+    q2, k2, v2 = qkv2.unbind(-3)
+    nb.na2d(q2, k2, v2, kernel_size=(7, 5)).float().square().mean().backward()
+    assert qkv2.grad is not None and torch.isfinite(qkv2.grad).all() and qkv2.grad.abs().max() > 0
