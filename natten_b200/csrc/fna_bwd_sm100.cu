@@ -17,14 +17,20 @@
 //   * The columns a row tile needs form a box of tiles in both passes: a query's keys are its
 //     window, and a key's queries are the inverse window - an interval per axis, because window
 //     start and end never decrease with the query coordinate (found by bisection).
-//   * TMEM: S [0,128) dP [128,256) acc0 [256,256+D) acc1 [384,384+D). P and dS (16-bit) overwrite
-//     S and dP in place, privately per thread, and feed the second MMAs from TMEM.
+//   * TMEM: S [0,128) dP [128,256) acc0 [256,256+D) acc1 [384,384+D). Pass dKdV: P and dS (16-bit)
+//     overwrite S and dP in place, privately per thread, and feed the second MMAs from TMEM; the
+//     four regions fill TMEM, so a column tile's products and its P / dS arithmetic alternate.
+//   * Pass dQ has one accumulator, so it is software-pipelined: dS goes to two 64-column buffers
+//     in [384,512), S / dP are handed back to the tensor pipe as soon as the softmax threads hold
+//     them in registers, and the next tile's S and dP are computed while this tile's dS is. The
+//     C1 (K) and C2 (V) column tiles have rings of their own there: a C2 stage is free after dP,
+//     a C1 stage only after the dQ product.
 //   * Row statistics (LSE, delta) are per thread in pass dQ; in pass dKdV they belong to the
 //     columns and are staged through shared memory per column tile.
 //   * Warp roles: 16 softmax warps (four threads per row, 32 columns each: the P / dS arithmetic
-//     is latency-bound, more warps per sub-partition hide it), 1 MMA-issue warp, 1
-//     load warp that also decodes work items and classifies tiles (descriptor / record rings as in
-//     the forward kernel). Every mbarrier wait is bounded; on expiry the CTA records a status word
+//     is latency-bound, more warps per sub-partition hide it), 1 MMA-issue warp (pass dQ: a
+//     second one for the dQ products, in another sub-partition), 1 load warp that also decodes
+//     work items and classifies tiles (descriptor / record rings as in the forward kernel). Every mbarrier wait is bounded; on expiry the CTA records a status word
 //     (shared with the forward kernel) and drains.
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -47,17 +53,23 @@ constexpr int kSoftmaxWarps = 16;   // 4 column parts x 4 warps (one thread per 
 constexpr int kSoftmaxThreads = 512;
 constexpr int kMmaWarp = 16;
 constexpr int kLoadWarp = 17;
-constexpr int kThreads = 576;
-// Registers are allocated to warps in groups of four, so 18 warps cost as much as 20: 96 per
+constexpr int kMma2Warp = 18;       // pass dQ: issues the dQ products (kMmaWarp issues S and dP)
+constexpr int kThreads = 608;
+// Registers are allocated to warps in groups of four, so 19 warps cost as much as 20: 96 per
 // thread; the 16-column chunks of the P / dS loop keep the live set well below that.
 constexpr int kTmemCols = 512;
-constexpr int kDescSlots = 4;
-constexpr int kDescBytes = 192;
+constexpr int kDescSlots = 3;
+constexpr int kDescBytes = 128;
+#ifndef B200NA_BWD_RING1
+#define B200NA_BWD_RING1 3
+#endif
 constexpr int kTileRecs = 8;
 
-// status word: (role << 8) | barrier id; roles 5 = softmax, 6 = mma, 7 = load (backward kernel)
+// status word: (role << 8) | barrier id; roles 5 = softmax, 6 = mma, 7 = load, 9 = second mma
+// issuer of pass dQ (backward kernel)
 enum : int { kStRFull = 1, kStREmpty, kStCFull, kStCEmpty, kStSdpFull, kStDsFull, kStAccFull,
-             kStAccEmpty, kStDescFull, kStDescEmpty, kStRecFull, kStRecEmpty, kStSmemAlign };
+             kStAccEmpty, kStDescFull, kStDescEmpty, kStRecFull, kStRecEmpty, kStSmemAlign,
+             kStSdpFree, kStDsFree, kStVFull, kStVEmpty };
 
 struct BwdTcParams {
   int ndim;
@@ -88,7 +100,23 @@ struct BwdTcParams {
   void* out1;               // dV (pass dKdV)
   int* status;
   unsigned long long* work;  // [0] next work item, [1] CTAs done (dynamic item scheduler)
+  long long* trace;          // instrumented builds only: [5 roles][1024] event stamps of CTA 0
 };
+
+// Event trace of CTA 0 in pass dQ (-DB200NA_BWD_TRACE=1): (clock << 8) | code per event.
+#if defined(B200NA_BWD_TRACE) && B200NA_BWD_TRACE
+#define BTRACE_DECL(skip) int btrace_n_ = -(skip);
+#define BTRACE(role, code)                                                              \
+  {                                                                                     \
+    if (kPipe && p.trace != nullptr && blockIdx.x == 0 && btrace_n_ < 1024) {           \
+      if (btrace_n_ >= 0) p.trace[(role) * 1024 + btrace_n_] = (clock64() << 8) | (code); \
+      ++btrace_n_;                                                                      \
+    }                                                                                   \
+  }
+#else
+#define BTRACE_DECL(skip)
+#define BTRACE(role, code) {}
+#endif
 
 struct Item {
   int b, h;                   // batch entry; head of the row tile (query head or kv head)
@@ -216,28 +244,35 @@ __device__ __forceinline__ void decode_item(const BwdTcParams& p, const WorkCurs
   it.n_tiles = it.n_na + (kKeyRows ? 0 : p.extra_tiles);
 }
 
-template <int D>
+// kPipe (pass dQ): the C1 and C2 column tiles live in rings of their own, because C2 (V) is free
+// again right after the dP product while C1 (K) is needed until the dQ product of its tile.
+template <int D, bool kPipe>
 struct Smem {
   static constexpr int kTileBytes = kTile * D * 2;          // one 128-token operand tile
-  static constexpr int kStages = (D == 128) ? 2 : 3;        // (C1, C2) pairs in flight
+  static constexpr int kStages = (D == 128) ? 2 : 3;        // (C1, C2) pairs, or C2 tiles, in flight
+  static constexpr int kRing1 = kPipe ? (D == 128 ? B200NA_BWD_RING1 : 4) : kStages;  // C1 ring
+  static constexpr int kStage1Bytes = kPipe ? kTileBytes : 2 * kTileBytes;
   static constexpr int kRowOff = 0;                         // R1, R2
   static constexpr int kColOff = 2 * kTileBytes;
-  static constexpr int kPrefOff = kColOff + kStages * 2 * kTileBytes;
+  static constexpr int kCol2Off = kColOff + kRing1 * kStage1Bytes;   // C2 ring (kPipe only)
+  static constexpr int kPrefOff = kCol2Off + (kPipe ? kStages * kTileBytes : 0);
   static constexpr int kPrefEntries = 136;
   static constexpr int kStatOff = kPrefOff + kPrefEntries * 16;   // column stats [2][2][128] fp32
-  static constexpr int kDescOff = kStatOff + 2 * 2 * kTile * 4;
+  static constexpr int kDescOff = kStatOff + (kPipe ? 0 : 2 * 2 * kTile * 4);
   static constexpr int kRecOff = kDescOff + kDescSlots * kDescBytes;
   static constexpr int kBarOff = kRecOff + kTileRecs * 16;
-  // r_full, r_empty, sdp_full, ds_full, acc_full, acc_empty, desc_full[4], desc_empty[4],
-  // rec_full[8], rec_empty[8], c_full[S], c_empty[S]
-  static constexpr int kNumBars = 6 + 2 * kDescSlots + 2 * kTileRecs + 2 * kStages;
+  // r_full, r_empty, sdp_full, sdp_free, acc_full, acc_empty, ds_full[2], ds_free[2],
+  // desc_full[], desc_empty[], rec_full[8], rec_empty[8], c_full[R1], c_empty[R1], v_full[S],
+  // v_empty[S]
+  static constexpr int kNumBars = 10 + 2 * kDescSlots + 2 * kTileRecs + 2 * kRing1 + 2 * kStages;
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;
   static constexpr int kBytes = kMiscOff + 16;
+  static_assert(kBytes <= 227 * 1024, "shared memory budget of one CTA");
 };
 
 struct Bars {
-  uint64_t *r_full, *r_empty, *sdp_full, *ds_full, *acc_full, *acc_empty;
-  uint64_t *desc_full, *desc_empty, *rec_full, *rec_empty, *c_full, *c_empty;
+  uint64_t *r_full, *r_empty, *sdp_full, *sdp_free, *acc_full, *acc_empty, *ds_full, *ds_free;
+  uint64_t *desc_full, *desc_empty, *rec_full, *rec_empty, *c_full, *c_empty, *v_full, *v_empty;
 };
 
 constexpr int kTileInterior = 1, kTileBoundary = 2, kTileRagged = 3;
@@ -283,8 +318,10 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
                const __grid_constant__ CUtensorMap tm_c1, const __grid_constant__ CUtensorMap tm_c2,
                const __grid_constant__ CUtensorMap tm_e1, const __grid_constant__ CUtensorMap tm_e2,
                const BwdTcParams p) {
-  using SM = Smem<D>;
+  constexpr bool kPipe = !kKeyRows;
+  using SM = Smem<D, kPipe>;
   constexpr int kStages = SM::kStages;
+  constexpr int kRing1 = SM::kRing1;
   constexpr int kTileBytes = SM::kTileBytes;
   constexpr int kDBlocks = D / 64;
   constexpr int kBlockBytes = kTile * 128;
@@ -293,6 +330,7 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* row_sm = smem + SM::kRowOff;
   uint8_t* col_sm = smem + SM::kColOff;
+  uint8_t* col2_sm = smem + SM::kCol2Off;
   uint4* pref = reinterpret_cast<uint4*>(smem + SM::kPrefOff);
   float* colstat = reinterpret_cast<float*>(smem + SM::kStatOff);  // [2 buf][lse | delta][128]
   uint8_t* desc_sm = smem + SM::kDescOff;
@@ -305,15 +343,19 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
   bars.r_full = bar_base + 0;
   bars.r_empty = bar_base + 1;
   bars.sdp_full = bar_base + 2;
-  bars.ds_full = bar_base + 3;
+  bars.sdp_free = bar_base + 3;
   bars.acc_full = bar_base + 4;
   bars.acc_empty = bar_base + 5;
-  bars.desc_full = bar_base + 6;
+  bars.ds_full = bar_base + 6;   // [2]
+  bars.ds_free = bar_base + 8;   // [2]
+  bars.desc_full = bar_base + 10;
   bars.desc_empty = bars.desc_full + kDescSlots;
   bars.rec_full = bars.desc_empty + kDescSlots;
   bars.rec_empty = bars.rec_full + kTileRecs;
   bars.c_full = bars.rec_empty + kTileRecs;
-  bars.c_empty = bars.c_full + kStages;
+  bars.c_empty = bars.c_full + kRing1;
+  bars.v_full = bars.c_empty + kRing1;
+  bars.v_empty = bars.v_full + kStages;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -327,20 +369,29 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
     ptx::mbar_init(bars.r_full, 1);
     ptx::mbar_init(bars.r_empty, 1);
     ptx::mbar_init(bars.sdp_full, 1);
-    ptx::mbar_init(bars.ds_full, kSoftmaxWarps);
+    ptx::mbar_init(bars.sdp_free, kSoftmaxWarps);
+    for (int s = 0; s < 2; ++s) {
+      ptx::mbar_init(bars.ds_full + s, kSoftmaxWarps);
+      ptx::mbar_init(bars.ds_free + s, 1);
+    }
     ptx::mbar_init(bars.acc_full, 1);
     ptx::mbar_init(bars.acc_empty, kSoftmaxWarps);
     for (int s = 0; s < kDescSlots; ++s) {
       ptx::mbar_init(bars.desc_full + s, 1);
-      ptx::mbar_init(bars.desc_empty + s, kSoftmaxWarps + 1);  // softmax warps + MMA thread
+      // softmax warps + the MMA-issuing threads
+      ptx::mbar_init(bars.desc_empty + s, kSoftmaxWarps + (kPipe ? 2 : 1));
     }
     for (int s = 0; s < kTileRecs; ++s) {
       ptx::mbar_init(bars.rec_full + s, 1);
       ptx::mbar_init(bars.rec_empty + s, kSoftmaxWarps);
     }
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < kRing1; ++s) {
       ptx::mbar_init(bars.c_full + s, 1);
       ptx::mbar_init(bars.c_empty + s, 1);
+    }
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(bars.v_full + s, 1);
+      ptx::mbar_init(bars.v_empty + s, 1);
     }
     ptx::fence_barrier_init();
   }
@@ -365,9 +416,14 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   constexpr uint32_t kSCol = 0, kDpCol = 128, kAcc0Col = 256, kAcc1Col = 384;
+  // Pass dQ keeps one accumulator, so columns [384, 512) are free: they hold two buffers of packed
+  // dS (64 columns each). With dS written there instead of over dP, the logit / dP columns are
+  // free again as soon as the softmax threads have read them, and the MMA thread computes the next
+  // column tile's S and dP while the threads turn this tile's values into dS.
+  constexpr uint32_t kDsCol = 384, kDsBufCols = 64;
 
   if (warp < kSoftmaxWarps) {
-    // ============ P / dS computation and the epilogue (two threads per row) ====================
+    // ============ P / dS computation and the epilogue (four threads per row) ====================
     const int part = warp >> 2;  // 0..3: columns [32 part, 32 part + 32) of every column tile
     const int row = ((warp & 3) << 5) | lane;
     const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) << 5) << 16);
@@ -375,7 +431,8 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
     const uint32_t my_dp = lane_addr + kDpCol + part * 32;
     const float c = p.scale_log2;
     constexpr float kLog2e = 1.4426950408889634f;
-    uint32_t ph_sdp = 0, ph_acc = 0, tseq = 0;
+    uint32_t ph_sdp = 0, ph_acc = 0, tseq = 0, dseq = 0;
+    BTRACE_DECL(4 * 40)
     // in-tile coordinates of this thread's row, and of the column whose statistics it fetches
     int tr[B200NA_MAX_DIM], tcol[B200NA_MAX_DIM];
     {
@@ -472,42 +529,84 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
         }
         ph_sdp ^= 1;
         ptx::tc_fence_after_sync();
-        // 16 columns at a time: p = 2^(s c - lse), ds = p (dp - delta); the packed results
-        // overwrite logit / dP columns this same thread has already consumed.
-#pragma unroll
-        for (int ch = 0; ch < 2; ++ch) {
-          uint32_t sr[16], dr[16];
-          ptx::tmem_ld16(my_s + ch * 16, sr);
-          ptx::tmem_ld16(my_dp + ch * 16, dr);
+        if (lane == 0 && (warp == 0 || warp == 15)) BTRACE(warp == 0 ? 2 : 3, 8);
+        if constexpr (kPipe) {
+          // all 32 logits and dP values of this thread into registers, then hand the columns
+          // back to the MMA thread before doing the arithmetic
+          uint32_t sr[32], dr[32];
+          ptx::tmem_ld32(my_s, sr);
+          ptx::tmem_ld32(my_dp, dr);
           ptx::tmem_ld_wait();
-          uint32_t pk[8], dk[8];
+          ptx::tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(bars.sdp_free);
+          if (lane == 0 && (warp == 0 || warp == 15)) BTRACE(warp == 0 ? 2 : 3, 9);
+          uint32_t dk[16];
 #pragma unroll
-          for (int j = 0; j < 16; j += 2) {
-            float l0 = row_l, l1 = row_l, d0 = row_d, d1 = row_d;
-            if (kKeyRows) {
-              const int col = part * 32 + ch * 16 + j;
-              const float2 lv = *reinterpret_cast<const float2*>(stat + col);
-              const float2 dv = *reinterpret_cast<const float2*>(stat + kTile + col);
-              l0 = lv.x; l1 = lv.y; d0 = dv.x; d1 = dv.y;
-            }
-            float p0 = ptx::ex2(fmaf(__uint_as_float(sr[j]), c, -l0));
-            float p1 = ptx::ex2(fmaf(__uint_as_float(sr[j + 1]), c, -l1));
+          for (int j = 0; j < 32; j += 2) {
+            float p0 = ptx::ex2(fmaf(__uint_as_float(sr[j]), c, -row_l));
+            float p1 = ptx::ex2(fmaf(__uint_as_float(sr[j + 1]), c, -row_l));
             if (!interior) {
-              p0 = ((mw >> (ch * 16 + j)) & 1u) ? p0 : 0.f;
-              p1 = ((mw >> (ch * 16 + j + 1)) & 1u) ? p1 : 0.f;
+              p0 = ((mw >> j) & 1u) ? p0 : 0.f;
+              p1 = ((mw >> (j + 1)) & 1u) ? p1 : 0.f;
             }
-            const float s0 = p0 * (__uint_as_float(dr[j]) - d0);
-            const float s1 = p1 * (__uint_as_float(dr[j + 1]) - d1);
-            pk[j >> 1] = pack2<kType>(p0, p1);
-            dk[j >> 1] = pack2<kType>(s0, s1);
+            dk[j >> 1] = pack2<kType>(p0 * (__uint_as_float(dr[j]) - row_d),
+                                      p1 * (__uint_as_float(dr[j + 1]) - row_d));
           }
-          if (kKeyRows) ptx::tmem_st8(my_s + ch * 8, pk);
-          ptx::tmem_st8(my_dp + ch * 8, dk);
+          if (lane == 0 && (warp == 0 || warp == 15)) BTRACE(warp == 0 ? 2 : 3, 10);
+          // the dS buffer of two tiles ago must have been consumed by its dQ product
+          const uint32_t buf = dseq & 1;
+          if (!__all_sync(0xffffffffu, wait_bar(bars.ds_free + buf, ((dseq >> 1) & 1) ^ 1,
+                                                abort_flag, p.status, (5 << 8) | kStDsFree))) {
+            alive = false;
+            break;
+          }
+          ++dseq;
+          ptx::tc_fence_after_sync();
+          ptx::tmem_st16(lane_addr + kDsCol + buf * kDsBufCols + part * 16, dk);
+          ptx::tmem_st_wait();
+          ptx::tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(bars.ds_full + buf);
+          if (lane == 0 && (warp == 0 || warp == 15)) BTRACE(warp == 0 ? 2 : 3, 11);
+        } else {
+          // 16 columns at a time: p = 2^(s c - lse), ds = p (dp - delta); the packed results
+          // overwrite logit / dP columns this same thread has already consumed.
+#pragma unroll
+          for (int ch = 0; ch < 2; ++ch) {
+            uint32_t sr[16], dr[16];
+            ptx::tmem_ld16(my_s + ch * 16, sr);
+            ptx::tmem_ld16(my_dp + ch * 16, dr);
+            ptx::tmem_ld_wait();
+            uint32_t pk[8], dk[8];
+#pragma unroll
+            for (int j = 0; j < 16; j += 2) {
+              float l0 = row_l, l1 = row_l, d0 = row_d, d1 = row_d;
+              if (kKeyRows) {
+                const int col = part * 32 + ch * 16 + j;
+                const float2 lv = *reinterpret_cast<const float2*>(stat + col);
+                const float2 dv = *reinterpret_cast<const float2*>(stat + kTile + col);
+                l0 = lv.x; l1 = lv.y; d0 = dv.x; d1 = dv.y;
+              }
+              float p0 = ptx::ex2(fmaf(__uint_as_float(sr[j]), c, -l0));
+              float p1 = ptx::ex2(fmaf(__uint_as_float(sr[j + 1]), c, -l1));
+              if (!interior) {
+                p0 = ((mw >> (ch * 16 + j)) & 1u) ? p0 : 0.f;
+                p1 = ((mw >> (ch * 16 + j + 1)) & 1u) ? p1 : 0.f;
+              }
+              const float s0 = p0 * (__uint_as_float(dr[j]) - d0);
+              const float s1 = p1 * (__uint_as_float(dr[j + 1]) - d1);
+              pk[j >> 1] = pack2<kType>(p0, p1);
+              dk[j >> 1] = pack2<kType>(s0, s1);
+            }
+            if (kKeyRows) ptx::tmem_st8(my_s + ch * 8, pk);
+            ptx::tmem_st8(my_dp + ch * 8, dk);
+          }
+          ptx::tmem_st_wait();
+          ptx::tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(bars.ds_full);
         }
-        ptx::tmem_st_wait();
-        ptx::tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(bars.ds_full);
       }
       if (!alive) break;
       // ---- epilogue: accumulators -> gradient rows ----
@@ -546,91 +645,172 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
         ptx::mbar_arrive(bars.desc_empty + dslot);
       }
     }
-  } else if (warp == kMmaWarp) {
+  } else if (warp == kMmaWarp || (kPipe && warp == kMma2Warp)) {
     // =============================== MMA issue ==============================================
+    // Pass dKdV: one thread issues everything. Pass dQ: the S / dP products and the dQ products
+    // are issued by two threads in warps of different sub-partitions - an issuing thread shares
+    // its scheduler with four busy softmax warps, and one thread alone cannot feed the tensor
+    // pipe at its rate then. The two streams touch disjoint TMEM columns and are ordered against
+    // each other through the softmax threads' barriers only.
     if (lane == 0) {
       constexpr uint32_t idesc_s = ptx::make_idesc(kType == kTyBf16 ? 1 : 0, 0, 0, kTile, kTile);
       constexpr uint32_t idesc_acc = ptx::make_idesc(kType == kTyBf16 ? 1 : 0, 0, 1, kTile, D);
       constexpr uint32_t desc_hi = ptx::smem_desc_hi_sw128();
       const uint32_t row_base = ptx::smem_u32(row_sm);
       const uint32_t col_base = ptx::smem_u32(col_sm);
+      const uint32_t col2_base = ptx::smem_u32(col2_sm);
       const uint32_t r1_lo = ptx::smem_desc_lo(row_base, 16);
       const uint32_t r2_lo = ptx::smem_desc_lo(row_base + kTileBytes, 16);
       const uint32_t s_tm = tmem_base + kSCol, dp_tm = tmem_base + kDpCol;
       const uint32_t acc0_tm = tmem_base + kAcc0Col, acc1_tm = tmem_base + kAcc1Col;
-      uint32_t ph_r = 0, ph_ds = 0, ph_ae = 1, slot = 0, ph_c = 0;
+      const bool second = kPipe && warp == kMma2Warp;
+      const int role = second ? 9 : 6;  // status word role
+      BTRACE_DECL(second ? 2 * 40 : 3 * 40)
+      // S = R1 C1^T and dP = R2 C2^T: both operands K-major, contraction over the head dim
+      auto issue_rc = [&](uint32_t d_tm, uint32_t r_lo, uint32_t ctile) {
+        const uint32_t bd = ptx::smem_desc_lo(ctile, 16);
+#pragma unroll
+        for (int kb = 0; kb < D / 16; ++kb) {
+          const uint32_t koff = ((kb >> 2) * kBlockBytes + (kb & 3) * 32) >> 4;
+          ptx::mma_ss_lohi(d_tm, r_lo + koff, desc_hi, bd + koff, desc_hi, idesc_s,
+                           kb > 0 ? 1u : 0u);
+        }
+      };
+      // acc += A C: A = 16-bit values in TMEM, 8 columns per 16-column step starting at `a_tm`
+      // with `a_pair_stride` columns between pairs of steps; B = the column tile read MN-major,
+      // contraction over the 128 columns
+      auto issue_acc = [&](uint32_t acc_tm, uint32_t a_tm, uint32_t a_pair_stride, uint32_t ctile,
+                           bool first) {
+        const uint32_t bd = ptx::smem_desc_lo(ctile, kBlockBytes);
+#pragma unroll
+        for (int ks = 0; ks < kTile / 16; ++ks)
+          ptx::mma_ts_lohi(acc_tm, a_tm + (ks >> 1) * a_pair_stride + (ks & 1) * 8,
+                           bd + ks * (2048 >> 4), desc_hi, idesc_acc, (first && ks == 0) ? 0u : 1u);
+      };
+      uint32_t ph_r = 0, ph_ds = 0, ph_ae = 1;
+      uint32_t slot = 0, ph_c = 0;    // ring position in the C1 (or combined) stages
+      uint32_t slot2 = 0, ph_v = 0;   // pass dQ: ring position in the C2 stages
+      uint32_t gt = 0;                // pass dQ: column tiles handled so far, over all items
       bool alive = true;
       for (uint32_t seq = 0; alive; ++seq) {
         const uint32_t dslot = seq % kDescSlots;
         if (!wait_bar(bars.desc_full + dslot, (seq / kDescSlots) & 1, abort_flag, p.status,
-                      (6 << 8) | kStDescFull)) break;
+                      (role << 8) | kStDescFull)) break;
         const int n = reinterpret_cast<const Item*>(desc_sm + dslot * kDescBytes)->n_tiles;
         ptx::mbar_arrive(bars.desc_empty + dslot);
         if (n < 0) break;
-        if (!wait_bar(bars.r_full, ph_r, abort_flag, p.status, (6 << 8) | kStRFull)) break;
-        ph_r ^= 1;
-        for (int t = 0; t < n; ++t) {
-          if (!wait_bar(bars.c_full + slot, ph_c, abort_flag, p.status, (6 << 8) | kStCFull)) {
-            alive = false; break;
-          }
-          const uint32_t c1 = col_base + slot * 2 * kTileBytes, c2 = c1 + kTileBytes;
-          ptx::tc_fence_after_sync();
-          {
-            // S = R1 C1^T and dP = R2 C2^T: both operands K-major, contraction over the head dim
-            const uint32_t b1 = ptx::smem_desc_lo(c1, 16), b2 = ptx::smem_desc_lo(c2, 16);
-#pragma unroll
-            for (int kb = 0; kb < D / 16; ++kb) {
-              const uint32_t koff = ((kb >> 2) * kBlockBytes + (kb & 3) * 32) >> 4;
-              ptx::mma_ss_lohi(s_tm, r1_lo + koff, desc_hi, b1 + koff, desc_hi, idesc_s,
-                               kb > 0 ? 1u : 0u);
-            }
-#pragma unroll
-            for (int kb = 0; kb < D / 16; ++kb) {
-              const uint32_t koff = ((kb >> 2) * kBlockBytes + (kb & 3) * 32) >> 4;
-              ptx::mma_ss_lohi(dp_tm, r2_lo + koff, desc_hi, b2 + koff, desc_hi, idesc_s,
-                               kb > 0 ? 1u : 0u);
-            }
-          }
-          ptx::tc_commit(bars.sdp_full);
-          // the row tiles are read by these products only: after the item's last pair they may
-          // be replaced by the next item's
-          if (t == n - 1) ptx::tc_commit(bars.r_empty);
-          if (!wait_bar(bars.ds_full, ph_ds, abort_flag, p.status, (6 << 8) | kStDsFull)) {
-            alive = false; break;
-          }
-          ph_ds ^= 1;
-          if (t == 0) {
-            // the previous item's epilogue must have drained the accumulators
-            if (!wait_bar(bars.acc_empty, ph_ae, abort_flag, p.status, (6 << 8) | kStAccEmpty)) {
+        if (kPipe && !second) {
+          // ---- pass dQ, first issuer: dP and S of each column tile as soon as the softmax
+          // threads have read the previous tile's. dP goes first: its C2 tile arrives early (a
+          // C2 stage is released right after the product).
+          if (!wait_bar(bars.r_full, ph_r, abort_flag, p.status, (role << 8) | kStRFull)) break;
+          ph_r ^= 1;
+          for (int t = 0; t < n; ++t) {
+            if (!wait_bar(bars.sdp_free, (gt & 1) ^ 1, abort_flag, p.status,
+                          (role << 8) | kStSdpFree) ||
+                !wait_bar(bars.v_full + slot2, ph_v, abort_flag, p.status,
+                          (role << 8) | kStVFull)) {
               alive = false; break;
             }
-            ph_ae ^= 1;
-          }
-          ptx::tc_fence_after_sync();
-          {
-            // acc0 += dS C1 (and acc1 += P C2): A from TMEM (the 16-bit values of columns
-            // [32 q, 32 q + 32) sit packed in columns [32 q, 32 q + 16), over the fp32 columns
-            // their owner thread consumed), B = the column tile read MN-major, contraction over
-            // the 128 columns
-            const uint32_t b1 = ptx::smem_desc_lo(c1, kBlockBytes);
-            const uint32_t b2 = ptx::smem_desc_lo(c2, kBlockBytes);
-#pragma unroll
-            for (int ks = 0; ks < kTile / 16; ++ks)
-              ptx::mma_ts_lohi(acc0_tm, dp_tm + (ks >> 1) * 32 + (ks & 1) * 8, b1 + ks * (2048 >> 4),
-                               desc_hi, idesc_acc, (t == 0 && ks == 0) ? 0u : 1u);
-            if (kKeyRows) {
-#pragma unroll
-              for (int ks = 0; ks < kTile / 16; ++ks)
-                ptx::mma_ts_lohi(acc1_tm, s_tm + (ks >> 1) * 32 + (ks & 1) * 8,
-                                 b2 + ks * (2048 >> 4), desc_hi, idesc_acc,
-                                 (t == 0 && ks == 0) ? 0u : 1u);
+            ++gt;
+            BTRACE(0, 1);
+            ptx::tc_fence_after_sync();
+            issue_rc(dp_tm, r2_lo, col2_base + slot2 * kTileBytes);
+            ptx::tc_commit(bars.v_empty + slot2);
+            if (++slot2 == kStages) {
+              slot2 = 0;
+              ph_v ^= 1;
+            }
+            if (!wait_bar(bars.c_full + slot, ph_c, abort_flag, p.status,
+                          (role << 8) | kStCFull)) {
+              alive = false; break;
+            }
+            BTRACE(0, 2);
+            ptx::tc_fence_after_sync();
+            issue_rc(s_tm, r1_lo, col_base + slot * kTileBytes);
+            ptx::tc_commit(bars.sdp_full);
+            // the row tiles are read by these products only
+            if (t == n - 1) ptx::tc_commit(bars.r_empty);
+            BTRACE(0, 3);
+            if (++slot == kRing1) {
+              slot = 0;
+              ph_c ^= 1;
             }
           }
-          ptx::tc_commit(bars.c_empty + slot);
-          if (t == n - 1) ptx::tc_commit(bars.acc_full);
-          if (++slot == kStages) {
-            slot = 0;
-            ph_c ^= 1;
+        } else if (kPipe) {
+          // ---- pass dQ, second issuer: dQ += dS C1 of each column tile when its dS is stored
+          for (int t = 0; t < n; ++t) {
+            const uint32_t buf = gt & 1;
+            // the C1 wait cannot block (S of this tile was computed from the same stage); it
+            // orders this thread's reads after the tile's arrival
+            if (!wait_bar(bars.ds_full + buf, (gt >> 1) & 1, abort_flag, p.status,
+                          (role << 8) | kStDsFull) ||
+                !wait_bar(bars.c_full + slot, ph_c, abort_flag, p.status,
+                          (role << 8) | kStCFull)) {
+              alive = false; break;
+            }
+            ++gt;
+            if (t == 0) {
+              // the previous item's epilogue must have drained the accumulator
+              if (!wait_bar(bars.acc_empty, ph_ae, abort_flag, p.status,
+                            (role << 8) | kStAccEmpty)) {
+                alive = false; break;
+              }
+              ph_ae ^= 1;
+            }
+            BTRACE(4, 4);
+            ptx::tc_fence_after_sync();
+            issue_acc(acc0_tm, tmem_base + kDsCol + buf * kDsBufCols, 16,
+                      col_base + slot * kTileBytes, t == 0);
+            ptx::tc_commit(bars.c_empty + slot);
+            ptx::tc_commit(bars.ds_free + buf);
+            if (t == n - 1) ptx::tc_commit(bars.acc_full);
+            BTRACE(4, 5);
+            if (++slot == kRing1) {
+              slot = 0;
+              ph_c ^= 1;
+            }
+          }
+        } else {
+          if (!wait_bar(bars.r_full, ph_r, abort_flag, p.status, (role << 8) | kStRFull)) break;
+          ph_r ^= 1;
+          for (int t = 0; t < n; ++t) {
+            if (!wait_bar(bars.c_full + slot, ph_c, abort_flag, p.status,
+                          (role << 8) | kStCFull)) {
+              alive = false; break;
+            }
+            const uint32_t c1 = col_base + slot * 2 * kTileBytes, c2 = c1 + kTileBytes;
+            ptx::tc_fence_after_sync();
+            issue_rc(s_tm, r1_lo, c1);
+            issue_rc(dp_tm, r2_lo, c2);
+            ptx::tc_commit(bars.sdp_full);
+            // the row tiles are read by these products only: after the item's last pair they
+            // may be replaced by the next item's
+            if (t == n - 1) ptx::tc_commit(bars.r_empty);
+            if (!wait_bar(bars.ds_full, ph_ds, abort_flag, p.status, (role << 8) | kStDsFull)) {
+              alive = false; break;
+            }
+            ph_ds ^= 1;
+            if (t == 0) {
+              // the previous item's epilogue must have drained the accumulators
+              if (!wait_bar(bars.acc_empty, ph_ae, abort_flag, p.status,
+                            (role << 8) | kStAccEmpty)) {
+                alive = false; break;
+              }
+              ph_ae ^= 1;
+            }
+            ptx::tc_fence_after_sync();
+            // acc0 += dS C1 and acc1 += P C2: the 16-bit values of columns [32 q, 32 q + 32)
+            // sit packed in columns [32 q, 32 q + 16), over the fp32 columns their owner
+            // thread consumed
+            issue_acc(acc0_tm, dp_tm, 32, c1, t == 0);
+            if (kKeyRows) issue_acc(acc1_tm, s_tm, 32, c2, t == 0);
+            ptx::tc_commit(bars.c_empty + slot);
+            if (t == n - 1) ptx::tc_commit(bars.acc_full);
+            if (++slot == kStages) {
+              slot = 0;
+              ph_c ^= 1;
+            }
           }
         }
       }
@@ -638,7 +818,8 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
   } else if (warp == kLoadWarp) {
     // ============ TMA loads, work-item decode, tile classification ==========================
     if (lane == 0) {
-      uint32_t ph_re = 1, slot = 0, ph_ce = 1, published = 0, tseq = 0;
+      uint32_t ph_re = 1, slot = 0, ph_ce = 1, slot2 = 0, ph_ve = 1, published = 0, tseq = 0;
+      BTRACE_DECL(2 * 40)
       bool alive = true;
       // items are drawn in order from an atomic counter (row tiles differ a lot in how many
       // column tiles they need: borders, the first rows of a causal axis)
@@ -714,18 +895,47 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
           tile_rec[tseq % kTileRecs] = rec;
           ptx::mbar_arrive(bars.rec_full + tseq % kTileRecs);
           ++tseq;
-          if (!wait_bar(bars.c_empty + slot, ph_ce, abort_flag, p.status, (7 << 8) | kStCEmpty)) {
-            alive = false; break;
+          if constexpr (kPipe) {
+            // C2 first: its stage is free long before the C1 stage of the same age
+            if (!wait_bar(bars.v_empty + slot2, ph_ve, abort_flag, p.status,
+                          (7 << 8) | kStVEmpty)) {
+              alive = false; break;
+            }
+            BTRACE(1, 6);
+            ptx::mbar_arrive_expect_tx(bars.v_full + slot2, kTileBytes);
+            for (int db = 0; db < kDBlocks; ++db)
+              ptx::tma_load_5d(col2_sm + slot2 * kTileBytes + db * kBlockBytes,
+                               is_extra ? &tm_e2 : &tm_c2, bars.v_full + slot2,
+                               col_head * D + db * 64, x0, x1, x2, b);
+            if (++slot2 == kStages) {
+              slot2 = 0;
+              ph_ve ^= 1;
+            }
+            if (!wait_bar(bars.c_empty + slot, ph_ce, abort_flag, p.status,
+                          (7 << 8) | kStCEmpty)) {
+              alive = false; break;
+            }
+            BTRACE(1, 7);
+            ptx::mbar_arrive_expect_tx(bars.c_full + slot, kTileBytes);
+            for (int db = 0; db < kDBlocks; ++db)
+              ptx::tma_load_5d(col_sm + slot * kTileBytes + db * kBlockBytes,
+                               is_extra ? &tm_e1 : &tm_c1, bars.c_full + slot,
+                               col_head * D + db * 64, x0, x1, x2, b);
+          } else {
+            if (!wait_bar(bars.c_empty + slot, ph_ce, abort_flag, p.status,
+                          (7 << 8) | kStCEmpty)) {
+              alive = false; break;
+            }
+            ptx::mbar_arrive_expect_tx(bars.c_full + slot, 2 * kTileBytes);
+            uint8_t* dst = col_sm + slot * 2 * kTileBytes;
+            for (int db = 0; db < kDBlocks; ++db) {
+              ptx::tma_load_5d(dst + db * kBlockBytes, is_extra ? &tm_e1 : &tm_c1,
+                               bars.c_full + slot, col_head * D + db * 64, x0, x1, x2, b);
+              ptx::tma_load_5d(dst + kTileBytes + db * kBlockBytes, is_extra ? &tm_e2 : &tm_c2,
+                               bars.c_full + slot, col_head * D + db * 64, x0, x1, x2, b);
+            }
           }
-          ptx::mbar_arrive_expect_tx(bars.c_full + slot, 2 * kTileBytes);
-          uint8_t* dst = col_sm + slot * 2 * kTileBytes;
-          for (int db = 0; db < kDBlocks; ++db) {
-            ptx::tma_load_5d(dst + db * kBlockBytes, is_extra ? &tm_e1 : &tm_c1,
-                             bars.c_full + slot, col_head * D + db * 64, x0, x1, x2, b);
-            ptx::tma_load_5d(dst + kTileBytes + db * kBlockBytes, is_extra ? &tm_e2 : &tm_c2,
-                             bars.c_full + slot, col_head * D + db * 64, x0, x1, x2, b);
-          }
-          if (++slot == kStages) {
+          if (++slot == kRing1) {
             slot = 0;
             ph_ce ^= 1;
           }
@@ -767,6 +977,8 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
 
 // ---- host side -------------------------------------------------------------------------------
 
+long long* g_bwd_trace = nullptr;
+
 template <int D, bool kBf16, bool kKeyRows>
 const void* bwd_kernel_for_ndim(int ndim) {
   constexpr int kType = kBf16 ? kTyBf16 : kTyF16;
@@ -788,7 +1000,7 @@ const void* bwd_kernel_variant(int D, bool bf16, int ndim, bool key_rows) {
 }
 
 // Opt-in shared memory per kernel variant and device, set once.
-int ensure_smem_attribute(const void* fn, int D) {
+int ensure_smem_attribute(const void* fn, int smem_bytes) {
   static std::mutex mu;
   static const void* done[64][24];
   int dev = 0;
@@ -799,7 +1011,7 @@ int ensure_smem_attribute(const void* fn, int D) {
     if (done[dev][i] == fn) return B200NA_OK;
     if (done[dev][i] == nullptr) {
       B200NA_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           D == 128 ? Smem<128>::kBytes : Smem<64>::kBytes));
+                                           smem_bytes));
       done[dev][i] = fn;
       return B200NA_OK;
     }
@@ -930,15 +1142,24 @@ extern "C" B200NA_API int b200na_na_backward_direct(
     p.out0 = dense ? d_add_k : (key_rows ? dk : dq);
     p.out1 = dense ? d_add_v : (key_rows ? dv : nullptr);
     if ((rc = fna_work_counters(&p.work)) != B200NA_OK) return rc;
+    p.trace = g_bwd_trace;
     const void* fn = bwd_kernel_variant(D, dtype == B200NA_BF16, kernel_ndim, key_rows);
-    if ((rc = ensure_smem_attribute(fn, D)) != B200NA_OK) return rc;
+    const int smem_bytes = key_rows ? (D == 128 ? Smem<128, false>::kBytes : Smem<64, false>::kBytes)
+                                    : (D == 128 ? Smem<128, true>::kBytes : Smem<64, true>::kBytes);
+    if ((rc = ensure_smem_attribute(fn, smem_bytes)) != B200NA_OK) return rc;
     const int grid = (int)(p.total_work < sms ? p.total_work : sms);
     void* args_q[] = {(void*)&mq, (void*)&mdo, (void*)&mk, (void*)&mv, (void*)&mek, (void*)&mev, (void*)&p};
     void* args_k[] = {(void*)&mk, (void*)&mv, (void*)&mq, (void*)&mdo, (void*)&mek, (void*)&mev, (void*)&p};
     void* args_e[] = {(void*)&mek, (void*)&mev, (void*)&mqf, (void*)&mdof, (void*)&mek, (void*)&mev, (void*)&p};
     B200NA_CUDA_TRY(cudaLaunchKernel(fn, dim3(grid), dim3(kThreads),
-                                     dense ? args_e : (key_rows ? args_k : args_q),
-                                     D == 128 ? Smem<128>::kBytes : Smem<64>::kBytes, stream));
+                                     dense ? args_e : (key_rows ? args_k : args_q), smem_bytes,
+                                     stream));
   }
   return B200NA_OK;
 }
+
+#if defined(B200NA_BWD_TRACE) && B200NA_BWD_TRACE
+extern "C" B200NA_API void b200na_debug_set_bwd_trace(void* buf) {
+  b200na::g_bwd_trace = reinterpret_cast<long long*>(buf);
+}
+#endif
