@@ -69,7 +69,7 @@ constexpr int kTileRecs = 8;
 // issuer of pass dQ (backward kernel)
 enum : int { kStRFull = 1, kStREmpty, kStCFull, kStCEmpty, kStSdpFull, kStDsFull, kStAccFull,
              kStAccEmpty, kStDescFull, kStDescEmpty, kStRecFull, kStRecEmpty, kStSmemAlign,
-             kStSdpFree, kStDsFree, kStVFull, kStVEmpty };
+             kStSdpFree, kStDsFree, kStVFull, kStVEmpty, kStDpFull, kStPFull };
 
 struct BwdTcParams {
   int ndim;
@@ -272,6 +272,8 @@ struct Smem {
 
 struct Bars {
   uint64_t *r_full, *r_empty, *sdp_full, *sdp_free, *acc_full, *acc_empty, *ds_full, *ds_free;
+  // pass dKdV only: these share the slots of ds_free[0] and ds_full[1], which pass dQ alone uses
+  uint64_t *dp_full, *p_full;
   uint64_t *desc_full, *desc_empty, *rec_full, *rec_empty, *c_full, *c_empty, *v_full, *v_empty;
 };
 
@@ -348,6 +350,8 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
   bars.acc_empty = bar_base + 5;
   bars.ds_full = bar_base + 6;   // [2]
   bars.ds_free = bar_base + 8;   // [2]
+  bars.dp_full = bar_base + 8;
+  bars.p_full = bar_base + 7;
   bars.desc_full = bar_base + 10;
   bars.desc_empty = bars.desc_full + kDescSlots;
   bars.rec_full = bars.desc_empty + kDescSlots;
@@ -431,7 +435,7 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
     const uint32_t my_dp = lane_addr + kDpCol + part * 32;
     const float c = p.scale_log2;
     constexpr float kLog2e = 1.4426950408889634f;
-    uint32_t ph_sdp = 0, ph_acc = 0, tseq = 0, dseq = 0;
+    uint32_t ph_sdp = 0, ph_dp = 0, ph_acc = 0, tseq = 0, dseq = 0;
     BTRACE_DECL(4 * 40)
     // in-tile coordinates of this thread's row, and of the column whose statistics it fetches
     int tr[B200NA_MAX_DIM], tcol[B200NA_MAX_DIM];
@@ -570,37 +574,64 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
           if (lane == 0) ptx::mbar_arrive(bars.ds_full + buf);
           if (lane == 0 && (warp == 0 || warp == 15)) BTRACE(warp == 0 ? 2 : 3, 11);
         } else {
-          // 16 columns at a time: p = 2^(s c - lse), ds = p (dp - delta); the packed results
-          // overwrite logit / dP columns this same thread has already consumed.
-#pragma unroll
-          for (int ch = 0; ch < 2; ++ch) {
-            uint32_t sr[16], dr[16];
-            ptx::tmem_ld16(my_s + ch * 16, sr);
-            ptx::tmem_ld16(my_dp + ch * 16, dr);
+          // Pass dKdV. The two 128-column regions swap roles with every tile: S arrives in
+          // region `reg`, dP in the other one. P = 2^(s c - lse) needs S only, so it is computed
+          // (and stored, 16-bit, over the first half of this thread's consumed logits) while the
+          // dP product still runs; dS = P (dP - delta) follows once dP is there and goes over
+          // the second half. As soon as dP is in registers its region is handed back, and the
+          // next tile's S is computed there during this tile's dS arithmetic and products.
+          const uint32_t reg = dseq & 1;
+          ++dseq;
+          const uint32_t my_r = lane_addr + (reg ? kDpCol : kSCol) + part * 32;
+          const uint32_t my_o = lane_addr + (reg ? kSCol : kDpCol) + part * 32;
+          float pf[32];
+          {
+            uint32_t sr[32];
+            ptx::tmem_ld32(my_r, sr);
             ptx::tmem_ld_wait();
-            uint32_t pk[8], dk[8];
+            uint32_t pk[16];
 #pragma unroll
-            for (int j = 0; j < 16; j += 2) {
-              float l0 = row_l, l1 = row_l, d0 = row_d, d1 = row_d;
-              if (kKeyRows) {
-                const int col = part * 32 + ch * 16 + j;
-                const float2 lv = *reinterpret_cast<const float2*>(stat + col);
-                const float2 dv = *reinterpret_cast<const float2*>(stat + kTile + col);
-                l0 = lv.x; l1 = lv.y; d0 = dv.x; d1 = dv.y;
-              }
-              float p0 = ptx::ex2(fmaf(__uint_as_float(sr[j]), c, -l0));
-              float p1 = ptx::ex2(fmaf(__uint_as_float(sr[j + 1]), c, -l1));
+            for (int j = 0; j < 32; j += 2) {
+              const float2 lv = *reinterpret_cast<const float2*>(stat + part * 32 + j);
+              float p0 = ptx::ex2(fmaf(__uint_as_float(sr[j]), c, -lv.x));
+              float p1 = ptx::ex2(fmaf(__uint_as_float(sr[j + 1]), c, -lv.y));
               if (!interior) {
-                p0 = ((mw >> (ch * 16 + j)) & 1u) ? p0 : 0.f;
-                p1 = ((mw >> (ch * 16 + j + 1)) & 1u) ? p1 : 0.f;
+                p0 = ((mw >> j) & 1u) ? p0 : 0.f;
+                p1 = ((mw >> (j + 1)) & 1u) ? p1 : 0.f;
               }
-              const float s0 = p0 * (__uint_as_float(dr[j]) - d0);
-              const float s1 = p1 * (__uint_as_float(dr[j + 1]) - d1);
+              pf[j] = p0;
+              pf[j + 1] = p1;
               pk[j >> 1] = pack2<kType>(p0, p1);
-              dk[j >> 1] = pack2<kType>(s0, s1);
             }
-            if (kKeyRows) ptx::tmem_st8(my_s + ch * 8, pk);
-            ptx::tmem_st8(my_dp + ch * 8, dk);
+            ptx::tmem_st16(my_r, pk);
+          }
+          // P is complete: its product with C2 can start while dS is still being computed
+          ptx::tmem_st_wait();
+          ptx::tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(bars.p_full);
+          if (!__all_sync(0xffffffffu, wait_bar(bars.dp_full, ph_dp, abort_flag, p.status,
+                                                (5 << 8) | kStDpFull))) {
+            alive = false;
+            break;
+          }
+          ph_dp ^= 1;
+          ptx::tc_fence_after_sync();
+          {
+            uint32_t dr[32];
+            ptx::tmem_ld32(my_o, dr);
+            ptx::tmem_ld_wait();
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(bars.sdp_free);
+            uint32_t dk[16];
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) {
+              const float2 dv = *reinterpret_cast<const float2*>(stat + kTile + part * 32 + j);
+              dk[j >> 1] = pack2<kType>(pf[j] * (__uint_as_float(dr[j]) - dv.x),
+                                        pf[j + 1] * (__uint_as_float(dr[j + 1]) - dv.y));
+            }
+            ptx::tmem_st16(my_r + 16, dk);
           }
           ptx::tmem_st_wait();
           ptx::tc_fence_before_sync();
@@ -687,10 +718,11 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
           ptx::mma_ts_lohi(acc_tm, a_tm + (ks >> 1) * a_pair_stride + (ks & 1) * 8,
                            bd + ks * (2048 >> 4), desc_hi, idesc_acc, (first && ks == 0) ? 0u : 1u);
       };
-      uint32_t ph_r = 0, ph_ds = 0, ph_ae = 1;
+      uint32_t ph_r = 0, ph_ae = 1;
       uint32_t slot = 0, ph_c = 0;    // ring position in the C1 (or combined) stages
       uint32_t slot2 = 0, ph_v = 0;   // pass dQ: ring position in the C2 stages
-      uint32_t gt = 0;                // pass dQ: column tiles handled so far, over all items
+      uint32_t gt = 0;                // column tiles handled so far, over all items
+      uint32_t slot_d = 0;            // pass dKdV: stage of the tile whose accumulations come next
       bool alive = true;
       for (uint32_t seq = 0; alive; ++seq) {
         const uint32_t dslot = seq % kDescSlots;
@@ -772,25 +804,33 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
             }
           }
         } else {
+          // ---- pass dKdV, per tile t: dV += P C2 when P is stored; S of tile t + 1 as soon as
+          // the softmax threads have taken dP of tile t out of the region it goes to; dK += dS C1
+          // when dS is stored; then dP of tile t + 1 (it overwrites tile t's P / dS operands,
+          // behind their readers in issue order).
           if (!wait_bar(bars.r_full, ph_r, abort_flag, p.status, (role << 8) | kStRFull)) break;
           ph_r ^= 1;
+          const uint32_t reg_tm[2] = {s_tm, dp_tm};
+          // first tile of the item: S, then dP (the other region's last readers, the previous
+          // item's accumulations, were issued before)
+          if (!wait_bar(bars.c_full + slot, ph_c, abort_flag, p.status, (role << 8) | kStCFull) ||
+              !wait_bar(bars.sdp_free, (gt & 1) ^ 1, abort_flag, p.status,
+                        (role << 8) | kStSdpFree))
+            break;
+          uint32_t c_cur = col_base + slot * 2 * kTileBytes, c_next = 0;
+          ptx::tc_fence_after_sync();
+          issue_rc(reg_tm[gt & 1], r1_lo, c_cur);
+          ptx::tc_commit(bars.sdp_full);
+          issue_rc(reg_tm[(gt & 1) ^ 1], r2_lo, c_cur + kTileBytes);
+          ptx::tc_commit(bars.dp_full);
+          if (n == 1) ptx::tc_commit(bars.r_empty);
+          ++gt;
+          if (++slot == kStages) {
+            slot = 0;
+            ph_c ^= 1;
+          }
           for (int t = 0; t < n; ++t) {
-            if (!wait_bar(bars.c_full + slot, ph_c, abort_flag, p.status,
-                          (role << 8) | kStCFull)) {
-              alive = false; break;
-            }
-            const uint32_t c1 = col_base + slot * 2 * kTileBytes, c2 = c1 + kTileBytes;
-            ptx::tc_fence_after_sync();
-            issue_rc(s_tm, r1_lo, c1);
-            issue_rc(dp_tm, r2_lo, c2);
-            ptx::tc_commit(bars.sdp_full);
-            // the row tiles are read by these products only: after the item's last pair they
-            // may be replaced by the next item's
-            if (t == n - 1) ptx::tc_commit(bars.r_empty);
-            if (!wait_bar(bars.ds_full, ph_ds, abort_flag, p.status, (role << 8) | kStDsFull)) {
-              alive = false; break;
-            }
-            ph_ds ^= 1;
+            const uint32_t k = gt - 1;  // global index of tile t (its S was the last one issued)
             if (t == 0) {
               // the previous item's epilogue must have drained the accumulators
               if (!wait_bar(bars.acc_empty, ph_ae, abort_flag, p.status,
@@ -799,18 +839,49 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
               }
               ph_ae ^= 1;
             }
-            ptx::tc_fence_after_sync();
-            // acc0 += dS C1 and acc1 += P C2: the 16-bit values of columns [32 q, 32 q + 32)
-            // sit packed in columns [32 q, 32 q + 16), over the fp32 columns their owner
-            // thread consumed
-            issue_acc(acc0_tm, dp_tm, 32, c1, t == 0);
-            if (kKeyRows) issue_acc(acc1_tm, s_tm, 32, c2, t == 0);
-            ptx::tc_commit(bars.c_empty + slot);
-            if (t == n - 1) ptx::tc_commit(bars.acc_full);
-            if (++slot == kStages) {
-              slot = 0;
-              ph_c ^= 1;
+            // Of a thread's columns [32 q, 32 q + 32) of the tile's region, [32 q, 32 q + 16)
+            // hold its packed P and [32 q + 16, 32 q + 32) its dS.
+            // acc1 += P C2 as soon as P is stored, while the threads still work on dS
+            if (!wait_bar(bars.p_full, k & 1, abort_flag, p.status, (role << 8) | kStPFull)) {
+              alive = false; break;
             }
+            ptx::tc_fence_after_sync();
+            issue_acc(acc1_tm, reg_tm[k & 1], 32, c_cur + kTileBytes, t == 0);
+            if (t + 1 < n) {
+              // S of the next tile, into the region dP of this tile has been taken out of
+              if (!wait_bar(bars.c_full + slot, ph_c, abort_flag, p.status,
+                            (role << 8) | kStCFull) ||
+                  !wait_bar(bars.sdp_free, (gt & 1) ^ 1, abort_flag, p.status,
+                            (role << 8) | kStSdpFree)) {
+                alive = false; break;
+              }
+              c_next = col_base + slot * 2 * kTileBytes;
+              ptx::tc_fence_after_sync();
+              issue_rc(reg_tm[gt & 1], r1_lo, c_next);
+              ptx::tc_commit(bars.sdp_full);
+              ++gt;
+              if (++slot == kStages) {
+                slot = 0;
+                ph_c ^= 1;
+              }
+            }
+            // acc0 += dS C1
+            if (!wait_bar(bars.ds_full, k & 1, abort_flag, p.status, (role << 8) | kStDsFull)) {
+              alive = false; break;
+            }
+            ptx::tc_fence_after_sync();
+            issue_acc(acc0_tm, reg_tm[k & 1] + 16, 32, c_cur, t == 0);
+            ptx::tc_commit(bars.c_empty + slot_d);
+            if (t == n - 1) ptx::tc_commit(bars.acc_full);
+            if (++slot_d == kStages) slot_d = 0;
+            if (t + 1 < n) {
+              // dP of the next tile over this tile's P / dS, behind their readers in issue order
+              issue_rc(reg_tm[k & 1], r2_lo, c_next + kTileBytes);
+              ptx::tc_commit(bars.dp_full);
+              // the row tiles are read by the S / dP products only
+              if (t + 1 == n - 1) ptx::tc_commit(bars.r_empty);
+            }
+            c_cur = c_next;
           }
         }
       }
