@@ -108,7 +108,7 @@ struct BwdTcParams {
 #define BTRACE_DECL(skip) int btrace_n_ = -(skip);
 #define BTRACE(role, code)                                                              \
   {                                                                                     \
-    if (kPipe && p.trace != nullptr && blockIdx.x == 0 && btrace_n_ < 1024) {           \
+    if (p.trace != nullptr && blockIdx.x == 0 && btrace_n_ < 1024) {                 \
       if (btrace_n_ >= 0) p.trace[(role) * 1024 + btrace_n_] = (clock64() << 8) | (code); \
       ++btrace_n_;                                                                      \
     }                                                                                   \
@@ -589,6 +589,7 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
             uint32_t sr[32];
             ptx::tmem_ld32(my_r, sr);
             ptx::tmem_ld_wait();
+            if (lane == 0 && (warp == 0 || warp == 15)) BTRACE(warp == 0 ? 2 : 3, 9);
             uint32_t pk[16];
 #pragma unroll
             for (int j = 0; j < 32; j += 2) {
@@ -605,11 +606,13 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
             }
             ptx::tmem_st16(my_r, pk);
           }
+          if (lane == 0 && (warp == 0 || warp == 15)) BTRACE(warp == 0 ? 2 : 3, 10);
           // P is complete: its product with C2 can start while dS is still being computed
           ptx::tmem_st_wait();
           ptx::tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive(bars.p_full);
+          if (lane == 0 && (warp == 0 || warp == 15)) BTRACE(warp == 0 ? 2 : 3, 11);
           if (!__all_sync(0xffffffffu, wait_bar(bars.dp_full, ph_dp, abort_flag, p.status,
                                                 (5 << 8) | kStDpFull))) {
             alive = false;
@@ -617,6 +620,7 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
           }
           ph_dp ^= 1;
           ptx::tc_fence_after_sync();
+          if (lane == 0 && (warp == 0 || warp == 15)) BTRACE(warp == 0 ? 2 : 3, 12);
           {
             uint32_t dr[32];
             ptx::tmem_ld32(my_o, dr);
@@ -624,6 +628,7 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
             ptx::tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(bars.sdp_free);
+            if (lane == 0 && (warp == 0 || warp == 15)) BTRACE(warp == 0 ? 2 : 3, 13);
             uint32_t dk[16];
 #pragma unroll
             for (int j = 0; j < 32; j += 2) {
@@ -637,6 +642,7 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
           ptx::tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive(bars.ds_full);
+          if (lane == 0 && (warp == 0 || warp == 15)) BTRACE(warp == 0 ? 2 : 3, 14);
         }
       }
       if (!alive) break;
@@ -845,8 +851,10 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
             if (!wait_bar(bars.p_full, k & 1, abort_flag, p.status, (role << 8) | kStPFull)) {
               alive = false; break;
             }
+            BTRACE(0, 1);
             ptx::tc_fence_after_sync();
             issue_acc(acc1_tm, reg_tm[k & 1], 32, c_cur + kTileBytes, t == 0);
+            BTRACE(0, 2);
             if (t + 1 < n) {
               // S of the next tile, into the region dP of this tile has been taken out of
               if (!wait_bar(bars.c_full + slot, ph_c, abort_flag, p.status,
@@ -856,9 +864,11 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
                 alive = false; break;
               }
               c_next = col_base + slot * 2 * kTileBytes;
+              BTRACE(0, 3);
               ptx::tc_fence_after_sync();
               issue_rc(reg_tm[gt & 1], r1_lo, c_next);
               ptx::tc_commit(bars.sdp_full);
+              BTRACE(0, 4);
               ++gt;
               if (++slot == kStages) {
                 slot = 0;
@@ -869,15 +879,18 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
             if (!wait_bar(bars.ds_full, k & 1, abort_flag, p.status, (role << 8) | kStDsFull)) {
               alive = false; break;
             }
+            BTRACE(0, 5);
             ptx::tc_fence_after_sync();
             issue_acc(acc0_tm, reg_tm[k & 1] + 16, 32, c_cur, t == 0);
             ptx::tc_commit(bars.c_empty + slot_d);
+            BTRACE(0, 6);
             if (t == n - 1) ptx::tc_commit(bars.acc_full);
             if (++slot_d == kStages) slot_d = 0;
             if (t + 1 < n) {
               // dP of the next tile over this tile's P / dS, behind their readers in issue order
               issue_rc(reg_tm[k & 1], r2_lo, c_next + kTileBytes);
               ptx::tc_commit(bars.dp_full);
+              BTRACE(0, 7);
               // the row tiles are read by the S / dP products only
               if (t + 1 == n - 1) ptx::tc_commit(bars.r_empty);
             }
@@ -1049,6 +1062,7 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
 // ---- host side -------------------------------------------------------------------------------
 
 long long* g_bwd_trace = nullptr;
+int g_bwd_trace_pass = 0;
 
 template <int D, bool kBf16, bool kKeyRows>
 const void* bwd_kernel_for_ndim(int ndim) {
@@ -1213,7 +1227,7 @@ extern "C" B200NA_API int b200na_na_backward_direct(
     p.out0 = dense ? d_add_k : (key_rows ? dk : dq);
     p.out1 = dense ? d_add_v : (key_rows ? dv : nullptr);
     if ((rc = fna_work_counters(&p.work)) != B200NA_OK) return rc;
-    p.trace = g_bwd_trace;
+    p.trace = pass == g_bwd_trace_pass ? g_bwd_trace : nullptr;
     const void* fn = bwd_kernel_variant(D, dtype == B200NA_BF16, kernel_ndim, key_rows);
     const int smem_bytes = key_rows ? (D == 128 ? Smem<128, false>::kBytes : Smem<64, false>::kBytes)
                                     : (D == 128 ? Smem<128, true>::kBytes : Smem<64, true>::kBytes);
@@ -1230,7 +1244,8 @@ extern "C" B200NA_API int b200na_na_backward_direct(
 }
 
 #if defined(B200NA_BWD_TRACE) && B200NA_BWD_TRACE
-extern "C" B200NA_API void b200na_debug_set_bwd_trace(void* buf) {
+extern "C" B200NA_API void b200na_debug_set_bwd_trace(void* buf, int pass) {
   b200na::g_bwd_trace = reinterpret_cast<long long*>(buf);
+  b200na::g_bwd_trace_pass = pass;
 }
 #endif
