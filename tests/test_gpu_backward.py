@@ -79,6 +79,12 @@ def test_layer_trains():
     ((6, 10, 12), (3, 4, 5), (1, 2, 1), (1, 1, 1), (True, False, False), 1, 1, 64, 300),
     ((33, 30), (3, 5), (1, 2), (3, 2), (False, True), 4, 2, 32, 0),       # head dim 32: zero-padded
     ((500,), (21,), (1,), (1,), (True,), 2, 2, 96, 19),                   # head dim 96 -> 128
+    # more work items than CTAs: every CTA carries its ring positions, barrier phases and the
+    # parity of its S / dP regions from one row tile to the next
+    ((12000,), (129,), (1,), (1,), (True,), 2, 2, 128, 0),
+    ((9000,), (200,), (7,), (1,), (False,), 4, 2, 64, 40),
+    ((96, 96), (9, 9), (1, 1), (1, 1), (False, True), 2, 2, 128, 0),
+    ((10, 40, 48), (3, 5, 8), (1, 1, 4), (1, 1, 1), (True, False, False), 2, 1, 128, 130),
 ])
 def test_tensor_core_backward_against_oracle_and_cuda_core_kernels(shape, ks, st, di, ca, hq, hkv,
                                                                    D, n_extra):
