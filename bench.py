@@ -182,6 +182,31 @@ def make_inputs(cfg, b_local, h_local, seed, device, slab=None):
     return host, extra
 
 
+def host_threads():
+    """Cores this process may really run on: the affinity mask, capped by the cgroup CPU quota
+    (threads beyond the quota only add contention)."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    for path in ("/sys/fs/cgroup/cpu.max", "/sys/fs/cgroup/cpu/cpu.cfs_quota_us"):
+        try:
+            with open(path) as f:
+                parts = f.read().split()
+            if path.endswith("cpu.max"):
+                if parts[0] != "max":
+                    n = min(n, max(1, math.ceil(int(parts[0]) / int(parts[1]))))
+            else:
+                quota = int(parts[0])
+                if quota > 0:
+                    with open("/sys/fs/cgroup/cpu/cpu.cfs_period_us") as f:
+                        n = min(n, max(1, math.ceil(quota / int(f.read().split()[0]))))
+            break
+        except (OSError, ValueError, IndexError):
+            continue
+    return max(1, n)
+
+
 def cpu_baseline(cfg, budget_s=12.0, acc64=False):
     """Times the oracle (fp32-accumulating port of the reference's naive kernel, OpenMP on all host
     cores) on a bounded sample of the workload: all query rows of `heads` (batch, head) slices, or
@@ -190,7 +215,7 @@ def cpu_baseline(cfg, budget_s=12.0, acc64=False):
     _, _, _, _, shape, D, ks, st, di, ca, n_extra, mul = cfg
     rng = np.random.default_rng(0)
     N = math.prod(shape)
-    cores = os.cpu_count() or 1
+    cores = oracle.set_threads(host_threads())
     pairs_per_row = (attended_pairs(shape, ks, st, di, ca) + n_extra * N) / N
 
     def run(heads, rows):

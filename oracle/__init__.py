@@ -54,7 +54,13 @@ def _load():
         _lib.na_oracle_dense.restype = ctypes.c_int
         _lib.na_oracle_merge.restype = ctypes.c_int
         _lib.na_oracle_backward.restype = ctypes.c_int
+        _lib.na_oracle_set_threads.restype = ctypes.c_int
     return _lib
+
+
+def set_threads(n: int) -> int:
+    """Bound the OpenMP threads of the calls that follow; returns the number in effect."""
+    return int(_load().na_oracle_set_threads(ctypes.c_int(int(n))))
 
 
 def _ints(x: Sequence[int]):

@@ -28,6 +28,21 @@
 #include <stdint.h>
 #include <stdlib.h>
 #include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+/* Threads the following calls may use (the benchmark's CPU-baseline leg bounds them by the
+ * cores this process may really run on); returns the value in effect. */
+int na_oracle_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+  return omp_get_max_threads();
+#else
+  (void)n;
+  return 1;
+#endif
+}
 
 #define NA_MAX_DIM 3
 
