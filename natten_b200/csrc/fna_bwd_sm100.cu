@@ -361,7 +361,9 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
   bars.v_full = bars.c_empty + kRing1;
   bars.v_empty = bars.v_full + kStages;
 
-  const int warp = threadIdx.x >> 5;
+  // read through a shuffle so that the compiler knows the value is warp-uniform: role branches
+  // are then uniform, and address arithmetic inside them can use the uniform datapath
+  const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);
   const int lane = threadIdx.x & 31;
 
   if ((ptx::smem_u32(smem) & 1023u) != 0) {
@@ -418,7 +420,7 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
   ptx::tc_fence_before_sync();
   __syncthreads();
   ptx::tc_fence_after_sync();
-  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_base = __shfl_sync(0xffffffffu, *tmem_slot, 0);
   constexpr uint32_t kSCol = 0, kDpCol = 128, kAcc0Col = 256, kAcc1Col = 384;
   // Pass dQ keeps one accumulator, so columns [384, 512) are free: they hold two buffers of packed
   // dS (64 columns each). With dS written there instead of over dP, the logit / dP columns are
@@ -689,7 +691,9 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
     // its scheduler with four busy softmax warps, and one thread alone cannot feed the tensor
     // pipe at its rate then. The two streams touch disjoint TMEM columns and are ordered against
     // each other through the softmax threads' barriers only.
-    if (lane == 0) {
+    {
+      // the whole warp runs this role; lane 0 performs the MMAs, commits and arrives
+      const uint32_t issue = lane == 0;
       constexpr uint32_t idesc_s = ptx::make_idesc(kType == kTyBf16 ? 1 : 0, 0, 0, kTile, kTile);
       constexpr uint32_t idesc_acc = ptx::make_idesc(kType == kTyBf16 ? 1 : 0, 0, 1, kTile, D);
       constexpr uint32_t desc_hi = ptx::smem_desc_hi_sw128();
@@ -702,6 +706,9 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
       const uint32_t acc0_tm = tmem_base + kAcc0Col, acc1_tm = tmem_base + kAcc1Col;
       const bool second = kPipe && warp == kMma2Warp;
       const int role = second ? 9 : 6;  // status word role
+      auto wait_all = [&](uint64_t* bar, uint32_t parity, volatile int* af, int* st, int code) {
+        return __all_sync(0xffffffffu, wait_bar(bar, parity, af, st, code)) != 0;
+      };
       BTRACE_DECL(second ? 2 * 40 : 3 * 40)
       // S = R1 C1^T and dP = R2 C2^T: both operands K-major, contraction over the head dim
       auto issue_rc = [&](uint32_t d_tm, uint32_t r_lo, uint32_t ctile) {
@@ -709,7 +716,7 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
 #pragma unroll
         for (int kb = 0; kb < D / 16; ++kb) {
           const uint32_t koff = ((kb >> 2) * kBlockBytes + (kb & 3) * 32) >> 4;
-          ptx::mma_ss_lohi(d_tm, r_lo + koff, desc_hi, bd + koff, desc_hi, idesc_s,
+          ptx::mma_ss_lohi_if(issue, d_tm, r_lo + koff, desc_hi, bd + koff, desc_hi, idesc_s,
                            kb > 0 ? 1u : 0u);
         }
       };
@@ -721,7 +728,7 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
         const uint32_t bd = ptx::smem_desc_lo(ctile, kBlockBytes);
 #pragma unroll
         for (int ks = 0; ks < kTile / 16; ++ks)
-          ptx::mma_ts_lohi(acc_tm, a_tm + (ks >> 1) * a_pair_stride + (ks & 1) * 8,
+          ptx::mma_ts_lohi_if(issue, acc_tm, a_tm + (ks >> 1) * a_pair_stride + (ks & 1) * 8,
                            bd + ks * (2048 >> 4), desc_hi, idesc_acc, (first && ks == 0) ? 0u : 1u);
       };
       uint32_t ph_r = 0, ph_ae = 1;
@@ -732,44 +739,45 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
       bool alive = true;
       for (uint32_t seq = 0; alive; ++seq) {
         const uint32_t dslot = seq % kDescSlots;
-        if (!wait_bar(bars.desc_full + dslot, (seq / kDescSlots) & 1, abort_flag, p.status,
+        if (!wait_all(bars.desc_full + dslot, (seq / kDescSlots) & 1, abort_flag, p.status,
                       (role << 8) | kStDescFull)) break;
-        const int n = reinterpret_cast<const Item*>(desc_sm + dslot * kDescBytes)->n_tiles;
-        ptx::mbar_arrive(bars.desc_empty + dslot);
+        const int n = __shfl_sync(
+            0xffffffffu, reinterpret_cast<const Item*>(desc_sm + dslot * kDescBytes)->n_tiles, 0);
+        ptx::mbar_arrive_if(issue, bars.desc_empty + dslot);
         if (n < 0) break;
         if (kPipe && !second) {
           // ---- pass dQ, first issuer: dP and S of each column tile as soon as the softmax
           // threads have read the previous tile's. dP goes first: its C2 tile arrives early (a
           // C2 stage is released right after the product).
-          if (!wait_bar(bars.r_full, ph_r, abort_flag, p.status, (role << 8) | kStRFull)) break;
+          if (!wait_all(bars.r_full, ph_r, abort_flag, p.status, (role << 8) | kStRFull)) break;
           ph_r ^= 1;
           for (int t = 0; t < n; ++t) {
-            if (!wait_bar(bars.sdp_free, (gt & 1) ^ 1, abort_flag, p.status,
+            if (!wait_all(bars.sdp_free, (gt & 1) ^ 1, abort_flag, p.status,
                           (role << 8) | kStSdpFree) ||
-                !wait_bar(bars.v_full + slot2, ph_v, abort_flag, p.status,
+                !wait_all(bars.v_full + slot2, ph_v, abort_flag, p.status,
                           (role << 8) | kStVFull)) {
               alive = false; break;
             }
             ++gt;
-            BTRACE(0, 1);
+            if (lane == 0) BTRACE(0, 1);
             ptx::tc_fence_after_sync();
             issue_rc(dp_tm, r2_lo, col2_base + slot2 * kTileBytes);
-            ptx::tc_commit(bars.v_empty + slot2);
+            ptx::tc_commit_if(issue, bars.v_empty + slot2);
             if (++slot2 == kStages) {
               slot2 = 0;
               ph_v ^= 1;
             }
-            if (!wait_bar(bars.c_full + slot, ph_c, abort_flag, p.status,
+            if (!wait_all(bars.c_full + slot, ph_c, abort_flag, p.status,
                           (role << 8) | kStCFull)) {
               alive = false; break;
             }
-            BTRACE(0, 2);
+            if (lane == 0) BTRACE(0, 2);
             ptx::tc_fence_after_sync();
             issue_rc(s_tm, r1_lo, col_base + slot * kTileBytes);
-            ptx::tc_commit(bars.sdp_full);
+            ptx::tc_commit_if(issue, bars.sdp_full);
             // the row tiles are read by these products only
-            if (t == n - 1) ptx::tc_commit(bars.r_empty);
-            BTRACE(0, 3);
+            if (t == n - 1) ptx::tc_commit_if(issue, bars.r_empty);
+            if (lane == 0) BTRACE(0, 3);
             if (++slot == kRing1) {
               slot = 0;
               ph_c ^= 1;
@@ -781,29 +789,29 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
             const uint32_t buf = gt & 1;
             // the C1 wait cannot block (S of this tile was computed from the same stage); it
             // orders this thread's reads after the tile's arrival
-            if (!wait_bar(bars.ds_full + buf, (gt >> 1) & 1, abort_flag, p.status,
+            if (!wait_all(bars.ds_full + buf, (gt >> 1) & 1, abort_flag, p.status,
                           (role << 8) | kStDsFull) ||
-                !wait_bar(bars.c_full + slot, ph_c, abort_flag, p.status,
+                !wait_all(bars.c_full + slot, ph_c, abort_flag, p.status,
                           (role << 8) | kStCFull)) {
               alive = false; break;
             }
             ++gt;
             if (t == 0) {
               // the previous item's epilogue must have drained the accumulator
-              if (!wait_bar(bars.acc_empty, ph_ae, abort_flag, p.status,
+              if (!wait_all(bars.acc_empty, ph_ae, abort_flag, p.status,
                             (role << 8) | kStAccEmpty)) {
                 alive = false; break;
               }
               ph_ae ^= 1;
             }
-            BTRACE(4, 4);
+            if (lane == 0) BTRACE(4, 4);
             ptx::tc_fence_after_sync();
             issue_acc(acc0_tm, tmem_base + kDsCol + buf * kDsBufCols, 16,
                       col_base + slot * kTileBytes, t == 0);
-            ptx::tc_commit(bars.c_empty + slot);
-            ptx::tc_commit(bars.ds_free + buf);
-            if (t == n - 1) ptx::tc_commit(bars.acc_full);
-            BTRACE(4, 5);
+            ptx::tc_commit_if(issue, bars.c_empty + slot);
+            ptx::tc_commit_if(issue, bars.ds_free + buf);
+            if (t == n - 1) ptx::tc_commit_if(issue, bars.acc_full);
+            if (lane == 0) BTRACE(4, 5);
             if (++slot == kRing1) {
               slot = 0;
               ph_c ^= 1;
@@ -814,22 +822,22 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
           // the softmax threads have taken dP of tile t out of the region it goes to; dK += dS C1
           // when dS is stored; then dP of tile t + 1 (it overwrites tile t's P / dS operands,
           // behind their readers in issue order).
-          if (!wait_bar(bars.r_full, ph_r, abort_flag, p.status, (role << 8) | kStRFull)) break;
+          if (!wait_all(bars.r_full, ph_r, abort_flag, p.status, (role << 8) | kStRFull)) break;
           ph_r ^= 1;
           const uint32_t reg_tm[2] = {s_tm, dp_tm};
           // first tile of the item: S, then dP (the other region's last readers, the previous
           // item's accumulations, were issued before)
-          if (!wait_bar(bars.c_full + slot, ph_c, abort_flag, p.status, (role << 8) | kStCFull) ||
-              !wait_bar(bars.sdp_free, (gt & 1) ^ 1, abort_flag, p.status,
+          if (!wait_all(bars.c_full + slot, ph_c, abort_flag, p.status, (role << 8) | kStCFull) ||
+              !wait_all(bars.sdp_free, (gt & 1) ^ 1, abort_flag, p.status,
                         (role << 8) | kStSdpFree))
             break;
           uint32_t c_cur = col_base + slot * 2 * kTileBytes, c_next = 0;
           ptx::tc_fence_after_sync();
           issue_rc(reg_tm[gt & 1], r1_lo, c_cur);
-          ptx::tc_commit(bars.sdp_full);
+          ptx::tc_commit_if(issue, bars.sdp_full);
           issue_rc(reg_tm[(gt & 1) ^ 1], r2_lo, c_cur + kTileBytes);
-          ptx::tc_commit(bars.dp_full);
-          if (n == 1) ptx::tc_commit(bars.r_empty);
+          ptx::tc_commit_if(issue, bars.dp_full);
+          if (n == 1) ptx::tc_commit_if(issue, bars.r_empty);
           ++gt;
           if (++slot == kStages) {
             slot = 0;
@@ -839,7 +847,7 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
             const uint32_t k = gt - 1;  // global index of tile t (its S was the last one issued)
             if (t == 0) {
               // the previous item's epilogue must have drained the accumulators
-              if (!wait_bar(bars.acc_empty, ph_ae, abort_flag, p.status,
+              if (!wait_all(bars.acc_empty, ph_ae, abort_flag, p.status,
                             (role << 8) | kStAccEmpty)) {
                 alive = false; break;
               }
@@ -848,27 +856,27 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
             // Of a thread's columns [32 q, 32 q + 32) of the tile's region, [32 q, 32 q + 16)
             // hold its packed P and [32 q + 16, 32 q + 32) its dS.
             // acc1 += P C2 as soon as P is stored, while the threads still work on dS
-            if (!wait_bar(bars.p_full, k & 1, abort_flag, p.status, (role << 8) | kStPFull)) {
+            if (!wait_all(bars.p_full, k & 1, abort_flag, p.status, (role << 8) | kStPFull)) {
               alive = false; break;
             }
-            BTRACE(0, 1);
+            if (lane == 0) BTRACE(0, 1);
             ptx::tc_fence_after_sync();
             issue_acc(acc1_tm, reg_tm[k & 1], 32, c_cur + kTileBytes, t == 0);
-            BTRACE(0, 2);
+            if (lane == 0) BTRACE(0, 2);
             if (t + 1 < n) {
               // S of the next tile, into the region dP of this tile has been taken out of
-              if (!wait_bar(bars.c_full + slot, ph_c, abort_flag, p.status,
+              if (!wait_all(bars.c_full + slot, ph_c, abort_flag, p.status,
                             (role << 8) | kStCFull) ||
-                  !wait_bar(bars.sdp_free, (gt & 1) ^ 1, abort_flag, p.status,
+                  !wait_all(bars.sdp_free, (gt & 1) ^ 1, abort_flag, p.status,
                             (role << 8) | kStSdpFree)) {
                 alive = false; break;
               }
               c_next = col_base + slot * 2 * kTileBytes;
-              BTRACE(0, 3);
+              if (lane == 0) BTRACE(0, 3);
               ptx::tc_fence_after_sync();
               issue_rc(reg_tm[gt & 1], r1_lo, c_next);
-              ptx::tc_commit(bars.sdp_full);
-              BTRACE(0, 4);
+              ptx::tc_commit_if(issue, bars.sdp_full);
+              if (lane == 0) BTRACE(0, 4);
               ++gt;
               if (++slot == kStages) {
                 slot = 0;
@@ -876,23 +884,23 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
               }
             }
             // acc0 += dS C1
-            if (!wait_bar(bars.ds_full, k & 1, abort_flag, p.status, (role << 8) | kStDsFull)) {
+            if (!wait_all(bars.ds_full, k & 1, abort_flag, p.status, (role << 8) | kStDsFull)) {
               alive = false; break;
             }
-            BTRACE(0, 5);
+            if (lane == 0) BTRACE(0, 5);
             ptx::tc_fence_after_sync();
             issue_acc(acc0_tm, reg_tm[k & 1] + 16, 32, c_cur, t == 0);
-            ptx::tc_commit(bars.c_empty + slot_d);
-            BTRACE(0, 6);
-            if (t == n - 1) ptx::tc_commit(bars.acc_full);
+            ptx::tc_commit_if(issue, bars.c_empty + slot_d);
+            if (lane == 0) BTRACE(0, 6);
+            if (t == n - 1) ptx::tc_commit_if(issue, bars.acc_full);
             if (++slot_d == kStages) slot_d = 0;
             if (t + 1 < n) {
               // dP of the next tile over this tile's P / dS, behind their readers in issue order
               issue_rc(reg_tm[k & 1], r2_lo, c_next + kTileBytes);
-              ptx::tc_commit(bars.dp_full);
-              BTRACE(0, 7);
+              ptx::tc_commit_if(issue, bars.dp_full);
+              if (lane == 0) BTRACE(0, 7);
               // the row tiles are read by the S / dP products only
-              if (t + 1 == n - 1) ptx::tc_commit(bars.r_empty);
+              if (t + 1 == n - 1) ptx::tc_commit_if(issue, bars.r_empty);
             }
             c_cur = c_next;
           }
