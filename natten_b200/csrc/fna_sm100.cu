@@ -381,7 +381,9 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   bars.kv_full = bar_base + 10 + 2 * kDescSlots + kTileRecs;
   bars.kv_empty = bar_base + 10 + 2 * kDescSlots + kTileRecs + kStages;
 
-  const int warp = threadIdx.x >> 5;
+  // read through a shuffle so that the compiler knows the value is warp-uniform: role branches
+  // are then uniform, and address arithmetic inside them can use the uniform datapath
+  const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);
   const int lane = threadIdx.x & 31;
 
   // ---- setup -------------------------------------------------------------------------------
@@ -431,7 +433,7 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   ptx::tc_fence_before_sync();
   __syncthreads();
   ptx::tc_fence_after_sync();
-  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_base = __shfl_sync(0xffffffffu, *tmem_slot, 0);
   // TMEM columns: S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [384,384+D); P aliases S.
   auto s_col = [](int half) -> uint32_t { return (uint32_t)half * 128u; };
   auto o_col = [](int half) -> uint32_t { return 256u + (uint32_t)half * 128u; };
@@ -713,7 +715,13 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     if (row == 0 && part == 0) { PROF_FLUSH(half) }
   } else if (warp == kMmaWarp) {
     // =============================== MMA issue ==============================================
-    if (lane == 0) {
+    {
+      // the whole warp runs this role, converged, so that descriptor arithmetic stays in uniform
+      // registers; lane 0 performs the MMAs, commits and arrives
+      const uint32_t issue = lane == 0;
+      auto wait_all = [&](uint64_t* bar, uint32_t parity, volatile int* af, int* st, int code) {
+        return __all_sync(0xffffffffu, wait_bar(bar, parity, af, st, code)) != 0;
+      };
       // element format codes of the instruction descriptor: kind::f16 0 = fp16, 1 = bf16;
       // kind::f8f6f4 0 = e4m3, 1 = e5m2 (P is always e4m3)
       constexpr int kFmt = kF8 ? (kType == kTyE5m2 ? 1 : 0) : (kType == kTyBf16 ? 1 : 0);
@@ -743,10 +751,10 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         for (int kb = 0; kb < D * kES / 32; ++kb) {
           const uint32_t koff = ((kb >> 2) * kBlockBytes + (kb & 3) * 32) >> 4;
           if (kF8)
-            ptx::mma_ss_lohi_f8(d, a_lo + koff, desc_hi, b_lo + koff, desc_hi, idesc_qk,
+            ptx::mma_ss_lohi_f8_if(issue, d, a_lo + koff, desc_hi, b_lo + koff, desc_hi, idesc_qk,
                                 kb > 0 ? 1u : 0u);
           else
-            ptx::mma_ss_lohi(d, a_lo + koff, desc_hi, b_lo + koff, desc_hi, idesc_qk,
+            ptx::mma_ss_lohi_if(issue, d, a_lo + koff, desc_hi, b_lo + koff, desc_hi, idesc_qk,
                              kb > 0 ? 1u : 0u);
         }
       };
@@ -761,12 +769,12 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           // columns at [0,16) resp. [64,80); V rows are 128 bytes, 32 rows per step
 #pragma unroll
           for (int ks = 0; ks < kKVTile / 32; ++ks)
-            ptx::mma_ts_lohi_f8(d, a + (ks >> 1) * 64 + (ks & 1) * 8, b_lo + ks * (4096 >> 4),
+            ptx::mma_ts_lohi_f8_if(issue, d, a + (ks >> 1) * 64 + (ks & 1) * 8, b_lo + ks * (4096 >> 4),
                                 desc_hi, idesc_pv, (first && ks == 0) ? 0u : 1u);
         } else {
 #pragma unroll
           for (int ks = 0; ks < kKVTile / 16; ++ks)
-            ptx::mma_ts_lohi(d, a + (ks >> 2) * 64 + (ks & 3) * 8, b_lo + ks * (2048 >> 4),
+            ptx::mma_ts_lohi_if(issue, d, a + (ks >> 2) * 64 + (ks & 3) * 8, b_lo + ks * (2048 >> 4),
                              desc_hi, idesc_pv, (first && ks == 0) ? 0u : 1u);
         }
       };
@@ -774,18 +782,18 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       PROF2_DECL
       for (uint32_t seq = 0; alive; ++seq) {
         const Item* itp = fetch_item(desc_sm, bars, seq, abort_flag, p.status, 2);
-        if (itp == nullptr) break;
-        const int n = itp->n_tiles;  // all this role needs
-        release_item(bars, seq);
+        if (!__all_sync(0xffffffffu, itp != nullptr)) break;
+        const int n = __shfl_sync(0xffffffffu, itp->n_tiles, 0);  // all this role needs
+        ptx::mbar_arrive_if(issue, bars.desc_empty + seq % kDescSlots);
         if (n < 0) break;
         PROF2_MARK(6)
-        if (!wait_bar(bars.q_full, ph_q, abort_flag, p.status, (2 << 8) | kStSQFull)) break;
+        if (!wait_all(bars.q_full, ph_q, abort_flag, p.status, (2 << 8) | kStSQFull)) break;
         ph_q ^= 1;
         PROF2_MARK(0)
         TRACE2(2, 10)
         // tile 0: S_h = Q_h K0^T for both halves
         const uint32_t slot_k = ring.slot;
-        if (!wait_bar(bars.kv_full + slot_k, ring.phase, abort_flag, p.status,
+        if (!wait_all(bars.kv_full + slot_k, ring.phase, abort_flag, p.status,
                       (2 << 8) | kStKVFull)) break;
         ring.advance();
         PROF2_MARK(1)
@@ -793,15 +801,15 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           issue_qk(h, kv_base + slot_k * kTileBytes);
-          ptx::tc_commit(bars.s_full + h);
+          ptx::tc_commit_if(issue, bars.s_full + h);
         }
-        ptx::tc_commit(bars.kv_empty + slot_k);
-        if (n == 1) ptx::tc_commit(bars.q_empty);
+        ptx::tc_commit_if(issue, bars.kv_empty + slot_k);
+        if (n == 1) ptx::tc_commit_if(issue, bars.q_empty);
         for (int iter = 0; iter < n && alive; ++iter) {
           // Both operands of this iteration (V of this tile, K of the next) are waited for up
           // front, so that nothing but the softmax hand-off separates the MMA bursts below.
           const uint32_t slot_v = ring.slot;
-          if (!wait_bar(bars.kv_full + slot_v, ring.phase, abort_flag, p.status,
+          if (!wait_all(bars.kv_full + slot_v, ring.phase, abort_flag, p.status,
                         (2 << 8) | kStKVFull)) { alive = false; break; }
           ring.advance();
           TRACE2(2, 11)
@@ -809,7 +817,7 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           uint32_t slot_kn = 0;
           if (more) {
             slot_kn = ring.slot;
-            if (!wait_bar(bars.kv_full + slot_kn, ring.phase, abort_flag, p.status,
+            if (!wait_all(bars.kv_full + slot_kn, ring.phase, abort_flag, p.status,
                           (2 << 8) | kStKVFull)) { alive = false; break; }
             ring.advance();
             TRACE2(2, 16)
@@ -818,14 +826,14 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           const uint32_t k_addr = kv_base + slot_kn * kTileBytes;
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
-            if (!wait_bar(bars.p_full + h, ph_p[h], abort_flag, p.status, (2 << 8) | kStPFull)) {
+            if (!wait_all(bars.p_full + h, ph_p[h], abort_flag, p.status, (2 << 8) | kStPFull)) {
               alive = false; break;
             }
             ph_p[h] ^= 1;
             TRACE2(2, 12 + h)
             if (iter == 0) {
               // the previous item's epilogue must have drained O_h before it is overwritten
-              if (!wait_bar(bars.o_empty + h, ph_oe[h], abort_flag, p.status,
+              if (!wait_all(bars.o_empty + h, ph_oe[h], abort_flag, p.status,
                             (2 << 8) | kStOEmpty)) { alive = false; break; }
               ph_oe[h] ^= 1;
             }
@@ -834,17 +842,17 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             TRACE2(2, 14 + h)
             if (more) {
               issue_qk(h, k_addr);
-              ptx::tc_commit(bars.s_full + h);
+              ptx::tc_commit_if(issue, bars.s_full + h);
               TRACE2(2, 17 + h)
             } else {
-              ptx::tc_commit(bars.o_full + h);
+              ptx::tc_commit_if(issue, bars.o_full + h);
             }
           }
           if (!alive) break;
-          ptx::tc_commit(bars.kv_empty + slot_v);
+          ptx::tc_commit_if(issue, bars.kv_empty + slot_v);
           if (more) {
-            ptx::tc_commit(bars.kv_empty + slot_kn);
-            if (iter + 2 == n) ptx::tc_commit(bars.q_empty);  // last Q.K^T has been issued
+            ptx::tc_commit_if(issue, bars.kv_empty + slot_kn);
+            if (iter + 2 == n) ptx::tc_commit_if(issue, bars.q_empty);  // last Q.K^T has been issued
           }
         }
       }
