@@ -84,7 +84,7 @@ def algorithmic_flops(cfg, units=None) -> float:
 # DRAM traffic of the attention kernel per (batch x head) unit, bytes, from the ncu capture of a
 # reduced case summarised in profiles/fna_fwd_kernel_c2.md (dram__bytes_read.sum +
 # dram__bytes_write.sum of one launch / units in that launch); scaled by the units of a launch.
-NCU_TRAFFIC_PER_UNIT = {"c2": (203.11e6 + 50.35e6) / 8,
+NCU_TRAFFIC_PER_UNIT = {"c2": (202.86e6 + 49.00e6) / 8,
                         # profiles/fna_fwd_kernel_c4.md: 4 heads captured
                         "c4": (204.06e6 + 50.56e6) / 4}
 
