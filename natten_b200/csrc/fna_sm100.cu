@@ -3,12 +3,14 @@
 //
 // Functional contract = the reference's Blackwell FNA forward
 // (csrc/src/blackwell_fna_forward.cu:57-267 host contract; mask geometry
-// csrc/include/natten/cuda/fna_blackwell/collective/fna_fusion.hpp:88-124, 284-489): operands
-// are token-permuted [B', S, H, D] tensors, a CTA owns a 256-row query tile and walks the
-// bounding box of key/value tiles (128 rows each) its queries' windows touch.
+// csrc/include/natten/cuda/fna_blackwell/collective/fna_fusion.hpp:88-124, 284-489): a CTA owns
+// a 256-row query tile and walks the bounding box of key/value tiles (128 rows each) its
+// queries' windows touch. Operands are either the caller's [B, *X, H, D] tensors, gathered tile
+// by tile through rank-5 tensor maps (direct mode), or token-permuted [B', S, H, D] tensors.
 // The design is this library's own:
-//   * warp roles: 2 softmax warpgroups (one 128-row half each, one thread per row),
-//     1 MMA-issue warp, 1 TMA-load warp; persistent CTAs stride over (q-tile, head, batch').
+//   * warp roles: 16 softmax warps (a 128-row half per 8 warps, two threads per row),
+//     1 MMA-issue warp (run converged, lane 0 performs the MMAs), 1 TMA-load warp that also
+//     decodes work items; persistent CTAs draw (q-tile, head, batch') items from a counter.
 //   * TMEM: S0 S1 O0 O1 (128 fp32 columns each at D = 128); P (16-bit) overwrites S in place and
 //     feeds P.V straight from TMEM; the O rescale is lazy (only when a row maximum grows by more
 //     than 2^8) and is done by the softmax threads between the two MMAs of their half.
@@ -734,8 +736,9 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       bool alive = true;
 
       // Descriptors are kept as (low, high) words: the high word is one constant, the low word
-      // of a tile is computed once and each K step adds a compile-time offset to it. The issuing
-      // thread runs alone in its warp, so every instruction here is on the critical path.
+      // of a tile is computed once and each K step adds a compile-time offset to it. Every
+      // instruction of this role is on the critical path: the stream is warp-uniform so that
+      // this arithmetic is done in uniform registers, where the MMA instruction takes it from.
       constexpr uint32_t desc_hi = ptx::smem_desc_hi_sw128();
       const uint32_t q_lo[2] = {ptx::smem_desc_lo(q_base, 16),
                                 ptx::smem_desc_lo(q_base + kTileBytes, 16)};
