@@ -754,11 +754,11 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         for (int kb = 0; kb < D * kES / 32; ++kb) {
           const uint32_t koff = ((kb >> 2) * kBlockBytes + (kb & 3) * 32) >> 4;
           if (kF8)
-            ptx::mma_ss_lohi_f8_if(issue, d, a_lo + koff, desc_hi, b_lo + koff, desc_hi, idesc_qk,
-                                kb > 0 ? 1u : 0u);
+            ptx::mma_ss_lohi_f8_if(issue, d, a_lo + koff, desc_hi, b_lo + koff, desc_hi,
+                                   idesc_qk, kb > 0 ? 1u : 0u);
           else
             ptx::mma_ss_lohi_if(issue, d, a_lo + koff, desc_hi, b_lo + koff, desc_hi, idesc_qk,
-                             kb > 0 ? 1u : 0u);
+                                kb > 0 ? 1u : 0u);
         }
       };
       // P for keys [0,64) sits in S columns [0,32), for keys [64,128) in columns [64,96): each
@@ -772,13 +772,15 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           // columns at [0,16) resp. [64,80); V rows are 128 bytes, 32 rows per step
 #pragma unroll
           for (int ks = 0; ks < kKVTile / 32; ++ks)
-            ptx::mma_ts_lohi_f8_if(issue, d, a + (ks >> 1) * 64 + (ks & 1) * 8, b_lo + ks * (4096 >> 4),
-                                desc_hi, idesc_pv, (first && ks == 0) ? 0u : 1u);
+            ptx::mma_ts_lohi_f8_if(issue, d, a + (ks >> 1) * 64 + (ks & 1) * 8,
+                                   b_lo + ks * (4096 >> 4), desc_hi, idesc_pv,
+                                   (first && ks == 0) ? 0u : 1u);
         } else {
 #pragma unroll
           for (int ks = 0; ks < kKVTile / 16; ++ks)
-            ptx::mma_ts_lohi_if(issue, d, a + (ks >> 2) * 64 + (ks & 3) * 8, b_lo + ks * (2048 >> 4),
-                             desc_hi, idesc_pv, (first && ks == 0) ? 0u : 1u);
+            ptx::mma_ts_lohi_if(issue, d, a + (ks >> 2) * 64 + (ks & 3) * 8,
+                                b_lo + ks * (2048 >> 4), desc_hi, idesc_pv,
+                                (first && ks == 0) ? 0u : 1u);
         }
       };
 
