@@ -14,15 +14,6 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
-__device__ __forceinline__ bool elect_one() {
-  uint32_t pred = 0;
-  asm volatile(
-      "{\n\t.reg .pred P;\n\t"
-      "elect.sync _|P, 0xffffffff;\n\t"
-      "selp.u32 %0, 1, 0, P;\n\t}\n"
-      : "=r"(pred));
-  return pred != 0;
-}
 
 // ---- mbarrier ---------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
@@ -92,73 +83,22 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
                : "memory");
 }
 
-// ---- tcgen05: fences / commit -----------------------------------------------------------
+// ---- tcgen05: fences -------------------------------------------------------------------
 __device__ __forceinline__ void tc_fence_before_sync() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 }
 __device__ __forceinline__ void tc_fence_after_sync() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
-// Arrives once on `bar` when every tcgen05.mma issued so far by this thread has completed.
-__device__ __forceinline__ void tc_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-                   smem_u32(bar))
-               : "memory");
-}
-// Makes generic-proxy shared-memory writes visible to the async proxy (TMA / UMMA reads).
-__device__ __forceinline__ void fence_proxy_async_smem() {
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
 
-// ---- tcgen05: MMA -----------------------------------------------------------------------
-// D[tmem] (+)= A[smem desc] * B[smem desc], kind::f16 (fp16/bf16 operands, fp32 accumulate).
-__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                       uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// D[tmem] (+)= A[tmem] * B[smem desc].
-__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
-                                       uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n"
-      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-
-// Same MMAs with the 64-bit descriptors passed as (lo, hi) halves: the issuing thread keeps the
-// constant high word in a register and only adds a small offset to the low word per K step.
-__device__ __forceinline__ void mma_ss_lohi(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi,
-                                            uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
-                                            uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
-      "mov.b64 da, {%1, %2};\n\t"
-      "mov.b64 db, {%3, %4};\n\t"
-      "setp.ne.b32 p, %6, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}\n"
-      ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void mma_ts_lohi(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo,
-                                            uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
-      "mov.b64 db, {%2, %3};\n\t"
-      "setp.ne.b32 p, %5, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}\n"
-      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// The same MMAs, commit and arrive for a whole converged warp: every lane executes the
-// instruction stream (so that operand arithmetic stays warp-uniform and can be done in uniform
-// registers), the lanes with `issue` != 0 perform the operation.
+// ---- tcgen05: MMA, commit ---------------------------------------------------------------
+// D[tmem] (+)= A * B with fp32 accumulation; A from shared memory (ss) or from TMEM (ts), B from
+// shared memory; kind::f16 takes fp16/bf16 operands (K = 16 per instruction), kind::f8f6f4 8-bit
+// ones (K = 32). The 64-bit shared-memory descriptors are passed as (low, high) words: the high
+// word is a constant and a K step only adds a small offset to the low word.
+// All forms are written for a whole converged warp: every lane executes the instruction stream
+// (so that operand arithmetic stays warp-uniform and can be done in uniform registers), the
+// lanes with `issue` != 0 perform the operation.
 __device__ __forceinline__ void mma_ss_lohi_if(uint32_t issue, uint32_t d_tmem, uint32_t a_lo,
                                                uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
                                                uint32_t idesc, uint32_t accumulate) {
@@ -211,6 +151,7 @@ __device__ __forceinline__ void mma_ts_lohi_f8_if(uint32_t issue, uint32_t d_tme
       ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate), "r"(issue)
       : "memory");
 }
+// Arrives once on `bar` when every tcgen05.mma issued so far by the performing thread is complete.
 __device__ __forceinline__ void tc_commit_if(uint32_t issue, uint64_t* bar) {
   asm volatile(
       "{\n\t.reg .pred q;\n\t"
@@ -227,53 +168,20 @@ __device__ __forceinline__ void mbar_arrive_if(uint32_t issue, uint64_t* bar) {
       ::"r"(smem_u32(bar)), "r"(issue)
       : "memory");
 }
-// kind::f8f6f4 forms (8-bit operands, K = 32 per instruction, fp32 accumulate).
-__device__ __forceinline__ void mma_ss_lohi_f8(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi,
-                                               uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
-                                               uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
-      "mov.b64 da, {%1, %2};\n\t"
-      "mov.b64 db, {%3, %4};\n\t"
-      "setp.ne.b32 p, %6, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %5, p;\n\t}\n"
-      ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void mma_ts_lohi_f8(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo,
-                                               uint32_t b_hi, uint32_t idesc,
-                                               uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
-      "mov.b64 db, {%2, %3};\n\t"
-      "setp.ne.b32 p, %5, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], db, %4, p;\n\t}\n"
-      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// Low / high words of the 128-byte-swizzle descriptor below (low: address and leading offset;
+// Shared-memory matrix descriptor (64-bit) of a 128-byte-swizzled operand tile whose rows are
+// 128 bytes wide and packed back to back (what a TMA load with SWIZZLE_128B and a 64-element
+// 16-bit inner box produces): 8-row groups are 1024 bytes apart (stride byte offset), and the
+// leading byte offset is the distance between 64-element column blocks of an MN-major operand
+// (ignored for K-major ones). Kept as its low / high words (low: address and leading offset;
 // high: stride offset 1024 B, version, layout). Addresses are < 256 KB, so adding a byte offset
 // >> 4 to the low word never carries into the leading-offset field.
 __device__ __forceinline__ uint32_t smem_desc_lo(uint32_t smem_addr, uint32_t lbo_bytes) {
   return ((smem_addr & 0x3FFFFu) >> 4) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
 }
 __host__ __device__ constexpr uint32_t smem_desc_hi_sw128() {
-  return ((1024u >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
-}
-
-// Shared-memory matrix descriptor (64-bit) for a 128-byte-swizzled operand tile whose rows are
-// 128 bytes wide and packed back to back (what a TMA load with SWIZZLE_128B and a 64-element
-// 16-bit inner box produces): 8-row groups are 1024 bytes apart (stride byte offset), and
-// `lbo_bytes` is the distance between 64-element column blocks (used by MN-major operands only).
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr, uint32_t lbo_bytes,
-                                                    uint32_t sbo_bytes = 1024u) {
-  uint64_t d = 0;
-  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);          // start address, bits [0,14)
-  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;     // leading byte offset, bits [16,30)
-  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;     // stride byte offset, bits [32,46)
-  d |= (uint64_t)1 << 46;                                // descriptor version (Blackwell)
-  d |= (uint64_t)2 << 61;                                // layout type: SWIZZLE_128B
-  return d;
+  return ((1024u >> 4) & 0x3FFFu)   // stride byte offset, descriptor bits [32,46)
+         | (1u << 14)               // descriptor version (Blackwell), bit 46
+         | (2u << 29);              // layout type SWIZZLE_128B, bits [61,64)
 }
 
 // Instruction descriptor for kind::f16: fp32 accumulate, A/B both fp16 (fmt 0) or bf16 (fmt 1).
@@ -325,18 +233,6 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr)
       : "memory");
 }
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
-      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
-        "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]),
-        "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]),
-        "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
-        "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-      : "memory");
-}
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
@@ -371,14 +267,6 @@ __device__ __forceinline__ void tmem_st_wait() {
 }
 
 // Register re-partitioning between warpgroups (all 4 warps of a warpgroup must execute it).
-template <int N>
-__device__ __forceinline__ void reg_alloc() {
-  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
-}
-template <int N>
-__device__ __forceinline__ void reg_dealloc() {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
-}
 
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
