@@ -3,6 +3,10 @@ argument validation that happens before any CUDA call returns the documented cod
 import ctypes
 import os
 import re
+import shutil
+import subprocess
+
+import pytest
 
 import natten_b200._lib as L
 
@@ -21,6 +25,19 @@ def test_header_symbols_are_exported():
     for name in declared:
         assert hasattr(lib, name), f"{name} declared in the header but not exported"
     assert sorted(L.SYMBOLS) == declared
+
+
+@pytest.mark.parametrize("compiler,flags", [("gcc", ["-std=c99", "-x", "c"]),
+                                            ("g++", ["-std=c++11", "-x", "c++"])])
+def test_header_is_plain_c_and_cxx(tmp_path, compiler, flags):
+    """The boundary is a C ABI: the header must compile on its own as C99 and as C++ (no torch or
+    CUDA headers, plain pointers and sizes)."""
+    if shutil.which(compiler) is None:
+        pytest.skip(f"{compiler} not installed")
+    src = tmp_path / "use_header.c"
+    src.write_text('#include "natten_b200.h"\nint main(void) { return b200na_version() < 0; }\n')
+    subprocess.run([compiler, *flags, "-Wall", "-Wextra", "-Werror", "-pedantic",
+                    "-I", os.path.join(ROOT, "include"), "-fsyntax-only", str(src)], check=True)
 
 
 def test_version_and_strerror():
