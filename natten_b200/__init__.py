@@ -7,7 +7,13 @@ operators. Importing the package loads ``lib/libnatten_b200.so`` and raises if i
 from . import _lib  # noqa: F401  (fails loudly when the CUDA library is not built)
 from .functional import (BACKEND_NAME, FMHA_BACKEND_NAME, attention, choose_tile_shapes,
                          fna_forward_op, fna_forward_permuted, fna_forward_direct, direct_layout_supported,
-                         can_run_b200_fna, get_configs_for_b200_fna, get_bwd_configs_for_b200_fna, fused_workspace_bytes, merge_attentions,
+                         can_run_b200_fna, get_configs_for_b200_fna, get_bwd_configs_for_b200_fna,
+                         get_configs_for_b200_fmha, get_bwd_configs_for_b200_fmha,
+                         get_configs_for_cutlass_blackwell_fna,
+                         get_bwd_configs_for_cutlass_blackwell_fna,
+                         get_configs_for_cutlass_blackwell_fmha,
+                         get_bwd_configs_for_cutlass_blackwell_fmha,
+                         fused_workspace_bytes, merge_attentions,
                          na1d, na2d, na3d, na_forward_fused,
                          neighborhood_attention_generic, token_permute_operation,
                          token_unpermute_operation)
@@ -21,7 +27,9 @@ __all__ = [
     "na1d", "na2d", "na3d", "attention", "merge_attentions", "neighborhood_attention_generic",
     "NeighborhoodAttention1D", "NeighborhoodAttention2D", "NeighborhoodAttention3D",
     "na_forward_from_host", "can_run_b200_fna", "get_configs_for_b200_fna",
-    "get_bwd_configs_for_b200_fna",
+    "get_bwd_configs_for_b200_fna", "get_configs_for_b200_fmha", "get_bwd_configs_for_b200_fmha",
+    "get_configs_for_cutlass_blackwell_fna", "get_bwd_configs_for_cutlass_blackwell_fna",
+    "get_configs_for_cutlass_blackwell_fmha", "get_bwd_configs_for_cutlass_blackwell_fmha",
     "token_permute_operation", "token_unpermute_operation", "fna_forward_op",
     "fna_forward_permuted", "fna_forward_direct", "direct_layout_supported", "na_forward_fused", "fused_workspace_bytes", "choose_tile_shapes", "BACKEND_NAME", "FMHA_BACKEND_NAME",
 ]

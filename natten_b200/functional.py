@@ -606,6 +606,32 @@ def get_bwd_configs_for_b200_fna(query: Tensor, key: Tensor, value: Tensor):
     return _all_tile_shapes(query.dim() - 3, 7, 7)
 
 
+def get_configs_for_b200_fmha(query: Tensor, key: Tensor, value: Tensor):
+    """Forward `(q_tile_size, kv_tile_size)` pairs of the dense-attention mode: one, the kernel's
+    256-row query tile and 128-row key/value tile. Counterpart of the reference's
+    `get_configs_for_cutlass_blackwell_fmha` (src/natten/backends/configs/__init__.py:97-125)."""
+    if not query.is_cuda or query.dtype not in (torch.float16, torch.bfloat16) + tuple(FP8_DTYPES):
+        return []
+    return [(Q_TILE_SIZE, KV_TILE_SIZE)]
+
+
+def get_bwd_configs_for_b200_fmha(query: Tensor, key: Tensor, value: Tensor):
+    """Backward `(q_tile_size, kv_tile_size)` pairs of the dense-attention mode (128-token tiles);
+    empty for 8-bit operands. Counterpart of `get_bwd_configs_for_cutlass_blackwell_fmha`
+    (src/natten/backends/configs/__init__.py:128-156)."""
+    if not query.is_cuda or query.dtype not in (torch.float16, torch.bfloat16):
+        return []
+    return [(128, 128)]
+
+
+# The reference's names for the same queries, so that code written against its Blackwell backend
+# keeps working after the import is switched (src/natten/__init__.py:66-106).
+get_configs_for_cutlass_blackwell_fna = get_configs_for_b200_fna
+get_bwd_configs_for_cutlass_blackwell_fna = get_bwd_configs_for_b200_fna
+get_configs_for_cutlass_blackwell_fmha = get_configs_for_b200_fmha
+get_bwd_configs_for_cutlass_blackwell_fmha = get_bwd_configs_for_b200_fmha
+
+
 MAX_TMA_BOX = 256      # positions a tensor-map box may span per axis
 MAX_TMA_ELEMENT_STRIDE = 8
 

@@ -147,3 +147,19 @@ def test_backend_names():
         nb.attention(q, q, q, backend="cutlass-fmha")
     with pytest.raises(RuntimeError):             # accepted name, but CPU tensors
         nb.na1d(q, q, q, 3, backend="blackwell-fna")
+
+
+def test_config_queries_answer_to_the_reference_names():
+    """The tile-shape queries exist under the reference's Blackwell names too; on CPU tensors they
+    answer "no configuration", like the reference's do for operands its backend cannot run."""
+    q = torch.zeros(1, 16, 16, 2, 64, dtype=torch.bfloat16)
+    assert nb.get_configs_for_cutlass_blackwell_fna is nb.get_configs_for_b200_fna
+    assert nb.get_bwd_configs_for_cutlass_blackwell_fna is nb.get_bwd_configs_for_b200_fna
+    for fn in (nb.get_configs_for_cutlass_blackwell_fna, nb.get_bwd_configs_for_cutlass_blackwell_fna,
+               nb.get_configs_for_cutlass_blackwell_fmha, nb.get_bwd_configs_for_cutlass_blackwell_fmha):
+        assert fn(q, q, q) == []
+    # every forward pair the search considers is a 256 / 128-token factorisation
+    for tq, tkv in F._all_tile_shapes(2, 8, 7):
+        assert np.prod(tq) == 256 and np.prod(tkv) == 128
+    for tq, tkv in F._all_tile_shapes(3, 7, 7):
+        assert np.prod(tq) == 128 and np.prod(tkv) == 128
