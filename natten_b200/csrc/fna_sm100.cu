@@ -29,6 +29,7 @@
 #include "common.cuh"
 #include "fna_device.cuh"
 #include "fna_host.cuh"
+#include "fna_instrument.cuh"
 #include "ptx.cuh"
 
 namespace b200na {
@@ -97,43 +98,14 @@ struct FnaParams {
 #endif
 };
 
-// Cycle-counter instrumentation, compiled only with -DB200NA_PROFILE (never in the product build).
-#ifdef B200NA_PROFILE
-#define TRACE(role, code) { if (blockIdx.x == 0 && trace_n_ < 1024) { p.prof[148 * 32 + (role) * 1024 + trace_n_] = (clock64() << 8) | (code); ++trace_n_; } }
-#define PROF_DECL int trace_n_ = 0; long long prof_[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long prof_t_ = clock64(); const long long prof_t0_ = prof_t_;
-#define PROF_MARK(i) { const long long n_ = clock64(); prof_[i] += n_ - prof_t_; prof_t_ = n_; }
-#define PROF_FLUSH(role) { prof_[7] = clock64() - prof_t0_; for (int i_ = 0; i_ < 8; ++i_) p.prof[((long long)blockIdx.x * 4 + (role)) * 8 + i_] = prof_[i_]; }
-#if B200NA_PROFILE >= 2
-// MMA / load threads: one 32-bit clock read and one shared-memory store per event (anything
-// heavier perturbs the single issuing thread); block 0 copies the ring to global at teardown.
-#define TRACE2(role, code) { if (trace2_n_ < 1024) { trace2_buf_[((role) - 2) * 1024 + trace2_n_] = ((uint32_t)clock() << 5) | (code); ++trace2_n_; } }
-#define PROF2_DECL int trace2_n_ = 0; uint32_t* trace2_buf_ = reinterpret_cast<uint32_t*>(smem + SM::kBytes);
-#define PROF2_MARK(i) {}
-#define PROF2_FLUSH(role) {}
-#else
-#define TRACE2(role, code) {}
-#define PROF2_DECL
-#define PROF2_MARK(i) {}
-#define PROF2_FLUSH(role) {}
-#endif
-#else
-#define TRACE2(role, code) {}
-#define PROF2_DECL
-#define PROF2_MARK(i) {}
-#define PROF2_FLUSH(role) {}
-#define TRACE(role, code) {}
-#define PROF_DECL
-#define PROF_MARK(i) {}
-#define PROF_FLUSH(role) {}
-#endif
-
 struct Item {
   int bp, h, hk, qt;
   int b;                      // batch entry (bp / G)
   int g[B200NA_MAX_DIM];      // dilation group offset per axis
   int L[B200NA_MAX_DIM];      // extent of this dilation group (dense: number of keys)
   int q_lo[B200NA_MAX_DIM];   // first query coordinate of the tile
-  int kv_t0[B200NA_MAX_DIM];  // first kv tile (tile units) per axis
+  int kv_lo[B200NA_MAX_DIM];  // first key coordinate of the first kv tile per axis
+  int kv_t0[B200NA_MAX_DIM];  // the same in tile units (permuted operands: tiles lie on a grid)
   int kv_n[B200NA_MAX_DIM];   // kv tiles per axis
   int ws_hi[B200NA_MAX_DIM];  // window start of the tile's last query
   int we_lo[B200NA_MAX_DIM];  // window end of the tile's first query
@@ -166,7 +138,8 @@ __device__ __forceinline__ void axis_window(const FnaParams& p, int a, int i, in
   }
 }
 
-// Coordinates of work item w = ((bp * Hq) + h) * n_qtiles + qt.
+// Coordinates of work item w = ((bp * Hq) + h) * n_qtiles + qt (decode_item turns qt into tile
+// coordinates and walks causal axes from the far end, see there).
 struct WorkCursor {
   long long w;
   int qt, h, bp;
@@ -186,13 +159,13 @@ __device__ __forceinline__ int div_fast(int x, int d, int sh) { return sh >= 0 ?
 // avoided wherever the launch parameters allow (no dilation, unit stride, power-of-two tiles).
 template <int NDIM>
 __device__ __forceinline__ void decode_item(const FnaParams& p, const WorkCursor& cur, Item& it) {
-  it.qt = cur.qt;
   it.h = cur.h;
   it.bp = cur.bp;
   it.hk = (p.Hq == p.Hkv) ? cur.h : cur.h / (p.Hq / p.Hkv);
   it.b = (p.G > 1) ? cur.bp / p.G : cur.bp;
   int gl = (p.G > 1) ? cur.bp - it.b * p.G : 0;
   int ql = cur.qt;
+  int qt = 0, qt_mul = 1;
   it.n_tiles = 1;
   it.skip = 0;
 #pragma unroll
@@ -211,6 +184,12 @@ __device__ __forceinline__ void decode_item(const FnaParams& p, const WorkCursor
         r = ql - qn * p.Rq[a];
         ql = qn;
       }
+      // Longest items first: along a causal axis the number of kv tiles grows with the query
+      // coordinate, so that axis is walked from its far end and the items a CTA draws last -
+      // the ones that decide how long the other CTAs idle at the end - are the short ones.
+      if (p.causal[a]) r = p.Rq[a] - 1 - r;
+      qt += r * qt_mul;
+      qt_mul *= p.Rq[a];
       if (!p.dense && r * p.Tq[a] >= p.q_len[a]) it.skip = 1;  // tile holds padding rows only
       if (p.direct && r * p.Tq[a] >= it.L[a]) it.skip = 1;     // beyond this dilation group
       it.q_lo[a] = p.q_org[a] + r * p.Tq[a];
@@ -220,36 +199,53 @@ __device__ __forceinline__ void decode_item(const FnaParams& p, const WorkCursor
       axis_window(p, a, q_hi, it.L[a], s_hi, e_hi);
       it.ws_hi[a] = s_hi;
       it.we_lo[a] = e_lo;
-      // windows are in layout coordinates, the key/value buffer starts at kv_org
-      it.kv_t0[a] = div_fast(s_lo - p.kv_org[a], p.Tkv[a], p.tkv_shift[a]);
-      it.kv_n[a] = div_fast(e_hi - p.kv_org[a] + p.Tkv[a] - 1, p.Tkv[a], p.tkv_shift[a]) - it.kv_t0[a];
+      if (p.direct) {
+        // Tiles gathered from the caller's layout may start at any coordinate: the walk begins
+        // at the first key any query of the item attends, so a window that is a whole number of
+        // tiles wide costs exactly that many tiles, wherever it starts.
+        it.kv_lo[a] = s_lo;
+        it.kv_t0[a] = 0;
+        it.kv_n[a] = div_fast(e_hi - s_lo + p.Tkv[a] - 1, p.Tkv[a], p.tkv_shift[a]);
+      } else {
+        // windows are in layout coordinates, the key/value buffer starts at kv_org and is tiled
+        // from there
+        it.kv_t0[a] = div_fast(s_lo - p.kv_org[a], p.Tkv[a], p.tkv_shift[a]);
+        it.kv_n[a] = div_fast(e_hi - p.kv_org[a] + p.Tkv[a] - 1, p.Tkv[a], p.tkv_shift[a]) - it.kv_t0[a];
+        it.kv_lo[a] = p.kv_org[a] + it.kv_t0[a] * p.Tkv[a];
+      }
       it.n_tiles *= it.kv_n[a];
     } else {
-      it.L[a] = 1; it.q_lo[a] = 0; it.kv_t0[a] = 0; it.kv_n[a] = 1; it.ws_hi[a] = 0; it.we_lo[a] = 1;
-      it.g[a] = 0;
+      it.L[a] = 1; it.q_lo[a] = 0; it.kv_lo[a] = 0; it.kv_t0[a] = 0; it.kv_n[a] = 1;
+      it.ws_hi[a] = 0; it.we_lo[a] = 1; it.g[a] = 0;
     }
   }
+  it.qt = qt;
   if (p.dense && it.qt * kQTile >= p.Sq) it.skip = 1;
   it.n_na = it.n_tiles;
   it.n_tiles += p.extra_tiles;
 }
+// Position of the kv-tile walk of one item: tile counters per axis (from 0) and the layout
+// coordinate of the tile's first key per axis.
+struct KvWalk {
+  int c[B200NA_MAX_DIM];
+  int lo[B200NA_MAX_DIM];
+};
+// First row of the tile in a token-permuted key/value operand.
 template <int NDIM>
-__device__ __forceinline__ int kv_tile_row(const FnaParams& p, const int (&c)[B200NA_MAX_DIM]) {
-  if (NDIM == 1) return c[0] * kKVTile;
-  if (NDIM == 2) return (c[0] + p.Rkv[0] * c[1]) * kKVTile;
-  return (c[0] + p.Rkv[0] * (c[1] + p.Rkv[1] * c[2])) * kKVTile;
+__device__ __forceinline__ int kv_tile_row(const FnaParams& p, const Item& it, const KvWalk& w) {
+  if (NDIM == 1) return (it.kv_t0[0] + w.c[0]) * kKVTile;
+  if (NDIM == 2) return (it.kv_t0[0] + w.c[0] + p.Rkv[0] * (it.kv_t0[1] + w.c[1])) * kKVTile;
+  return (it.kv_t0[0] + w.c[0] +
+          p.Rkv[0] * (it.kv_t0[1] + w.c[1] + p.Rkv[1] * (it.kv_t0[2] + w.c[2]))) * kKVTile;
 }
 // True when every key of the tile lies inside the window of every query of the item.
 template <int NDIM>
 __device__ __forceinline__ bool kv_tile_interior(const FnaParams& p, const Item& it,
-                                                 const int (&c)[B200NA_MAX_DIM]) {
+                                                 const KvWalk& w) {
   bool in = true;
 #pragma unroll
   for (int a = 0; a < B200NA_MAX_DIM; ++a) {
-    if (a < NDIM) {
-      const int lo = p.kv_org[a] + c[a] * p.Tkv[a];
-      in = in && (lo >= it.ws_hi[a]) && (lo + p.Tkv[a] <= it.we_lo[a]);
-    }
+    if (a < NDIM) in = in && (w.lo[a] >= it.ws_hi[a]) && (w.lo[a] + p.Tkv[a] <= it.we_lo[a]);
   }
   return in;
 }
@@ -328,20 +324,19 @@ __device__ __forceinline__ void release_item(const Bars& bars, uint32_t seq) {
 
 // Advances the colexicographic kv-tile walk by one tile (no divisions on the per-tile path).
 template <int NDIM>
-__device__ __forceinline__ void kv_tile_next(const Item& it, int (&c)[B200NA_MAX_DIM]) {
-  if (NDIM == 1) {
-    ++c[0];
-    return;
-  }
-  if (++c[0] < it.kv_t0[0] + it.kv_n[0]) return;
-  c[0] = it.kv_t0[0];
-  if (NDIM == 2) {
-    ++c[1];
-    return;
-  }
-  if (++c[1] < it.kv_t0[1] + it.kv_n[1]) return;
-  c[1] = it.kv_t0[1];
-  ++c[2];
+__device__ __forceinline__ void kv_tile_next(const FnaParams& p, const Item& it, KvWalk& w) {
+  ++w.c[0];
+  w.lo[0] += p.Tkv[0];
+  if (NDIM == 1 || w.c[0] < it.kv_n[0]) return;
+  w.c[0] = 0;
+  w.lo[0] = it.kv_lo[0];
+  ++w.c[1];
+  w.lo[1] += p.Tkv[1];
+  if (NDIM == 2 || w.c[1] < it.kv_n[1]) return;
+  w.c[1] = 0;
+  w.lo[1] = it.kv_lo[1];
+  ++w.c[2];
+  w.lo[2] += p.Tkv[2];
 }
 
 template <int D, int kType, int NDIM>
@@ -526,36 +521,48 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         PROF_MARK(0)
         if (row == 0 && part == 0) TRACE(half, 1)
         ptx::tc_fence_after_sync();
-        // Pass 1: row maximum of the raw logits over this thread's 64 columns. Chunk 1 is read
-        // first and dropped, chunk 0 stays in registers for pass 2.
-        uint32_t sr[32];
-        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-        ptx::tmem_ld32(my_s + 32, sr);
+        // The thread's 64 logit columns are handled as four chunks of 16 through two register
+        // buffers: while one chunk is being worked on the next one is already on its way from
+        // tensor memory, so only the first load of the tile is waited for in full.
+        // Pass 1: row maximum of the raw logits, chunks 3, 2, 1, 0 - chunk 0 stays in `rb`.
+        uint32_t ra[16], rb[16];
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+        auto chunk_bits = [&](int ch) -> uint32_t {
+          return ((ch < 2 ? mw0 : mw1) >> ((ch & 1) * 16)) & 0xffffu;
+        };
+        auto mask16 = [&](uint32_t (&x)[16], int ch) {
+          if (!interior) {
+            const uint32_t bits = chunk_bits(ch);
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (!((bits >> j) & 1u)) x[j] = 0xff800000u;  // -inf
+          }
+        };
+        auto max16 = [&](const uint32_t (&x)[16]) {
+#pragma unroll
+          for (int j = 0; j < 16; j += 4) {
+            mx0 = ptx::max3(mx0, __uint_as_float(x[j]), __uint_as_float(x[j + 1]));
+            mx1 = ptx::max3(mx1, __uint_as_float(x[j + 2]), __uint_as_float(x[j + 3]));
+          }
+        };
+        ptx::tmem_ld16(my_s + 48, ra);
         ptx::tmem_ld_wait();
-        if (!interior) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (!((mw1 >> j) & 1u)) sr[j] = 0xff800000u;  // -inf
-        }
-#pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-          mx0 = ptx::max3(mx0, __uint_as_float(sr[j]), __uint_as_float(sr[j + 1]));
-          mx1 = ptx::max3(mx1, __uint_as_float(sr[j + 2]), __uint_as_float(sr[j + 3]));
-        }
-        ptx::tmem_ld32(my_s, sr);
+        ptx::tmem_ld16(my_s + 32, rb);
+        mask16(ra, 3);
+        max16(ra);
+        ptx::tmem_ld_wait();
+        ptx::tmem_ld16(my_s + 16, ra);
+        mask16(rb, 2);
+        max16(rb);
+        ptx::tmem_ld_wait();
+        ptx::tmem_ld16(my_s, rb);
+        mask16(ra, 1);
+        max16(ra);
         ptx::tmem_ld_wait();
         PROF_MARK(1)
-        if (!interior) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (!((mw0 >> j) & 1u)) sr[j] = 0xff800000u;
-        }
-#pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-          mx2 = ptx::max3(mx2, __uint_as_float(sr[j]), __uint_as_float(sr[j + 1]));
-          mx3 = ptx::max3(mx3, __uint_as_float(sr[j + 2]), __uint_as_float(sr[j + 3]));
-        }
-        const float my_max = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+        mask16(rb, 0);
+        max16(rb);
+        const float my_max = fmaxf(mx0, mx1);
         float* xm = xmax + (((iter & 1) * 2 + half) * 2) * kHalf;
         xm[part * kHalf + row] = my_max;
         named_bar_sync(bar_id, kSoftmaxThreadsPerHalf);
@@ -572,57 +579,59 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             // O_half is quiescent here: P.V of the previous tile completed before s_full fired.
 #pragma unroll
             for (int ch = 0; ch < D / 32; ++ch) {
-              uint32_t orr[16];
-              ptx::tmem_ld16(my_o + ch * 16, orr);
+              ptx::tmem_ld16(my_o + ch * 16, ra);
               ptx::tmem_ld_wait();
 #pragma unroll
-              for (int j = 0; j < 16; ++j) orr[j] = __float_as_uint(__uint_as_float(orr[j]) * f);
-              ptx::tmem_st16(my_o + ch * 16, orr);
+              for (int j = 0; j < 16; ++j) ra[j] = __float_as_uint(__uint_as_float(ra[j]) * f);
+              ptx::tmem_st16(my_o + ch * 16, ra);
             }
           }
         }
         const float neg_mc = (m == -INFINITY) ? 0.f : -m * c;
-        // Pass 2: p = 2^(s*c - m*c), 32 columns at a time; each packed chunk of P overwrites
-        // logit columns this same thread has already consumed, so no other thread is involved.
+        // Pass 2: p = 2^(s*c - m*c), chunk by chunk; each packed chunk of P overwrites logit
+        // columns this same thread has already consumed, so no other thread is involved.
         float sm0 = 0.f, sm1 = 0.f;
-#pragma unroll
-        for (int ch = 0; ch < 2; ++ch) {
-          if (ch == 1) {
-            ptx::tmem_ld32(my_s + 32, sr);
-            ptx::tmem_ld_wait();
-            if (!interior) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (!((mw1 >> j) & 1u)) sr[j] = 0xff800000u;
-            }
-          }
+        auto exp16 = [&](const uint32_t (&x)[16], int ch) {
           if (kF8) {
             // 8-bit operands: P is rounded to e4m3, four probabilities per TMEM column
-            uint32_t pk[8];
+            uint32_t pk[4];
 #pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              const float p0 = ptx::ex2(fmaf(__uint_as_float(sr[j]), c, neg_mc));
-              const float p1 = ptx::ex2(fmaf(__uint_as_float(sr[j + 1]), c, neg_mc));
-              const float p2 = ptx::ex2(fmaf(__uint_as_float(sr[j + 2]), c, neg_mc));
-              const float p3 = ptx::ex2(fmaf(__uint_as_float(sr[j + 3]), c, neg_mc));
+            for (int j = 0; j < 16; j += 4) {
+              const float p0 = ptx::ex2(fmaf(__uint_as_float(x[j]), c, neg_mc));
+              const float p1 = ptx::ex2(fmaf(__uint_as_float(x[j + 1]), c, neg_mc));
+              const float p2 = ptx::ex2(fmaf(__uint_as_float(x[j + 2]), c, neg_mc));
+              const float p3 = ptx::ex2(fmaf(__uint_as_float(x[j + 3]), c, neg_mc));
               sm0 += p0 + p2;
               sm1 += p1 + p3;
               pk[j >> 2] = ptx::pack4_e4m3(p0, p1, p2, p3);
             }
-            ptx::tmem_st8(my_p + ch * 8, pk);
+            ptx::tmem_st4(my_p + ch * 4, pk);
           } else {
-            uint32_t pk[16];
+            uint32_t pk[8];
 #pragma unroll
-            for (int j = 0; j < 32; j += 2) {
-              const float p0 = ptx::ex2(fmaf(__uint_as_float(sr[j]), c, neg_mc));
-              const float p1 = ptx::ex2(fmaf(__uint_as_float(sr[j + 1]), c, neg_mc));
+            for (int j = 0; j < 16; j += 2) {
+              const float p0 = ptx::ex2(fmaf(__uint_as_float(x[j]), c, neg_mc));
+              const float p1 = ptx::ex2(fmaf(__uint_as_float(x[j + 1]), c, neg_mc));
               sm0 += p0;
               sm1 += p1;
               pk[j >> 1] = pack2<kType>(p0, p1);
             }
-            ptx::tmem_st16(my_p + ch * 16, pk);
+            ptx::tmem_st8(my_p + ch * 8, pk);
           }
-        }
+        };
+        ptx::tmem_ld16(my_s + 16, ra);
+        exp16(rb, 0);
+        ptx::tmem_ld_wait();
+        ptx::tmem_ld16(my_s + 32, rb);
+        mask16(ra, 1);
+        exp16(ra, 1);
+        ptx::tmem_ld_wait();
+        ptx::tmem_ld16(my_s + 48, ra);
+        mask16(rb, 2);
+        exp16(rb, 2);
+        ptx::tmem_ld_wait();
+        mask16(ra, 3);
+        exp16(ra, 3);
         sum += sm0 + sm1;
         PROF_MARK(2)
         ptx::tmem_st_wait();
@@ -864,7 +873,7 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       PROF2_FLUSH(2)
     }
   } else if (warp == kLoadWarp) {
-    // ====================== TMA loads (warps 10-11 only donate registers) ===================
+    // =============================== TMA loads + item decode ================================
     if (lane == 0) {
       uint32_t ph_qe = 1;
       RingPos<kStages> ring;
@@ -928,30 +937,29 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                                db * kBlockElems, it.h, it.qt * kQTile + h * kHalf, bp);
             }
           }
-        int tc[B200NA_MAX_DIM] = {it.kv_t0[0], it.kv_t0[1], it.kv_t0[2]};
+        KvWalk walk = {{0, 0, 0}, {it.kv_lo[0], it.kv_lo[1], it.kv_lo[2]}};
         const Item* next = nullptr;
         const int publish_at = imin(kStages / 2 - 1, n_tiles - 1);
         for (int iter = 0; iter < n_tiles && alive; ++iter) {
           const bool is_extra = iter >= n_na;
-          const int row0 = is_extra ? (iter - n_na) * kKVTile : kv_tile_row<NDIM>(p, tc);
+          const int row0 = is_extra ? (iter - n_na) * kKVTile
+                                    : (p.direct ? 0 : kv_tile_row<NDIM>(p, it, walk));
           int4 rec;
           if (is_extra) {
             const int valid = p.n_extra - (iter - n_na) * kKVTile;
             rec = make_int4(valid >= kKVTile ? 0 : 2, valid, 0, 0);
           } else {
-            rec = make_int4(kv_tile_interior<NDIM>(p, it, tc) ? 0 : 1,
-                            p.kv_org[0] + tc[0] * p.Tkv[0],
-                            NDIM > 1 ? p.kv_org[1] + tc[1] * p.Tkv[1] : 0,
-                            NDIM > 2 ? p.kv_org[2] + tc[2] * p.Tkv[2] : 0);
+            rec = make_int4(kv_tile_interior<NDIM>(p, it, walk) ? 0 : 1, walk.lo[0],
+                            NDIM > 1 ? walk.lo[1] : 0, NDIM > 2 ? walk.lo[2] : 0);
           }
           // direct mode: coordinates of the tile's first key in the caller's layout
           int xk[B200NA_MAX_DIM] = {0, 0, 0};
           if (p.direct && !is_extra) {
 #pragma unroll
             for (int a = 0; a < B200NA_MAX_DIM; ++a)
-              xk[a] = (a < NDIM) ? tc[a] * p.Tkv[a] * p.dil[a] + it.g[a] : 0;
+              xk[a] = (a < NDIM) ? walk.lo[a] * p.dil[a] + it.g[a] : 0;
           }
-          if (!is_extra) kv_tile_next<NDIM>(it, tc);
+          if (!is_extra) kv_tile_next<NDIM>(p, it, walk);
           // extra tokens are shared by the dilation groups of a batch entry
           const int b_src = is_extra ? it.b : bp;
           for (int kv = 0; kv < 2; ++kv) {

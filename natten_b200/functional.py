@@ -95,8 +95,11 @@ def group_extent(X: int, d: int, g: int) -> int:
     return X // d + (1 - ((g + (d - (X % d))) // d))
 
 
-def _axis_tile_cost(X: int, k: int, s: int, d: int, causal: bool, tq: int, tkv: int) -> int:
-    """KV tiles visited along one axis, summed over that axis' query tiles (largest group)."""
+def _axis_tile_cost(X: int, k: int, s: int, d: int, causal: bool, tq: int, tkv: int,
+                    aligned: bool = False) -> int:
+    """KV tiles visited along one axis, summed over that axis' query tiles (largest group).
+    `aligned`: the tile walk of a query tile starts at the first key its queries attend (tiles
+    gathered from the caller's layout); otherwise key/value tiles lie on a grid from 0."""
     L = group_extent(X, d, 0)
     total = 0
     for q_lo in range(0, L, tq):
@@ -104,7 +107,7 @@ def _axis_tile_cost(X: int, k: int, s: int, d: int, causal: bool, tq: int, tkv: 
         st = window_start(q_lo, k, s, L, causal)
         s_hi = window_start(q_hi, k, s, L, causal)
         en = window_end(q_hi, s_hi, k, L, causal)
-        total += -(-en // tkv) - st // tkv
+        total += -(-(en - st) // tkv) if aligned else -(-en // tkv) - st // tkv
     return total
 
 
@@ -136,18 +139,23 @@ def _choose_tile_shapes(shape: DimensionType, kernel_size: DimensionType, stride
     n = len(shape)
     if n == 1:
         return (Q_TILE_SIZE,), (KV_TILE_SIZE,)
-    cost: Dict[Tuple[int, int, int], int] = {}
+    cost: Dict[Tuple[int, int, int, bool], int] = {}
     for a in range(n):
         for eq in range(9):
             for ek in range(8):
-                cost[(a, 1 << eq, 1 << ek)] = _axis_tile_cost(
-                    shape[a], kernel_size[a], stride[a], dilation[a], is_causal[a], 1 << eq, 1 << ek)
+                for aligned in (False, True):
+                    cost[(a, 1 << eq, 1 << ek, aligned)] = _axis_tile_cost(
+                        shape[a], kernel_size[a], stride[a], dilation[a], is_causal[a], 1 << eq,
+                        1 << ek, aligned)
     best = None
     for tq in _pow2_compositions(8, n):
         for tkv in _pow2_compositions(7, n):
+            # tiles the kernel can gather from the caller's layout start at the window; tile
+            # shapes that need token-permuted copies are tied to the tile grid
+            aligned = direct_layout_supported(tq, tkv, dilation)
             c = 1
             for a in range(n):
-                c *= cost[(a, tq[a], tkv[a])]
+                c *= cost[(a, tq[a], tkv[a], aligned)]
             # ties: prefer tiles that are long along the last (memory-contiguous) axis
             key = (c, -tq[-1], -tkv[-1])
             if best is None or key < best[0]:

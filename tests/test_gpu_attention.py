@@ -90,12 +90,13 @@ def test_tensor_core_kernel_with_explicit_tile_shapes(name, qt, kvt):
     ((9, 11, 13), (3, 3, 3), (1, 1, 1), (3, 2, 4), (False, True, False), (4, 8, 8), (4, 4, 8), 17, 2, 2, 64),
     ((5, 7, 300), (2, 2, 31), (1, 1, 1), (1, 1, 2), (False, False, True), (1, 2, 128), (1, 1, 128), 0, 1, 1, 64),
 ])
-def test_direct_layout_is_bit_identical_to_the_permuted_flow(shape, ks, st, di, ca, qt, kvt,
-                                                             n_extra, hq, hkv, D):
+def test_direct_layout_agrees_with_the_permuted_flow(shape, ks, st, di, ca, qt, kvt,
+                                                     n_extra, hq, hkv, D):
     """The kernel reading the caller's layout through tensor maps (one launch, no scratch) against
-    permute -> kernel -> unpermute with the same tiles: same arithmetic in the same order, so
-    every bit of O and LSE agrees; ragged extents, dilation groups of unequal size, GQA and extra
-    tokens included. Also checked against the oracle."""
+    permute -> kernel -> unpermute with the same tile shapes; ragged extents, dilation groups of
+    unequal size, GQA and extra tokens included. The two walk the keys in different tiles (gathered
+    tiles start at the first attended key, permuted ones lie on the tile grid), so they agree to
+    rounding, not bit for bit; both are checked against the oracle."""
     torch.manual_seed(33)
     q = torch.randn(2, *shape, hq, D).bfloat16()
     k, v = (torch.randn(2, *shape, hkv, D).bfloat16() for _ in range(2))
@@ -108,13 +109,14 @@ def test_direct_layout_is_bit_identical_to_the_permuted_flow(shape, ks, st, di, 
     o_d, l_d = nb.fna_forward_direct(*args)
     o_p, l_p = nb.fna_forward_permuted(*args)
     assert L.device_status() == 0
-    assert torch.equal(o_d, o_p)
-    assert torch.equal(l_d, l_p)
+    assert (o_d.float() - o_p.float()).abs().max().item() <= TOL_16
+    assert (l_d - l_p).abs().max().item() <= 1e-3
     want_o, want_l = oracle.na_forward(
         q.float().numpy(), k.float().numpy(), v.float().numpy(), ks, st, di, ca,
         add_k=ak.float().numpy() if n_extra else None, add_v=av.float().numpy() if n_extra else None)
-    assert np.abs(o_d.float().cpu().numpy() - want_o).max() <= TOL_16
-    assert np.abs(l_d.cpu().numpy() - want_l).max() <= TOL_16
+    for o, l in ((o_d, l_d), (o_p, l_p)):
+        assert np.abs(o.float().cpu().numpy() - want_o).max() <= TOL_16
+        assert np.abs(l.cpu().numpy() - want_l).max() <= TOL_16
 
 
 def test_direct_layout_limits():
@@ -274,7 +276,8 @@ def test_spatial_slabs_reproduce_the_unsharded_result(shape, ks, st, ca, world):
         o, l = sharding.fna_forward_slab(q[:, t0:t1].contiguous(), k[:, lo:hi].contiguous(),
                                          v[:, lo:hi].contiguous(), shape, t0, lo, ks, st, ca)
         assert L.device_status() == 0
-        assert (o.float() - full_o[:, t0:t1].float()).abs().max().item() <= 4e-3, r
+        # slab and unsharded call tile the keys differently: equal up to bf16 rounding of O
+        assert (o.float() - full_o[:, t0:t1].float()).abs().max().item() <= 1e-2, r
         assert (l - full_l[:, t0:t1]).abs().max().item() <= 2e-3, r
     # a slab that does not hold every needed key is refused, not silently wrong
     t0, t1 = plan.slabs[world - 1]
@@ -291,8 +294,10 @@ def test_spatial_slabs_reproduce_the_unsharded_result(shape, ks, st, ca, world):
     ((1000,), (33,), (1,), (3,), (False,)),
 ])
 def test_single_call_c_entry_equals_the_operator(shape, ks, st, di, ca):
-    """b200na_na_forward (permute -> attention -> unpermute in one C call, caller workspace) gives
-    bit-identical results to na1d/na2d/na3d, also when the workspace is reused by a second call."""
+    """b200na_na_forward (permute -> attention -> unpermute in one C call, caller workspace) agrees
+    with na1d/na2d/na3d to rounding (the operator gathers its tiles from the caller's layout and
+    starts them at the first attended key; the C call tiles permuted copies on a grid), and gives
+    the same bits when the workspace is reused by a second call."""
     torch.manual_seed(21)
     q, k, v = (torch.randn(2, *shape, 2, 64, device="cuda").half() for _ in range(3))
     want_o, want_l = _na_fn(len(shape))(q, k, v, ks, st, di, ca, return_lse=True)
@@ -300,10 +305,15 @@ def test_single_call_c_entry_equals_the_operator(shape, ks, st, di, ca):
     need = nb.fused_workspace_bytes(shape, di, tq, tkv, 2, 2, 2, 64)
     assert (need == 0) == (shape == (1024,))
     ws = torch.full((max(need, 1),), 0xAB, dtype=torch.uint8, device="cuda")
+    first = None
     for _ in range(2):
         o, l = nb.na_forward_fused(q, k, v, ks, st, di, ca, workspace=ws)
         assert L.device_status() == 0
-        assert torch.equal(o, want_o) and torch.equal(l, want_l)
+        assert (o.float() - want_o.float()).abs().max().item() <= TOL_16
+        assert (l - want_l).abs().max().item() <= 1e-3
+        if first is not None:
+            assert torch.equal(o, first[0]) and torch.equal(l, first[1])
+        first = (o.clone(), l.clone())
     if need:
         with pytest.raises(L.NattenB200Error):
             nb.na_forward_fused(q, k, v, ks, st, di, ca, workspace=ws[:need - 256])

@@ -105,14 +105,20 @@ def test_tile_shape_selection_is_valid_and_no_worse_than_reference_defaults():
         n = len(shape)
 
         def cost(tq_, tkv_):
-            return np.prod([F._axis_tile_cost(shape[a], k[a], s[a], d[a], c[a], tq_[a], tkv_[a])
-                            for a in range(n)], dtype=np.float64)
+            # gathered tiles start at the first attended key, permuted ones lie on the tile grid
+            aligned = nb.direct_layout_supported(tq_, tkv_, d)
+            return np.prod([F._axis_tile_cost(shape[a], k[a], s[a], d[a], c[a], tq_[a], tkv_[a],
+                                              aligned) for a in range(n)], dtype=np.float64)
         # compare per query token (tiles may differ in count)
         def per_token(tq_, tkv_):
             return cost(tq_, tkv_) / np.prod([-(-F.group_extent(shape[a], d[a], 0) // tq_[a])
                                               for a in range(n)])
         assert cost(tq, tkv) <= cost(*ref_default[n])
     assert nb.choose_tile_shapes((4096,), (64,), (1,), (1,), (False,)) == ((256,), (128,))
+    # a window that is a whole number of tiles wide costs exactly that many gathered tiles,
+    # wherever it starts: 32 keys from 16 j - 8 are two 16-key tiles, three on the grid
+    assert F._axis_tile_cost(256, 32, 16, 1, False, 16, 16, aligned=True) == 2 * 16
+    assert F._axis_tile_cost(256, 32, 16, 1, False, 16, 16, aligned=False) == 3 * 16 - 2
 
 
 def test_layout_predicates_and_backward_tile_choice():
