@@ -521,48 +521,36 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         PROF_MARK(0)
         if (row == 0 && part == 0) TRACE(half, 1)
         ptx::tc_fence_after_sync();
-        // The thread's 64 logit columns are handled as four chunks of 16 through two register
-        // buffers: while one chunk is being worked on the next one is already on its way from
-        // tensor memory, so only the first load of the tile is waited for in full.
-        // Pass 1: row maximum of the raw logits, chunks 3, 2, 1, 0 - chunk 0 stays in `rb`.
-        uint32_t ra[16], rb[16];
-        float mx0 = -INFINITY, mx1 = -INFINITY;
-        auto chunk_bits = [&](int ch) -> uint32_t {
-          return ((ch < 2 ? mw0 : mw1) >> ((ch & 1) * 16)) & 0xffffu;
-        };
-        auto mask16 = [&](uint32_t (&x)[16], int ch) {
-          if (!interior) {
-            const uint32_t bits = chunk_bits(ch);
+        // Pass 1: row maximum of the raw logits over this thread's 64 columns. Chunk 1 is read
+        // first and dropped, chunk 0 stays in registers for pass 2.
+        uint32_t sr[32];
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+        ptx::tmem_ld32(my_s + 32, sr);
+        ptx::tmem_ld_wait();
+        if (!interior) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j)
-              if (!((bits >> j) & 1u)) x[j] = 0xff800000u;  // -inf
-          }
-        };
-        auto max16 = [&](const uint32_t (&x)[16]) {
+          for (int j = 0; j < 32; ++j)
+            if (!((mw1 >> j) & 1u)) sr[j] = 0xff800000u;  // -inf
+        }
 #pragma unroll
-          for (int j = 0; j < 16; j += 4) {
-            mx0 = ptx::max3(mx0, __uint_as_float(x[j]), __uint_as_float(x[j + 1]));
-            mx1 = ptx::max3(mx1, __uint_as_float(x[j + 2]), __uint_as_float(x[j + 3]));
-          }
-        };
-        ptx::tmem_ld16(my_s + 48, ra);
-        ptx::tmem_ld_wait();
-        ptx::tmem_ld16(my_s + 32, rb);
-        mask16(ra, 3);
-        max16(ra);
-        ptx::tmem_ld_wait();
-        ptx::tmem_ld16(my_s + 16, ra);
-        mask16(rb, 2);
-        max16(rb);
-        ptx::tmem_ld_wait();
-        ptx::tmem_ld16(my_s, rb);
-        mask16(ra, 1);
-        max16(ra);
+        for (int j = 0; j < 32; j += 4) {
+          mx0 = ptx::max3(mx0, __uint_as_float(sr[j]), __uint_as_float(sr[j + 1]));
+          mx1 = ptx::max3(mx1, __uint_as_float(sr[j + 2]), __uint_as_float(sr[j + 3]));
+        }
+        ptx::tmem_ld32(my_s, sr);
         ptx::tmem_ld_wait();
         PROF_MARK(1)
-        mask16(rb, 0);
-        max16(rb);
-        const float my_max = fmaxf(mx0, mx1);
+        if (!interior) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (!((mw0 >> j) & 1u)) sr[j] = 0xff800000u;
+        }
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+          mx2 = ptx::max3(mx2, __uint_as_float(sr[j]), __uint_as_float(sr[j + 1]));
+          mx3 = ptx::max3(mx3, __uint_as_float(sr[j + 2]), __uint_as_float(sr[j + 3]));
+        }
+        const float my_max = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
         float* xm = xmax + (((iter & 1) * 2 + half) * 2) * kHalf;
         xm[part * kHalf + row] = my_max;
         named_bar_sync(bar_id, kSoftmaxThreadsPerHalf);
@@ -579,59 +567,57 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             // O_half is quiescent here: P.V of the previous tile completed before s_full fired.
 #pragma unroll
             for (int ch = 0; ch < D / 32; ++ch) {
-              ptx::tmem_ld16(my_o + ch * 16, ra);
+              uint32_t orr[16];
+              ptx::tmem_ld16(my_o + ch * 16, orr);
               ptx::tmem_ld_wait();
 #pragma unroll
-              for (int j = 0; j < 16; ++j) ra[j] = __float_as_uint(__uint_as_float(ra[j]) * f);
-              ptx::tmem_st16(my_o + ch * 16, ra);
+              for (int j = 0; j < 16; ++j) orr[j] = __float_as_uint(__uint_as_float(orr[j]) * f);
+              ptx::tmem_st16(my_o + ch * 16, orr);
             }
           }
         }
         const float neg_mc = (m == -INFINITY) ? 0.f : -m * c;
-        // Pass 2: p = 2^(s*c - m*c), chunk by chunk; each packed chunk of P overwrites logit
-        // columns this same thread has already consumed, so no other thread is involved.
+        // Pass 2: p = 2^(s*c - m*c), 32 columns at a time; each packed chunk of P overwrites
+        // logit columns this same thread has already consumed, so no other thread is involved.
         float sm0 = 0.f, sm1 = 0.f;
-        auto exp16 = [&](const uint32_t (&x)[16], int ch) {
+#pragma unroll
+        for (int ch = 0; ch < 2; ++ch) {
+          if (ch == 1) {
+            ptx::tmem_ld32(my_s + 32, sr);
+            ptx::tmem_ld_wait();
+            if (!interior) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (!((mw1 >> j) & 1u)) sr[j] = 0xff800000u;
+            }
+          }
           if (kF8) {
             // 8-bit operands: P is rounded to e4m3, four probabilities per TMEM column
-            uint32_t pk[4];
+            uint32_t pk[8];
 #pragma unroll
-            for (int j = 0; j < 16; j += 4) {
-              const float p0 = ptx::ex2(fmaf(__uint_as_float(x[j]), c, neg_mc));
-              const float p1 = ptx::ex2(fmaf(__uint_as_float(x[j + 1]), c, neg_mc));
-              const float p2 = ptx::ex2(fmaf(__uint_as_float(x[j + 2]), c, neg_mc));
-              const float p3 = ptx::ex2(fmaf(__uint_as_float(x[j + 3]), c, neg_mc));
+            for (int j = 0; j < 32; j += 4) {
+              const float p0 = ptx::ex2(fmaf(__uint_as_float(sr[j]), c, neg_mc));
+              const float p1 = ptx::ex2(fmaf(__uint_as_float(sr[j + 1]), c, neg_mc));
+              const float p2 = ptx::ex2(fmaf(__uint_as_float(sr[j + 2]), c, neg_mc));
+              const float p3 = ptx::ex2(fmaf(__uint_as_float(sr[j + 3]), c, neg_mc));
               sm0 += p0 + p2;
               sm1 += p1 + p3;
               pk[j >> 2] = ptx::pack4_e4m3(p0, p1, p2, p3);
             }
-            ptx::tmem_st4(my_p + ch * 4, pk);
+            ptx::tmem_st8(my_p + ch * 8, pk);
           } else {
-            uint32_t pk[8];
+            uint32_t pk[16];
 #pragma unroll
-            for (int j = 0; j < 16; j += 2) {
-              const float p0 = ptx::ex2(fmaf(__uint_as_float(x[j]), c, neg_mc));
-              const float p1 = ptx::ex2(fmaf(__uint_as_float(x[j + 1]), c, neg_mc));
+            for (int j = 0; j < 32; j += 2) {
+              const float p0 = ptx::ex2(fmaf(__uint_as_float(sr[j]), c, neg_mc));
+              const float p1 = ptx::ex2(fmaf(__uint_as_float(sr[j + 1]), c, neg_mc));
               sm0 += p0;
               sm1 += p1;
               pk[j >> 1] = pack2<kType>(p0, p1);
             }
-            ptx::tmem_st8(my_p + ch * 8, pk);
+            ptx::tmem_st16(my_p + ch * 16, pk);
           }
-        };
-        ptx::tmem_ld16(my_s + 16, ra);
-        exp16(rb, 0);
-        ptx::tmem_ld_wait();
-        ptx::tmem_ld16(my_s + 32, rb);
-        mask16(ra, 1);
-        exp16(ra, 1);
-        ptx::tmem_ld_wait();
-        ptx::tmem_ld16(my_s + 48, ra);
-        mask16(rb, 2);
-        exp16(rb, 2);
-        ptx::tmem_ld_wait();
-        mask16(ra, 3);
-        exp16(ra, 3);
+        }
         sum += sm0 + sm1;
         PROF_MARK(2)
         ptx::tmem_st_wait();
