@@ -177,6 +177,27 @@ B200NA_API int b200na_fna_forward_sharded(
     const int* q_origin, const int* q_extent, const int* kv_origin, b200na_stream_t stream);
 
 /*
+ * One rank's slab on the caller's layout, no permuted copies: q, o, lse are contiguous
+ * [B, *q_extent, H, D] tensors holding layout coordinates [q_origin, q_origin + q_extent) of an
+ * undilated token layout global_shape, k and v hold [kv_origin, kv_origin + kv_extent). Window
+ * arithmetic stays in layout coordinates (mask.hpp:59-89); the reference has no counterpart.
+ *   clip_to_kv == 0: the key/value slab must hold every key the local queries' windows reach,
+ *     otherwise B200NA_ERR_INVALID_ARGUMENT.
+ *   clip_to_kv != 0: partial attention over the keys that are present - every window is cut to
+ *     the slab; a query none of whose keys are present gets O = 0 and LSE = -inf. Partial
+ *     results over disjoint key slabs combine with b200na_merge to the full result, which lets
+ *     a rank attend its own frames while the frames of other ranks are still in flight
+ *     (the use the reference's merge_attentions hints at, src/natten/attn_merge.py:199-204).
+ * Also the building block for streaming a host-resident problem through the GPU along axis 0.
+ */
+B200NA_API int b200na_na_forward_direct_sharded(
+    const void* q, const void* k, const void* v, void* o, float* lse, int ndim,
+    const int* global_shape, const int* kernel, const int* stride, const int* causal,
+    const int* q_tile, const int* kv_tile, const int* q_origin, const int* q_extent,
+    const int* kv_origin, const int* kv_extent, int clip_to_kv, int B, int Hq, int Hkv, int D,
+    int dtype, float scale, b200na_stream_t stream);
+
+/*
  * Whole operator in one call: token permute of Q, K, V -> fused attention -> unpermute of O and
  * LSE, i.e. the forward of the reference's Python backend adapter
  * (src/natten/backends/blackwell_fna.py:91-181) for hosts that bind this C ABI directly.
@@ -305,7 +326,9 @@ B200NA_API int b200na_na_backward_direct(
  * (reference: src/natten/attn_merge.py:48-105; call site src/natten/functional.py:548-554).
  *   o = o0 - sigmoid(l1 - l0) * (o0 - o1);  l = l0 - logsigmoid(l0 - l1)   (fp32 arithmetic)
  *   o0, o1, o: [rows, D] of `dtype`; l0, l1, l: [rows] fp32; rows = B * N * H.
- * o may alias o0 or o1, l may alias l0 or l1.
+ * An input whose LSE is -inf (no keys) leaves the other input unchanged.
+ * o may alias o0 or o1 (each element is read before it is written, by the same thread); l must
+ * not alias l0 or l1 (B200NA_ERR_INVALID_ARGUMENT): every thread of a row reads both.
  */
 B200NA_API int b200na_merge(const void* o0, const float* l0, const void* o1, const float* l1, void* o,
                  float* l, int64_t rows, int D, int dtype, b200na_stream_t stream);

@@ -22,7 +22,7 @@ F32, F16, BF16, E4M3, E5M2 = 0, 1, 2, 3, 4
 # Every symbol include/natten_b200.h declares.
 SYMBOLS = (
     "b200na_strerror", "b200na_version", "b200na_token_permute", "b200na_token_unpermute",
-    "b200na_fna_forward", "b200na_fna_forward_sharded", "b200na_fna_forward_extra_kv", "b200na_na_forward_direct", "b200na_na_forward_direct_strided",
+    "b200na_fna_forward", "b200na_fna_forward_sharded", "b200na_na_forward_direct_sharded", "b200na_fna_forward_extra_kv", "b200na_na_forward_direct", "b200na_na_forward_direct_strided",
     "b200na_fmha_forward",
     "b200na_na_forward", "b200na_na_forward_workspace_bytes", "b200na_na_forward_static", "b200na_na_forward_simt", "b200na_na_backward_simt", "b200na_na_backward_direct", "b200na_merge",
     "b200na_device_status",
@@ -79,6 +79,9 @@ def _load() -> ctypes.CDLL:
     lib.b200na_na_backward_direct.restype = c_int
     lib.b200na_na_backward_direct.argtypes = [c_void_p] * 8 + [c_int] + [c_void_p] * 6 + [
         c_int, ip, ip, ip, ip, ip, ip, ip, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]
+    lib.b200na_na_forward_direct_sharded.restype = c_int
+    lib.b200na_na_forward_direct_sharded.argtypes = [c_void_p] * 5 + [c_int] + [ip] * 10 + [
+        c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]
     lib.b200na_fna_forward_sharded.restype = c_int
     lib.b200na_fna_forward_sharded.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                                c_int, ip, ip, ip, ip, ip, ip, ip, ip, ip,

@@ -77,6 +77,11 @@ struct FnaParams {
   int q_org[B200NA_MAX_DIM];   // layout coordinate of local query index 0 (spatial sharding; else 0)
   int kv_org[B200NA_MAX_DIM];  // layout coordinate of local key/value index 0
   int q_len[B200NA_MAX_DIM];   // number of real (non-padding) local query coordinates per axis
+  int o_ext[B200NA_MAX_DIM];   // direct: extents of the Q / O / LSE tensors (rows are written there)
+  int kv_ext[B200NA_MAX_DIM];  // direct: extents of the K / V tensors
+  int clip;                    // windows are cut to the keys [clip_lo, clip_hi) that are present
+  int clip_lo[B200NA_MAX_DIM];
+  int clip_hi[B200NA_MAX_DIM];
   int dense;                // dense attention: one axis, window = all keys (or causal prefix)
   int direct;               // Q/K/V/O/LSE are in the caller's [B, *X, H, D] layout (no permutation)
   long long tok_stride[3];  // direct: elements between consecutive tokens of q, k, v (0 = H * D)
@@ -136,6 +141,13 @@ __device__ __forceinline__ void axis_window(const FnaParams& p, int a, int i, in
     st = win_start(i, p.kernel[a], p.stride[a], L, p.causal[a]);
     en = win_end(i, st, p.kernel[a], L, p.causal[a]);
   }
+  if (p.clip) {
+    // partial attention over the keys that are present: the rest of the window belongs to
+    // another call, whose result is merged with this one. Start and end stay monotone in i;
+    // an empty window is [st, st).
+    st = imin(imax(st, p.clip_lo[a]), p.clip_hi[a]);
+    en = imax(imin(en, p.clip_hi[a]), st);
+  }
 }
 
 // Coordinates of work item w = ((bp * Hq) + h) * n_qtiles + qt (decode_item turns qt into tile
@@ -191,7 +203,7 @@ __device__ __forceinline__ void decode_item(const FnaParams& p, const WorkCursor
       qt += r * qt_mul;
       qt_mul *= p.Rq[a];
       if (!p.dense && r * p.Tq[a] >= p.q_len[a]) it.skip = 1;  // tile holds padding rows only
-      if (p.direct && r * p.Tq[a] >= it.L[a]) it.skip = 1;     // beyond this dilation group
+      if (p.direct && p.q_org[a] + r * p.Tq[a] >= it.L[a]) it.skip = 1;  // beyond this dilation group
       it.q_lo[a] = p.q_org[a] + r * p.Tq[a];
       const int q_hi = it.q_lo[a] + p.Tq[a] - 1;
       int s_lo, e_lo, s_hi, e_hi;
@@ -206,6 +218,12 @@ __device__ __forceinline__ void decode_item(const FnaParams& p, const WorkCursor
         it.kv_lo[a] = s_lo;
         it.kv_t0[a] = 0;
         it.kv_n[a] = div_fast(e_hi - s_lo + p.Tkv[a] - 1, p.Tkv[a], p.tkv_shift[a]);
+        if (p.clip && e_hi <= s_lo) {
+          // none of the item's keys are present along this axis: one tile, masked for every row,
+          // so that the rows still get O = 0 and LSE = -inf for the merge
+          it.kv_lo[a] = imin(s_lo, p.clip_hi[a] - 1);
+          it.kv_n[a] = 1;
+        }
       } else {
         // windows are in layout coordinates, the key/value buffer starts at kv_org and is tiled
         // from there
@@ -649,8 +667,8 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         for (int a = 0; a < B200NA_MAX_DIM; ++a) {
           if (a < NDIM) {
             const int qa = it.q_lo[a] + tq[a];
-            valid = valid && qa < it.L[a];
-            tok = tok * p.X[a] + (qa * p.dil[a] + it.g[a]);
+            valid = valid && qa < it.L[a] && qa - p.q_org[a] < p.q_len[a];
+            tok = tok * p.o_ext[a] + ((qa - p.q_org[a]) * p.dil[a] + it.g[a]);
           }
         }
         out_row = tok * p.Hq + it.h;
@@ -914,8 +932,8 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
               int x[B200NA_MAX_DIM];
 #pragma unroll
               for (int a = 0; a < B200NA_MAX_DIM; ++a)
-                x[a] = (it.q_lo[a] + ((h && a == p.half_axis) ? (p.Tq[a] >> 1) : 0)) * p.dil[a] +
-                       it.g[a];
+                x[a] = (it.q_lo[a] - p.q_org[a] +
+                        ((h && a == p.half_axis) ? (p.Tq[a] >> 1) : 0)) * p.dil[a] + it.g[a];
               ptx::tma_load_5d(q_sm + h * kTileBytes + db * kBlockBytes, &tm_q, bars.q_full,
                                it.h * D + db * kBlockElems, x[0], x[1], x[2], it.b);
             } else {
@@ -943,7 +961,7 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           if (p.direct && !is_extra) {
 #pragma unroll
             for (int a = 0; a < B200NA_MAX_DIM; ++a)
-              xk[a] = (a < NDIM) ? walk.lo[a] * p.dil[a] + it.g[a] : 0;
+              xk[a] = (a < NDIM) ? (walk.lo[a] - p.kv_org[a]) * p.dil[a] + it.g[a] : 0;
           }
           if (!is_extra) kv_tile_next<NDIM>(p, it, walk);
           // extra tokens are shared by the dilation groups of a batch entry
@@ -1203,9 +1221,9 @@ int launch_fna(const void* q, const void* k, const void* v, FnaParams& p, int D,
     for (int a = 0; a < B200NA_MAX_DIM; ++a)
       half_tile[a] = (a == p.half_axis) ? p.Tq[a] / 2 : p.Tq[a];
     const int B = p.Bp / p.G;
-    if ((rc = make_tensor_map_direct(&tq, q, dtype, B, p.X, p.Hq, D, half_tile, p.dil, p.tok_stride[0])) != B200NA_OK) return rc;
-    if ((rc = make_tensor_map_direct(&tk, k, dtype, B, p.X, p.Hkv, D, p.Tkv, p.dil, p.tok_stride[1])) != B200NA_OK) return rc;
-    if ((rc = make_tensor_map_direct(&tv, v, dtype, B, p.X, p.Hkv, D, p.Tkv, p.dil, p.tok_stride[2])) != B200NA_OK) return rc;
+    if ((rc = make_tensor_map_direct(&tq, q, dtype, B, p.o_ext, p.Hq, D, half_tile, p.dil, p.tok_stride[0])) != B200NA_OK) return rc;
+    if ((rc = make_tensor_map_direct(&tk, k, dtype, B, p.kv_ext, p.Hkv, D, p.Tkv, p.dil, p.tok_stride[1])) != B200NA_OK) return rc;
+    if ((rc = make_tensor_map_direct(&tv, v, dtype, B, p.kv_ext, p.Hkv, D, p.Tkv, p.dil, p.tok_stride[2])) != B200NA_OK) return rc;
   } else {
     if ((rc = make_tensor_map(&tq, q, dtype, p.Bp, p.Sq, p.Hq, D)) != B200NA_OK) return rc;
     if ((rc = make_tensor_map(&tk, k, dtype, p.Bp, p.Skv, p.Hkv, D)) != B200NA_OK) return rc;
@@ -1360,9 +1378,16 @@ int fna_direct_impl(const void* q, const void* k, const void* v, void* o, float*
                     const int* shape, const int* kernel, const int* stride, const int* dilation,
                     const int* causal, const int* q_tile, const int* kv_tile, int B, int Hq,
                     int Hkv, int D, int dtype, float scale, const void* add_k, const void* add_v,
-                    int n_extra, const long long* token_strides, b200na_stream_t stream) {
+                    int n_extra, const long long* token_strides, b200na_stream_t stream,
+                    const int* q_origin = nullptr, const int* q_extent = nullptr,
+                    const int* kv_origin = nullptr, const int* kv_extent = nullptr, int clip = 0) {
   if (!q || !k || !v || !o || !shape || !kernel || !q_tile || !kv_tile)
     return B200NA_ERR_INVALID_ARGUMENT;
+  // slabs: q / o / lse hold layout coordinates [q_origin, q_origin + q_extent), k / v hold
+  // [kv_origin, kv_origin + kv_extent); window arithmetic stays in layout coordinates
+  const bool sharded = q_origin || q_extent || kv_origin || kv_extent;
+  if (sharded && !(q_origin && q_extent && kv_origin && kv_extent)) return B200NA_ERR_INVALID_ARGUMENT;
+  if (clip && !sharded) return B200NA_ERR_INVALID_ARGUMENT;
   if (n_extra < 0 || (n_extra > 0 && (!add_k || !add_v))) return B200NA_ERR_INVALID_ARGUMENT;
   if (B < 1 || Hq < 1 || Hkv < 1 || Hq % Hkv != 0) return B200NA_ERR_INVALID_ARGUMENT;
   if (!variant_supported(D, dtype)) return B200NA_ERR_UNSUPPORTED;
@@ -1389,9 +1414,35 @@ int fna_direct_impl(const void* q, const void* k, const void* v, void* o, float*
     p.tkv_shift[a] = -1;
     for (int sh = 0; sh < 8; ++sh)
       if (p.Tkv[a] == (1 << sh)) p.tkv_shift[a] = sh;
-    const int need = (p.X[a] + p.dil[a] - 1) / p.dil[a];  // largest dilation group
+    int need = (p.X[a] + p.dil[a] - 1) / p.dil[a];  // largest dilation group
     p.q_org[a] = 0;
     p.kv_org[a] = 0;
+    p.o_ext[a] = p.X[a];
+    p.kv_ext[a] = p.X[a];
+    p.clip_lo[a] = 0;
+    p.clip_hi[a] = p.X[a];
+    if (sharded) {
+      if (p.dil[a] != 1) return B200NA_ERR_UNSUPPORTED;
+      p.q_org[a] = on ? q_origin[a] : 0;
+      p.kv_org[a] = on ? kv_origin[a] : 0;
+      p.o_ext[a] = on ? q_extent[a] : 1;
+      p.kv_ext[a] = on ? kv_extent[a] : 1;
+      if (p.q_org[a] < 0 || p.kv_org[a] < 0 || p.o_ext[a] < 1 || p.kv_ext[a] < 1 ||
+          p.q_org[a] + p.o_ext[a] > p.X[a] || p.kv_org[a] + p.kv_ext[a] > p.X[a])
+        return B200NA_ERR_INVALID_ARGUMENT;
+      need = p.o_ext[a];
+      const int first = p.q_org[a], last = p.q_org[a] + p.o_ext[a] - 1;
+      const int lo = win_start(first, p.kernel[a], p.stride[a], p.X[a], p.causal[a]);
+      const int st_last = win_start(last, p.kernel[a], p.stride[a], p.X[a], p.causal[a]);
+      const int hi = win_end(last, st_last, p.kernel[a], p.X[a], p.causal[a]);
+      if (clip) {
+        p.clip_lo[a] = p.kv_org[a];
+        p.clip_hi[a] = p.kv_org[a] + p.kv_ext[a];
+      } else if (lo < p.kv_org[a] || hi > p.kv_org[a] + p.kv_ext[a]) {
+        // the key/value slab must hold every key the local queries' windows reach
+        return B200NA_ERR_INVALID_ARGUMENT;
+      }
+    }
     p.q_len[a] = need;
     p.Rq[a] = (need + p.Tq[a] - 1) / p.Tq[a];
     p.Rkv[a] = (need + p.Tkv[a] - 1) / p.Tkv[a];
@@ -1407,6 +1458,7 @@ int fna_direct_impl(const void* q, const void* k, const void* v, void* o, float*
       (long long)Hq * D > 0x7fffffffLL)
     return B200NA_ERR_UNSUPPORTED;
   p.dense = 0;
+  p.clip = clip ? 1 : 0;
   p.Bp = B * p.G; p.Hq = Hq; p.Hkv = Hkv;
   p.Sq = (int)sq; p.Skv = (int)skv;
   p.n_qtiles = (int)(sq / kQTile);
@@ -1442,6 +1494,19 @@ extern "C" B200NA_API int b200na_na_forward_direct_strided(
   return b200na::fna_direct_impl(q, k, v, o, lse, ndim, shape, kernel, stride, dilation, causal,
                                  q_tile, kv_tile, B, Hq, Hkv, D, dtype, scale, add_k, add_v,
                                  n_extra, ts, stream);
+}
+
+extern "C" B200NA_API int b200na_na_forward_direct_sharded(
+    const void* q, const void* k, const void* v, void* o, float* lse, int ndim,
+    const int* global_shape, const int* kernel, const int* stride, const int* causal,
+    const int* q_tile, const int* kv_tile, const int* q_origin, const int* q_extent,
+    const int* kv_origin, const int* kv_extent, int clip_to_kv, int B, int Hq, int Hkv, int D,
+    int dtype, float scale, b200na_stream_t stream) {
+  if (!q_origin || !q_extent || !kv_origin || !kv_extent) return B200NA_ERR_INVALID_ARGUMENT;
+  return b200na::fna_direct_impl(q, k, v, o, lse, ndim, global_shape, kernel, stride, nullptr,
+                                 causal, q_tile, kv_tile, B, Hq, Hkv, D, dtype, scale, nullptr,
+                                 nullptr, 0, nullptr, stream, q_origin, q_extent, kv_origin,
+                                 kv_extent, clip_to_kv);
 }
 
 extern "C" B200NA_API int b200na_fna_forward_sharded(

@@ -26,9 +26,9 @@ template <> struct Cvt<__nv_bfloat16> {
 
 // One thread owns kElems consecutive elements (16 bytes) of one row.
 template <class T, int kElems, bool kVec>
-__global__ void __launch_bounds__(256) merge_kernel(const T* __restrict__ o0,
+__global__ void __launch_bounds__(256) merge_kernel(const T* o0,   // o may alias o0 or o1:
                                                     const float* __restrict__ l0,
-                                                    const T* __restrict__ o1,
+                                                    const T* o1,   // no __restrict__ on these
                                                     const float* __restrict__ l1, T* o, float* l,
                                                     int64_t rows, int D, int chunks) {
   const int64_t total = rows * chunks;
@@ -61,9 +61,11 @@ __global__ void __launch_bounds__(256) merge_kernel(const T* __restrict__ o0,
       }
     }
     if (chunk == 0) {
-      // l0 - logsigmoid(l0 - l1), logsigmoid(x) = min(x, 0) - log1p(exp(-|x|))
-      const float x = a - b;
-      l[row] = a - (fminf(x, 0.f) - log1pf(expf(-fabsf(x))));
+      // l0 - logsigmoid(l0 - l1) = max(l0, l1) + log1p(exp(-|l0 - l1|)); written from the larger
+      // one so that an empty partial result (LSE = -inf, what a clipped slab call returns for a
+      // query none of whose keys it holds) merges to the other input instead of NaN
+      const float mx = fmaxf(a, b);
+      l[row] = mx == -INFINITY ? -INFINITY : mx + log1pf(expf(-fabsf(a - b)));
     }
   }
 }
@@ -102,6 +104,9 @@ extern "C" B200NA_API int b200na_merge(const void* o0, const float* l0, const vo
                             b200na_stream_t stream) {
   if (!o0 || !l0 || !o1 || !l1 || !o || !l || rows < 0 || D < 1)
     return B200NA_ERR_INVALID_ARGUMENT;
+  // every thread of a row reads l0[row] and l1[row], one of them writes l[row]: the output LSE
+  // must be a buffer of its own
+  if (l == l0 || l == l1) return B200NA_ERR_INVALID_ARGUMENT;
   if (rows == 0) return B200NA_OK;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   switch (dtype) {

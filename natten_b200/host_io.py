@@ -2,16 +2,21 @@
 
 The reference's operators take device tensors only; a caller whose data sits in (pinned) host
 memory pays host -> device copies of Q, K, V and a device -> host copy of the result around every
-call. Batch entries are independent, so this helper pipelines them: while one batch chunk is
-being computed, the next chunk's operands are already crossing PCIe in one direction and the
-previous chunk's result in the other (separate copy streams; the link is full duplex).
+call. This helper pipelines the three: while one piece is being computed, the next piece's
+operands are already crossing PCIe in one direction and the previous piece's result in the other
+(separate copy streams; the link is full duplex). Pieces are slabs of the outermost token axis
+where the problem allows it (undilated fp16 / bf16, no extra tokens) - a slab of queries only
+needs the key/value frames its windows reach, which for all but its last frames have arrived with
+earlier slabs - and whole batch entries otherwise.
 """
 from typing import Any, Optional, Tuple
 
 import torch
 from torch import Tensor
 
-from .functional import neighborhood_attention_generic
+from .checks import check_all_args
+from .functional import (TENSOR_CORE_HEAD_DIMS, choose_tile_shapes, direct_layout_supported,
+                         neighborhood_attention_generic)
 
 
 def na_forward_from_host(query: Tensor, key: Tensor, value: Tensor, kernel_size: Any,
@@ -37,6 +42,10 @@ def na_forward_from_host(query: Tensor, key: Tensor, value: Tensor, kernel_size:
     if lse is None:
         lse = torch.empty(query.shape[:-1], dtype=torch.float32).pin_memory()
     has_extra = additional_keys is not None and additional_values is not None
+    if not has_extra and batch_chunk == 1:
+        plan = _slab_plan(query, key, kernel_size, stride, dilation, is_causal)
+        if plan is not None:
+            return _stream_slabs(query, key, value, plan, scale, out, lse, dev)
     cur = torch.cuda.current_stream(dev)
     s_in, s_out = _copy_streams(dev)
     s_in.wait_stream(cur)
@@ -75,3 +84,69 @@ def _copy_streams(dev: torch.device):
     if key not in _streams:
         _streams[key] = (torch.cuda.Stream(dev), torch.cuda.Stream(dev))
     return _streams[key]
+
+
+def _slab_plan(query: Tensor, key: Tensor, kernel_size, stride, dilation, is_causal):
+    """Slabs of axis 0 to stream the problem in, or None when it has to go whole: needs fp16 /
+    bf16 operands with a tensor-core head dim, no dilation, tile shapes the kernel gathers from
+    the caller's layout, and an axis 0 long enough for at least four slabs."""
+    from .sharding import kv_range_for_slab
+    na_dim = query.dim() - 3
+    if query.dtype not in (torch.float16, torch.bfloat16) or query.shape[-1] not in TENSOR_CORE_HEAD_DIMS:
+        return None
+    ks, st, di, ca = check_all_args(na_dim, kernel_size, stride, dilation, is_causal)
+    if any(d != 1 for d in di) or key.shape[1:1 + na_dim] != query.shape[1:1 + na_dim]:
+        return None
+    shape = tuple(int(x) for x in query.shape[1:1 + na_dim])
+    tq, tkv = choose_tile_shapes(shape, ks, st, di, ca)
+    if not direct_layout_supported(tq, tkv, di):
+        return None
+    # slabs of about 1/8 of the axis, whole query tiles each
+    step = max(tq[0], -(-shape[0] // 8 // tq[0]) * tq[0])
+    if shape[0] < 4 * step:
+        return None
+    slabs = []
+    for a in range(0, shape[0], step):
+        b = min(shape[0], a + step)
+        lo, hi = kv_range_for_slab(a, b, shape[0], ks[0], st[0], ca[0])
+        slabs.append((a, b, lo, hi))
+    return dict(shape=shape, ks=ks, st=st, ca=ca, tq=tq, tkv=tkv, slabs=slabs)
+
+
+def _stream_slabs(query, key, value, plan, scale, out, lse, dev):
+    from .sharding import fna_forward_slab
+    shape, slabs = plan["shape"], plan["slabs"]
+    cur = torch.cuda.current_stream(dev)
+    s_in, s_out = _copy_streams(dev)
+    s_in.wait_stream(cur)
+    s_out.wait_stream(cur)
+    for b in range(query.shape[0]):
+        with torch.cuda.stream(s_in):
+            qd, kd, vd = (torch.empty((1,) + tuple(t.shape[1:]), dtype=t.dtype, device=dev)
+                          for t in (query, key, value))
+        od = torch.empty_like(qd)
+        ld = torch.empty(qd.shape[:-1], dtype=torch.float32, device=dev)
+        for t in (qd, kd, vd):
+            t.record_stream(cur)
+        od.record_stream(s_out)
+        ld.record_stream(s_out)
+        have = 0      # key/value frames of this batch entry already on their way to the device
+        for a, e, lo, hi in slabs:
+            with torch.cuda.stream(s_in):
+                if hi > have:
+                    kd[:, have:hi].copy_(key[b:b + 1, have:hi], non_blocking=True)
+                    vd[:, have:hi].copy_(value[b:b + 1, have:hi], non_blocking=True)
+                    have = hi
+                qd[:, a:e].copy_(query[b:b + 1, a:e], non_blocking=True)
+                arrived = s_in.record_event()
+            cur.wait_event(arrived)
+            fna_forward_slab(qd[:, a:e], kd[:, lo:hi], vd[:, lo:hi], shape, a, lo, plan["ks"],
+                             plan["st"], plan["ca"], scale, plan["tq"], plan["tkv"],
+                             out=od[:, a:e], lse=ld[:, a:e])
+            done = cur.record_event()
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(done)
+                out[b:b + 1, a:e].copy_(od[:, a:e], non_blocking=True)
+                lse[b:b + 1, a:e].copy_(ld[:, a:e], non_blocking=True)
+    cur.wait_stream(s_out)
+    return out, lse

@@ -145,19 +145,71 @@ def exchange_halo(k_local: Tensor, v_local: Tensor, plan: HaloPlan, rank: int,
     return k_slab, v_slab, lo
 
 
+def exchange_halo_parts(k_local: Tensor, v_local: Tensor, plan: HaloPlan, rank: int,
+                        group: Optional[dist.ProcessGroup] = None):
+    """Starts the halo exchange and returns without waiting for it: ``(parts, requests, keep)``.
+    `parts` is a list of ``(k_part, v_part, first_frame)`` - contiguous buffers in this rank's
+    own memory holding received frames from `first_frame` on; they are valid once every request
+    in `requests` has been waited for (on CUDA tensors ``wait()`` orders the current stream after
+    the transfer, it does not block the host). `keep` holds the send buffers, which must stay
+    alive until then. Own frames are not copied anywhere."""
+    t0, t1 = plan.slabs[rank]
+    ops, parts, keep = [], [], []
+    for dst, (a, b) in plan.send_list(rank):
+        ks, vs = k_local[:, a - t0:b - t0].contiguous(), v_local[:, a - t0:b - t0].contiguous()
+        keep += [ks, vs]
+        ops.append(dist.P2POp(dist.isend, ks, dst, group))
+        ops.append(dist.P2POp(dist.isend, vs, dst, group))
+    lo, hi = plan.needs[rank]
+    recvs = plan.recv_list(rank)
+    if k_local.shape[0] == 1:
+        # batch 1: a frame range is one contiguous block, so everything before the slab lands in
+        # one buffer and everything after it in another (at most two partial calls later)
+        for first, last in ((lo, t0), (t1, hi)):
+            if last <= first:
+                continue
+            shape = list(k_local.shape)
+            shape[1] = last - first
+            kp = torch.empty(shape, dtype=k_local.dtype, device=k_local.device)
+            vp = torch.empty(shape, dtype=v_local.dtype, device=v_local.device)
+            parts.append((kp, vp, first))
+            for src, (a, b) in recvs:
+                if first <= a and b <= last:
+                    ops.append(dist.P2POp(dist.irecv, kp[:, a - first:b - first], src, group))
+                    ops.append(dist.P2POp(dist.irecv, vp[:, a - first:b - first], src, group))
+    else:
+        for src, (a, b) in recvs:
+            shape = list(k_local.shape)
+            shape[1] = b - a
+            kp = torch.empty(shape, dtype=k_local.dtype, device=k_local.device)
+            vp = torch.empty(shape, dtype=v_local.dtype, device=v_local.device)
+            parts.append((kp, vp, a))
+            ops.append(dist.P2POp(dist.irecv, kp, src, group))
+            ops.append(dist.P2POp(dist.irecv, vp, src, group))
+    reqs = dist.batch_isend_irecv(ops) if ops else []
+    return parts, reqs, keep
+
+
 def fna_forward_slab(q_local: Tensor, k_slab: Tensor, v_slab: Tensor,
                      global_shape: Sequence[int], q_origin0: int, kv_origin0: int,
                      kernel_size: Sequence[int], stride: Sequence[int],
                      is_causal: Sequence[bool], scale: Optional[float] = None,
-                     q_tile_shape=None, kv_tile_shape=None) -> Tuple[Tensor, Tensor]:
+                     q_tile_shape=None, kv_tile_shape=None, clip: bool = False,
+                     permuted: bool = False, out: Optional[Tensor] = None,
+                     lse: Optional[Tensor] = None) -> Tuple[Tensor, Tensor]:
     """Attention for query coordinates ``[q_origin0, q_origin0 + q_local.shape[1])`` of axis 0
     against a key/value slab that starts at coordinate ``kv_origin0`` (no communication here).
-    permute -> `b200na_fna_forward_sharded` -> unpermute."""
+    One launch on the slabs as they lie (`b200na_na_forward_direct_sharded`); tile shapes a
+    tensor-map box cannot express, or ``permuted=True``, take permute ->
+    `b200na_fna_forward_sharded` -> unpermute. ``clip=True``: partial attention over the keys the
+    slab holds (windows cut to it; a query with no key there gets O = 0, LSE = -inf), to be
+    combined with the other parts by `merge_attentions`. `out` / `lse` (contiguous, the slab's
+    shape) receive the result when given (direct launch only)."""
     import ctypes
 
     from . import _lib
     from .functional import (_DTYPE_CODE, _ptr, _stream, choose_tile_shapes,
-                             token_permute_operation, token_unpermute_operation)
+                             direct_layout_supported)
 
     nd = len(global_shape)
     global_shape = tuple(int(x) for x in global_shape)
@@ -168,6 +220,51 @@ def fna_forward_slab(q_local: Tensor, k_slab: Tensor, v_slab: Tensor,
         q_tile_shape, kv_tile_shape = choose_tile_shapes(
             local, tuple(int(k) for k in kernel_size), tuple(int(s) for s in stride), (1,) * nd,
             tuple(bool(c) for c in is_causal))
+    dil = (1,) * nd
+    if permuted or not direct_layout_supported(q_tile_shape, kv_tile_shape, dil):
+        if clip:
+            raise NotImplementedError("partial (clipped) slab attention needs tile shapes the "
+                                      "kernel can gather from the slabs directly")
+        return _fna_forward_slab_permuted(q_local, k_slab, v_slab, global_shape, q_origin0,
+                                          kv_origin0, kernel_size, stride, is_causal, scale,
+                                          q_tile_shape, kv_tile_shape)
+    q_local, k_slab, v_slab = q_local.contiguous(), k_slab.contiguous(), v_slab.contiguous()
+    B, Hq, D = q_local.shape[0], q_local.shape[-2], q_local.shape[-1]
+    Hkv = k_slab.shape[-2]
+    if out is None:
+        out = torch.empty_like(q_local)
+    if lse is None:
+        lse = torch.empty(q_local.shape[:-1], dtype=torch.float32, device=q_local.device)
+    if not (out.is_contiguous() and lse.is_contiguous() and out.shape == q_local.shape):
+        raise ValueError("out / lse must be contiguous tensors of the query slab's shape")
+    scale = float(scale) if scale else float(D) ** -0.5
+    q_origin = (int(q_origin0),) + (0,) * (nd - 1)
+    kv_origin = (int(kv_origin0),) + (0,) * (nd - 1)
+    with torch.cuda.device(q_local.device):
+        _lib.check(_lib.lib.b200na_na_forward_direct_sharded(
+            _ptr(q_local), _ptr(k_slab), _ptr(v_slab), _ptr(out), _ptr(lse), nd,
+            _lib.ints(global_shape), _lib.ints(kernel_size), _lib.ints(stride),
+            _lib.ints([1 if c else 0 for c in is_causal]), _lib.ints(q_tile_shape),
+            _lib.ints(kv_tile_shape), _lib.ints(q_origin), _lib.ints(q_local.shape[1:1 + nd]),
+            _lib.ints(kv_origin), _lib.ints(k_slab.shape[1:1 + nd]), 1 if clip else 0, B, Hq, Hkv,
+            D, _DTYPE_CODE[q_local.dtype], ctypes.c_float(scale), _stream(q_local)),
+            "b200na_na_forward_direct_sharded")
+    return out, lse
+
+
+def _fna_forward_slab_permuted(q_local: Tensor, k_slab: Tensor, v_slab: Tensor,
+                               global_shape, q_origin0: int, kv_origin0: int, kernel_size,
+                               stride, is_causal, scale, q_tile_shape, kv_tile_shape
+                               ) -> Tuple[Tensor, Tensor]:
+    """The slab through token-permuted copies: permute -> `b200na_fna_forward_sharded` ->
+    unpermute."""
+    import ctypes
+
+    from . import _lib
+    from .functional import (_DTYPE_CODE, _ptr, _stream, token_permute_operation,
+                             token_unpermute_operation)
+
+    nd = len(global_shape)
     dil = (1,) * nd
     q_perm, q_local_shape, q_shape = token_permute_operation(q_local, q_tile_shape, dil)
     k_perm, _, kv_shape = token_permute_operation(k_slab, kv_tile_shape, dil)
@@ -203,16 +300,39 @@ def na_forward_spatial_shard(q_local: Tensor, k_local: Tensor, v_local: Tensor,
                              scale: Optional[float] = None, rank: Optional[int] = None,
                              world: Optional[int] = None,
                              group: Optional[dist.ProcessGroup] = None,
-                             q_tile_shape=None, kv_tile_shape=None) -> Tuple[Tensor, Tensor]:
-    """Neighborhood attention forward for this rank's slab of axis 0 (dilation 1): halo exchange,
-    then the slab kernel. Inputs are ``[B, t1 - t0, *rest, H, D]`` (fp16/bf16, head dim 64 or
-    128); returns the rank's slab of the output and logsumexp, identical to the same rows of the
-    unsharded result."""
+                             q_tile_shape=None, kv_tile_shape=None,
+                             overlap: bool = True) -> Tuple[Tensor, Tensor]:
+    """Neighborhood attention forward for this rank's slab of axis 0 (dilation 1). Inputs are
+    ``[B, t1 - t0, *rest, H, D]`` (fp16/bf16, head dim 64 or 128); returns the rank's slab of the
+    output and logsumexp, equal to the same rows of the unsharded result up to rounding.
+
+    ``overlap=True`` (default): the halo transfers are started first, the rank then attends its
+    OWN key/value frames (windows cut to the slab) while the frames of the other ranks are in
+    flight, attends each received block once it has landed, and folds the partial results
+    together with the LSE merge - the use the reference's `merge_attentions` hints at
+    (src/natten/attn_merge.py:199-204). ``overlap=False``: exchange, then one kernel over the
+    assembled key/value slab."""
+    from .functional import merge_attentions
+
     rank = dist.get_rank(group) if rank is None else rank
     world = dist.get_world_size(group) if world is None else world
     plan = make_halo_plan(int(global_shape[0]), world, int(kernel_size[0]), int(stride[0]),
                           bool(is_causal[0]))
     t0, _ = plan.slabs[rank]
-    k_slab, v_slab, lo = exchange_halo(k_local, v_local, plan, rank, group)
-    return fna_forward_slab(q_local, k_slab, v_slab, global_shape, t0, lo, kernel_size, stride,
-                            is_causal, scale, q_tile_shape, kv_tile_shape)
+    if not overlap or not plan.recv_list(rank):
+        k_slab, v_slab, lo = exchange_halo(k_local, v_local, plan, rank, group)
+        return fna_forward_slab(q_local, k_slab, v_slab, global_shape, t0, lo, kernel_size, stride,
+                                is_causal, scale, q_tile_shape, kv_tile_shape)
+    nd = len(global_shape)
+    parts, reqs, keep = exchange_halo_parts(k_local, v_local, plan, rank, group)
+    out, lse = fna_forward_slab(q_local, k_local, v_local, global_shape, t0, t0, kernel_size,
+                                stride, is_causal, scale, q_tile_shape, kv_tile_shape, clip=True)
+    for r in reqs:
+        r.wait()      # orders the current stream after the transfers
+    flat_o, flat_l = out.flatten(1, nd), lse.flatten(1, nd)
+    for kp, vp, first in parts:
+        o2, l2 = fna_forward_slab(q_local, kp, vp, global_shape, t0, first, kernel_size, stride,
+                                  is_causal, scale, q_tile_shape, kv_tile_shape, clip=True)
+        flat_o, flat_l = merge_attentions([flat_o, o2.flatten(1, nd)], [flat_l, l2.flatten(1, nd)])
+    del keep
+    return flat_o.reshape(out.shape), flat_l.reshape(lse.shape)

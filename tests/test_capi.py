@@ -89,7 +89,11 @@ def test_merge_and_simt_reject_bad_arguments():
     one = ctypes.c_void_p(16)
     assert L.lib.b200na_merge(None, one, one, one, one, one, 4, 8, L.F32, None) == L.ERR_INVALID_ARGUMENT
     assert L.lib.b200na_merge(one, one, one, one, one, one, 4, 8, 7, None) == L.ERR_INVALID_ARGUMENT
-    assert L.lib.b200na_merge(one, one, one, one, one, one, 0, 8, L.F32, None) == L.OK
+    two = ctypes.c_void_p(32)
+    assert L.lib.b200na_merge(one, one, one, one, one, two, 0, 8, L.F32, None) == L.OK
+    # the merged LSE must be a buffer of its own (the merged output may overwrite an input)
+    assert L.lib.b200na_merge(one, one, one, two, one, one, 4, 8, L.F32, None) == L.ERR_INVALID_ARGUMENT
+    assert L.lib.b200na_merge(one, one, one, two, one, two, 4, 8, L.F32, None) == L.ERR_INVALID_ARGUMENT
     f = L.lib.b200na_na_forward_simt
     assert f(one, one, one, one, None, 1, L.ints([8]), L.ints([9]), None, None, None, 1, 1, 1, 8,
              L.F32, 1.0, None, None, 0, None) == L.ERR_INVALID_ARGUMENT

@@ -2,6 +2,8 @@
 (tests/golden/) and the CPU oracle.
 
 Tolerances (max-abs, on output and logsumexp): 1e-4 for fp32 operands, 2e-2 for fp16/bf16."""
+import ctypes
+
 import numpy as np
 import pytest
 import torch
@@ -178,6 +180,30 @@ def test_merge_matches_reference():
         assert np.abs(l3.cpu().numpy() - z["merge/merge3/lse"]).max() <= 4e-6
 
 
+def test_merge_in_place_and_with_an_empty_input():
+    """The merged output may overwrite one of its inputs (each element is read before it is
+    written); an input without keys (LSE = -inf, O = 0) leaves the other one unchanged."""
+    torch.manual_seed(4)
+    o0, o1 = (torch.randn(3, 50, 2, 256, device="cuda") for _ in range(2))   # fp32, D = 256
+    l0, l1 = (torch.randn(3, 50, 2, device="cuda") for _ in range(2))
+    want_o, want_l = nb.merge_attentions([o0, o1], [l0, l1])
+    got_l = torch.empty_like(l0)
+    dst = o0.clone()
+    L.check(L.lib.b200na_merge(ctypes.c_void_p(dst.data_ptr()), ctypes.c_void_p(l0.data_ptr()),
+                               ctypes.c_void_p(o1.data_ptr()), ctypes.c_void_p(l1.data_ptr()),
+                               ctypes.c_void_p(dst.data_ptr()), ctypes.c_void_p(got_l.data_ptr()),
+                               l0.numel(), 256, L.F32,
+                               ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)),
+            "b200na_merge")
+    assert torch.equal(dst, want_o) and torch.equal(got_l, want_l)
+    empty_l = torch.full_like(l1, float("-inf"))
+    for order in (0, 1):
+        outs = [o0, torch.zeros_like(o1)][::1 if order == 0 else -1]
+        lses = [l0, empty_l][::1 if order == 0 else -1]
+        m_o, m_l = nb.merge_attentions(outs, lses)
+        assert torch.equal(m_o, o0) and torch.equal(m_l, l0)
+
+
 def test_merge_equals_attention_over_concatenated_keys():
     """The property the reference's own merge test uses (tests/test_attn_merge.py:92-114)."""
     torch.manual_seed(2)
@@ -262,23 +288,42 @@ def test_tensor_core_kernel_agrees_with_cuda_core_kernel_on_every_row():
     ((4096,), (512,), (64,), (False,), 4),
 ])
 def test_spatial_slabs_reproduce_the_unsharded_result(shape, ks, st, ca, world):
-    """Every rank's slab computed with b200na_fna_forward_sharded (ranks emulated one after the
-    other on this GPU; the halo is sliced from the global tensors) equals the unsharded rows."""
+    """Every rank's slab (ranks emulated one after the other on this GPU; the halo is sliced from
+    the global tensors) equals the unsharded rows: one launch on the slabs as they lie, the same
+    through token-permuted copies, and the overlapped form - partial attention over the rank's
+    own frames and over each halo block (windows cut to the block), folded with the LSE merge."""
     from natten_b200 import sharding
     torch.manual_seed(11)
     q, k, v = (torch.randn(1, *shape, 2, 128, device="cuda").bfloat16() for _ in range(3))
     fn = _na_fn(len(shape))
+    nd = len(shape)
     full_o, full_l = fn(q, k, v, ks, st, 1, ca, return_lse=True)
     plan = sharding.make_halo_plan(shape[0], world, ks[0], st[0], ca[0])
     for r in range(world):
         t0, t1 = plan.slabs[r]
         lo, hi = plan.needs[r]
-        o, l = sharding.fna_forward_slab(q[:, t0:t1].contiguous(), k[:, lo:hi].contiguous(),
-                                         v[:, lo:hi].contiguous(), shape, t0, lo, ks, st, ca)
+        ql = q[:, t0:t1].contiguous()
+        for permuted in (False, True):
+            o, l = sharding.fna_forward_slab(ql, k[:, lo:hi].contiguous(), v[:, lo:hi].contiguous(),
+                                             shape, t0, lo, ks, st, ca, permuted=permuted)
+            assert L.device_status() == 0
+            # slab and unsharded call tile the keys differently: equal up to bf16 rounding of O
+            assert (o.float() - full_o[:, t0:t1].float()).abs().max().item() <= 1e-2, (r, permuted)
+            assert (l - full_l[:, t0:t1]).abs().max().item() <= 2e-3, (r, permuted)
+        # own frames first, then the frames before and after the slab, merged
+        o, l = sharding.fna_forward_slab(ql, k[:, t0:t1].contiguous(), v[:, t0:t1].contiguous(),
+                                         shape, t0, t0, ks, st, ca, clip=True)
+        o, l = o.flatten(1, nd), l.flatten(1, nd)
+        for a, b in ((lo, t0), (t1, hi)):
+            if b <= a:
+                continue
+            o2, l2 = sharding.fna_forward_slab(ql, k[:, a:b].contiguous(), v[:, a:b].contiguous(),
+                                               shape, t0, a, ks, st, ca, clip=True)
+            o, l = nb.merge_attentions([o, o2.flatten(1, nd)], [l, l2.flatten(1, nd)])
         assert L.device_status() == 0
-        # slab and unsharded call tile the keys differently: equal up to bf16 rounding of O
-        assert (o.float() - full_o[:, t0:t1].float()).abs().max().item() <= 1e-2, r
-        assert (l - full_l[:, t0:t1]).abs().max().item() <= 2e-3, r
+        assert torch.isfinite(l).all()
+        assert (o.float() - full_o[:, t0:t1].flatten(1, nd).float()).abs().max().item() <= 1.6e-2, r
+        assert (l - full_l[:, t0:t1].flatten(1, nd)).abs().max().item() <= 2e-3, r
     # a slab that does not hold every needed key is refused, not silently wrong
     t0, t1 = plan.slabs[world - 1]
     lo, hi = plan.needs[world - 1]

@@ -102,6 +102,27 @@ def test_host_operand_entry_point_matches_the_device_call():
         nb.na_forward_from_host(q.cuda(), k, v, **args)
 
 
+@pytest.mark.gpu
+def test_host_operand_entry_point_streams_slabs_of_the_outermost_axis():
+    """Undilated 16-bit problems without extra tokens go through the GPU slab by slab along axis 0
+    (the copies of one slab overlap the kernel of another); same result as the device call."""
+    torch.manual_seed(10)
+    for shape, ks, st, ca in [((64, 24), (9, 7), (1, 2), (True, False)),
+                              ((48, 8, 8), (5, 4, 4), (1, 2, 2), (False, False, False)),
+                              ((4096,), (300,), (1,), (False,))]:
+        q, k, v = (torch.randn(2, *shape, 2, 64).half().pin_memory() for _ in range(3))
+        from natten_b200 import host_io
+        assert host_io._slab_plan(q, k, ks, st, 1, ca) is not None
+        fn = {1: nb.na1d, 2: nb.na2d, 3: nb.na3d}[len(shape)]
+        want_o, want_l = fn(q.cuda(), k.cuda(), v.cuda(), kernel_size=ks, stride=st, is_causal=ca,
+                            return_lse=True)
+        out, lse = nb.na_forward_from_host(q, k, v, ks, st, 1, ca)
+        torch.cuda.current_stream().synchronize()
+        assert L.device_status() == 0
+        assert (out.float() - want_o.cpu().float()).abs().max().item() <= 1e-2
+        assert (lse - want_l.cpu()).abs().max().item() <= 2e-3
+
+
 def test_reference_backend_names_and_config_listing():
     q = torch.randn(1, 20, 24, 2, 64, device="cuda").half()
     a = nb.na2d(q, q, q, 5, backend="blackwell-fna")          # the reference's name is an alias
