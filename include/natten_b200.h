@@ -2,9 +2,20 @@
  * natten_b200 — C ABI of the B200 (sm_100a) neighborhood-attention forward path.
  *
  * Every entry point takes plain device pointers, sizes and a CUDA stream handle, launches its
- * kernels asynchronously on that stream, never allocates or frees device memory, never
- * synchronises the stream, and returns B200NA_OK or a negative error code (text via
- * b200na_strerror). The caller owns every buffer, including scratch.
+ * kernels asynchronously on that stream and returns B200NA_OK or a negative error code (text via
+ * b200na_strerror). The caller owns every buffer, including scratch. After the first attention
+ * call on a device the library neither allocates nor frees device memory and never synchronises
+ * a stream; that first call does a one-time set-up of the device (kernel attributes, two small
+ * synchronising cudaMemset calls on the library's own status word and work counters) and should
+ * be made before any stream capture.
+ *
+ * Streams and CUDA graphs: the attention kernels hand out their work items through a pair of
+ * device counters. Launches on one stream share that stream's pair (they run one after the
+ * other); a launch recorded under stream capture gets a pair of its own, from a pool of 3072
+ * handed out in turn, and keeps it for every replay. Any number of streams and graph replays may
+ * therefore run next to each other; the limits are 1024 distinct eager streams per device and
+ * 3072 captured attention launches alive at the same time (beyond them pairs are shared again,
+ * and two kernels that share a pair while both are in flight compute wrong results).
  *
  * Tensor layouts are the reference's: heads-last and contiguous.
  *   token layout tensors   [B, X0(, X1(, X2)), H, D]
@@ -237,7 +248,11 @@ B200NA_API int b200na_na_forward(const void* q, const void* k, const void* v, vo
  *     problem exceeds B200NA_STATIC_WORKSPACE_BYTES (use b200na_na_forward then);
  *   - calls no cudaMalloc / cudaFree and no allocating library routine;
  *   - the first call on each device looks up the array's device address (and does the library's
- *     usual one-time per-device set-up); make that first call outside any stream capture;
+ *     usual one-time per-device set-up); make that first call outside any stream capture. With
+ *     CUDA's lazy module loading that first call is also the moment the driver brings the
+ *     module holding the array (and each kernel's code, on its first launch) onto the device: a
+ *     caller about to hand its memory budget away should make one small call per device and
+ *     dtype at start-up, before it does - later calls then change nothing in device memory;
  *   - all calls on a device share the one array, which keeps whatever the previous call left in
  *     it (nothing in it needs clearing between calls); two calls that can overlap on the GPU —
  *     different streams, or the same stream from unsynchronised threads — race on it and corrupt
@@ -334,9 +349,12 @@ B200NA_API int b200na_merge(const void* o0, const float* l0, const void* o1, con
                  float* l, int64_t rows, int D, int dtype, b200na_stream_t stream);
 
 /*
- * Device-side status of the tensor-core kernels on the current device: 0 if no bounded wait has
- * expired since the last call, else a non-zero diagnostic word (role and barrier that gave up).
- * Synchronises the device; resets the word. The reference has no counterpart: its kernels spin
+ * Device-side status of the tensor-core kernels on the current device. Returns B200NA_OK with
+ * *status == 0 if no bounded wait has expired since the last call; otherwise returns
+ * B200NA_ERR_KERNEL_TIMEOUT and stores a non-zero diagnostic word (role << 8 | barrier that gave
+ * up): the results of the launches since the last call are not to be used. Synchronises the
+ * device (so it is a check for tests and debugging, not for every step) and resets the word; the
+ * context stays usable. The reference has no counterpart: its kernels spin
  * without a bound (csrc/include/natten/cuda/fna_blackwell/kernel/
  * sm100_fna_fwd_kernel_tma_warpspecialized.hpp).
  */

@@ -137,10 +137,29 @@ def check(code: int, where: str, kernel_launches: int = 1) -> None:
     if code != OK:
         raise NattenB200Error(code, where, strerror(code))
     launches += kernel_launches
+    if CHECK_STATUS and kernel_launches > 0:
+        raise_on_kernel_timeout(where)
 
 
 def device_status() -> int:
-    """Synchronises the current device and returns (and clears) the kernels' status word."""
+    """Synchronises the current device and returns (and clears) the kernels' status word: 0, or
+    (role << 8 | barrier) of the first bounded wait that expired since the last call."""
     st = ctypes.c_int(0)
-    check(lib.b200na_device_status(ctypes.byref(st)), "b200na_device_status", kernel_launches=0)
+    code = lib.b200na_device_status(ctypes.byref(st))
+    if code not in (OK, ERR_KERNEL_TIMEOUT):
+        check(code, "b200na_device_status", kernel_launches=0)
     return st.value
+
+
+# NATTEN_B200_CHECK_STATUS=1: every operator call is followed by a device synchronisation and a
+# look at the status word, and raises if a bounded wait expired inside a kernel (debugging aid;
+# it serialises host and device).
+CHECK_STATUS = os.environ.get("NATTEN_B200_CHECK_STATUS", "0") not in ("", "0")
+
+
+def raise_on_kernel_timeout(where: str) -> None:
+    if CHECK_STATUS:
+        word = device_status()
+        if word != 0:
+            raise NattenB200Error(ERR_KERNEL_TIMEOUT, where,
+                                  f"{strerror(ERR_KERNEL_TIMEOUT)} (status word {word:#x})")

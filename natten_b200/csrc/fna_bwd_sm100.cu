@@ -1234,7 +1234,7 @@ extern "C" B200NA_API int b200na_na_backward_direct(
     p.total_work = n_rtiles * p.row_heads * B * p.G;
     p.out0 = dense ? d_add_k : (key_rows ? dk : dq);
     p.out1 = dense ? d_add_v : (key_rows ? dv : nullptr);
-    if ((rc = fna_work_counters(&p.work)) != B200NA_OK) return rc;
+    if ((rc = fna_work_counters(&p.work, stream)) != B200NA_OK) return rc;
     p.trace = pass == g_bwd_trace_pass ? g_bwd_trace : nullptr;
     const void* fn = bwd_kernel_variant(D, dtype == B200NA_BF16, kernel_ndim, key_rows);
     const int smem_bytes = key_rows ? (D == 128 ? Smem<128, false>::kBytes : Smem<64, false>::kBytes)

@@ -12,7 +12,12 @@
 
 namespace b200na {
 
+#ifdef B200NA_TEST_HOOKS
+// test-hook build: waits give up after about a millisecond, so that a test can make one expire
+constexpr long long kWaitLimitCycles = 2000000ll;
+#else
 constexpr long long kWaitLimitCycles = 4000000000ll;  // ~2 s at 2 GHz
+#endif
 
 // Operand element types of the kernel templates.
 enum : int { kTyF16 = 0, kTyBf16 = 1, kTyE4m3 = 2, kTyE5m2 = 3 };

@@ -17,10 +17,11 @@ int fna_make_tensor_map_direct(CUtensorMap* tm, const void* ptr, int dtype, int 
 // device status word that bounded waits report into.
 int fna_device_info(int* sms, int** status_ptr);
 
-// A zeroed pair of device counters {next work item, CTAs finished} for one launch of a persistent
-// kernel that hands out its items dynamically; the kernel's last CTA must zero the pair again.
-// Pairs are handed out in turn from a pool of 64 per device.
-int fna_work_counters(unsigned long long** pair);
+// A zeroed pair of device counters {next work item, CTAs finished} for one launch on `stream` of a
+// persistent kernel that hands out its items dynamically; the kernel's last CTA must zero the
+// pair again. Launches on one stream share that stream's pair (they cannot overlap); a launch
+// under stream capture gets a pair of its own from a pool of 3072 that is handed out in turn.
+int fna_work_counters(unsigned long long** pair, cudaStream_t stream);
 
 // delta[row] = sum_d o[row, d] * d_out[row, d] (fp32), rows of D elements of `dtype`.
 int launch_delta(const void* o, const void* d_out, float* delta, int64_t rows, int D, int dtype,

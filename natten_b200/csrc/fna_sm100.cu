@@ -24,6 +24,7 @@
 
 #include <atomic>
 #include <mutex>
+#include <unordered_map>
 #include <type_traits>
 
 #include "common.cuh"
@@ -56,9 +57,14 @@ enum : int { kStSQFull = 1, kStSFull, kStPFull, kStOFull, kStOEmpty, kStKVFull, 
              kStQEmpty, kStSmemAlign, kStDescFull, kStDescEmpty, kStRecFull };
 
 __device__ int g_status_word;
-// Work counters of the dynamic item scheduler: [slot][0] = next item, [slot][1] = CTAs finished.
-// A launch takes the next slot in turn; the last CTA to finish zeroes its pair again.
-constexpr int kCounterSlots = 64;
+// Work counters of the dynamic item scheduler: [slot][0] = next item, [slot][1] = CTAs finished;
+// the last CTA of a launch to finish zeroes its pair again. Two kernels in flight must never
+// share a pair, so pairs belong to streams: launches on one stream run one after the other and
+// reuse that stream's pair ([0, kStreamSlots)). A launch that is being captured into a CUDA graph
+// may later be replayed on any stream, next to anything: it takes a pair of its own from a
+// separate pool that is handed out in turn ([kStreamSlots, kCounterSlots)).
+constexpr int kStreamSlots = 1024;
+constexpr int kCounterSlots = 4096;
 __device__ unsigned long long g_work_counters[kCounterSlots][2];
 
 struct FnaParams {
@@ -100,6 +106,9 @@ struct FnaParams {
   unsigned long long* work;  // [0] next work item, [1] CTAs done (see g_work_counters)
 #ifdef B200NA_PROFILE
   long long* prof;  // [grid][4 roles][8] cycle counters (instrumented builds only)
+#endif
+#ifdef B200NA_TEST_HOOKS
+  int test_withhold;  // test-hook build: CTA 0 keeps back the record of its n-th tile (0 = off)
 #endif
 };
 
@@ -976,6 +985,9 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             // kTileRecs, so the entry it replaces is long consumed.
             if (kv == 0) {
               tile_rec[tseq % kTileRecs] = rec;
+#ifdef B200NA_TEST_HOOKS
+              if (!(blockIdx.x == 0 && p.test_withhold != 0 && (int)tseq + 1 == p.test_withhold))
+#endif
               ptx::mbar_arrive(bars.rec_full + tseq % kTileRecs);
               ++tseq;
             }
@@ -1160,7 +1172,9 @@ struct DeviceState {
   int sms = 0;
   int* status_ptr = nullptr;
   unsigned long long* counters = nullptr;  // g_work_counters on this device
-  std::atomic<unsigned> next_slot{0};      // launches take the counter pairs in turn
+  std::mutex slot_mu;
+  std::unordered_map<cudaStream_t, int> stream_slot;   // counter pair of each stream seen so far
+  unsigned next_graph_slot = 0;                        // captured launches take theirs in turn
 };
 
 // Per-device one-time setup: capability check, opt-in shared memory, status word address.
@@ -1206,6 +1220,9 @@ int device_state(DeviceState** out) {
 #ifdef B200NA_PROFILE
 long long* g_prof_buffer = nullptr;
 #endif
+#ifdef B200NA_TEST_HOOKS
+int g_test_withhold = 0;
+#endif
 
 int launch_fna(const void* q, const void* k, const void* v, FnaParams& p, int D, int dtype,
                cudaStream_t stream, const void* add_k = nullptr, const void* add_v = nullptr) {
@@ -1240,11 +1257,12 @@ int launch_fna(const void* q, const void* k, const void* v, FnaParams& p, int D,
   }
   p.extra_tiles = (p.n_extra + kKVTile - 1) / kKVTile;
   p.status = st->status_ptr;
-  // A launch captured into a CUDA graph keeps its pair for every replay; replays of one graph are
-  // ordered, and 64 other launches lie between two uses of a pair otherwise.
-  if ((rc = fna_work_counters(&p.work)) != B200NA_OK) return rc;
+  if ((rc = fna_work_counters(&p.work, stream)) != B200NA_OK) return rc;
 #ifdef B200NA_PROFILE
   p.prof = g_prof_buffer;
+#endif
+#ifdef B200NA_TEST_HOOKS
+  p.test_withhold = g_test_withhold;
 #endif
   p.total_work = (long long)p.n_qtiles * p.Hq * p.Bp;
   if (p.total_work == 0) return B200NA_OK;
@@ -1270,11 +1288,28 @@ int fna_make_tensor_map_direct(CUtensorMap* tm, const void* ptr, int dtype, int 
                                int H, int D, const int* tile, const int* dil) {
   return make_tensor_map_direct(tm, ptr, dtype, B, X, H, D, tile, dil);
 }
-int fna_work_counters(unsigned long long** pair) {
+int fna_work_counters(unsigned long long** pair, cudaStream_t stream) {
   DeviceState* st = nullptr;
   const int rc = device_state(&st);
   if (rc != B200NA_OK) return rc;
-  *pair = st->counters + 2 * (st->next_slot.fetch_add(1) % kCounterSlots);
+  cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+  B200NA_CUDA_TRY(cudaStreamIsCapturing(stream, &capturing));
+  std::lock_guard<std::mutex> lk(st->slot_mu);
+  int slot;
+  if (capturing != cudaStreamCaptureStatusNone) {
+    // a graph node keeps its pair for every replay; nodes get distinct pairs until the pool of
+    // kCounterSlots - kStreamSlots has gone round once
+    slot = kStreamSlots + (int)(st->next_graph_slot++ % (unsigned)(kCounterSlots - kStreamSlots));
+  } else {
+    auto it = st->stream_slot.find(stream);
+    if (it == st->stream_slot.end()) {
+      // more streams than pairs: later streams share by position (not expected in practice)
+      const int fresh = (int)(st->stream_slot.size() % (size_t)kStreamSlots);
+      it = st->stream_slot.emplace(stream, fresh).first;
+    }
+    slot = it->second;
+  }
+  *pair = st->counters + 2 * slot;
   return B200NA_OK;
 }
 int fna_device_info(int* sms, int** status_ptr) {
@@ -1594,6 +1629,15 @@ extern "C" B200NA_API void b200na_debug_set_prof(void* buf) {
 }
 #endif
 
+#ifdef B200NA_TEST_HOOKS
+// Test-hook build only (never the product library): from now on the load warp of CTA 0 keeps
+// back the record of its n-th key/value tile, so that the wait for it expires; 0 switches it off.
+extern "C" B200NA_API int b200na_test_withhold_record(int n) {
+  b200na::g_test_withhold = n;
+  return B200NA_OK;
+}
+#endif
+
 extern "C" B200NA_API int b200na_device_status(int* status) {
   using namespace b200na;
   if (!status) return B200NA_ERR_INVALID_ARGUMENT;
@@ -1602,6 +1646,9 @@ extern "C" B200NA_API int b200na_device_status(int* status) {
   if (rc != B200NA_OK) return rc;
   B200NA_CUDA_TRY(cudaDeviceSynchronize());
   B200NA_CUDA_TRY(cudaMemcpy(status, st->status_ptr, sizeof(int), cudaMemcpyDeviceToHost));
-  if (*status != 0) B200NA_CUDA_TRY(cudaMemset(st->status_ptr, 0, sizeof(int)));
+  if (*status != 0) {
+    B200NA_CUDA_TRY(cudaMemset(st->status_ptr, 0, sizeof(int)));
+    return B200NA_ERR_KERNEL_TIMEOUT;
+  }
   return B200NA_OK;
 }

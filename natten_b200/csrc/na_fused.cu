@@ -35,12 +35,21 @@ int make_plan(FusedPlan& pl, int ndim, const int* shape, const int* dilation, co
     const int rk = ((shape[a] + kv_tile[a] - 1) / kv_tile[a] + d - 1) / d;
     pl.q_shape[a] = rq * q_tile[a];
     pl.kv_shape[a] = rk * kv_tile[a];
+    if ((int64_t)pl.G * d > (1 << 20) || pl.sq > ((int64_t)1 << 40) / pl.q_shape[a] ||
+        pl.skv > ((int64_t)1 << 40) / pl.kv_shape[a])
+      return B200NA_ERR_UNSUPPORTED;
     pl.G *= d;
     pl.sq *= pl.q_shape[a];
     pl.skv *= pl.kv_shape[a];
     ident = ident && d == 1 && pl.q_shape[a] == shape[a] && pl.kv_shape[a] == shape[a];
   }
   pl.identity = ident;
+  // sizes far beyond any device's memory are refused before the byte sums below could wrap
+  const int64_t kMaxElems = (int64_t)1 << 46;
+  if ((int64_t)B * pl.G > kMaxElems / pl.sq || (int64_t)B * pl.G > kMaxElems / pl.skv ||
+      (int64_t)B * pl.G * pl.sq > kMaxElems / ((int64_t)Hq * D) ||
+      (int64_t)B * pl.G * pl.skv > kMaxElems / ((int64_t)Hkv * D))
+    return B200NA_ERR_UNSUPPORTED;
   const int64_t bp = (int64_t)B * pl.G;
   int64_t off = 0;
   pl.off_q = off; off += ident ? 0 : align_up(bp * pl.sq * Hq * D * elem_bytes);

@@ -21,12 +21,28 @@ import natten_b200._lib as L
 pytestmark = pytest.mark.gpu
 
 
-def _call_static(q, k, v, shape, ks, st, di, ca, tq, tkv, scale):
+def _call_static(q, k, v, shape, ks, st, di, ca, tq, tkv, scale, watch_memory=False):
     """Straight through ctypes: outputs are the only tensors created here, the entry itself gets
-    nothing but pointers to inputs and outputs."""
+    nothing but pointers to inputs and outputs. With `watch_memory` the driver's free-byte count
+    and torch's allocator statistics are read right before and right after the call (and again
+    once the kernels have run) and must not have moved."""
     out = torch.empty_like(q)
     lse = torch.empty(q.shape[:-1], dtype=torch.float32, device=q.device)
     torch.cuda.synchronize()
+    before = (torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated(),
+              torch.cuda.memory_reserved())
+    rc = _static_entry(q, k, v, out, lse, shape, ks, st, di, ca, tq, tkv, scale)
+    if watch_memory:
+        after_call = (torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated(),
+                      torch.cuda.memory_reserved())
+        torch.cuda.synchronize()
+        after_run = (torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated(),
+                     torch.cuda.memory_reserved())
+        assert after_call == before and after_run == before, (before, after_call, after_run)
+    return rc, out, lse
+
+
+def _static_entry(q, k, v, out, lse, shape, ks, st, di, ca, tq, tkv, scale):
     rc = L.lib.b200na_na_forward_static(
         ctypes.c_void_p(q.data_ptr()), ctypes.c_void_p(k.data_ptr()), ctypes.c_void_p(v.data_ptr()),
         ctypes.c_void_p(out.data_ptr()), ctypes.c_void_p(lse.data_ptr()), len(shape),
@@ -34,7 +50,7 @@ def _call_static(q, k, v, shape, ks, st, di, ca, tq, tkv, scale):
         L.ints(tq), L.ints(tkv), q.shape[0], q.shape[-2], k.shape[-2], q.shape[-1],
         {torch.float16: L.F16, torch.bfloat16: L.BF16}[q.dtype], ctypes.c_float(scale),
         ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
-    return rc, out, lse
+    return rc
 
 
 def test_static_workspace_entry_matches_the_workspace_entry_twice_in_a_row():
@@ -51,7 +67,15 @@ def test_static_workspace_entry_matches_the_workspace_entry_twice_in_a_row():
         assert 0 < need <= L.STATIC_WORKSPACE_BYTES
         want_o, want_l = nb.na_forward_fused(q, k, v, ks, st, di, ca, q_tile_shape=tq,
                                              kv_tile_shape=tkv)
-        rc, out, lse = _call_static(q, k, v, shape, ks, st, di, ca, tq, tkv, D ** -0.5)
+        # first call for this dtype / head dim: the driver may still load kernel code now
+        rc, _, _ = _call_static(q, k, v, shape, ks, st, di, ca, tq, tkv, D ** -0.5)
+        assert rc == L.OK, L.strerror(rc)
+        torch.cuda.synchronize()
+        # from here on the entry must leave device memory exactly as it finds it: neither the
+        # driver's free-byte count nor torch's allocator may move across the call itself
+        # (_call_static creates the two output tensors before it takes its readings)
+        rc, out, lse = _call_static(q, k, v, shape, ks, st, di, ca, tq, tkv, D ** -0.5,
+                                    watch_memory=True)
         assert rc == L.OK, L.strerror(rc)
         assert L.device_status() == 0
         # same kernels on the same data: bit-identical, well inside the 2e-2 the other tests allow
