@@ -429,12 +429,21 @@ def spatial_subrecord(cfg, world, rank, dev, barrier, steps):
     dtype = {"bf16": torch.bfloat16, "fp16": torch.float16}[dt]
     plan = sharding.make_halo_plan(shape[0], world, ks[0], st[0], ca[0])
     t0, t1 = plan.slabs[rank]
-    g = torch.Generator(device=dev).manual_seed(2000 + rank)
-    q, k, v = (torch.randn((B, t1 - t0, *shape[1:], H, D), generator=g, device=dev,
-                           dtype=torch.float32).to(dtype) for _ in range(3))
+    def frames(which, a, b):
+        # frame t of tensor `which` is a function of (which, t) alone, so a rank can rebuild the
+        # frames its neighbours own and check what the exchange delivered
+        out = []
+        for t in range(a, b):
+            g = torch.Generator(device=dev).manual_seed(5000 + 100 * which + t)
+            out.append(torch.randn((B, 1, *shape[1:], H, D), generator=g, device=dev,
+                                   dtype=torch.float32).to(dtype))
+        return torch.cat(out, dim=1)
+
+    q, k, v = (frames(i, t0, t1) for i in range(3))
 
     def run():
-        return sharding.na_forward_spatial_shard(q, k, v, shape, ks, st, ca, rank=rank, world=world)
+        return sharding.na_forward_spatial_shard(q, k, v, shape, ks, st, ca, rank=rank, world=world,
+                                                 plan=plan)
 
     def exchange_only():
         return sharding.exchange_halo(k, v, plan, rank)
@@ -459,9 +468,20 @@ def spatial_subrecord(cfg, world, rank, dev, barrier, steps):
     x1.record()
     barrier()
     xms = x0.elapsed_time(x1) / steps
-    t = torch.tensor([ms, xms], device=dev, dtype=torch.float64)
+    # the overlapped result on real ranks against one kernel over locally rebuilt halo frames
+    lo, hi = plan.needs[rank]
+    got_o, got_l = run()
+    ref_o, ref_l = sharding.fna_forward_slab(q, frames(1, lo, hi), frames(2, lo, hi), shape, t0, lo,
+                                             ks, st, ca)
+    err_o = float((got_o.float() - ref_o.float()).abs().max())
+    err_l = float((got_l - ref_l).abs().max())
+    del got_o, got_l, ref_o, ref_l
+    t = torch.tensor([ms, xms, err_o, err_l], device=dev, dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, xms = (float(x) for x in t.tolist())
+    ms, xms, err_o, err_l = (float(x) for x in t.tolist())
+    if err_o > 2e-2 or err_l > 2e-2:
+        raise SystemExit(f"spatial partitioning: slab differs from the local reference "
+                         f"(out {err_o:.3e}, lse {err_l:.3e})")
     frame_bytes = math.prod(shape[1:]) * H * D * q.element_size() * B
     halo = [plan.halo_frames(r) * frame_bytes * 2 for r in range(world)]
     return dict(partition="slabs of axis 0 (T), all heads per rank; halo of K/V frames by NCCL "
@@ -470,7 +490,10 @@ def spatial_subrecord(cfg, world, rank, dev, barrier, steps):
                 ms_per_step=ms, value=algorithmic_flops(cfg) / (ms * 1e-3) / 1e12,
                 unit="TFLOP/s", exchange_ms=xms,
                 halo_bytes=int(max(halo)), halo_frames=int(max(plan.halo_frames(r) for r in range(world))),
-                slab_frames=int(t1 - t0), steps=steps)
+                slabs=[list(x) for x in plan.slabs], steps=steps,
+                checked=dict(against="one kernel over locally rebuilt halo frames, every row of "
+                                     "every rank's slab", max_abs_out=err_o, max_abs_lse=err_l,
+                             tol=2e-2))
 
 
 def main():

@@ -87,8 +87,36 @@ class HaloPlan:
         return sum(b - a for _, (a, b) in self.recv_list(rank))
 
 
-def make_halo_plan(extent: int, world: int, kernel: int, stride: int, causal: bool) -> HaloPlan:
-    slabs = slab_bounds(extent, world)
+def balanced_slab_bounds(extent: int, world: int, kernel: int, stride: int, causal: bool,
+                         align: int = 1) -> List[Tuple[int, int]]:
+    """Contiguous slabs of axis 0 with near-equal attention work instead of near-equal length: a
+    frame costs as many key frames as its window holds, which on a causal axis grows over the
+    first `kernel` frames. Boundaries are multiples of `align` (the query tile's extent)."""
+    cost = []
+    for t in range(extent):
+        st = window_start(t, kernel, stride, extent, causal)
+        cost.append(window_end(t, st, kernel, extent, causal) - st)
+    total = float(sum(cost))
+    bounds, acc, t = [0], 0.0, 0
+    for r in range(1, world):
+        target = total * r / world
+        while t < extent and acc + cost[t] / 2 < target:
+            acc += cost[t]
+            t += 1
+        b = int(round(t / align)) * align
+        b = min(max(b, bounds[-1] + align), extent - (world - r) * align)
+        bounds.append(b)
+        # keep the running sum consistent with the boundary actually chosen
+        acc, t = float(sum(cost[:b])), b
+    bounds.append(extent)
+    return [(bounds[i], bounds[i + 1]) for i in range(world)]
+
+
+def make_halo_plan(extent: int, world: int, kernel: int, stride: int, causal: bool,
+                   balanced: bool = False, align: int = 1) -> HaloPlan:
+    """`balanced`: slabs of near-equal work (see balanced_slab_bounds) instead of equal length."""
+    slabs = (balanced_slab_bounds(extent, world, kernel, stride, causal, align) if balanced
+             else slab_bounds(extent, world))
     if any(t1 <= t0 for t0, t1 in slabs):
         raise ValueError(f"axis of extent {extent} cannot be split over {world} ranks")
     needs = [kv_range_for_slab(t0, t1, extent, kernel, stride, causal) for t0, t1 in slabs]
@@ -301,7 +329,8 @@ def na_forward_spatial_shard(q_local: Tensor, k_local: Tensor, v_local: Tensor,
                              world: Optional[int] = None,
                              group: Optional[dist.ProcessGroup] = None,
                              q_tile_shape=None, kv_tile_shape=None,
-                             overlap: bool = True) -> Tuple[Tensor, Tensor]:
+                             overlap: bool = True, plan: Optional[HaloPlan] = None
+                             ) -> Tuple[Tensor, Tensor]:
     """Neighborhood attention forward for this rank's slab of axis 0 (dilation 1). Inputs are
     ``[B, t1 - t0, *rest, H, D]`` (fp16/bf16, head dim 64 or 128); returns the rank's slab of the
     output and logsumexp, equal to the same rows of the unsharded result up to rounding.
@@ -311,14 +340,18 @@ def na_forward_spatial_shard(q_local: Tensor, k_local: Tensor, v_local: Tensor,
     flight, attends each received block once it has landed, and folds the partial results
     together with the LSE merge - the use the reference's `merge_attentions` hints at
     (src/natten/attn_merge.py:199-204). ``overlap=False``: exchange, then one kernel over the
-    assembled key/value slab."""
+    assembled key/value slab. `plan`: the halo plan the inputs were sliced by (default: slabs of
+    equal length; `make_halo_plan(..., balanced=True)` gives slabs of equal work)."""
     from .functional import merge_attentions
 
     rank = dist.get_rank(group) if rank is None else rank
     world = dist.get_world_size(group) if world is None else world
-    plan = make_halo_plan(int(global_shape[0]), world, int(kernel_size[0]), int(stride[0]),
-                          bool(is_causal[0]))
-    t0, _ = plan.slabs[rank]
+    if plan is None:
+        plan = make_halo_plan(int(global_shape[0]), world, int(kernel_size[0]), int(stride[0]),
+                              bool(is_causal[0]))
+    t0, t1 = plan.slabs[rank]
+    if q_local.shape[1] != t1 - t0:
+        raise ValueError(f"rank {rank} owns frames [{t0}, {t1}) but got {q_local.shape[1]} frames")
     if not overlap or not plan.recv_list(rank):
         k_slab, v_slab, lo = exchange_halo(k_local, v_local, plan, rank, group)
         return fna_forward_slab(q_local, k_slab, v_slab, global_shape, t0, lo, kernel_size, stride,

@@ -37,8 +37,11 @@ def test_shard_batch_heads_blocks():
     (32, 4, 16, 1, True), (32, 2, 16, 1, True),
     (40, 4, 7, 1, False), (37, 3, 8, 4, False), (64, 8, 9, 3, True),
 ])
-def test_halo_plan_covers_every_window(extent, world, k, s, causal):
-    plan = sharding.make_halo_plan(extent, world, k, s, causal)
+@pytest.mark.parametrize("balanced", [False, True])
+def test_halo_plan_covers_every_window(extent, world, k, s, causal, balanced):
+    plan = sharding.make_halo_plan(extent, world, k, s, causal, balanced=balanced)
+    assert plan.slabs[0][0] == 0 and plan.slabs[-1][1] == extent
+    assert all(plan.slabs[r][1] == plan.slabs[r + 1][0] for r in range(world - 1))
     for r, (t0, t1) in enumerate(plan.slabs):
         lo, hi = plan.needs[r]
         for i in range(t0, t1):
@@ -54,10 +57,28 @@ def test_halo_plan_covers_every_window(extent, world, k, s, causal):
             assert not (got & set(range(a, b)))
             got |= set(range(a, b))
         assert got == set(range(lo, hi))
-    if (extent, world, k, s, causal) == (32, 8, 16, 1, True):
+    if (extent, world, k, s, causal, balanced) == (32, 8, 16, 1, True, False):
         # a causal window of 16 reaches 15 frames back, not kernel_size / 2
         assert plan.needs[4] == (16 - 15, 20)
         assert plan.halo_frames(4) == 15 and plan.halo_frames(0) == 0
+
+
+def test_balanced_slabs_equalise_the_work_of_a_causal_axis():
+    """Config 5's T axis over two ranks: frames 0..15 have windows of 1..16 key frames, the rest
+    16 each (392 in all); equal-length slabs give 136 / 256, balanced ones 200 / 192."""
+    def work(t0, t1):
+        return sum(window_end(t, window_start(t, 16, 1, 32, True), 16, 32, True)
+                   - window_start(t, 16, 1, 32, True) for t in range(t0, t1))
+    even = sharding.make_halo_plan(32, 2, 16, 1, True).slabs
+    bal = sharding.make_halo_plan(32, 2, 16, 1, True, balanced=True, align=2).slabs
+    assert [work(*x) for x in even] == [136, 256]
+    assert bal == [(0, 20), (20, 32)] and [work(*x) for x in bal] == [200, 192]
+    # boundaries respect the alignment, every rank keeps at least one aligned block
+    for world in (2, 4, 8):
+        slabs = sharding.make_halo_plan(32, world, 16, 1, True, balanced=True, align=2).slabs
+        assert all(a % 2 == 0 and b > a for a, b in slabs)
+        assert max(work(*x) for x in slabs) <= max(work(*x) for x in
+                                                   sharding.make_halo_plan(32, world, 16, 1, True).slabs)
 
 
 def _free_port():
@@ -82,6 +103,18 @@ def _exchange_worker(rank, world, port, extent, k, s, causal, batch, q):
                                             plan, rank)
         lo2, hi2 = plan.needs[rank]
         ok = lo == lo2 and torch.equal(ks, K[:, lo2:hi2]) and torch.equal(vs, V[:, lo2:hi2])
+        # the non-blocking form used by the overlapped path: received blocks only, own frames
+        # are not copied
+        parts, reqs, keep = sharding.exchange_halo_parts(K[:, t0:t1].contiguous(),
+                                                         V[:, t0:t1].contiguous(), plan, rank)
+        for r in reqs:
+            r.wait()
+        covered = set()
+        for kp, vp, first in parts:
+            n = kp.shape[1]
+            ok = ok and torch.equal(kp, K[:, first:first + n]) and torch.equal(vp, V[:, first:first + n])
+            covered |= set(range(first, first + n))
+        ok = ok and covered == set(range(lo2, hi2)) - set(range(t0, t1))
         q.put((rank, bool(ok)))
     finally:
         dist.destroy_process_group()
