@@ -518,6 +518,8 @@ def main():
     ap.add_argument("--no-check", action="store_true", help="skip the oracle check of the output")
     ap.add_argument("--no-kernels", action="store_true",
                     help="skip the permute / unpermute / merge bandwidth legs")
+    ap.add_argument("--kernel-steps", type=int, default=10,
+                    help="timed launches per bandwidth-bound kernel in the `kernels` legs")
     ap.add_argument("--check-rows", type=int, default=4608,
                     help="query rows per (batch, head) slice compared with the oracle")
     ap.add_argument("--no-e2e", action="store_true")
@@ -682,7 +684,8 @@ def main():
     peaks = read_peaks()
     kernels = None
     if rank == 0 and tensor_core and not spatial and not args.no_kernels:
-        kernels = kernels_leg(cfg, nb, dq, dk, out, lse, q_tile, kv_tile, peaks)
+        kernels = kernels_leg(cfg, nb, dq, dk, out, lse, q_tile, kv_tile, peaks,
+                              steps=args.kernel_steps)
 
     # ---- end to end through the public operator with HOST buffers ----
     e2e_ms = None

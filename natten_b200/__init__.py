@@ -5,6 +5,7 @@ Public surface mirrors the reference's for this path (src/natten/__init__.py:66-
 operators. Importing the package loads ``lib/libnatten_b200.so`` and raises if it is missing.
 """
 from . import _lib  # noqa: F401  (fails loudly when the CUDA library is not built)
+from .log import get_logger  # noqa: F401
 from .functional import (BACKEND_NAME, FMHA_BACKEND_NAME, attention, choose_tile_shapes,
                          fna_forward_op, fna_forward_permuted, fna_forward_direct, direct_layout_supported,
                          can_run_b200_fna, get_configs_for_b200_fna, get_bwd_configs_for_b200_fna,

@@ -21,9 +21,12 @@ import torch
 from torch import Tensor
 
 from . import _lib, ops
+from .log import get_logger
 from .checks import (CausalArgType, DimensionType, additional_kv_tensor_checks, check_all_args,
                      check_args_against_input, check_tile_shape, fmha_tensor_checks,
                      is_self_attention, na_tensor_checks)
+
+logger = get_logger("natten_b200.functional")
 
 BACKEND_NAME = "b200-fna"
 FMHA_BACKEND_NAME = "b200-fmha"
@@ -45,12 +48,26 @@ def _padded_head_dim(dtype: torch.dtype, head_dim: int) -> int:
     fp16 / bf16 below 128 go to 64 or 128; everything else is left alone."""
     if dtype in (torch.float16, torch.bfloat16) and head_dim < 128 and head_dim not in (64,):
         return 64 if head_dim < 64 else 128
+    # 8-bit floats: the reference's Blackwell kernels take every multiple of 16
+    # (csrc/src/blackwell_fna_forward.cu:178-191); the kernel here is built for 128
+    if dtype in FP8_DTYPES and head_dim < FP8_HEAD_DIM and head_dim % 16 == 0:
+        return FP8_HEAD_DIM
     return head_dim
 
 
+def _pad_head_dim(t: Tensor, padded_dim: int) -> Tensor:
+    """`t` with its last axis zero-padded to `padded_dim` (8-bit floats have no pad kernel in
+    torch: zeros + copy)."""
+    if t.dtype in FP8_DTYPES:
+        out = torch.zeros(t.shape[:-1] + (padded_dim,), dtype=t.dtype, device=t.device)
+        out[..., :t.shape[-1]].copy_(t)
+        return out
+    return torch.nn.functional.pad(t, (0, padded_dim - t.shape[-1]))
+
+
 def _tensor_core_supported(dtype: torch.dtype, head_dim: int) -> bool:
-    """Operand types of the tcgen05 kernels: fp16 / bf16 with head dim 64 or 128, 8-bit floats
-    (forward only) with head dim 128."""
+    """Operand types of the tcgen05 kernels as built: fp16 / bf16 with head dim 64 or 128, 8-bit
+    floats (forward only) with head dim 128 (smaller head dims reach them zero-padded)."""
     if dtype in (torch.float16, torch.bfloat16):
         return head_dim in TENSOR_CORE_HEAD_DIMS
     return dtype in FP8_DTYPES and head_dim == FP8_HEAD_DIM
@@ -313,7 +330,7 @@ def attention(query: Tensor, key: Tensor, value: Tensor, is_causal: bool = False
     q, k, v = (t.contiguous() for t in (query, key, value))
     padded_dim = _padded_head_dim(query.dtype, D)   # see neighborhood_attention_generic
     if padded_dim != D:
-        q, k, v = (torch.nn.functional.pad(t, (0, padded_dim - D)) for t in (q, k, v))
+        q, k, v = (_pad_head_dim(t, padded_dim) for t in (q, k, v))
     out, lse = ops.fmha_forward(q, k, v, bool(is_causal), float(scale))
     if padded_dim != D:
         out = out[..., :D].contiguous()
@@ -348,14 +365,16 @@ def neighborhood_attention_generic(
     _require_cuda(query, key, value, additional_keys, additional_values)
     has_extra = additional_keys is not None and additional_values is not None
 
-    if is_self_attention(query, kernel_size, is_causal, has_extra):
+    # A window that covers the whole layout is plain attention (the reference takes the same
+    # shortcut, src/natten/functional.py:423-447). With extra tokens attached the reference
+    # concatenates them to K/V first; here that case stays on the neighborhood kernel, which
+    # attends the extra tokens in the same softmax without a copy and - unlike dense attention
+    # with more keys than queries - has a backward, so the call stays trainable.
+    if is_self_attention(query, kernel_size, is_causal, has_extra) and not has_extra:
         query_shape = query.shape
         q = query.flatten(1, na_dim)
         k = key.flatten(1, na_dim)
         v = value.flatten(1, na_dim)
-        if has_extra:
-            k = torch.cat([k, additional_keys], dim=1)
-            v = torch.cat([v, additional_values], dim=1)
         fmha_kwargs = {kk: vv for kk, vv in (attention_kwargs or {}).items()
                        if kk not in ("unfused_extra_kv", "permuted_layout")}
         out, lse = attention(q, k, v, is_causal=is_causal[0], scale=scale, return_lse=True,
@@ -387,10 +406,11 @@ def neighborhood_attention_generic(
     head_dim = query.shape[-1]
     padded_dim = _padded_head_dim(query.dtype, head_dim)
     if padded_dim != head_dim:
-        grow = (0, padded_dim - head_dim)
-        q, k, v = (torch.nn.functional.pad(t, grow) for t in (q, k, v))
+        logger.debug("head dim %d zero-padded to %d for the tensor-core kernels", head_dim,
+                     padded_dim)
+        q, k, v = (_pad_head_dim(t, padded_dim) for t in (q, k, v))
         if fuse_extra:
-            ak, av = torch.nn.functional.pad(ak, grow), torch.nn.functional.pad(av, grow)
+            ak, av = _pad_head_dim(ak, padded_dim), _pad_head_dim(av, padded_dim)
     if backward_q_tile_shape is not None:
         backward_q_tile_shape = check_tile_shape(na_dim, backward_q_tile_shape,
                                                  "backward_q_tile_shape", BACKWARD_TILE_SIZE)
@@ -445,11 +465,14 @@ def na_forward_op(query: Tensor, key: Tensor, value: Tensor, additional_keys: Op
     is_causal = tuple(bool(c) for c in is_causal)
     tensor_core = _tensor_core_supported(query.dtype, query.shape[-1])
     if not tensor_core and query.dtype in FP8_DTYPES:
-        raise NotImplementedError(f"natten_b200: 8-bit operands need head dim {FP8_HEAD_DIM}, got "
-                                  f"{query.shape[-1]}.")
+        raise NotImplementedError("natten_b200: 8-bit operands need a head dim that is a multiple "
+                                  f"of 16 and at most {FP8_HEAD_DIM}, got {query.shape[-1]}.")
     if not tensor_core:
         # fp32 operands (and other head dims): CUDA-core kernel on the original layout, extra KV
         # tokens fused into the same softmax.
+        logger.debug("na%dd %s: CUDA-core kernel (dtype %s, head dim %d), shape %s kernel %s "
+                     "stride %s dilation %s causal %s", na_dim, BACKEND_NAME, query.dtype,
+                     query.shape[-1], shape, kernel_size, stride, dilation, is_causal)
         query, key, value = query.contiguous(), key.contiguous(), value.contiguous()
         return ops.na_forward_simt(query, key, value, additional_keys, additional_values,
                                    list(kernel_size), list(stride), list(dilation),
@@ -459,7 +482,22 @@ def na_forward_op(query: Tensor, key: Tensor, value: Tensor, additional_keys: Op
         q_tile_shape = tuple(q_tile_shape) or auto_q
         kv_tile_shape = tuple(kv_tile_shape) or auto_kv
     q_tile_shape, kv_tile_shape = tuple(q_tile_shape), tuple(kv_tile_shape)
-    if not permuted_layout and direct_layout_supported(q_tile_shape, kv_tile_shape, dilation):
+    direct = not permuted_layout and direct_layout_supported(q_tile_shape, kv_tile_shape, dilation)
+    if logger.debug_enabled:
+        tiles = math.prod(_axis_tile_cost(shape[a], kernel_size[a], stride[a], dilation[a],
+                                          is_causal[a], q_tile_shape[a], kv_tile_shape[a], direct)
+                          for a in range(na_dim))
+        items = math.prod(-(-group_extent(shape[a], dilation[a], 0) // q_tile_shape[a])
+                          for a in range(na_dim))
+        logger.debug("na%dd %s: tensor-core kernel on %s, dtype %s head dim %d, shape %s kernel "
+                     "%s stride %s dilation %s causal %s, q_tile %s kv_tile %s, %.1f kv tiles per "
+                     "query tile (+%d extra-token tiles), %d extra tokens", na_dim, BACKEND_NAME,
+                     "the caller's layout (one launch)" if direct else "token-permuted copies",
+                     query.dtype, query.shape[-1], shape, kernel_size, stride, dilation, is_causal,
+                     q_tile_shape, kv_tile_shape, tiles / max(1, items),
+                     0 if additional_keys is None else -(-additional_keys.shape[1] // 128),
+                     0 if additional_keys is None else additional_keys.shape[1])
+    if direct:
         # one kernel on the caller's layout: no permuted copies of Q/K/V/O/LSE at all
         return fna_forward_direct(query, key, value, kernel_size, stride, dilation, is_causal,
                                   scale, q_tile_shape, kv_tile_shape, additional_keys,

@@ -26,6 +26,9 @@ import torch.distributed as dist
 from torch import Tensor
 
 from .functional import window_end, window_start
+from .log import get_logger
+
+logger = get_logger("natten_b200.sharding")
 
 
 def unit_range(n_units: int, world: int, rank: int) -> Tuple[int, int]:
@@ -357,6 +360,9 @@ def na_forward_spatial_shard(q_local: Tensor, k_local: Tensor, v_local: Tensor,
         return fna_forward_slab(q_local, k_slab, v_slab, global_shape, t0, lo, kernel_size, stride,
                                 is_causal, scale, q_tile_shape, kv_tile_shape)
     nd = len(global_shape)
+    logger.debug("rank %d/%d: frames [%d, %d) of %d, halo %s, exchange overlapped with the "
+                 "attention over the rank's own frames", rank, world, t0, t1, int(global_shape[0]),
+                 [(src, rng) for src, rng in plan.recv_list(rank)])
     parts, reqs, keep = exchange_halo_parts(k_local, v_local, plan, rank, group)
     out, lse = fna_forward_slab(q_local, k_local, v_local, global_shape, t0, t0, kernel_size,
                                 stride, is_causal, scale, q_tile_shape, kv_tile_shape, clip=True)

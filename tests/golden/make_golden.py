@@ -21,7 +21,10 @@ import sys
 
 import numpy as np
 
-REF = os.environ.get("REFERENCE_SRC", "/root/reference/src")
+REF = os.environ.get("REFERENCE_SRC")
+if not REF:
+    raise SystemExit("set REFERENCE_SRC to the `src` directory of a checkout of the reference "
+                     "(the one that holds the `natten` package)")
 sys.path.insert(0, REF)
 os.environ.setdefault("NATTEN_LOG_LEVEL", "error")
 sys.dont_write_bytecode = True

@@ -85,6 +85,10 @@ def test_layer_trains():
     ((9000,), (200,), (7,), (1,), (False,), 4, 2, 64, 40),
     ((96, 96), (9, 9), (1, 1), (1, 1), (False, True), 2, 2, 128, 0),
     ((10, 40, 48), (3, 5, 8), (1, 1, 4), (1, 1, 1), (True, False, False), 2, 1, 128, 130),
+    # window = whole layout with extra tokens attached: stays on the neighborhood kernels (dense
+    # attention with more keys than queries has no backward)
+    ((12, 20), (12, 20), (1, 1), (1, 1), (False, False), 2, 2, 64, 50),
+    ((300,), (300,), (1,), (1,), (False,), 2, 1, 128, 33),
 ])
 def test_tensor_core_backward_against_oracle_and_cuda_core_kernels(shape, ks, st, di, ca, hq, hkv,
                                                                    D, n_extra):

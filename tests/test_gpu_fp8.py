@@ -56,7 +56,27 @@ def test_fp8_forward_matches_oracle(dtype, shape, ks, st, di, ca, n_extra, hq, h
     assert np.abs(lse.cpu().numpy() - want_l).max() <= 2e-2
 
 
-def test_fp8_needs_head_dim_128():
-    q = torch.randn(1, 64, 2, 64, device="cuda").to(torch.float8_e4m3fn)
+@pytest.mark.parametrize("D", [16, 64, 96])
+def test_fp8_head_dims_below_128_run_zero_padded(D):
+    """The reference's Blackwell kernels take 8-bit operands with every head dim that is a multiple
+    of 16 (csrc/src/blackwell_fna_forward.cu:178-191); here they are zero-padded to 128."""
+    torch.manual_seed(42)
+    dtype = torch.float8_e4m3fn
+    shape, ks, st, ca = (24, 40), (7, 9), (1, 2), (False, True)
+    q, k, v = (torch.randn(1, *shape, 2, D).to(dtype) for _ in range(3))
+    out, lse = nb.na2d(q.cuda(), k.cuda(), v.cuda(), kernel_size=ks, stride=st, is_causal=ca,
+                       return_lse=True)
+    assert L.device_status() == 0
+    assert out.shape == q.shape and out.dtype == dtype
+    want_o, want_l = oracle.na_forward(q.float().numpy(), k.float().numpy(), v.float().numpy(),
+                                       ks, st, 1, ca)
+    err = np.abs(out.float().cpu().numpy() - want_o)
+    rel, floor, mean = OUT_TOL[dtype]
+    assert (err <= rel * np.abs(want_o) + floor).all() and err.mean() <= mean
+    assert np.abs(lse.cpu().numpy() - want_l).max() <= 2e-2
+
+
+def test_fp8_head_dim_must_be_a_multiple_of_16():
+    q = torch.randn(1, 64, 2, 40, device="cuda").to(torch.float8_e4m3fn)
     with pytest.raises(NotImplementedError):
         nb.na1d(q, q, q, kernel_size=9)

@@ -1,0 +1,141 @@
+"""The problem lists of the reference's own Blackwell FNA test (tests/test_blackwell_fna.py:153-176
+one-dimensional, :205-226 two-dimensional, :317-338 three-dimensional; each problem there runs
+with every combination of causal axes, :188-189, :239-240, :351-353) replayed against the oracle:
+fp16 operands, every causal combination, the kernel on the caller's layout and the permuted flow.
+Head dims the tensor-core kernels do not take natively (16, 32, 48, 72, 96, 120) run zero-padded.
+
+The reference compares its Blackwell backend with its CUTLASS 2.x backend on these problems at an
+absolute tolerance of 1e-2 (fp16); neither builds here, so the comparison is with the CPU oracle
+(pinned to the reference's own outputs in tests/test_oracle.py) at this repository's 2e-2. Large
+problems are checked on a sample of query rows (half uniform, half in the border bands)."""
+import itertools
+
+import numpy as np
+import pytest
+import torch
+
+import natten_b200 as nb
+import natten_b200._lib as L
+import oracle
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-2
+MAX_ROWS = 1536
+
+# (batch, heads, heads_kv, head_dim, shape, kernel_size, stride, dilation)
+PROBLEMS_1D = [
+    (1, 4, 2, 64, (128,), (127,), (1,), (1,)),
+    (1, 4, 2, 48, (128,), (15,), (1,), (1,)),
+    (1, 4, 1, 64, (128,), (15,), (1,), (1,)),
+    (1, 2, 1, 72, (128,), (15,), (1,), (1,)),
+    (1, 2, 2, 64, (128,), (15,), (1,), (1,)),
+    (2, 4, 4, 120, (128,), (63,), (31,), (1,)),
+    (2, 4, 2, 96, (128,), (63,), (31,), (1,)),
+    (2, 4, 1, 128, (128,), (63,), (31,), (1,)),
+    (4, 3, 3, 128, (256,), (255,), (82,), (1,)),
+    (4, 3, 1, 128, (256,), (255,), (82,), (1,)),
+    (1, 1, 1, 128, (32768,), (2048,), (2048,), (1,)),
+    (1, 1, 1, 128, (32768,), (2048,), (256,), (1,)),
+    (1, 1, 1, 128, (32768,), (2048,), (128,), (1,)),
+    (1, 1, 1, 128, (32768,), (2048,), (1,), (1,)),
+    (1, 1, 1, 32, (128,), (3,), (2,), (5,)),
+    (1, 1, 1, 32, (128,), (3,), (1,), (1,)),
+    (1, 1, 1, 32, (128,), (3,), (2,), (10,)),
+    (1, 1, 1, 64, (128,), (8,), (7,), (5,)),
+    (1, 1, 1, 128, (128,), (61,), (33,), (1,)),
+    (1, 1, 1, 32, (125,), (3,), (1,), (1,)),
+    (1, 2, 2, 64, (125,), (15,), (1,), (1,)),
+    (1, 1, 1, 128, (256,), (3,), (2,), (10,)),
+]
+PROBLEMS_2D = [
+    (1, 12, 12, 32, (17, 16), (3, 8), (1, 2), (1, 1)),
+    (1, 12, 6, 16, (17, 16), (3, 8), (1, 2), (1, 1)),
+    (1, 12, 4, 32, (17, 16), (3, 8), (1, 2), (1, 1)),
+    (1, 2, 2, 32, (5, 25), (5, 16), (1, 16), (1, 1)),
+    (1, 2, 1, 48, (5, 25), (5, 16), (1, 16), (1, 1)),
+    (1, 1, 1, 32, (84, 19), (7, 3), (1, 1), (1, 1)),
+    (1, 1, 1, 32, (84, 19), (7, 3), (1, 1), (5, 1)),
+    (1, 1, 1, 128, (19, 29), (8, 8), (1, 1), (2, 3)),
+    (1, 1, 1, 96, (48, 17), (24, 16), (1, 1), (2, 1)),
+    (1, 1, 1, 128, (67, 80), (12, 7), (8, 4), (5, 11)),
+    (1, 1, 1, 72, (8, 8), (8, 8), (1, 1), (1, 1)),
+    (1, 1, 1, 128, (33, 33), (24, 16), (1, 1), (1, 1)),
+    (1, 1, 1, 32, (16, 16), (16, 16), (1, 1), (1, 1)),
+    (1, 1, 1, 128, (44, 80), (44, 80), (1, 1), (1, 1)),
+    (1, 1, 1, 32, (40, 20), (3, 7), (1, 1), (1, 1)),
+    (1, 1, 1, 32, (16, 16), (3, 3), (1, 1), (1, 1)),
+    (1, 1, 1, 128, (44, 80), (9, 10), (1, 1), (1, 1)),
+    (1, 1, 1, 64, (28, 40), (17, 31), (1, 1), (1, 1)),
+    (1, 1, 1, 64, (36, 40), (36, 40), (12, 13), (1, 1)),
+    (1, 1, 1, 128, (44, 80), (44, 80), (4, 8), (1, 1)),
+]
+PROBLEMS_3D = [
+    (4, 8, 4, 48, (32, 10, 10), (7, 3, 3), (5, 1, 1), (1, 2, 3)),
+    (4, 8, 2, 64, (32, 10, 10), (7, 3, 3), (5, 1, 1), (1, 2, 3)),
+    (4, 8, 1, 64, (32, 10, 10), (7, 3, 3), (5, 1, 1), (1, 2, 3)),
+    (1, 1, 1, 64, (18, 37, 12), (14, 16, 12), (12, 8, 1), (1, 2, 1)),
+    (1, 1, 1, 32, (13, 11, 9), (3, 4, 3), (2, 3, 3), (1, 1, 1)),
+    (1, 1, 1, 32, (13, 11, 9), (3, 4, 3), (2, 3, 3), (3, 2, 2)),
+    (1, 4, 4, 32, (8, 8, 16), (3, 3, 3), (2, 1, 2), (2, 2, 4)),
+    (1, 1, 1, 72, (57, 20, 88), (20, 4, 6), (1, 1, 1), (2, 1, 1)),
+    (1, 1, 1, 96, (57, 32, 32), (10, 32, 32), (1, 1, 1), (1, 1, 1)),
+    (1, 1, 1, 120, (32, 64, 64), (16, 16, 16), (1, 2, 2), (1, 1, 1)),
+    (1, 1, 1, 128, (30, 48, 80), (18, 24, 24), (16, 8, 8), (1, 1, 1)),
+    (1, 1, 1, 128, (16, 44, 80), (12, 32, 32), (8, 22, 16), (1, 1, 1)),
+    (1, 1, 1, 128, (31, 32, 32), (10, 32, 32), (1, 1, 1), (1, 1, 1)),
+    (1, 1, 1, 128, (30, 32, 32), (10, 32, 32), (1, 1, 1), (1, 1, 1)),
+    (1, 1, 1, 32, (16, 16, 16), (16, 16, 16), (1, 1, 1), (1, 1, 1)),
+    (1, 1, 1, 32, (8, 4, 8), (7, 3, 7), (1, 1, 1), (1, 1, 1)),
+    (1, 1, 1, 32, (16, 16, 16), (15, 15, 15), (1, 1, 1), (1, 1, 1)),
+    (1, 1, 1, 64, (24, 28, 40), (24, 28, 40), (1, 1, 1), (1, 1, 1)),
+    (1, 1, 1, 32, (16, 16, 16), (16, 16, 16), (2, 4, 5), (1, 1, 1)),
+]
+ALL = ([("1d", i, p) for i, p in enumerate(PROBLEMS_1D)] +
+       [("2d", i, p) for i, p in enumerate(PROBLEMS_2D)] +
+       [("3d", i, p) for i, p in enumerate(PROBLEMS_3D)])
+
+
+def _rows(shape, kernel, dilation, n_rows, seed):
+    """Flat token indices: half uniform, half inside one (dilated) kernel size of an axis end."""
+    rng = np.random.default_rng(seed)
+    n_tok = int(np.prod(shape))
+    if n_tok <= n_rows:
+        return None
+    picks = [rng.integers(0, n_tok, size=n_rows // 2)]
+    nd = len(shape)
+    per = max(1, (n_rows - n_rows // 2) // (2 * nd))
+    for a in range(nd):
+        band = min(kernel[a] * dilation[a], shape[a])
+        for side in (0, 1):
+            coords = [rng.integers(0, shape[b], size=per) for b in range(nd)]
+            coords[a] = rng.integers(0, band, size=per) + (0 if side == 0 else shape[a] - band)
+            picks.append(np.ravel_multi_index(coords, shape))
+    return np.unique(np.concatenate(picks)).astype(np.int64)
+
+
+@pytest.mark.parametrize("dim,index,problem", ALL, ids=[f"{d}-{i}" for d, i, _ in ALL])
+def test_reference_problem_list_against_oracle(dim, index, problem):
+    B, H, Hkv, D, shape, ks, st, di = problem
+    nd = len(shape)
+    torch.manual_seed(1000 * nd + index)
+    q = torch.randn(B, *shape, H, D).half()
+    k, v = (torch.randn(B, *shape, Hkv, D).half() for _ in range(2))
+    fn = {1: nb.na1d, 2: nb.na2d, 3: nb.na3d}[nd]
+    rows = _rows(shape, ks, di, MAX_ROWS, index)
+    qf, kf, vf = (t.float().numpy() for t in (q, k, v))
+    qc, kc, vc = q.cuda(), k.cuda(), v.cuda()
+    for ca in itertools.product([True, False], repeat=nd):
+        want_o, want_l = oracle.na_forward(qf, kf, vf, ks, st, di, ca, tok_idx=rows)
+        for layout in ({}, {"permuted_layout": True}):
+            out, lse = fn(qc, kc, vc, kernel_size=ks, stride=st, dilation=di, is_causal=ca,
+                          return_lse=True, attention_kwargs=layout)
+            assert L.device_status() == 0
+            got_o = out.flatten(1, nd).float().cpu().numpy()
+            got_l = lse.flatten(1, nd).cpu().numpy()
+            if rows is not None:
+                got_o, got_l = got_o[:, rows], got_l[:, rows]
+            else:
+                got_o = got_o.reshape(want_o.shape)
+                got_l = got_l.reshape(want_l.shape)
+            assert np.abs(got_o - want_o).max() <= TOL, (ca, layout)
+            assert np.abs(got_l - want_l).max() <= TOL, (ca, layout)

@@ -169,3 +169,23 @@ def test_config_queries_answer_to_the_reference_names():
         assert np.prod(tq) == 256 and np.prod(tkv) == 128
     for tq, tkv in F._all_tile_shapes(3, 7, 7):
         assert np.prod(tq) == 128 and np.prod(tkv) == 128
+
+
+def test_logger_follows_the_reference_environment_variables(tmp_path):
+    """NATTEN_LOG_LEVEL / NATTEN_LOG_PIPE as in the reference (src/natten/utils/log.py:43-134):
+    debug lines reach the chosen file only at level debug."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = ("from natten_b200.log import get_logger; l = get_logger('natten_b200.test'); "
+            "l.debug('tile %s', (4, 8, 8)); l.info('hello'); print(l.debug_enabled)")
+    for level, expect_debug in (("debug", True), ("warning", False), ("", False)):
+        pipe = tmp_path / f"log_{level or 'default'}.txt"
+        env = dict(os.environ, NATTEN_LOG_LEVEL=level, NATTEN_LOG_PIPE=str(pipe), PYTHONPATH=root)
+        res = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True,
+                             check=True)
+        text = pipe.read_text() if pipe.exists() else ""
+        assert ("tile (4, 8, 8)" in text) == expect_debug
+        assert ("hello" in text) == (level != "warning")
+        assert res.stdout.strip() == str(expect_debug)
