@@ -199,14 +199,17 @@ B200NA_API int b200na_fna_forward_sharded(
  *     results over disjoint key slabs combine with b200na_merge to the full result, which lets
  *     a rank attend its own frames while the frames of other ranks are still in flight
  *     (the use the reference's merge_attentions hints at, src/natten/attn_merge.py:199-204).
+ * add_k / add_v: n_extra extra key/value tokens [B, n_extra, Hkv, D] every query attends (NULL and
+ * 0 for none); when partial results are merged, pass them to exactly one of the calls.
  * Also the building block for streaming a host-resident problem through the GPU along axis 0.
  */
 B200NA_API int b200na_na_forward_direct_sharded(
-    const void* q, const void* k, const void* v, void* o, float* lse, int ndim,
-    const int* global_shape, const int* kernel, const int* stride, const int* causal,
-    const int* q_tile, const int* kv_tile, const int* q_origin, const int* q_extent,
-    const int* kv_origin, const int* kv_extent, int clip_to_kv, int B, int Hq, int Hkv, int D,
-    int dtype, float scale, b200na_stream_t stream);
+    const void* q, const void* k, const void* v, const void* add_k, const void* add_v,
+    int n_extra, void* o, float* lse, int ndim, const int* global_shape, const int* kernel,
+    const int* stride, const int* causal, const int* q_tile, const int* kv_tile,
+    const int* q_origin, const int* q_extent, const int* kv_origin, const int* kv_extent,
+    int clip_to_kv, int B, int Hq, int Hkv, int D, int dtype, float scale,
+    b200na_stream_t stream);
 
 /*
  * Whole operator in one call: token permute of Q, K, V -> fused attention -> unpermute of O and

@@ -80,7 +80,8 @@ def _load() -> ctypes.CDLL:
     lib.b200na_na_backward_direct.argtypes = [c_void_p] * 8 + [c_int] + [c_void_p] * 6 + [
         c_int, ip, ip, ip, ip, ip, ip, ip, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]
     lib.b200na_na_forward_direct_sharded.restype = c_int
-    lib.b200na_na_forward_direct_sharded.argtypes = [c_void_p] * 5 + [c_int] + [ip] * 10 + [
+    lib.b200na_na_forward_direct_sharded.argtypes = [c_void_p] * 5 + [c_int, c_void_p, c_void_p,
+                                                     c_int] + [ip] * 10 + [
         c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]
     lib.b200na_fna_forward_sharded.restype = c_int
     lib.b200na_fna_forward_sharded.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,

@@ -1532,15 +1532,16 @@ extern "C" B200NA_API int b200na_na_forward_direct_strided(
 }
 
 extern "C" B200NA_API int b200na_na_forward_direct_sharded(
-    const void* q, const void* k, const void* v, void* o, float* lse, int ndim,
-    const int* global_shape, const int* kernel, const int* stride, const int* causal,
-    const int* q_tile, const int* kv_tile, const int* q_origin, const int* q_extent,
-    const int* kv_origin, const int* kv_extent, int clip_to_kv, int B, int Hq, int Hkv, int D,
-    int dtype, float scale, b200na_stream_t stream) {
+    const void* q, const void* k, const void* v, const void* add_k, const void* add_v,
+    int n_extra, void* o, float* lse, int ndim, const int* global_shape, const int* kernel,
+    const int* stride, const int* causal, const int* q_tile, const int* kv_tile,
+    const int* q_origin, const int* q_extent, const int* kv_origin, const int* kv_extent,
+    int clip_to_kv, int B, int Hq, int Hkv, int D, int dtype, float scale,
+    b200na_stream_t stream) {
   if (!q_origin || !q_extent || !kv_origin || !kv_extent) return B200NA_ERR_INVALID_ARGUMENT;
   return b200na::fna_direct_impl(q, k, v, o, lse, ndim, global_shape, kernel, stride, nullptr,
-                                 causal, q_tile, kv_tile, B, Hq, Hkv, D, dtype, scale, nullptr,
-                                 nullptr, 0, nullptr, stream, q_origin, q_extent, kv_origin,
+                                 causal, q_tile, kv_tile, B, Hq, Hkv, D, dtype, scale, add_k,
+                                 add_v, n_extra, nullptr, stream, q_origin, q_extent, kv_origin,
                                  kv_extent, clip_to_kv);
 }
 

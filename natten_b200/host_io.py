@@ -5,7 +5,7 @@ memory pays host -> device copies of Q, K, V and a device -> host copy of the re
 call. This helper pipelines the three: while one piece is being computed, the next piece's
 operands are already crossing PCIe in one direction and the previous piece's result in the other
 (separate copy streams; the link is full duplex). Pieces are slabs of the outermost token axis
-where the problem allows it (undilated fp16 / bf16, no extra tokens) - a slab of queries only
+where the problem allows it (undilated fp16 / bf16) - a slab of queries only
 needs the key/value frames its windows reach, which for all but its last frames have arrived with
 earlier slabs - and whole batch entries otherwise.
 """
@@ -42,10 +42,12 @@ def na_forward_from_host(query: Tensor, key: Tensor, value: Tensor, kernel_size:
     if lse is None:
         lse = torch.empty(query.shape[:-1], dtype=torch.float32).pin_memory()
     has_extra = additional_keys is not None and additional_values is not None
-    if not has_extra and batch_chunk == 1:
+    if batch_chunk == 1:
         plan = _slab_plan(query, key, kernel_size, stride, dilation, is_causal)
         if plan is not None:
-            return _stream_slabs(query, key, value, plan, scale, out, lse, dev)
+            return _stream_slabs(query, key, value, plan, scale, out, lse, dev,
+                                 additional_keys if has_extra else None,
+                                 additional_values if has_extra else None)
     cur = torch.cuda.current_stream(dev)
     s_in, s_out = _copy_streams(dev)
     s_in.wait_stream(cur)
@@ -113,23 +115,34 @@ def _slab_plan(query: Tensor, key: Tensor, kernel_size, stride, dilation, is_cau
     return dict(shape=shape, ks=ks, st=st, ca=ca, tq=tq, tkv=tkv, slabs=slabs)
 
 
-def _stream_slabs(query, key, value, plan, scale, out, lse, dev):
+def _stream_slabs(query, key, value, plan, scale, out, lse, dev, add_k=None, add_v=None):
     from .sharding import fna_forward_slab
     shape, slabs = plan["shape"], plan["slabs"]
+    B = query.shape[0]
     cur = torch.cuda.current_stream(dev)
     s_in, s_out = _copy_streams(dev)
     s_in.wait_stream(cur)
     s_out.wait_stream(cur)
-    for b in range(query.shape[0]):
-        with torch.cuda.stream(s_in):
+    # Device buffers for one batch entry, two sets used in turn. They are allocated on the
+    # current stream and every use on the copy streams is ordered before the end of this call
+    # (the two wait_stream calls at the bottom), so the caching allocator may hand them out again
+    # right away: no allocation - and no device synchronisation - in steady state.
+    with torch.cuda.device(dev):
+        sets = []
+        for _ in range(min(2, B)):
             qd, kd, vd = (torch.empty((1,) + tuple(t.shape[1:]), dtype=t.dtype, device=dev)
                           for t in (query, key, value))
-        od = torch.empty_like(qd)
-        ld = torch.empty(qd.shape[:-1], dtype=torch.float32, device=dev)
-        for t in (qd, kd, vd):
-            t.record_stream(cur)
-        od.record_stream(s_out)
-        ld.record_stream(s_out)
+            sets.append((qd, kd, vd, torch.empty_like(qd),
+                         torch.empty(qd.shape[:-1], dtype=torch.float32, device=dev)))
+        with torch.cuda.stream(s_in):
+            # extra tokens are small: all batch entries at once, ahead of everything else
+            akd = add_k.to(dev, non_blocking=True) if add_k is not None else None
+            avd = add_v.to(dev, non_blocking=True) if add_v is not None else None
+    drained = [None, None]   # per set: event after the last D2H copy that read it
+    for b in range(B):
+        qd, kd, vd, od, ld = sets[b % 2]
+        if drained[b % 2] is not None:
+            s_in.wait_event(drained[b % 2])   # entry b - 2 has left these buffers
         have = 0      # key/value frames of this batch entry already on their way to the device
         for a, e, lo, hi in slabs:
             with torch.cuda.stream(s_in):
@@ -142,11 +155,15 @@ def _stream_slabs(query, key, value, plan, scale, out, lse, dev):
             cur.wait_event(arrived)
             fna_forward_slab(qd[:, a:e], kd[:, lo:hi], vd[:, lo:hi], shape, a, lo, plan["ks"],
                              plan["st"], plan["ca"], scale, plan["tq"], plan["tkv"],
-                             out=od[:, a:e], lse=ld[:, a:e])
+                             out=od[:, a:e], lse=ld[:, a:e],
+                             additional_keys=akd[b:b + 1] if akd is not None else None,
+                             additional_values=avd[b:b + 1] if avd is not None else None)
             done = cur.record_event()
             with torch.cuda.stream(s_out):
                 s_out.wait_event(done)
                 out[b:b + 1, a:e].copy_(od[:, a:e], non_blocking=True)
                 lse[b:b + 1, a:e].copy_(ld[:, a:e], non_blocking=True)
+        drained[b % 2] = s_out.record_event()
     cur.wait_stream(s_out)
+    cur.wait_stream(s_in)
     return out, lse

@@ -227,7 +227,8 @@ def fna_forward_slab(q_local: Tensor, k_slab: Tensor, v_slab: Tensor,
                      is_causal: Sequence[bool], scale: Optional[float] = None,
                      q_tile_shape=None, kv_tile_shape=None, clip: bool = False,
                      permuted: bool = False, out: Optional[Tensor] = None,
-                     lse: Optional[Tensor] = None) -> Tuple[Tensor, Tensor]:
+                     lse: Optional[Tensor] = None, additional_keys: Optional[Tensor] = None,
+                     additional_values: Optional[Tensor] = None) -> Tuple[Tensor, Tensor]:
     """Attention for query coordinates ``[q_origin0, q_origin0 + q_local.shape[1])`` of axis 0
     against a key/value slab that starts at coordinate ``kv_origin0`` (no communication here).
     One launch on the slabs as they lie (`b200na_na_forward_direct_sharded`); tile shapes a
@@ -235,7 +236,8 @@ def fna_forward_slab(q_local: Tensor, k_slab: Tensor, v_slab: Tensor,
     `b200na_fna_forward_sharded` -> unpermute. ``clip=True``: partial attention over the keys the
     slab holds (windows cut to it; a query with no key there gets O = 0, LSE = -inf), to be
     combined with the other parts by `merge_attentions`. `out` / `lse` (contiguous, the slab's
-    shape) receive the result when given (direct launch only)."""
+    shape) receive the result when given, `additional_keys` / `additional_values`
+    ``[B, M, Hkv, D]`` are attended by every query (both: direct launch only)."""
     import ctypes
 
     from . import _lib
@@ -253,9 +255,10 @@ def fna_forward_slab(q_local: Tensor, k_slab: Tensor, v_slab: Tensor,
             tuple(bool(c) for c in is_causal))
     dil = (1,) * nd
     if permuted or not direct_layout_supported(q_tile_shape, kv_tile_shape, dil):
-        if clip:
-            raise NotImplementedError("partial (clipped) slab attention needs tile shapes the "
-                                      "kernel can gather from the slabs directly")
+        if clip or additional_keys is not None or out is not None:
+            raise NotImplementedError("partial (clipped) slab attention, extra tokens and "
+                                      "caller-provided outputs need tile shapes the kernel can "
+                                      "gather from the slabs directly")
         return _fna_forward_slab_permuted(q_local, k_slab, v_slab, global_shape, q_origin0,
                                           kv_origin0, kernel_size, stride, is_causal, scale,
                                           q_tile_shape, kv_tile_shape)
@@ -273,7 +276,11 @@ def fna_forward_slab(q_local: Tensor, k_slab: Tensor, v_slab: Tensor,
     kv_origin = (int(kv_origin0),) + (0,) * (nd - 1)
     with torch.cuda.device(q_local.device):
         _lib.check(_lib.lib.b200na_na_forward_direct_sharded(
-            _ptr(q_local), _ptr(k_slab), _ptr(v_slab), _ptr(out), _ptr(lse), nd,
+            _ptr(q_local), _ptr(k_slab), _ptr(v_slab),
+            _ptr(additional_keys.contiguous()) if additional_keys is not None else None,
+            _ptr(additional_values.contiguous()) if additional_keys is not None else None,
+            0 if additional_keys is None else int(additional_keys.shape[1]),
+            _ptr(out), _ptr(lse), nd,
             _lib.ints(global_shape), _lib.ints(kernel_size), _lib.ints(stride),
             _lib.ints([1 if c else 0 for c in is_causal]), _lib.ints(q_tile_shape),
             _lib.ints(kv_tile_shape), _lib.ints(q_origin), _lib.ints(q_local.shape[1:1 + nd]),

@@ -104,23 +104,29 @@ def test_host_operand_entry_point_matches_the_device_call():
 
 @pytest.mark.gpu
 def test_host_operand_entry_point_streams_slabs_of_the_outermost_axis():
-    """Undilated 16-bit problems without extra tokens go through the GPU slab by slab along axis 0
-    (the copies of one slab overlap the kernel of another); same result as the device call."""
+    """Undilated 16-bit problems go through the GPU slab by slab along axis 0 (the copies of one
+    slab overlap the kernel of another), extra tokens included; same result as the device call."""
+    from natten_b200 import host_io
     torch.manual_seed(10)
-    for shape, ks, st, ca in [((64, 24), (9, 7), (1, 2), (True, False)),
-                              ((48, 8, 8), (5, 4, 4), (1, 2, 2), (False, False, False)),
-                              ((4096,), (300,), (1,), (False,))]:
-        q, k, v = (torch.randn(2, *shape, 2, 64).half().pin_memory() for _ in range(3))
-        from natten_b200 import host_io
+    for shape, ks, st, ca, n_extra in [((64, 24), (9, 7), (1, 2), (True, False), 0),
+                                       ((48, 8, 8), (5, 4, 4), (1, 2, 2), (False, False, False), 40),
+                                       ((4096,), (300,), (1,), (False,), 0)]:
+        q, k, v = (torch.randn(3, *shape, 2, 64).half().pin_memory() for _ in range(3))
+        ak = av = None
+        if n_extra:
+            ak, av = (torch.randn(3, n_extra, 2, 64).half().pin_memory() for _ in range(2))
         assert host_io._slab_plan(q, k, ks, st, 1, ca) is not None
         fn = {1: nb.na1d, 2: nb.na2d, 3: nb.na3d}[len(shape)]
         want_o, want_l = fn(q.cuda(), k.cuda(), v.cuda(), kernel_size=ks, stride=st, is_causal=ca,
-                            return_lse=True)
-        out, lse = nb.na_forward_from_host(q, k, v, ks, st, 1, ca)
-        torch.cuda.current_stream().synchronize()
-        assert L.device_status() == 0
-        assert (out.float() - want_o.cpu().float()).abs().max().item() <= 1e-2
-        assert (lse - want_l.cpu()).abs().max().item() <= 2e-3
+                            additional_keys=ak.cuda() if n_extra else None,
+                            additional_values=av.cuda() if n_extra else None, return_lse=True)
+        for _ in range(2):      # the second call reuses the first one's device buffers
+            out, lse = nb.na_forward_from_host(q, k, v, ks, st, 1, ca, additional_keys=ak,
+                                               additional_values=av)
+            torch.cuda.current_stream().synchronize()
+            assert L.device_status() == 0
+            assert (out.float() - want_o.cpu().float()).abs().max().item() <= 1e-2
+            assert (lse - want_l.cpu()).abs().max().item() <= 2e-3
 
 
 def test_reference_backend_names_and_config_listing():
