@@ -116,12 +116,14 @@ def algorithmic_flops(cfg, units=None) -> float:
     return 4.0 * D * pairs * (B * H if units is None else units)
 
 
-# DRAM traffic of the attention kernel per (batch x head) unit, bytes, from the ncu capture of a
-# reduced case summarised in profiles/fna_fwd_kernel_c2.md (dram__bytes_read.sum +
-# dram__bytes_write.sum of one launch / units in that launch); scaled by the units of a launch.
+# DRAM traffic of the attention kernel per (batch x head) unit, bytes, from ncu captures of reduced
+# cases (dram__bytes_read.sum + dram__bytes_write.sum of one launch / units in that launch),
+# summarised in profiles/fna_fwd_kernel_c2.md and profiles/fna_fwd_kernel_c5_c4_c3.md; scaled by
+# the units of a launch.
 NCU_TRAFFIC_PER_UNIT = {"c2": (202.86e6 + 49.00e6) / 8,
-                        # profiles/fna_fwd_kernel_c4.md: 4 heads captured
-                        "c4": (204.06e6 + 50.56e6) / 4}
+                        "c3": (50.49e6 + 2.18e6) / 4,
+                        "c4": (204.81e6 + 51.43e6) / 4,
+                        "c5": (473.82e6 + 141.28e6) / 4}
 
 
 def read_peaks():
