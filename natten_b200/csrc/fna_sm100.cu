@@ -108,7 +108,7 @@ struct FnaParams {
   long long* prof;  // [grid][4 roles][8] cycle counters (instrumented builds only)
 #endif
 #ifdef B200NA_TEST_HOOKS
-  int test_withhold;  // test-hook build: CTA 0 keeps back the record of its n-th tile (0 = off)
+  int test_withhold;  // test-hook build: every CTA keeps back the record of its n-th tile (0 = off)
 #endif
 };
 
@@ -986,7 +986,7 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             if (kv == 0) {
               tile_rec[tseq % kTileRecs] = rec;
 #ifdef B200NA_TEST_HOOKS
-              if (!(blockIdx.x == 0 && p.test_withhold != 0 && (int)tseq + 1 == p.test_withhold))
+              if (!(p.test_withhold != 0 && (int)tseq + 1 == p.test_withhold))
 #endif
               ptx::mbar_arrive(bars.rec_full + tseq % kTileRecs);
               ++tseq;
@@ -1631,7 +1631,7 @@ extern "C" B200NA_API void b200na_debug_set_prof(void* buf) {
 #endif
 
 #ifdef B200NA_TEST_HOOKS
-// Test-hook build only (never the product library): from now on the load warp of CTA 0 keeps
+// Test-hook build only (never the product library): from now on the load warp of every CTA keeps
 // back the record of its n-th key/value tile, so that the wait for it expires; 0 switches it off.
 extern "C" B200NA_API int b200na_test_withhold_record(int n) {
   b200na::g_test_withhold = n;
