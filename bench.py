@@ -429,7 +429,11 @@ def spatial_subrecord(cfg, world, rank, dev, barrier, steps):
     from natten_b200 import sharding
     _, dt, B, H, shape, D, ks, st, di, ca, _, _ = cfg
     dtype = {"bf16": torch.bfloat16, "fp16": torch.float16}[dt]
-    plan = sharding.make_halo_plan(shape[0], world, ks[0], st[0], ca[0])
+    import natten_b200 as nb
+    q_tile, _ = nb.choose_tile_shapes(shape, ks, st, di, ca)
+    # slabs of equal attention work (the first 15 frames of a causal axis have shorter windows)
+    plan = sharding.make_halo_plan(shape[0], world, ks[0], st[0], ca[0], balanced=True,
+                                   align=q_tile[0])
     t0, t1 = plan.slabs[rank]
     def frames(which, a, b):
         # frame t of tensor `which` is a function of (which, t) alone, so a rank can rebuild the

@@ -1167,6 +1167,13 @@ int smem_bytes_of(int D, int dtype) {
   return D == 128 ? Smem<128, 2>::kBytes : Smem<64, 2>::kBytes;
 }
 
+// shared memory of the event trace of instrumented builds (none in the product build)
+#if defined(B200NA_PROFILE) && B200NA_PROFILE >= 2
+constexpr int kTraceSmem = 8192;
+#else
+constexpr int kTraceSmem = 0;
+#endif
+
 struct DeviceState {
   bool ready = false;
   int sms = 0;
@@ -1198,7 +1205,7 @@ int device_state(DeviceState** out) {
           if (!variant_supported(D, dtypes[t])) continue;
           const void* fn = kernel_variant(D, dtypes[t], nd);
           B200NA_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               smem_bytes_of(D, dtypes[t]) + 8192));
+                                               smem_bytes_of(D, dtypes[t]) + kTraceSmem));
           cudaFuncAttributes fa;
           B200NA_CUDA_TRY(cudaFuncGetAttributes(&fa, fn));
           // one CTA of kThreads threads must fit the register file
@@ -1269,11 +1276,7 @@ int launch_fna(const void* q, const void* k, const void* v, FnaParams& p, int D,
   const int grid = (int)(p.total_work < st->sms ? p.total_work : st->sms);
   const void* fn = kernel_variant(D, dtype, p.ndim);
   void* args[] = {(void*)&tq, (void*)&tk, (void*)&tv, (void*)&tek, (void*)&tev, (void*)&p};
-#if defined(B200NA_PROFILE) && B200NA_PROFILE >= 2
-  constexpr int kExtraSmem = 8192;
-#else
-  constexpr int kExtraSmem = 0;
-#endif
+  constexpr int kExtraSmem = kTraceSmem;
   B200NA_CUDA_TRY(cudaLaunchKernel(fn, dim3(grid), dim3(kThreads), args,
                                    smem_bytes_of(D, dtype) + kExtraSmem,
                                    stream));

@@ -501,7 +501,7 @@ def na_forward_op(query: Tensor, key: Tensor, value: Tensor, additional_keys: Op
         # one kernel on the caller's layout: no permuted copies of Q/K/V/O/LSE at all
         return fna_forward_direct(query, key, value, kernel_size, stride, dilation, is_causal,
                                   scale, q_tile_shape, kv_tile_shape, additional_keys,
-                                  additional_values)
+                                  additional_values, _inside_op=True)
     return fna_forward_permuted(query.contiguous(), key.contiguous(), value.contiguous(),
                                 kernel_size, stride, dilation, is_causal, scale, q_tile_shape,
                                 kv_tile_shape, additional_keys, additional_values)
@@ -703,16 +703,19 @@ def fna_forward_direct(query: Tensor, key: Tensor, value: Tensor, kernel_size: D
                        stride: DimensionType, dilation: DimensionType, is_causal: CausalArgType,
                        scale: float, q_tile_shape: DimensionType, kv_tile_shape: DimensionType,
                        additional_keys: Optional[Tensor] = None,
-                       additional_values: Optional[Tensor] = None) -> Tuple[Tensor, Tensor]:
+                       additional_values: Optional[Tensor] = None,
+                       _inside_op: bool = False) -> Tuple[Tensor, Tensor]:
     """The fused kernel on the original heads-last layout: what the reference does as
     permute -> kernel -> unpermute (src/natten/backends/blackwell_fna.py:111-165) in one launch,
     the tile gathers (dilation included) done by the kernel's tensor-map loads."""
     q, k, v = query, key, value   # token-strided views are fine, see ops.na_forward_direct
     ak = additional_keys.contiguous() if additional_keys is not None else None
     av = additional_values.contiguous() if additional_values is not None else None
-    out, lse = ops.na_forward_direct(q, k, v, ak, av, list(kernel_size), list(stride),
-                                     list(dilation), [bool(c) for c in is_causal], float(scale),
-                                     list(q_tile_shape), list(kv_tile_shape))
+    op = getattr(ops.na_forward_direct, "raw", ops.na_forward_direct) if _inside_op \
+        else ops.na_forward_direct
+    out, lse = op(q, k, v, ak, av, list(kernel_size), list(stride), list(dilation),
+                  [bool(c) for c in is_causal], float(scale), list(q_tile_shape),
+                  list(kv_tile_shape))
     return out, lse
 
 

@@ -48,6 +48,9 @@ def _op(name: str, fake: Callable):
         op = torch.library.custom_op(f"{NAMESPACE}::{name}", fn, mutates_args=(),
                                      device_types="cuda")
         op.register_fake(fake)
+        # the plain function, for callers that already run inside another op's body (a second
+        # trip through the dispatcher would only add host time)
+        op.raw = fn
         return op
     return wrap
 
