@@ -102,9 +102,11 @@ B200NA_API int b200na_token_unpermute(const void* in, void* out, int ndim, const
  *   qkv_shape: original token layout X; q_shape / kv_shape: padded per-group extents R_a*T_a
  *   (prod = Sq / Skv). prod(q_tile) must be 256 and prod(kv_tile) 128; tiles divide the shapes.
  *   kernel/stride/dilation/causal: the reference's kernel_size / stride / dilation / is_causal.
- *   dtype: B200NA_F16 or B200NA_BF16 with D in {64, 128}, or B200NA_E4M3 / B200NA_E5M2 with
- *   D = 128 (the reference's 8-bit forward, csrc/src/blackwell_fna_forward.cu:178-191: fp32
- *   accumulation and softmax, P rounded to e4m3 before P.V, O in the operand type);
+ *   dtype: B200NA_F16 or B200NA_BF16 with D a multiple of 8, or B200NA_E4M3 / B200NA_E5M2 with D
+ *   a multiple of 16 (the reference's rules, csrc/src/blackwell_fna_forward.cu:123-138, 178-191;
+ *   8-bit: fp32 accumulation and softmax, P rounded to e4m3 before P.V, O in the operand type),
+ *   8 <= D <= 128. The kernels are built for 64 and 128 channels (8-bit: 128); the channels a
+ *   smaller head dim lacks are zeros the tensor-map boxes fill in, and O rows are D wide.
  *   Hq % Hkv == 0. scale multiplies q.k.
  * Rows of o/lse that correspond to padding tokens are left unspecified.
  */
@@ -142,7 +144,10 @@ B200NA_API int b200na_fna_forward_extra_kv(
  * Results are those of b200na_token_permute + b200na_fna_forward_extra_kv +
  * b200na_token_unpermute with the same tile shapes.
  *   q_tile / kv_tile: prod = 256 / 128; tile[a] * dilation[a] <= 256 and dilation[a] <= 8 on
- *   every axis, otherwise B200NA_ERR_UNSUPPORTED (use the permuted path then).
+ *   every axis, otherwise B200NA_ERR_UNSUPPORTED (use the permuted path then). Also
+ *   B200NA_ERR_UNSUPPORTED: a head dim other than 64 / 128 (8-bit: 128) on a 3-D layout with
+ *   B > 1 (the tensor map then has no axis left for the batch entry; call per batch entry, or
+ *   use the permuted path).
  *   add_k / add_v [B, n_extra, Hkv, D]: optional extra tokens every query attends (n_extra = 0
  *   and NULL for none).
  */
@@ -275,8 +280,8 @@ B200NA_API int b200na_na_forward_static(const void* q, const void* k, const void
  * used for the extra (cross-attention) KV tokens and the self-attention fast path.
  *   q: [B, Nq, Hq, D]; k, v: [B, Nk, Hkv, D]; o: [B, Nq, Hq, D]; lse: [B, Nq, Hq] or NULL.
  *   causal != 0 requires Nq == Nk (query i sees keys 0..i). Nq, Nk need not be tile multiples.
- *   fp16/bf16 with D in {64, 128} run on the tensor cores; fp32 operands and other head dims
- *   (D <= 256) run on CUDA cores with fp32 arithmetic.
+ *   fp16/bf16 with D a multiple of 8 up to 128 (8-bit floats: of 16) run on the tensor cores;
+ *   fp32 operands and other head dims (D <= 256) run on CUDA cores with fp32 arithmetic.
  */
 B200NA_API int b200na_fmha_forward(const void* q, const void* k, const void* v, void* o, float* lse, int B,
                         int Nq, int Nk, int Hq, int Hkv, int D, int dtype, float scale, int causal,

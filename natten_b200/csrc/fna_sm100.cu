@@ -95,6 +95,8 @@ struct FnaParams {
   int n_extra;              // extra key/value tokens every query attends (0 = none)
   int extra_tiles;          // ceil(n_extra / 128): KV tiles appended to every item's walk
   int Bp, Hq, Hkv;
+  int d_real;               // head dim of the tensors (<= the kernel's D; the rest reads as zeros)
+  int sep_heads;            // direct: tensor maps list the head as an axis of its own (d_real < D)
   int Sq, Skv;              // rows per batch' in the q / kv tensors
   int n_qtiles;             // ceil(Sq / 256)
   long long total_work;     // n_qtiles * Hq * Bp
@@ -706,7 +708,9 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         for (int v4 = 0; v4 < 32 / kPer; ++v4)
           pk[ch * (32 / kPer) + v4] = pack_out16<kType>(orr + v4 * kPer, inv);
       }
-      uint8_t* const orow = valid ? o_ptr + (out_row * D + part * (D / 2)) * kES : nullptr;
+      // rows of the output tensor are d_real elements wide; chunks past that are not stored
+      uint8_t* const orow = valid ? o_ptr + (out_row * p.d_real + part * (D / 2)) * kES : nullptr;
+      const int my_chunks = imin(imax((p.d_real - part * (D / 2)) / kPer, 0), kChunks);
       uint4* const stage = reinterpret_cast<uint4*>(smem + SM::kStageOff + warp * SM::kStageBytes);
 #pragma unroll
       for (int rd = 0; rd < 32 / kRowsPerRound; ++rd) {
@@ -726,7 +730,8 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           // the row's address lives in the lane that owns the row (null: padding row)
           const unsigned long long rp = __shfl_sync(
               0xffffffffu, (unsigned long long)(uintptr_t)orow, rd * kRowsPerRound + lr);
-          if (rp != 0ull) *reinterpret_cast<uint4*>((uint8_t*)(uintptr_t)rp + cidx * 16) = val;
+          if (rp != 0ull && cidx < my_chunks)
+            *reinterpret_cast<uint4*>((uint8_t*)(uintptr_t)rp + cidx * 16) = val;
         }
       }
       if (p.lse != nullptr && valid && part == 0)
@@ -943,8 +948,16 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
               for (int a = 0; a < B200NA_MAX_DIM; ++a)
                 x[a] = (it.q_lo[a] - p.q_org[a] +
                         ((h && a == p.half_axis) ? (p.Tq[a] >> 1) : 0)) * p.dil[a] + it.g[a];
-              ptx::tma_load_5d(q_sm + h * kTileBytes + db * kBlockBytes, &tm_q, bars.q_full,
-                               it.h * D + db * kBlockElems, x[0], x[1], x[2], it.b);
+              if (p.sep_heads) {
+                // (channel, head, then the layout axes and the batch entry): channels past the
+                // tensor's head dim come back as zeros
+                if (NDIM < 3) x[NDIM] = it.b;
+                ptx::tma_load_5d(q_sm + h * kTileBytes + db * kBlockBytes, &tm_q, bars.q_full,
+                                 db * kBlockElems, it.h, x[0], x[1], x[2]);
+              } else {
+                ptx::tma_load_5d(q_sm + h * kTileBytes + db * kBlockBytes, &tm_q, bars.q_full,
+                                 it.h * D + db * kBlockElems, x[0], x[1], x[2], it.b);
+              }
             } else {
               ptx::tma_load_4d(q_sm + h * kTileBytes + db * kBlockBytes, &tm_q, bars.q_full,
                                db * kBlockElems, it.h, it.qt * kQTile + h * kHalf, bp);
@@ -993,7 +1006,11 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             }
             ptx::mbar_arrive_expect_tx(bars.kv_full + slot, kTileBytes);
             for (int db = 0; db < kDBlocks; ++db) {
-              if (p.direct && !is_extra)
+              if (p.direct && !is_extra && p.sep_heads)
+                ptx::tma_load_5d(kv_sm + slot * kTileBytes + db * kBlockBytes,
+                                 kv == 0 ? &tm_k : &tm_v, bars.kv_full + slot, db * kBlockElems, hk,
+                                 xk[0], NDIM < 2 ? it.b : xk[1], NDIM < 3 ? (NDIM < 2 ? 0 : it.b) : xk[2]);
+              else if (p.direct && !is_extra)
                 ptx::tma_load_5d(kv_sm + slot * kTileBytes + db * kBlockBytes,
                                  kv == 0 ? &tm_k : &tm_v, bars.kv_full + slot, hk * D + db * kBlockElems,
                                  xk[0], xk[1], xk[2], it.b);
@@ -1109,11 +1126,49 @@ int make_tensor_map(CUtensorMap* tm, const void* ptr, int dtype, int Bp, int S, 
 // it picks the tile's tokens of one dilation group; positions past an extent read as zeros.
 int make_tensor_map_direct(CUtensorMap* tm, const void* ptr, int dtype, int B, const int* X,
                            int H, int D, const int* tile, const int* dil,
-                           long long token_stride = 0) {
+                           long long token_stride = 0, int ndim_sep = 0) {
   EncodeTiledFn enc = nullptr;
   int rc = get_encode_fn(&enc);
   if (rc != B200NA_OK) return rc;
   const cuuint64_t es = (cuuint64_t)elem_bytes_of(dtype);
+  if (ndim_sep > 0) {
+    // Head dim below the kernel's: the head becomes an axis of its own, (D, H, then the ndim_sep
+    // layout axes, then the batch entry), so that a 128-byte box of channels reads zeros past
+    // the head dim instead of the next head. Five axes in all: three layout axes leave no room
+    // for the batch axis, so that case needs B == 1.
+    if (ndim_sep == 3 && B != 1) return B200NA_ERR_UNSUPPORTED;
+    const cuuint64_t row = (cuuint64_t)(token_stride > 0 ? token_stride : (long long)H * D) * es;
+    if (row % 16 != 0 || (D * es) % 16 != 0 || row < (cuuint64_t)H * D * es) return B200NA_ERR_ALIGNMENT;
+    cuuint64_t dims[5] = {(cuuint64_t)D, (cuuint64_t)H, 1, 1, 1};
+    cuuint64_t strides[4] = {(cuuint64_t)D * es, row, row, row};
+    cuuint32_t box[5] = {(cuuint32_t)(128 / es), 1, 1, 1, 1};
+    cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    // byte stride of layout axis a: row * prod(X[a+1 .. ndim_sep-1])
+    cuuint64_t tokens = 1;
+    for (int a = 0; a < ndim_sep; ++a) tokens *= (cuuint64_t)X[a];
+    cuuint64_t below = tokens;
+    for (int a = 0; a < ndim_sep; ++a) {
+      below /= (cuuint64_t)X[a];
+      dims[2 + a] = (cuuint64_t)X[a];
+      strides[1 + a] = row * below;
+      box[2 + a] = (cuuint32_t)(tile[a] * dil[a]);
+      estr[2 + a] = (cuuint32_t)dil[a];
+      if (box[2 + a] > 256 || estr[2 + a] > 8) return B200NA_ERR_UNSUPPORTED;
+    }
+    if (ndim_sep < 3) {
+      dims[2 + ndim_sep] = (cuuint64_t)B;
+      strides[1 + ndim_sep] = row * tokens;
+    }
+    for (int a = ndim_sep + 1; a < 3; ++a) strides[1 + a] = row * tokens * (cuuint64_t)B;  // extent 1
+    const CUresult r = enc(tm, tma_type_of(dtype), 5, const_cast<void*>(ptr), dims, strides, box,
+                           estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+      set_last_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
+      return B200NA_ERR_CUDA;
+    }
+    return B200NA_OK;
+  }
   // bytes from one token to the next: H * D elements when the tensor is contiguous, more when it
   // is a view into a wider row (q, k or v inside a fused [.., 3, H, D] projection output)
   const cuuint64_t row = (cuuint64_t)(token_stride > 0 ? token_stride : (long long)H * D) * es;
@@ -1144,11 +1199,21 @@ const void* kernel_for_ndim(int ndim) {
   if (ndim == 2) return (const void*)fna_fwd_kernel<D, kType, 2>;
   return (const void*)fna_fwd_kernel<D, kType, 3>;
 }
-// Supported (head dim, dtype) pairs: 16-bit floats with 64 / 128, 8-bit floats with 128.
+// Built (head dim, dtype) pairs: 16-bit floats with 64 / 128, 8-bit floats with 128.
 bool variant_supported(int D, int dtype) {
   if (dtype == B200NA_F16 || dtype == B200NA_BF16) return D == 64 || D == 128;
   if (dtype == B200NA_E4M3 || dtype == B200NA_E5M2) return D == 128;
   return false;
+}
+// Head dim of the kernel variant that takes tensors of head dim D (0: none). The reference's
+// Blackwell kernels accept every multiple of 8, 16 for 8-bit floats
+// (csrc/src/blackwell_fna_forward.cu:123-138, 178-191); here the missing channels of a smaller
+// head dim are zeros the tensor-map boxes fill in, and the output rows keep the tensors' width.
+int kernel_head_dim(int D, int dtype) {
+  if (D < 8 || D > 128) return 0;
+  if (dtype == B200NA_F16 || dtype == B200NA_BF16) return D % 8 != 0 ? 0 : (D <= 64 ? 64 : 128);
+  if (dtype == B200NA_E4M3 || dtype == B200NA_E5M2) return D % 16 != 0 ? 0 : 128;
+  return 0;
 }
 const void* kernel_variant(int D, int dtype, int ndim) {
   switch (dtype) {
@@ -1239,15 +1304,20 @@ int launch_fna(const void* q, const void* k, const void* v, FnaParams& p, int D,
   const uintptr_t al = reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) |
                        reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(p.o);
   if (al % 16 != 0) return B200NA_ERR_ALIGNMENT;
+  const int Dk = kernel_head_dim(D, dtype);   // D is the tensors' head dim, Dk the kernel's
+  if (Dk == 0) return B200NA_ERR_UNSUPPORTED;
+  p.d_real = D;
+  p.sep_heads = (p.direct && D != Dk) ? 1 : 0;
   CUtensorMap tq, tk, tv;
   if (p.direct) {
     int half_tile[B200NA_MAX_DIM];
     for (int a = 0; a < B200NA_MAX_DIM; ++a)
       half_tile[a] = (a == p.half_axis) ? p.Tq[a] / 2 : p.Tq[a];
     const int B = p.Bp / p.G;
-    if ((rc = make_tensor_map_direct(&tq, q, dtype, B, p.o_ext, p.Hq, D, half_tile, p.dil, p.tok_stride[0])) != B200NA_OK) return rc;
-    if ((rc = make_tensor_map_direct(&tk, k, dtype, B, p.kv_ext, p.Hkv, D, p.Tkv, p.dil, p.tok_stride[1])) != B200NA_OK) return rc;
-    if ((rc = make_tensor_map_direct(&tv, v, dtype, B, p.kv_ext, p.Hkv, D, p.Tkv, p.dil, p.tok_stride[2])) != B200NA_OK) return rc;
+    const int sep = p.sep_heads ? p.ndim : 0;
+    if ((rc = make_tensor_map_direct(&tq, q, dtype, B, p.o_ext, p.Hq, D, half_tile, p.dil, p.tok_stride[0], sep)) != B200NA_OK) return rc;
+    if ((rc = make_tensor_map_direct(&tk, k, dtype, B, p.kv_ext, p.Hkv, D, p.Tkv, p.dil, p.tok_stride[1], sep)) != B200NA_OK) return rc;
+    if ((rc = make_tensor_map_direct(&tv, v, dtype, B, p.kv_ext, p.Hkv, D, p.Tkv, p.dil, p.tok_stride[2], sep)) != B200NA_OK) return rc;
   } else {
     if ((rc = make_tensor_map(&tq, q, dtype, p.Bp, p.Sq, p.Hq, D)) != B200NA_OK) return rc;
     if ((rc = make_tensor_map(&tk, k, dtype, p.Bp, p.Skv, p.Hkv, D)) != B200NA_OK) return rc;
@@ -1274,11 +1344,11 @@ int launch_fna(const void* q, const void* k, const void* v, FnaParams& p, int D,
   p.total_work = (long long)p.n_qtiles * p.Hq * p.Bp;
   if (p.total_work == 0) return B200NA_OK;
   const int grid = (int)(p.total_work < st->sms ? p.total_work : st->sms);
-  const void* fn = kernel_variant(D, dtype, p.ndim);
+  const void* fn = kernel_variant(Dk, dtype, p.ndim);
   void* args[] = {(void*)&tq, (void*)&tk, (void*)&tv, (void*)&tek, (void*)&tev, (void*)&p};
   constexpr int kExtraSmem = kTraceSmem;
   B200NA_CUDA_TRY(cudaLaunchKernel(fn, dim3(grid), dim3(kThreads), args,
-                                   smem_bytes_of(D, dtype) + kExtraSmem,
+                                   smem_bytes_of(Dk, dtype) + kExtraSmem,
                                    stream));
   return B200NA_OK;
 }
@@ -1338,7 +1408,7 @@ int fna_forward_impl(
   if (!q || !k || !v || !o || !qkv_shape || !q_shape || !kv_shape || !kernel || !q_tile || !kv_tile)
     return B200NA_ERR_INVALID_ARGUMENT;
   if (Bp < 1 || Hq < 1 || Hkv < 1 || Hq % Hkv != 0) return B200NA_ERR_INVALID_ARGUMENT;
-  if (!variant_supported(D, dtype)) return B200NA_ERR_UNSUPPORTED;
+  if (kernel_head_dim(D, dtype) == 0) return B200NA_ERR_UNSUPPORTED;
   if (!(scale > 0.f)) return B200NA_ERR_INVALID_ARGUMENT;
   const bool sharded = q_origin != nullptr || kv_origin != nullptr || q_extent != nullptr;
   if (sharded && !(q_origin && kv_origin && q_extent)) return B200NA_ERR_INVALID_ARGUMENT;
@@ -1428,7 +1498,7 @@ int fna_direct_impl(const void* q, const void* k, const void* v, void* o, float*
   if (clip && !sharded) return B200NA_ERR_INVALID_ARGUMENT;
   if (n_extra < 0 || (n_extra > 0 && (!add_k || !add_v))) return B200NA_ERR_INVALID_ARGUMENT;
   if (B < 1 || Hq < 1 || Hkv < 1 || Hq % Hkv != 0) return B200NA_ERR_INVALID_ARGUMENT;
-  if (!variant_supported(D, dtype)) return B200NA_ERR_UNSUPPORTED;
+  if (kernel_head_dim(D, dtype) == 0) return B200NA_ERR_UNSUPPORTED;
   if (!(scale > 0.f)) return B200NA_ERR_INVALID_ARGUMENT;
   NaAxes ax;
   int rc = fill_axes(ax, ndim, shape, kernel, stride, dilation, causal);
@@ -1595,8 +1665,8 @@ extern "C" B200NA_API int b200na_fmha_forward(const void* q, const void* k, cons
   if (dtype != B200NA_F32 && dtype != B200NA_F16 && dtype != B200NA_BF16 &&
       dtype != B200NA_E4M3 && dtype != B200NA_E5M2)
     return B200NA_ERR_INVALID_ARGUMENT;
-  if (elem_bytes_of(dtype) == 1 && !variant_supported(D, dtype)) return B200NA_ERR_UNSUPPORTED;
-  if (!variant_supported(D, dtype) || !(scale > 0.f))
+  if (elem_bytes_of(dtype) == 1 && kernel_head_dim(D, dtype) == 0) return B200NA_ERR_UNSUPPORTED;
+  if (kernel_head_dim(D, dtype) == 0 || !(scale > 0.f))
     return simt_dense_forward(q, k, v, o, lse, B, Nq, Nk, Hq, Hkv, D, dtype, scale, causal,
                               reinterpret_cast<cudaStream_t>(stream));
   FnaParams p;

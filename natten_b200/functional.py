@@ -65,12 +65,23 @@ def _pad_head_dim(t: Tensor, padded_dim: int) -> Tensor:
     return torch.nn.functional.pad(t, (0, padded_dim - t.shape[-1]))
 
 
-def _tensor_core_supported(dtype: torch.dtype, head_dim: int) -> bool:
-    """Operand types of the tcgen05 kernels as built: fp16 / bf16 with head dim 64 or 128, 8-bit
-    floats (forward only) with head dim 128 (smaller head dims reach them zero-padded)."""
+def _reads_natively(dtype: torch.dtype, head_dim: int) -> bool:
+    """Head dims the forward kernels read without a padded copy: the kernels are built for 64 and
+    128 (8-bit floats: 128), and a smaller head dim that keeps rows 16-byte aligned (a multiple of
+    8, or 16 for 8-bit floats - the reference's rule, csrc/src/blackwell_fna_forward.cu:123-138,
+    178-191) is read through tensor-map boxes that return zeros for the missing channels."""
     if dtype in (torch.float16, torch.bfloat16):
-        return head_dim in TENSOR_CORE_HEAD_DIMS
-    return dtype in FP8_DTYPES and head_dim == FP8_HEAD_DIM
+        return 8 <= head_dim <= 128 and head_dim % 8 == 0
+    return dtype in FP8_DTYPES and 16 <= head_dim <= FP8_HEAD_DIM and head_dim % 16 == 0
+
+
+def _tensor_core_supported(dtype: torch.dtype, head_dim: int) -> bool:
+    """Operands the tcgen05 forward kernels take as they are (see `_reads_natively`)."""
+    return _reads_natively(dtype, head_dim)
+
+
+def _wants_grad(*tensors: Optional[Tensor]) -> bool:
+    return torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors)
 
 
 def _ptr(t: Optional[Tensor]):
@@ -329,6 +340,8 @@ def attention(query: Tensor, key: Tensor, value: Tensor, is_causal: bool = False
         raise NotImplementedError(f"natten_b200.attention does not support dtype {query.dtype}.")
     q, k, v = (t.contiguous() for t in (query, key, value))
     padded_dim = _padded_head_dim(query.dtype, D)   # see neighborhood_attention_generic
+    if padded_dim != D and _reads_natively(query.dtype, D) and not _wants_grad(query, key, value):
+        padded_dim = D
     if padded_dim != D:
         q, k, v = (_pad_head_dim(t, padded_dim) for t in (q, k, v))
     out, lse = ops.fmha_forward(q, k, v, bool(is_causal), float(scale))
@@ -405,6 +418,15 @@ def neighborhood_attention_generic(
     # the pad and the slice - far faster than the CUDA-core kernel despite the wasted columns.
     head_dim = query.shape[-1]
     padded_dim = _padded_head_dim(query.dtype, head_dim)
+    # Without gradients no copy is needed at all: the kernel reads the narrow rows through
+    # tensor-map boxes that fill the missing channels with zeros and writes narrow output rows
+    # (three layout axes leave the tensor map no room for a batch axis, so 3-D needs batch 1).
+    # The backward kernels are built for the padded head dims only, so a call that will be
+    # differentiated keeps the pad / slice pair, which autograd differentiates through.
+    if (padded_dim != head_dim and _reads_natively(query.dtype, head_dim)
+            and not _wants_grad(query, key, value, additional_keys, additional_values)
+            and (na_dim < 3 or query.shape[0] == 1)):
+        padded_dim = head_dim
     if padded_dim != head_dim:
         logger.debug("head dim %d zero-padded to %d for the tensor-core kernels", head_dim,
                      padded_dim)

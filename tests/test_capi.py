@@ -72,7 +72,10 @@ def _fna(**kw):
 def test_fna_rejects_bad_arguments_before_touching_cuda():
     assert _fna(q=None) == L.ERR_INVALID_ARGUMENT
     assert _fna(dtype=L.F32) == L.ERR_UNSUPPORTED           # fp32 goes through the CUDA-core entry
-    assert _fna(D=96) == L.ERR_UNSUPPORTED
+    assert _fna(D=100) == L.ERR_UNSUPPORTED                  # head dim must be a multiple of 8
+    assert _fna(D=136) == L.ERR_UNSUPPORTED                  # ... and at most 128
+    assert _fna(D=96, dtype=L.E4M3) != L.ERR_UNSUPPORTED     # 8-bit floats: multiples of 16
+    assert _fna(D=24, dtype=L.E4M3) == L.ERR_UNSUPPORTED
     assert _fna(ker=[1]) == L.ERR_INVALID_ARGUMENT           # kernel_size >= 2
     assert _fna(ker=[600]) == L.ERR_INVALID_ARGUMENT         # kernel * dilation <= extent
     assert _fna(ker=[8], st=[9]) == L.ERR_INVALID_ARGUMENT   # stride <= kernel

@@ -421,22 +421,48 @@ def test_unsupported_inputs_fail_loudly():
         nb.attention(q, q, q, cumulative_seqlen_Q=torch.zeros(2, dtype=torch.int32, device="cuda"))
 
 
-@pytest.mark.parametrize("D", [8, 32, 48, 80, 96])
-def test_odd_head_dims_run_padded_on_tensor_cores(D):
-    """fp16/bf16 head dims below 128 other than 64 are zero-padded to 64 / 128 for the tensor-core
-    kernel; results match the oracle like any other, for neighborhood and dense attention."""
+@pytest.mark.parametrize("D", [8, 32, 48, 80, 96, 20])
+def test_head_dims_the_kernels_are_not_built_for(D):
+    """fp16/bf16 head dims below 128 other than 64 run on the 64 / 128-channel tensor-core kernels:
+    multiples of 8 are read as they lie (zero-filled tensor-map boxes, narrow output rows; no
+    copies) when no gradient is needed, the same inputs with a gradient - and head dims like 20 -
+    go through a zero-padded copy. All of them match the oracle, for neighborhood and dense
+    attention, on the caller's layout, on permuted copies, 1-D to 3-D."""
     torch.manual_seed(D)
     q, k, v = (torch.randn(2, 20, 28, 2, D).bfloat16() for _ in range(3))
     ks, st, di, ca = (5, 7), (1, 2), (2, 1), (False, True)
-    out, lse = nb.na2d(q.cuda(), k.cuda(), v.cuda(), ks, st, di, ca, return_lse=True)
-    assert out.shape == q.shape and out.is_contiguous()
     want_o, want_l = oracle.na_forward(q.float().numpy(), k.float().numpy(), v.float().numpy(),
                                        ks, st, di, ca)
-    assert np.abs(out.float().cpu().numpy() - want_o).max() <= TOL_16
-    assert np.abs(lse.cpu().numpy() - want_l).max() <= TOL_16
+    for kwargs in ({}, {"permuted_layout": True}):
+        for grad in (False, True):
+            qc = q.cuda().requires_grad_(grad)
+            out, lse = nb.na2d(qc, k.cuda(), v.cuda(), ks, st, di, ca, return_lse=True,
+                               attention_kwargs=kwargs)
+            assert out.shape == q.shape and out.is_contiguous()
+            assert np.abs(out.detach().float().cpu().numpy() - want_o).max() <= TOL_16
+            assert np.abs(lse.detach().cpu().numpy() - want_l).max() <= TOL_16
     a, b, c = (t.flatten(1, 2)[:, :300] for t in (q, k, v))
     o2, l2 = nb.attention(a.cuda(), b.cuda(), c.cuda(), return_lse=True)
     w2, wl2 = oracle.dense_attention(a.float().numpy(), b.float().numpy(), c.float().numpy())
     assert L.device_status() == 0
     assert np.abs(o2.float().cpu().numpy() - w2).max() <= TOL_16
     assert np.abs(l2.cpu().numpy() - wl2).max() <= TOL_16
+    # 1-D with extra tokens and 3-D (batch 1: read as it lies; batch 2: padded copy)
+    q1, k1, v1 = (torch.randn(2, 500, 2, D).bfloat16() for _ in range(3))
+    ak, av = (torch.randn(2, 37, 2, D).bfloat16() for _ in range(2))
+    o1, l1 = nb.na1d(q1.cuda(), k1.cuda(), v1.cuda(), 33, 2, 1, True, additional_keys=ak.cuda(),
+                     additional_values=av.cuda(), return_lse=True)
+    w1, wl1 = oracle.na_forward(q1.float().numpy(), k1.float().numpy(), v1.float().numpy(), (33,),
+                                (2,), (1,), (True,), add_k=ak.float().numpy(),
+                                add_v=av.float().numpy())
+    assert np.abs(o1.float().cpu().numpy() - w1).max() <= TOL_16
+    assert np.abs(l1.cpu().numpy() - wl1).max() <= TOL_16
+    for batch in (1, 2):
+        q3, k3, v3 = (torch.randn(batch, 6, 10, 12, 2, D).bfloat16() for _ in range(3))
+        o3, l3 = nb.na3d(q3.cuda(), k3.cuda(), v3.cuda(), (3, 4, 5), (1, 2, 1), 1,
+                         (True, False, False), return_lse=True)
+        w3, wl3 = oracle.na_forward(q3.float().numpy(), k3.float().numpy(), v3.float().numpy(),
+                                    (3, 4, 5), (1, 2, 1), (1, 1, 1), (True, False, False))
+        assert np.abs(o3.float().cpu().numpy() - w3).max() <= TOL_16
+        assert np.abs(l3.cpu().numpy() - wl3).max() <= TOL_16
+    assert L.device_status() == 0
