@@ -166,14 +166,16 @@ def is_self_attention(input_tensor: Tensor, kernel_size: DimensionType, is_causa
     return all(k == x and not c for x, k, c in zip(input_size, kernel_size, is_causal))
 
 
-def check_tile_shape(na_dim: int, tile_shape: Any, name: str, product: int) -> DimensionType:
+def check_tile_shape(na_dim: int, tile_shape: Any, name: str, product) -> DimensionType:
+    """`product`: the number of tokens the tile must hold, or a tuple of allowed numbers."""
+    allowed = tuple(product) if isinstance(product, (tuple, list)) else (int(product),)
     if (not isinstance(tile_shape, Sequence) or len(tile_shape) != na_dim
             or not all(isinstance(v, int) and v >= 1 for v in tile_shape)):
         raise ValueError(f"`{name}` must be a tuple of {na_dim} positive integers, got {tile_shape=}.")
     prod = 1
     for v in tile_shape:
         prod *= v
-    if prod != product:
-        raise ValueError(f"`{name}` must have {product} elements for this backend, got "
-                         f"{tile_shape=} ({prod} elements).")
+    if prod not in allowed:
+        raise ValueError(f"`{name}` must have {' or '.join(str(a) for a in allowed)} elements for "
+                         f"this backend, got {tile_shape=} ({prod} elements).")
     return tuple(int(v) for v in tile_shape)

@@ -6,7 +6,7 @@
 #pragma once
 
 #ifdef B200NA_PROFILE
-#define TRACE(role, code) { if (blockIdx.x == 0 && trace_n_ < 1024) { p.prof[148 * 32 + (role) * 1024 + trace_n_] = (clock64() << 8) | (code); ++trace_n_; } }
+#define TRACE(role, code) { if (blockIdx.x == 0 && trace_n_ < 1024) { p.prof[296 * 32 + (role) * 1024 + trace_n_] = (clock64() << 8) | (code); ++trace_n_; } }
 #define PROF_DECL int trace_n_ = 0; long long prof_[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long prof_t_ = clock64(); const long long prof_t0_ = prof_t_;
 #define PROF_MARK(i) { const long long n_ = clock64(); prof_[i] += n_ - prof_t_; prof_t_ = n_; }
 #define PROF_FLUSH(role) { prof_[7] = clock64() - prof_t0_; for (int i_ = 0; i_ < 8; ++i_) p.prof[((long long)blockIdx.x * 4 + (role)) * 8 + i_] = prof_[i_]; }

@@ -36,17 +36,14 @@
 namespace b200na {
 namespace {
 
-constexpr int kQTile = 256;      // query rows per CTA work item
+constexpr int kQTile = 256;      // query rows of a two-half work item (a one-half item has kHalf)
 constexpr int kHalf = 128;       // rows per softmax warpgroup / per MMA (M)
 constexpr int kKVTile = 128;     // key/value rows per tile (N of QK^T, K of P.V)
-constexpr int kSoftmaxWarps = 16; // 2 halves x 2 column parts x 4 warps (one thread per row and part)
-constexpr int kSoftmaxThreadsPerHalf = 256;
-constexpr int kMmaWarp = 16;
-constexpr int kLoadWarp = 17;
-constexpr int kThreads = 576;    // 16 softmax warps + MMA warp + load warp
-// Registers are allocated to warps in groups of four, so 18 warps cost as much as 20: the
-// per-thread ceiling is 65536 / 640 = 102 -> 96, which the streaming softmax loop fits into.
-constexpr int kTmemCols = 512;
+constexpr int kSoftmaxThreadsPerHalf = 256;   // 2 column parts x 4 warps, one thread per row and part
+// A CTA has 8 softmax warps per half, an MMA-issuing warp and a load warp: 18 warps with two
+// halves (registers are allocated to warps in groups of four, so they cost as much as 20: the
+// per-thread ceiling is 65536 / 640 = 102 -> 96, which the streaming softmax loop fits into), 10
+// warps with one half, two such CTAs per SM (the same 640 thread slots).
 constexpr int kDescSlots = 4;     // work-item descriptors the load warp may run ahead by
 constexpr int kDescBytes = 128;
 constexpr int kTileRecs = 8;      // per-tile records in flight (more than the K/V ring holds tiles)
@@ -95,6 +92,7 @@ struct FnaParams {
   int n_extra;              // extra key/value tokens every query attends (0 = none)
   int extra_tiles;          // ceil(n_extra / 128): KV tiles appended to every item's walk
   int Bp, Hq, Hkv;
+  int halves;               // 128-row halves of a query tile: 2 (256-token tile) or 1 (128)
   int d_real;               // head dim of the tensors (<= the kernel's D; the rest reads as zeros)
   int sep_heads;            // direct: tensor maps list the head as an axis of its own (d_real < D)
   int Sq, Skv;              // rows per batch' in the q / kv tensors
@@ -279,13 +277,17 @@ __device__ __forceinline__ bool kv_tile_interior(const FnaParams& p, const Item&
   return in;
 }
 
-// ES = bytes per operand element (2: fp16 / bf16, 1: 8-bit floats)
-template <int D, int ES>
+// ES = bytes per operand element (2: fp16 / bf16, 1: 8-bit floats); kH = 128-row halves of the
+// query tile a CTA owns: 2 (one CTA per SM) or 1 (two CTAs per SM, each with half the shared
+// memory and half the tensor memory)
+template <int D, int ES, int kH>
 struct Smem {
   static constexpr int kTileBytes = kKVTile * D * ES;       // one K or V tile / one Q half
-  static constexpr int kStages = (kTileBytes >= 32768) ? 4 : 6;  // ring slots shared by K and V
+  // ring slots shared by K and V
+  static constexpr int kStages = kH == 2 ? ((kTileBytes >= 32768) ? 4 : 6)
+                                         : ((kTileBytes >= 32768) ? 2 : 4);
   static constexpr int kQOff = 0;
-  static constexpr int kKVOff = 2 * kTileBytes;
+  static constexpr int kKVOff = kH * kTileBytes;
   static constexpr int kPrefOff = kKVOff + kStages * kTileBytes;
   static constexpr int kPrefEntries = 136;                  // sum(T_a + 1) <= 128 + 1 + 2 + 2
   static constexpr int kXchgOff = kPrefOff + kPrefEntries * 16;   // row max / row sum exchange
@@ -300,8 +302,9 @@ struct Smem {
   // 1 KB per softmax warp: output rows are regrouped there so that stores cover whole rows
   static constexpr int kStageOff = (kMiscOff + 16 + 127) / 128 * 128;
   static constexpr int kStageBytes = 1024;
-  static constexpr int kBytes = kStageOff + kSoftmaxWarps * kStageBytes;
-  static_assert(kBytes <= 227 * 1024, "shared memory budget");
+  static constexpr int kBytes = kStageOff + 8 * kH * kStageBytes;
+  // two CTAs of the one-half variant share an SM: 228 KB minus 1 KB the system keeps per CTA
+  static_assert(kBytes <= (kH == 2 ? 227 * 1024 : 113 * 1024), "shared memory budget");
   // a record is overwritten kTileRecs tiles later; its readers lag the load warp by at most
   // the tiles the K/V ring holds plus one
   static_assert(kTileRecs >= kStages / 2 + 3, "per-tile record ring too short");
@@ -368,14 +371,27 @@ __device__ __forceinline__ void kv_tile_next(const FnaParams& p, const Item& it,
   w.lo[2] += p.Tkv[2];
 }
 
-template <int D, int kType, int NDIM>
-__global__ void __launch_bounds__(kThreads, 1)
+// kH = 2: the CTA owns a 256-row query tile as two halves that alternate on the tensor pipe, one
+// CTA per SM. kH = 1: a 128-row query tile per CTA and two CTAs per SM - the two tiles then walk
+// key/value boxes of their own (the union of the windows of 128 queries is much smaller than
+// that of 256 when windows are small) and their item boundaries are staggered, so one CTA's
+// pipeline fill and drain overlaps the other's steady state. Chosen per problem by the host
+// (query tile of 128 or 256 tokens).
+template <int D, int kType, int NDIM, int kH>
+__global__ void __launch_bounds__((8 * kH + 2) * 32, kH == 1 ? 2 : 1)
 fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_ek,
                const __grid_constant__ CUtensorMap tm_ev, const FnaParams p) {
   constexpr int kES = kType >= kTyE4m3 ? 1 : 2;   // bytes per operand element
   constexpr bool kF8 = kES == 1;
-  using SM = Smem<D, kES>;
+  // the CTA-shape constants of this variant (the file-level ones are the two-half values)
+  constexpr int kQTile = kHalf * kH;
+  constexpr int kSoftmaxWarps = 8 * kH;
+  constexpr int kMmaWarp = kSoftmaxWarps;
+  constexpr int kLoadWarp = kSoftmaxWarps + 1;
+  constexpr int kThreads = (kSoftmaxWarps + 2) * 32;
+  constexpr int kTmemCols = 256 * kH;
+  using SM = Smem<D, kES, kH>;
   constexpr int kStages = SM::kStages;
   constexpr int kTileBytes = SM::kTileBytes;
   constexpr int kBlockElems = 128 / kES;           // elements of one 128-byte column block
@@ -460,9 +476,10 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   __syncthreads();
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = __shfl_sync(0xffffffffu, *tmem_slot, 0);
-  // TMEM columns: S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [384,384+D); P aliases S.
+  // TMEM columns (kH = 2): S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [384,384+D); (kH = 1):
+  // S0 [0,128) O0 [128,128+D); P aliases S.
   auto s_col = [](int half) -> uint32_t { return (uint32_t)half * 128u; };
-  auto o_col = [](int half) -> uint32_t { return 256u + (uint32_t)half * 128u; };
+  auto o_col = [](int half) -> uint32_t { return (uint32_t)kH * 128u + (uint32_t)half * 128u; };
 
   if (warp < kSoftmaxWarps) {
     // ======================= softmax + correction + epilogue ===============================
@@ -831,7 +848,7 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         PROF2_MARK(1)
         ptx::tc_fence_after_sync();
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
+        for (int h = 0; h < kH; ++h) {
           issue_qk(h, kv_base + slot_k * kTileBytes);
           ptx::tc_commit_if(issue, bars.s_full + h);
         }
@@ -857,7 +874,7 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           const uint32_t v_addr = kv_base + slot_v * kTileBytes;
           const uint32_t k_addr = kv_base + slot_kn * kTileBytes;
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
+          for (int h = 0; h < kH; ++h) {
             if (!wait_all(bars.p_full + h, ph_p[h], abort_flag, p.status, (2 << 8) | kStPFull)) {
               alive = false; break;
             }
@@ -937,8 +954,8 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const int n_tiles = it.n_tiles, n_na = it.n_na, bp = it.bp, hk = it.hk;
         if (!wait_bar(bars.q_empty, ph_qe, abort_flag, p.status, (3 << 8) | kStQEmpty)) break;
         ph_qe ^= 1;
-        ptx::mbar_arrive_expect_tx(bars.q_full, 2 * kTileBytes);
-        for (int h = 0; h < 2; ++h)
+        ptx::mbar_arrive_expect_tx(bars.q_full, kH * kTileBytes);
+        for (int h = 0; h < kH; ++h)
           for (int db = 0; db < kDBlocks; ++db) {
             if (p.direct) {
               // box = half a query tile in the caller's layout; dilation is the box's element
@@ -1045,7 +1062,7 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #if defined(B200NA_PROFILE) && B200NA_PROFILE >= 2
   if (blockIdx.x == 0) {
     const uint32_t* tb = reinterpret_cast<const uint32_t*>(smem + SM::kBytes);
-    for (int i = threadIdx.x; i < 2048; i += kThreads) p.prof[148 * 32 + 4096 + i] = tb[i];
+    for (int i = threadIdx.x; i < 2048; i += kThreads) p.prof[296 * 32 + 4096 + i] = tb[i];
   }
 #endif
   if (*abort_flag) {
@@ -1194,10 +1211,15 @@ int make_tensor_map_direct(CUtensorMap* tm, const void* ptr, int dtype, int B, c
 }
 
 template <int D, int kType>
-const void* kernel_for_ndim(int ndim) {
-  if (ndim == 1) return (const void*)fna_fwd_kernel<D, kType, 1>;
-  if (ndim == 2) return (const void*)fna_fwd_kernel<D, kType, 2>;
-  return (const void*)fna_fwd_kernel<D, kType, 3>;
+const void* kernel_for_ndim(int ndim, int halves) {
+  if (halves == 1) {
+    if (ndim == 1) return (const void*)fna_fwd_kernel<D, kType, 1, 1>;
+    if (ndim == 2) return (const void*)fna_fwd_kernel<D, kType, 2, 1>;
+    return (const void*)fna_fwd_kernel<D, kType, 3, 1>;
+  }
+  if (ndim == 1) return (const void*)fna_fwd_kernel<D, kType, 1, 2>;
+  if (ndim == 2) return (const void*)fna_fwd_kernel<D, kType, 2, 2>;
+  return (const void*)fna_fwd_kernel<D, kType, 3, 2>;
 }
 // Built (head dim, dtype) pairs: 16-bit floats with 64 / 128, 8-bit floats with 128.
 bool variant_supported(int D, int dtype) {
@@ -1215,22 +1237,31 @@ int kernel_head_dim(int D, int dtype) {
   if (dtype == B200NA_E4M3 || dtype == B200NA_E5M2) return D % 16 != 0 ? 0 : 128;
   return 0;
 }
-const void* kernel_variant(int D, int dtype, int ndim) {
+const void* kernel_variant(int D, int dtype, int ndim, int halves) {
   switch (dtype) {
     case B200NA_F16:
-      return D == 128 ? kernel_for_ndim<128, kTyF16>(ndim) : kernel_for_ndim<64, kTyF16>(ndim);
+      return D == 128 ? kernel_for_ndim<128, kTyF16>(ndim, halves)
+                      : kernel_for_ndim<64, kTyF16>(ndim, halves);
     case B200NA_BF16:
-      return D == 128 ? kernel_for_ndim<128, kTyBf16>(ndim) : kernel_for_ndim<64, kTyBf16>(ndim);
+      return D == 128 ? kernel_for_ndim<128, kTyBf16>(ndim, halves)
+                      : kernel_for_ndim<64, kTyBf16>(ndim, halves);
     case B200NA_E4M3:
-      return kernel_for_ndim<128, kTyE4m3>(ndim);
+      return kernel_for_ndim<128, kTyE4m3>(ndim, halves);
     default:
-      return kernel_for_ndim<128, kTyE5m2>(ndim);
+      return kernel_for_ndim<128, kTyE5m2>(ndim, halves);
   }
 }
-int smem_bytes_of(int D, int dtype) {
-  if (elem_bytes_of(dtype) == 1) return Smem<128, 1>::kBytes;
-  return D == 128 ? Smem<128, 2>::kBytes : Smem<64, 2>::kBytes;
+int smem_bytes_of(int D, int dtype, int halves) {
+  if (halves == 1) {
+    if (elem_bytes_of(dtype) == 1) return Smem<128, 1, 1>::kBytes;
+    return D == 128 ? Smem<128, 2, 1>::kBytes : Smem<64, 2, 1>::kBytes;
+  }
+  if (elem_bytes_of(dtype) == 1) return Smem<128, 1, 2>::kBytes;
+  return D == 128 ? Smem<128, 2, 2>::kBytes : Smem<64, 2, 2>::kBytes;
 }
+// threads of a CTA and CTAs per SM of the one- and two-half variants
+inline int threads_of(int halves) { return (8 * halves + 2) * 32; }
+inline int ctas_per_sm(int halves) { return halves == 1 ? 2 : 1; }
 
 // shared memory of the event trace of instrumented builds (none in the product build)
 #if defined(B200NA_PROFILE) && B200NA_PROFILE >= 2
@@ -1266,16 +1297,18 @@ int device_state(DeviceState** out) {
     const int dtypes[4] = {B200NA_F16, B200NA_BF16, B200NA_E4M3, B200NA_E5M2};
     for (int t = 0; t < 4; ++t)
       for (int D = 64; D <= 128; D += 64)
-        for (int nd = 1; nd <= B200NA_MAX_DIM; ++nd) {
-          if (!variant_supported(D, dtypes[t])) continue;
-          const void* fn = kernel_variant(D, dtypes[t], nd);
-          B200NA_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               smem_bytes_of(D, dtypes[t]) + kTraceSmem));
-          cudaFuncAttributes fa;
-          B200NA_CUDA_TRY(cudaFuncGetAttributes(&fa, fn));
-          // one CTA of kThreads threads must fit the register file
-          if (fa.numRegs * kThreads > 65536) return B200NA_ERR_UNSUPPORTED;
-        }
+        for (int nd = 1; nd <= B200NA_MAX_DIM; ++nd)
+          for (int halves = 1; halves <= 2; ++halves) {
+            if (!variant_supported(D, dtypes[t])) continue;
+            const void* fn = kernel_variant(D, dtypes[t], nd, halves);
+            B200NA_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 smem_bytes_of(D, dtypes[t], halves) + kTraceSmem));
+            cudaFuncAttributes fa;
+            B200NA_CUDA_TRY(cudaFuncGetAttributes(&fa, fn));
+            // the CTAs of an SM must fit the register file
+            if (fa.numRegs * threads_of(halves) * ctas_per_sm(halves) > 65536)
+              return B200NA_ERR_UNSUPPORTED;
+          }
     void* sp = nullptr;
     B200NA_CUDA_TRY(cudaGetSymbolAddress(&sp, g_status_word));
     st.status_ptr = reinterpret_cast<int*>(sp);
@@ -1312,7 +1345,7 @@ int launch_fna(const void* q, const void* k, const void* v, FnaParams& p, int D,
   if (p.direct) {
     int half_tile[B200NA_MAX_DIM];
     for (int a = 0; a < B200NA_MAX_DIM; ++a)
-      half_tile[a] = (a == p.half_axis) ? p.Tq[a] / 2 : p.Tq[a];
+      half_tile[a] = (a == p.half_axis && p.halves == 2) ? p.Tq[a] / 2 : p.Tq[a];
     const int B = p.Bp / p.G;
     const int sep = p.sep_heads ? p.ndim : 0;
     if ((rc = make_tensor_map_direct(&tq, q, dtype, B, p.o_ext, p.Hq, D, half_tile, p.dil, p.tok_stride[0], sep)) != B200NA_OK) return rc;
@@ -1343,12 +1376,13 @@ int launch_fna(const void* q, const void* k, const void* v, FnaParams& p, int D,
 #endif
   p.total_work = (long long)p.n_qtiles * p.Hq * p.Bp;
   if (p.total_work == 0) return B200NA_OK;
-  const int grid = (int)(p.total_work < st->sms ? p.total_work : st->sms);
-  const void* fn = kernel_variant(Dk, dtype, p.ndim);
+  const long long slots = (long long)st->sms * ctas_per_sm(p.halves);
+  const int grid = (int)(p.total_work < slots ? p.total_work : slots);
+  const void* fn = kernel_variant(Dk, dtype, p.ndim, p.halves);
   void* args[] = {(void*)&tq, (void*)&tk, (void*)&tv, (void*)&tek, (void*)&tev, (void*)&p};
   constexpr int kExtraSmem = kTraceSmem;
-  B200NA_CUDA_TRY(cudaLaunchKernel(fn, dim3(grid), dim3(kThreads), args,
-                                   smem_bytes_of(Dk, dtype) + kExtraSmem,
+  B200NA_CUDA_TRY(cudaLaunchKernel(fn, dim3(grid), dim3(threads_of(p.halves)), args,
+                                   smem_bytes_of(Dk, dtype, p.halves) + kExtraSmem,
                                    stream));
   return B200NA_OK;
 }
@@ -1460,13 +1494,14 @@ int fna_forward_impl(
     p.G *= p.dil[a];
     sq *= qs; skv *= ks; tq *= p.Tq[a]; tkv *= p.Tkv[a];
   }
-  if (tq != kQTile || tkv != kKVTile) return B200NA_ERR_INVALID_ARGUMENT;
+  if ((tq != kQTile && tq != kHalf) || tkv != kKVTile) return B200NA_ERR_INVALID_ARGUMENT;
+  p.halves = (int)(tq / kHalf);
   if (Bp % p.G != 0) return B200NA_ERR_INVALID_ARGUMENT;
   if (sq > 0x7fffffffLL || skv > 0x7fffffffLL) return B200NA_ERR_UNSUPPORTED;
   p.dense = 0;
   p.Bp = Bp; p.Hq = Hq; p.Hkv = Hkv;
   p.Sq = (int)sq; p.Skv = (int)skv;
-  p.n_qtiles = (int)(sq / kQTile);
+  p.n_qtiles = (int)(sq / tq);
   p.scale = scale;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.o = o;
@@ -1560,8 +1595,10 @@ int fna_direct_impl(const void* q, const void* k, const void* v, void* o, float*
     tq *= p.Tq[a]; tkv *= p.Tkv[a];
     tokens *= p.X[a];
   }
-  if (tq != kQTile || tkv != kKVTile) return B200NA_ERR_INVALID_ARGUMENT;
-  if (p.Tq[p.half_axis] % 2 != 0) return B200NA_ERR_UNSUPPORTED;
+  if ((tq != kQTile && tq != kHalf) || tkv != kKVTile) return B200NA_ERR_INVALID_ARGUMENT;
+  p.halves = (int)(tq / kHalf);
+  // a 256-token query tile is fetched as two boxes, split along its last non-unit axis
+  if (p.halves == 2 && p.Tq[p.half_axis] % 2 != 0) return B200NA_ERR_UNSUPPORTED;
   if (sq > 0x7fffffffLL || skv > 0x7fffffffLL || tokens * B > 0x7fffffffLL ||
       (long long)Hq * D > 0x7fffffffLL)
     return B200NA_ERR_UNSUPPORTED;
@@ -1569,7 +1606,7 @@ int fna_direct_impl(const void* q, const void* k, const void* v, void* o, float*
   p.clip = clip ? 1 : 0;
   p.Bp = B * p.G; p.Hq = Hq; p.Hkv = Hkv;
   p.Sq = (int)sq; p.Skv = (int)skv;
-  p.n_qtiles = (int)(sq / kQTile);
+  p.n_qtiles = (int)(sq / tq);
   p.scale = scale;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.o = o;
@@ -1687,6 +1724,7 @@ extern "C" B200NA_API int b200na_fmha_forward(const void* q, const void* k, cons
   p.Rq[0] = p.n_qtiles;
   p.Rkv[0] = (Nk + kKVTile - 1) / kKVTile;
   p.dense = 1;
+  p.halves = 2;
   p.Bp = B; p.Hq = Hq; p.Hkv = Hkv;
   p.Sq = Nq; p.Skv = Nk;
   p.scale = scale;

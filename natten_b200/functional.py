@@ -36,6 +36,13 @@ BACKEND_ALIASES = (None, BACKEND_NAME, "blackwell-fna")
 FMHA_BACKEND_ALIASES = (None, FMHA_BACKEND_NAME, "blackwell-fmha")
 Q_TILE_SIZE = 256
 KV_TILE_SIZE = 128
+# A query tile holds 256 tokens (one CTA per SM, two 128-row halves sharing every key/value tile)
+# or 128 (two CTAs per SM, each walking the key/value box of its own 128 queries): the smaller
+# tile wins when windows are small, because the union of the windows of 128 queries is much
+# smaller than that of 256. It pays with twice the key/value tile loads per query row and a
+# shallower load ring, so its tile count is charged this factor in the tile-shape choice.
+Q_TILE_SIZES = (256, 128)
+SMALL_Q_TILE_PENALTY = 1.15
 TENSOR_CORE_HEAD_DIMS = (64, 128)
 
 _DTYPE_CODE = ops.DTYPE_CODE
@@ -161,8 +168,8 @@ def choose_tile_shapes(shape: DimensionType, kernel_size: DimensionType, stride:
 def _choose_tile_shapes(shape: DimensionType, kernel_size: DimensionType, stride: DimensionType,
                         dilation: DimensionType, is_causal: CausalArgType
                         ) -> Tuple[DimensionType, DimensionType]:
-    """Picks (q_tile_shape, kv_tile_shape), 256 and 128 tokens, that minimise the number of
-    key/value tiles the kernel has to visit (the reference instead offers a fixed list:
+    """Picks (q_tile_shape, kv_tile_shape) - 256 or 128 query tokens, 128 key/value tokens - that
+    minimise the tile products the kernel has to compute (the reference instead offers a fixed list:
     src/natten/backends/configs/cutlass_blackwell/__init__.py:45-64)."""
     n = len(shape)
     if n == 1:
@@ -176,18 +183,20 @@ def _choose_tile_shapes(shape: DimensionType, kernel_size: DimensionType, stride
                         shape[a], kernel_size[a], stride[a], dilation[a], is_causal[a], 1 << eq,
                         1 << ek, aligned)
     best = None
-    for tq in _pow2_compositions(8, n):
-        for tkv in _pow2_compositions(7, n):
-            # tiles the kernel can gather from the caller's layout start at the window; tile
-            # shapes that need token-permuted copies are tied to the tile grid
-            aligned = direct_layout_supported(tq, tkv, dilation)
-            c = 1
-            for a in range(n):
-                c *= cost[(a, tq[a], tkv[a], aligned)]
-            # ties: prefer tiles that are long along the last (memory-contiguous) axis
-            key = (c, -tq[-1], -tkv[-1])
-            if best is None or key < best[0]:
-                best = (key, tq, tkv)
+    for q_log2, weight in ((8, 2.0), (7, SMALL_Q_TILE_PENALTY)):
+        # cost in 128-row x 128-key products: a 256-token query tile makes two per key/value tile
+        for tq in _pow2_compositions(q_log2, n):
+            for tkv in _pow2_compositions(7, n):
+                # tiles the kernel can gather from the caller's layout start at the window; tile
+                # shapes that need token-permuted copies are tied to the tile grid
+                aligned = direct_layout_supported(tq, tkv, dilation)
+                c = weight
+                for a in range(n):
+                    c *= cost[(a, tq[a], tkv[a], aligned)]
+                # ties: prefer tiles that are long along the last (memory-contiguous) axis
+                key = (c, -tq[-1], -tkv[-1])
+                if best is None or key < best[0]:
+                    best = (key, tq, tkv)
     assert best is not None
     return best[1], best[2]
 
@@ -400,7 +409,7 @@ def neighborhood_attention_generic(
     if query.dtype not in _DTYPE_CODE:
         raise NotImplementedError(f"natten_b200 does not support dtype {query.dtype}.")
     if q_tile_shape is not None:
-        q_tile_shape = check_tile_shape(na_dim, q_tile_shape, "q_tile_shape", Q_TILE_SIZE)
+        q_tile_shape = check_tile_shape(na_dim, q_tile_shape, "q_tile_shape", Q_TILE_SIZES)
     if kv_tile_shape is not None:
         kv_tile_shape = check_tile_shape(na_dim, kv_tile_shape, "kv_tile_shape", KV_TILE_SIZE)
     fuse_extra = has_extra and not (attention_kwargs or {}).get("unfused_extra_kv", False)
@@ -662,7 +671,7 @@ def get_configs_for_b200_fna(query: Tensor, key: Tensor, value: Tensor):
     `get_configs_for_cutlass_blackwell_fna` (src/natten/backends/configs/__init__.py:159-188)."""
     if not can_run_b200_fna(query, key, value):
         return []
-    return _all_tile_shapes(query.dim() - 3, 8, 7)
+    return _all_tile_shapes(query.dim() - 3, 8, 7) + _all_tile_shapes(query.dim() - 3, 7, 7)
 
 
 def get_bwd_configs_for_b200_fna(query: Tensor, key: Tensor, value: Tensor):
@@ -708,15 +717,17 @@ def direct_layout_supported(q_tile_shape: DimensionType, kv_tile_shape: Dimensio
                             dilation: DimensionType) -> bool:
     """Whether the fused kernel can read the caller's ``[B, *X, H, D]`` layout directly: a tile of
     one dilation group must fit a tensor-map box (tile * dilation <= 256 positions per axis,
-    dilation <= 8). The query tile is fetched as two halves split along its last non-unit axis."""
+    dilation <= 8). A 256-token query tile is fetched as two halves split along its last non-unit
+    axis, a 128-token one whole."""
     q_box = list(q_tile_shape)
-    split = 0
-    for a, t in enumerate(q_box):
-        if t > 1:
-            split = a
-    if q_box[split] % 2:
-        return False
-    q_box[split] //= 2
+    if math.prod(q_box) != KV_TILE_SIZE:
+        split = 0
+        for a, t in enumerate(q_box):
+            if t > 1:
+                split = a
+        if q_box[split] % 2:
+            return False
+        q_box[split] //= 2
     return all(d <= MAX_TMA_ELEMENT_STRIDE and tq * d <= MAX_TMA_BOX and tkv * d <= MAX_TMA_BOX
                for tq, tkv, d in zip(q_box, kv_tile_shape, dilation))
 
@@ -820,7 +831,7 @@ def na_forward_fused(query: Tensor, key: Tensor, value: Tensor, kernel_size, str
         auto_q, auto_kv = choose_tile_shapes(shape, kernel_size, stride, dilation, is_causal)
         q_tile_shape = q_tile_shape or auto_q
         kv_tile_shape = kv_tile_shape or auto_kv
-    q_tile_shape = check_tile_shape(na_dim, q_tile_shape, "q_tile_shape", Q_TILE_SIZE)
+    q_tile_shape = check_tile_shape(na_dim, q_tile_shape, "q_tile_shape", Q_TILE_SIZES)
     kv_tile_shape = check_tile_shape(na_dim, kv_tile_shape, "kv_tile_shape", KV_TILE_SIZE)
     need = fused_workspace_bytes(shape, dilation, q_tile_shape, kv_tile_shape, B, Hq, Hkv, D)
     if workspace is None and need > 0:

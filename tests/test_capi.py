@@ -79,7 +79,8 @@ def test_fna_rejects_bad_arguments_before_touching_cuda():
     assert _fna(ker=[1]) == L.ERR_INVALID_ARGUMENT           # kernel_size >= 2
     assert _fna(ker=[600]) == L.ERR_INVALID_ARGUMENT         # kernel * dilation <= extent
     assert _fna(ker=[8], st=[9]) == L.ERR_INVALID_ARGUMENT   # stride <= kernel
-    assert _fna(qt=[128]) == L.ERR_INVALID_ARGUMENT          # q tile must hold 256 tokens
+    assert _fna(qt=[64]) == L.ERR_INVALID_ARGUMENT           # q tile must hold 256 or 128 tokens
+    assert _fna(qt=[512]) == L.ERR_INVALID_ARGUMENT
     assert _fna(kvt=[64]) == L.ERR_INVALID_ARGUMENT          # kv tile must hold 128 tokens
     assert _fna(qs=[500]) == L.ERR_INVALID_ARGUMENT          # tile must divide the padded shape
     assert _fna(qs=[256]) == L.ERR_INVALID_ARGUMENT          # padded shape must cover the layout

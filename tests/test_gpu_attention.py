@@ -72,6 +72,13 @@ def test_16bit_path_matches_reference(name, dtype, layout):
     ("c5s_na3d_8x12x20_k4x6x6_s1x2x2_causalT", (8, 4, 8), (4, 4, 8)),
     ("c5s_na3d_8x12x20_k4x6x6_s1x2x2_causalT", (2, 8, 16), (2, 8, 8)),
     ("c5s_na3d_8x12x20_k4x6x6_s1x2x2_causalT", (1, 16, 16), (1, 2, 64)),
+    # 128-token query tiles: one 128-row tile per CTA, two CTAs per SM
+    ("c3s_na2d_32x32_k13_d2", (8, 16), (4, 32)),
+    ("c3s_na2d_32x32_k13_d2", (128, 1), (16, 8)),
+    ("c4s_na2d_32x32_k8_s4_extra24", (8, 16), (8, 16)),
+    ("c5s_na3d_8x12x20_k4x6x6_s1x2x2_causalT", (2, 8, 8), (2, 8, 8)),
+    ("c5s_na3d_8x12x20_k4x6x6_s1x2x2_causalT", (1, 4, 32), (4, 4, 8)),
+    ("c2s_na1d_1024_k128_causal", (128,), (128,)),
 ])
 def test_tensor_core_kernel_with_explicit_tile_shapes(name, qt, kvt):
     c = na_cases()[name]
@@ -416,7 +423,7 @@ def test_unsupported_inputs_fail_loudly():
         nb.na1d(q, q, q, kernel_size=5)
     q = torch.randn(1, 64, 2, 64, device="cuda").bfloat16()
     with pytest.raises(ValueError):
-        nb.na1d(q, q, q, kernel_size=5, q_tile_shape=(128,))
+        nb.na1d(q, q, q, kernel_size=5, q_tile_shape=(64,))
     with pytest.raises(NotImplementedError):
         nb.attention(q, q, q, cumulative_seqlen_Q=torch.zeros(2, dtype=torch.int32, device="cuda"))
 

@@ -138,8 +138,8 @@ def test_reference_backend_names_and_config_listing():
         nb.na2d(q, q, q, 5, backend="hopper-fna")
     assert nb.can_run_b200_fna(q, q, q)
     cfgs = nb.get_configs_for_b200_fna(q, q, q)
-    assert ((16, 16), (16, 8)) in cfgs and all(
-        qt[0] * qt[1] == 256 and kt[0] * kt[1] == 128 for qt, kt in cfgs)
+    assert ((16, 16), (16, 8)) in cfgs and ((8, 16), (16, 8)) in cfgs and all(
+        qt[0] * qt[1] in (256, 128) and kt[0] * kt[1] == 128 for qt, kt in cfgs)
     bwd = nb.get_bwd_configs_for_b200_fna(q, q, q)
     assert ((8, 16), (16, 8)) in bwd
     assert not nb.can_run_b200_fna(q.float(), q.float(), q.float())

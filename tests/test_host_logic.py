@@ -101,19 +101,22 @@ def test_tile_shape_selection_is_valid_and_no_worse_than_reference_defaults():
     ref_default = {2: ((16, 16), (16, 8)), 3: ((8, 4, 8), (4, 4, 8))}
     for shape, k, s, d, c in cases:
         tq, tkv = nb.choose_tile_shapes(shape, k, s, d, c)
-        assert np.prod(tq) == 256 and np.prod(tkv) == 128
+        assert np.prod(tq) in (256, 128) and np.prod(tkv) == 128
         n = len(shape)
 
         def cost(tq_, tkv_):
-            # gathered tiles start at the first attended key, permuted ones lie on the tile grid
+            # 128-row x 128-key products per query token; gathered tiles start at the first
+            # attended key, permuted ones lie on the tile grid
             aligned = nb.direct_layout_supported(tq_, tkv_, d)
-            return np.prod([F._axis_tile_cost(shape[a], k[a], s[a], d[a], c[a], tq_[a], tkv_[a],
-                                              aligned) for a in range(n)], dtype=np.float64)
-        # compare per query token (tiles may differ in count)
-        def per_token(tq_, tkv_):
-            return cost(tq_, tkv_) / np.prod([-(-F.group_extent(shape[a], d[a], 0) // tq_[a])
-                                              for a in range(n)])
+            tiles = np.prod([F._axis_tile_cost(shape[a], k[a], s[a], d[a], c[a], tq_[a], tkv_[a],
+                                               aligned) for a in range(n)], dtype=np.float64)
+            return tiles * (2.0 if np.prod(tq_) == 256 else F.SMALL_Q_TILE_PENALTY)
         assert cost(tq, tkv) <= cost(*ref_default[n])
+    # small windows take the 128-token query tile (two CTAs per SM), large ones the 256-token one
+    assert np.prod(nb.choose_tile_shapes((128, 128), (13, 13), (1, 1), (2, 2), (False, False))[0]) == 128
+    assert np.prod(nb.choose_tile_shapes((256, 256), (32, 32), (16, 16), (1, 1), (False, False))[0]) == 256
+    assert np.prod(nb.choose_tile_shapes((32, 48, 80), (16, 24, 24), (1, 8, 8), (1, 1, 1),
+                                         (True, False, False))[0]) == 256
     assert nb.choose_tile_shapes((4096,), (64,), (1,), (1,), (False,)) == ((256,), (128,))
     # a window that is a whole number of tiles wide costs exactly that many gathered tiles,
     # wherever it starts: 32 keys from 16 j - 8 are two 16-key tiles, three on the grid
