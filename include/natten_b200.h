@@ -100,7 +100,10 @@ B200NA_API int b200na_token_unpermute(const void* in, void* out, int ndim, const
  *   Bp = batch * prod(dilation); dilation group of a slice = Bp index mod prod(dilation),
  *   decoded colexicographically (axis 0 fastest).
  *   qkv_shape: original token layout X; q_shape / kv_shape: padded per-group extents R_a*T_a
- *   (prod = Sq / Skv). prod(q_tile) must be 256 and prod(kv_tile) 128; tiles divide the shapes.
+ *   (prod = Sq / Skv). prod(q_tile) must be 256 or 128 and prod(kv_tile) 128; tiles divide the
+ *   shapes. A 256-token query tile runs one CTA per SM with two 128-row halves that share every
+ *   key/value tile; a 128-token one runs two CTAs per SM, each walking the key/value box of its
+ *   own queries - fewer tile products when windows are small, twice the tile loads per row.
  *   kernel/stride/dilation/causal: the reference's kernel_size / stride / dilation / is_causal.
  *   dtype: B200NA_F16 or B200NA_BF16 with D a multiple of 8, or B200NA_E4M3 / B200NA_E5M2 with D
  *   a multiple of 16 (the reference's rules, csrc/src/blackwell_fna_forward.cu:123-138, 178-191;
@@ -143,7 +146,7 @@ B200NA_API int b200na_fna_forward_extra_kv(
  * done by the kernel's tensor-map loads, and every O / LSE row is stored at its final address.
  * Results are those of b200na_token_permute + b200na_fna_forward_extra_kv +
  * b200na_token_unpermute with the same tile shapes.
- *   q_tile / kv_tile: prod = 256 / 128; tile[a] * dilation[a] <= 256 and dilation[a] <= 8 on
+ *   q_tile / kv_tile: prod = 256 (or 128) / 128; tile[a] * dilation[a] <= 256 and dilation[a] <= 8 on
  *   every axis, otherwise B200NA_ERR_UNSUPPORTED (use the permuted path then). Also
  *   B200NA_ERR_UNSUPPORTED: a head dim other than 64 / 128 (8-bit: 128) on a 3-D layout with
  *   B > 1 (the tensor map then has no axis left for the batch entry; call per batch entry, or
@@ -221,7 +224,7 @@ B200NA_API int b200na_na_forward_direct_sharded(
  * LSE, i.e. the forward of the reference's Python backend adapter
  * (src/natten/backends/blackwell_fna.py:91-181) for hosts that bind this C ABI directly.
  *   q: [B, *shape, Hq, D]; k, v: [B, *shape, Hkv, D]; o: [B, *shape, Hq, D]; lse: [B, *shape, Hq]
- *   fp32 or NULL. dtype F16/BF16, D in {64, 128}, prod(q_tile) = 256, prod(kv_tile) = 128.
+ *   fp32 or NULL. dtype F16/BF16, D in {64, 128}, prod(q_tile) = 256 or 128, prod(kv_tile) = 128.
  *   workspace: device scratch for the permuted copies, 256-byte aligned, at least
  *   b200na_na_forward_workspace_bytes(...) bytes (0 for 1-D undilated tile-multiple layouts,
  *   which need no permutation). Contents are unspecified afterwards; calls that share a
