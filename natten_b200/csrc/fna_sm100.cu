@@ -11,6 +11,12 @@
 //   * warp roles: 16 softmax warps (a 128-row half per 8 warps, two threads per row),
 //     1 MMA-issue warp (run converged, lane 0 performs the MMAs), 1 TMA-load warp that also
 //     decodes work items; persistent CTAs draw (q-tile, head, batch') items from a counter.
+//     A second shape of the same template owns ONE 128-row half per CTA (10 warps, half the
+//     shared and tensor memory) and runs two CTAs per SM: for small windows, where 128 queries
+//     share far fewer keys than 256 do.
+//   * key/value tiles gathered from the caller's layout start at the first attended key instead
+//     of on a grid; head dims below the kernel's 64 / 128 channels are read through tensor maps
+//     with the head as an axis of its own (the missing channels come back as zeros).
 //   * TMEM: S0 S1 O0 O1 (128 fp32 columns each at D = 128); P (16-bit) overwrites S in place and
 //     feeds P.V straight from TMEM; the O rescale is lazy (only when a row maximum grows by more
 //     than 2^8) and is done by the softmax threads between the two MMAs of their half.
