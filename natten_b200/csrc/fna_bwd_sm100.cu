@@ -123,9 +123,11 @@ struct Item {
   int g[B200NA_MAX_DIM];      // dilation group offset per axis
   int L[B200NA_MAX_DIM];      // extent of this dilation group
   int r_lo[B200NA_MAX_DIM];   // first row coordinate of the tile (group coordinates)
-  int c_t0[B200NA_MAX_DIM];   // first column tile per axis
+  int c_org[B200NA_MAX_DIM];  // first column coordinate of the first column tile per axis: the
+                              // tiles start where the rows' columns start, not on a grid from 0
   int c_n[B200NA_MAX_DIM];    // column tiles per axis
-  // column tiles [int_lo, int_hi) of an axis lie inside the (inverse) window of every row
+  // column tiles [int_lo, int_hi) of an axis, counted from c_org, lie inside the (inverse)
+  // window of every row
   int int_lo[B200NA_MAX_DIM];
   int int_hi[B200NA_MAX_DIM];
   int n_tiles;                // column tiles to visit (times the heads of the group in pass dKdV),
@@ -225,18 +227,17 @@ __device__ __forceinline__ void decode_item(const BwdTcParams& p, const WorkCurs
       row_span<kKeyRows>(p, a, lo, L, s_lo, e_lo);
       row_span<kKeyRows>(p, a, last, L, s_hi, e_hi);
       const int Tc = p.Tc[a];
-      int t0 = s_lo / Tc;
-      int t1 = (e_hi + Tc - 1) / Tc;
-      if (t1 <= t0) t1 = t0 + 1;  // a key nobody attends: visit one (fully masked) tile
-      it.c_t0[a] = t0;
-      it.c_n[a] = t1 - t0;
-      it.int_lo[a] = (s_hi + Tc - 1) / Tc;
-      it.int_hi[a] = e_lo / Tc;
+      int n = (e_hi - s_lo + Tc - 1) / Tc;
+      if (n < 1) n = 1;  // a key nobody attends: visit one (fully masked) tile
+      it.c_org[a] = s_lo;
+      it.c_n[a] = n;
+      it.int_lo[a] = (s_hi - s_lo + Tc - 1) / Tc;
+      it.int_hi[a] = e_lo > s_lo ? (e_lo - s_lo) / Tc : 0;
       // rows past the extent (padding) interact with nothing: no tile is mask-free then
       if (lo + p.Tr[a] > Lr) it.int_hi[a] = it.int_lo[a];
       it.n_per_head *= it.c_n[a];
     } else {
-      it.g[a] = 0; it.L[a] = 1; it.r_lo[a] = 0; it.c_t0[a] = 0; it.c_n[a] = 1;
+      it.g[a] = 0; it.L[a] = 1; it.r_lo[a] = 0; it.c_org[a] = 0; it.c_n[a] = 1;
       it.int_lo[a] = 0; it.int_hi[a] = 1;
     }
   }
@@ -282,12 +283,12 @@ constexpr int kTileInterior = 1, kTileBoundary = 2, kTileRagged = 3;
 // Per-item constants of the column-tile walk and classification, held in registers by the load
 // thread (all its instructions are dependent, so shared-memory reads per tile would add latency).
 struct TileWalk {
-  int t0[B200NA_MAX_DIM], end[B200NA_MAX_DIM], int_lo[B200NA_MAX_DIM], int_hi[B200NA_MAX_DIM];
+  int org[B200NA_MAX_DIM], end[B200NA_MAX_DIM], int_lo[B200NA_MAX_DIM], int_hi[B200NA_MAX_DIM];
   __device__ __forceinline__ void load(const Item& it) {
 #pragma unroll
     for (int a = 0; a < B200NA_MAX_DIM; ++a) {
-      t0[a] = it.c_t0[a];
-      end[a] = it.c_t0[a] + it.c_n[a];
+      org[a] = it.c_org[a];
+      end[a] = it.c_n[a];
       int_lo[a] = it.int_lo[a];
       int_hi[a] = it.int_hi[a];
     }
@@ -304,13 +305,13 @@ struct TileWalk {
   template <int NDIM>
   __device__ __forceinline__ void next(int (&c)[B200NA_MAX_DIM]) const {
     if (++c[0] < end[0]) return;
-    c[0] = t0[0];
+    c[0] = 0;
     if (NDIM == 1) return;
     if (++c[1] < end[1]) return;
-    c[1] = t0[1];
+    c[1] = 0;
     if (NDIM == 2) return;
     if (++c[2] < end[2]) return;
-    c[2] = t0[2];
+    c[2] = 0;
   }
 };
 
@@ -958,7 +959,7 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
         }
         TileWalk tw;
         tw.load(it);
-        int tc[B200NA_MAX_DIM] = {tw.t0[0], tw.t0[1], tw.t0[2]};
+        int tc[B200NA_MAX_DIM] = {0, 0, 0};
         // head of the column tiles: the kv head of a query head, or the query heads of a kv head
         int col_head = kKeyRows ? it.h * p.rep : it.h / p.rep;
         int in_head = 0;
@@ -975,8 +976,9 @@ fna_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant_
             rec = make_int4(valid >= kTile ? kTileInterior : kTileRagged, valid, 0, 0);
             x0 = e0; x1 = 0; x2 = 0;
           } else {
-            const int k0 = tc[0] * p.Tc[0], k1 = NDIM > 1 ? tc[1] * p.Tc[1] : 0,
-                      k2 = NDIM > 2 ? tc[2] * p.Tc[2] : 0;
+            const int k0 = tw.org[0] + tc[0] * p.Tc[0],
+                      k1 = NDIM > 1 ? tw.org[1] + tc[1] * p.Tc[1] : 0,
+                      k2 = NDIM > 2 ? tw.org[2] + tc[2] * p.Tc[2] : 0;
             rec = make_int4(tw.template interior<NDIM>(tc) ? kTileInterior : kTileBoundary, k0, k1,
                             k2);
             x0 = k0 * p.dil[0] + g0; x1 = k1 * p.dil[1] + g1; x2 = k2 * p.dil[2] + g2;

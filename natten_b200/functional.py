@@ -12,6 +12,7 @@ unfused extra-token composition register no formula, so differentiating through 
 """
 from __future__ import annotations
 
+import bisect
 import ctypes
 import functools
 import math
@@ -143,6 +144,23 @@ def _axis_tile_cost(X: int, k: int, s: int, d: int, causal: bool, tq: int, tkv: 
         s_hi = window_start(q_hi, k, s, L, causal)
         en = window_end(q_hi, s_hi, k, L, causal)
         total += -(-(en - st) // tkv) if aligned else -(-en // tkv) - st // tkv
+    return total
+
+
+def _axis_inverse_tile_cost(X: int, k: int, s: int, d: int, causal: bool, tq: int,
+                            tkv: int) -> int:
+    """Query tiles visited along one axis, summed over that axis' key tiles (largest group), by a
+    pass whose stationary tile holds keys: the walk of a key tile starts at the first query that
+    attends one of its keys and ends after the last one."""
+    L = group_extent(X, d, 0)
+    starts = [window_start(i, k, s, L, causal) for i in range(L)]
+    ends = [window_end(i, starts[i], k, L, causal) for i in range(L)]
+    total = 0
+    for k_lo in range(0, L, tkv):
+        k_hi = min(k_lo + tkv, L) - 1
+        first = bisect.bisect_right(ends, k_lo)       # first query whose window ends beyond k_lo
+        last = bisect.bisect_right(starts, k_hi)      # first query whose window starts beyond k_hi
+        total += max(1, -(-(last - first) // tq))
     return total
 
 
@@ -602,8 +620,9 @@ def choose_backward_tile_shapes(shape: DimensionType, kernel_size: DimensionType
                                 stride: DimensionType, dilation: DimensionType,
                                 is_causal: CausalArgType) -> Tuple[DimensionType, DimensionType]:
     """(q_tile_shape, kv_tile_shape), 128 tokens each, for the backward kernels: the pair that
-    minimises the key/value tiles visited per query tile (the mirrored pass visits the same
-    (query tile, key/value tile) pairs from the other side)."""
+    minimises the tile products of both passes - key/value tiles visited per query tile (dQ) plus
+    query tiles visited per key/value tile (dK, dV). Both walks start at the first token the
+    stationary tile interacts with, not on a tile grid."""
     return _choose_backward_tile_shapes(
         tuple(int(x) for x in shape), tuple(int(x) for x in kernel_size),
         tuple(int(x) for x in stride), tuple(int(x) for x in dilation),
@@ -615,20 +634,24 @@ def _choose_backward_tile_shapes(shape, kernel_size, stride, dilation, is_causal
     n = len(shape)
     if n == 1:
         return (BACKWARD_TILE_SIZE,), (BACKWARD_TILE_SIZE,)
-    cost: Dict[Tuple[int, int, int], int] = {}
+    cost: Dict[Tuple[int, int, int], Tuple[int, int]] = {}
     for a in range(n):
         for eq in range(8):
             for ek in range(8):
-                cost[(a, 1 << eq, 1 << ek)] = _axis_tile_cost(
-                    shape[a], kernel_size[a], stride[a], dilation[a], is_causal[a], 1 << eq, 1 << ek)
+                args = (shape[a], kernel_size[a], stride[a], dilation[a], is_causal[a], 1 << eq,
+                        1 << ek)
+                cost[(a, 1 << eq, 1 << ek)] = (_axis_tile_cost(*args, True),
+                                               _axis_inverse_tile_cost(*args))
     best = None
     for tq in _pow2_compositions(7, n):
         for tkv in _pow2_compositions(7, n):
             if not backward_layout_supported(tq, tkv, dilation):
                 continue
-            c = 1
+            c_dq = c_dkdv = 1
             for a in range(n):
-                c *= cost[(a, tq[a], tkv[a])]
+                c_dq *= cost[(a, tq[a], tkv[a])][0]
+                c_dkdv *= cost[(a, tq[a], tkv[a])][1]
+            c = c_dq + c_dkdv
             key = (c, -tq[-1], -tkv[-1])
             if best is None or key < best[0]:
                 best = (key, tq, tkv)
