@@ -631,7 +631,10 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const float neg_mc = (m == -INFINITY) ? 0.f : -m * c;
         // Pass 2: p = 2^(s*c - m*c), 32 columns at a time; each packed chunk of P overwrites
         // logit columns this same thread has already consumed, so no other thread is involved.
-        float sm0 = 0.f, sm1 = 0.f;
+        // x = s c - m c and the row sums in packed (two-wide) arithmetic: half the instructions
+        // of the scalar forms for these two steps
+        const uint64_t c2 = ptx::f32x2(c, c), nmc2 = ptx::f32x2(neg_mc, neg_mc);
+        uint64_t acc0 = ptx::f32x2(0.f, 0.f), acc1 = acc0;
 #pragma unroll
         for (int ch = 0; ch < 2; ++ch) {
           if (ch == 1) {
@@ -648,29 +651,37 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             uint32_t pk[8];
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
-              const float p0 = ptx::ex2(fmaf(__uint_as_float(sr[j]), c, neg_mc));
-              const float p1 = ptx::ex2(fmaf(__uint_as_float(sr[j + 1]), c, neg_mc));
-              const float p2 = ptx::ex2(fmaf(__uint_as_float(sr[j + 2]), c, neg_mc));
-              const float p3 = ptx::ex2(fmaf(__uint_as_float(sr[j + 3]), c, neg_mc));
-              sm0 += p0 + p2;
-              sm1 += p1 + p3;
+              float x0, x1, x2, x3;
+              ptx::f32x2_split(ptx::fma_f32x2(ptx::f32x2(sr[j], sr[j + 1]), c2, nmc2), x0, x1);
+              ptx::f32x2_split(ptx::fma_f32x2(ptx::f32x2(sr[j + 2], sr[j + 3]), c2, nmc2), x2, x3);
+              const float p0 = ptx::ex2(x0), p1 = ptx::ex2(x1), p2 = ptx::ex2(x2), p3 = ptx::ex2(x3);
+              acc0 = ptx::add_f32x2(acc0, ptx::f32x2(p0, p1));
+              acc1 = ptx::add_f32x2(acc1, ptx::f32x2(p2, p3));
               pk[j >> 2] = ptx::pack4_e4m3(p0, p1, p2, p3);
             }
             ptx::tmem_st8(my_p + ch * 8, pk);
           } else {
             uint32_t pk[16];
 #pragma unroll
-            for (int j = 0; j < 32; j += 2) {
-              const float p0 = ptx::ex2(fmaf(__uint_as_float(sr[j]), c, neg_mc));
-              const float p1 = ptx::ex2(fmaf(__uint_as_float(sr[j + 1]), c, neg_mc));
-              sm0 += p0;
-              sm1 += p1;
+            for (int j = 0; j < 32; j += 4) {
+              float x0, x1, x2, x3;
+              ptx::f32x2_split(ptx::fma_f32x2(ptx::f32x2(sr[j], sr[j + 1]), c2, nmc2), x0, x1);
+              ptx::f32x2_split(ptx::fma_f32x2(ptx::f32x2(sr[j + 2], sr[j + 3]), c2, nmc2), x2, x3);
+              const float p0 = ptx::ex2(x0), p1 = ptx::ex2(x1), p2 = ptx::ex2(x2), p3 = ptx::ex2(x3);
+              acc0 = ptx::add_f32x2(acc0, ptx::f32x2(p0, p1));
+              acc1 = ptx::add_f32x2(acc1, ptx::f32x2(p2, p3));
               pk[j >> 1] = pack2<kType>(p0, p1);
+              pk[(j >> 1) + 1] = pack2<kType>(p2, p3);
             }
             ptx::tmem_st16(my_p + ch * 16, pk);
           }
         }
-        sum += sm0 + sm1;
+        {
+          float s0, s1, s2, s3;
+          ptx::f32x2_split(acc0, s0, s1);
+          ptx::f32x2_split(acc1, s2, s3);
+          sum += (s0 + s1) + (s2 + s3);
+        }
         PROF_MARK(2)
         ptx::tmem_st_wait();
         ptx::tc_fence_before_sync();

@@ -7,7 +7,12 @@ Head dims the tensor-core kernels do not take natively (16, 32, 48, 72, 96, 120)
 The reference compares its Blackwell backend with its CUTLASS 2.x backend on these problems at an
 absolute tolerance of 1e-2 (fp16); neither builds here, so the comparison is with the CPU oracle
 (pinned to the reference's own outputs in tests/test_oracle.py) at this repository's 2e-2. Large
-problems are checked on a sample of query rows (half uniform, half in the border bands)."""
+problems are checked on a sample of query rows (half uniform, half in the border bands).
+
+The reference runs the backward pass on the same problems (tests/test_blackwell_fna.py:88-148); the
+second test replays every problem whose gradients the CPU oracle finishes in a few seconds, with
+two causal combinations each, through autograd (tensor-core gradient kernels for head dims 64 and
+128 after zero-padding, which is how a call that needs gradients runs)."""
 import itertools
 
 import numpy as np
@@ -139,3 +144,37 @@ def test_reference_problem_list_against_oracle(dim, index, problem):
                 got_l = got_l.reshape(want_l.shape)
             assert np.abs(got_o - want_o).max() <= TOL, (ca, layout)
             assert np.abs(got_l - want_l).max() <= TOL, (ca, layout)
+
+
+MAX_BACKWARD_WORK = 2.0e9   # queries x window x head dim, summed over batch and heads
+
+
+def _backward_work(problem):
+    B, H, _, D, shape, ks, _, _ = problem
+    return float(B * H * D) * float(np.prod(shape)) * float(np.prod(ks))
+
+
+GRAD = [(d, i, p) for d, i, p in ALL if _backward_work(p) <= MAX_BACKWARD_WORK]
+
+
+@pytest.mark.parametrize("dim,index,problem", GRAD, ids=[f"{d}-{i}" for d, i, _ in GRAD])
+def test_reference_problem_list_gradients_against_oracle(dim, index, problem):
+    B, H, Hkv, D, shape, ks, st, di = problem
+    nd = len(shape)
+    torch.manual_seed(2000 * nd + index)
+    q = torch.randn(B, *shape, H, D).half()
+    k, v = (torch.randn(B, *shape, Hkv, D).half() for _ in range(2))
+    d_out = torch.randn(B, *shape, H, D).half()
+    fn = {1: nb.na1d, 2: nb.na2d, 3: nb.na3d}[nd]
+    combos = list(itertools.product([False, True], repeat=nd))
+    qf, kf, vf, df = (t.float().numpy() for t in (q, k, v, d_out))
+    for ca in {combos[0], combos[1 + index % (len(combos) - 1)]}:
+        want = oracle.na_backward(qf, kf, vf, df, ks, st, di, ca)
+        leaves = [t.cuda().requires_grad_() for t in (q, k, v)]
+        out = fn(*leaves, kernel_size=ks, stride=st, dilation=di, is_causal=ca)
+        out.backward(d_out.cuda())
+        assert L.device_status() == 0
+        for name, leaf, w in zip("qkv", leaves, want):
+            got = leaf.grad.float().cpu().numpy()
+            assert got.shape == w.shape
+            assert np.abs(got - w).max() <= TOL * max(1.0, np.abs(w).max()), (ca, name)
