@@ -525,7 +525,12 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       const int n_tiles = it.n_tiles;
       if (n_tiles < 0) break;  // end of this CTA's work list
       // window of this thread's query row
+      // Kept as start | end << 16 per axis in the 3-D kernel (the host admits 3-D extents below
+      // 2^16 only): six live registers less across the tile loop, which is what keeps the
+      // compiler from spilling inside it.
+      constexpr bool kPackWindow = NDIM == 3;
       int ws[B200NA_MAX_DIM], we[B200NA_MAX_DIM];
+      uint32_t wse[B200NA_MAX_DIM];
 #pragma unroll
       for (int a = 0; a < B200NA_MAX_DIM; ++a) {
         if (a < NDIM) {
@@ -533,6 +538,7 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         } else {
           ws[a] = 0; we[a] = 1;
         }
+        wse[a] = (uint32_t)ws[a] | ((uint32_t)we[a] << 16);
       }
       float m = -INFINITY, sum = 0.f;   // sum covers this thread's columns only
       bool alive = true;
@@ -559,6 +565,13 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           mw1 = v1 >= 32 ? ~0u : ((1u << v1) - 1u);
         } else if (!interior) {
           const int base3[B200NA_MAX_DIM] = {rec.y, rec.z, rec.w};
+          if constexpr (kPackWindow) {
+#pragma unroll
+            for (int a = 0; a < B200NA_MAX_DIM; ++a) {
+              ws[a] = (int)(wse[a] & 0xffffu);
+              we[a] = (int)(wse[a] >> 16);
+            }
+          }
           const uint4 mk = tile_mask<NDIM>(pref, p.Tkv, ws, we, base3);
           mw0 = part ? mk.z : mk.x;
           mw1 = part ? mk.w : mk.y;
@@ -1356,6 +1369,10 @@ int launch_fna(const void* q, const void* k, const void* v, FnaParams& p, int D,
   if (al % 16 != 0) return B200NA_ERR_ALIGNMENT;
   const int Dk = kernel_head_dim(D, dtype);   // D is the tensors' head dim, Dk the kernel's
   if (Dk == 0) return B200NA_ERR_UNSUPPORTED;
+  // the 3-D kernel keeps a row's window bounds as 16-bit halves of one register per axis
+  if (p.ndim == 3)
+    for (int a = 0; a < 3; ++a)
+      if (p.X[a] >= 65536) return B200NA_ERR_UNSUPPORTED;
   p.d_real = D;
   p.sep_heads = (p.direct && D != Dk) ? 1 : 0;
   CUtensorMap tq, tk, tv;

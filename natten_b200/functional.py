@@ -83,6 +83,9 @@ def _reads_natively(dtype: torch.dtype, head_dim: int) -> bool:
     return dtype in FP8_DTYPES and 16 <= head_dim <= FP8_HEAD_DIM and head_dim % 16 == 0
 
 
+MAX_3D_EXTENT = 65536   # 3-D problems with a longer axis run on the CUDA-core kernel
+
+
 def _tensor_core_supported(dtype: torch.dtype, head_dim: int) -> bool:
     """Operands the tcgen05 forward kernels take as they are (see `_reads_natively`)."""
     return _reads_natively(dtype, head_dim)
@@ -513,6 +516,8 @@ def na_forward_op(query: Tensor, key: Tensor, value: Tensor, additional_keys: Op
     kernel_size, stride, dilation = tuple(kernel_size), tuple(stride), tuple(dilation)
     is_causal = tuple(bool(c) for c in is_causal)
     tensor_core = _tensor_core_supported(query.dtype, query.shape[-1])
+    if na_dim == 3 and max(shape) >= MAX_3D_EXTENT and query.dtype not in FP8_DTYPES:
+        tensor_core = False     # the 3-D tensor-core kernel keeps window bounds in 16 bits
     if not tensor_core and query.dtype in FP8_DTYPES:
         raise NotImplementedError("natten_b200: 8-bit operands need a head dim that is a multiple "
                                   f"of 16 and at most {FP8_HEAD_DIM}, got {query.shape[-1]}.")
