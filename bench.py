@@ -121,9 +121,9 @@ def algorithmic_flops(cfg, units=None) -> float:
 # summarised in profiles/fna_fwd_kernel_c2.md and profiles/fna_fwd_kernel_c5_c4_c3.md; scaled by
 # the units of a launch.
 NCU_TRAFFIC_PER_UNIT = {"c2": (202.86e6 + 49.00e6) / 8,
-                        "c3": (50.49e6 + 2.18e6) / 4,
+                        "c3": (50.48e6 + 2.54e6) / 4,
                         "c4": (204.81e6 + 51.43e6) / 4,
-                        "c5": (473.82e6 + 141.28e6) / 4}
+                        "c5": (453.22e6 + 122.89e6) / 4}
 
 
 def read_peaks():

@@ -110,7 +110,9 @@ B200NA_API int b200na_token_unpermute(const void* in, void* out, int ndim, const
  *   8-bit: fp32 accumulation and softmax, P rounded to e4m3 before P.V, O in the operand type),
  *   8 <= D <= 128. The kernels are built for 64 and 128 channels (8-bit: 128); the channels a
  *   smaller head dim lacks are zeros the tensor-map boxes fill in, and O rows are D wide.
- *   Hq % Hkv == 0. scale multiplies q.k.
+ *   Hq % Hkv == 0. scale multiplies q.k. With ndim = 3 every axis of qkv_shape must be
+ *   shorter than 65536 tokens (B200NA_ERR_UNSUPPORTED otherwise; b200na_na_forward_simt has no
+ *   such limit).
  * Rows of o/lse that correspond to padding tokens are left unspecified.
  */
 B200NA_API int b200na_fna_forward(const void* q, const void* k, const void* v, void* o, float* lse, int ndim,
