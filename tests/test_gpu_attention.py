@@ -473,3 +473,30 @@ def test_head_dims_the_kernels_are_not_built_for(D):
         assert np.abs(o3.float().cpu().numpy() - w3).max() <= TOL_16
         assert np.abs(l3.cpu().numpy() - wl3).max() <= TOL_16
     assert L.device_status() == 0
+
+
+def test_three_dimensional_problems_with_a_very_long_axis_run_on_the_cuda_core_kernel():
+    """The 3-D tensor-core kernel keeps a row's window bounds in 16-bit halves, so the C entry
+    refuses 3-D shapes with an axis of 65536 tokens or more; the Python operator sends them to the
+    CUDA-core kernel, and the result still matches the oracle (checked on a sample of rows
+    that includes both ends of the long axis)."""
+    torch.manual_seed(21)
+    shape, ks, st, di, ca = (65600, 2, 2), (9, 2, 2), (1, 1, 1), (1, 1, 1), (True, False, False)
+    q, k, v = (torch.randn(1, *shape, 1, 64).half() for _ in range(3))
+    qc, kc, vc = q.cuda(), k.cuda(), v.cuda()
+    out, lse = nb.na3d(qc, kc, vc, ks, st, di, ca, return_lse=True)
+    assert L.device_status() == 0
+    rng = np.random.default_rng(3)
+    n_tok = int(np.prod(shape))
+    rows = np.unique(np.concatenate([np.arange(64), np.arange(n_tok - 64, n_tok),
+                                     rng.integers(0, n_tok, size=512)])).astype(np.int64)
+    want_o, want_l = oracle.na_forward(q.float().numpy(), k.float().numpy(), v.float().numpy(),
+                                       ks, st, di, ca, tok_idx=rows)
+    got_o = out.flatten(1, 3).float().cpu().numpy()[:, rows]
+    got_l = lse.flatten(1, 3).cpu().numpy()[:, rows]
+    assert np.abs(got_o - want_o).max() <= TOL_16
+    assert np.abs(got_l - want_l).max() <= TOL_16
+    # the tensor-core entry itself says so
+    with pytest.raises(L.NattenB200Error) as err:
+        nb.fna_forward_direct(qc, kc, vc, ks, st, di, ca, 64 ** -0.5, (64, 2, 2), (32, 2, 2))
+    assert err.value.code == L.ERR_UNSUPPORTED
