@@ -518,28 +518,32 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     }
 
     PROF_DECL
+    // window of this thread's query row
+    // Kept as start | end << 16 per axis in the 3-D kernel (the host admits 3-D extents below
+    // 2^16 only): six live registers less across the tile loop, which is what keeps the
+    // compiler from spilling inside it.
+    constexpr bool kPackWindow = NDIM == 3;
+    int ws[B200NA_MAX_DIM], we[B200NA_MAX_DIM];
+    uint32_t wse[B200NA_MAX_DIM];
+    auto row_window = [&](const Item& item, int (&s_)[B200NA_MAX_DIM], int (&e_)[B200NA_MAX_DIM]) {
+#pragma unroll
+      for (int a = 0; a < B200NA_MAX_DIM; ++a) {
+        if (a < NDIM) {
+          axis_window(p, a, item.q_lo[a] + tq[a], item.L[a], s_[a], e_[a]);
+        } else {
+          s_[a] = 0; e_[a] = 1;
+        }
+      }
+    };
+    const Item* itp = fetch_item(desc_sm, bars, 0, abort_flag, p.status, 1);
+    if (__all_sync(0xffffffffu, itp != nullptr) && itp->n_tiles >= 0) row_window(*itp, ws, we);
     for (uint32_t seq = 0;; ++seq) {
-      const Item* itp = fetch_item(desc_sm, bars, seq, abort_flag, p.status, 1);
       if (!__all_sync(0xffffffffu, itp != nullptr)) break;
       const Item& it = *itp;  // read in place: the fields do not occupy registers across a tile
       const int n_tiles = it.n_tiles;
       if (n_tiles < 0) break;  // end of this CTA's work list
-      // window of this thread's query row
-      // Kept as start | end << 16 per axis in the 3-D kernel (the host admits 3-D extents below
-      // 2^16 only): six live registers less across the tile loop, which is what keeps the
-      // compiler from spilling inside it.
-      constexpr bool kPackWindow = NDIM == 3;
-      int ws[B200NA_MAX_DIM], we[B200NA_MAX_DIM];
-      uint32_t wse[B200NA_MAX_DIM];
 #pragma unroll
-      for (int a = 0; a < B200NA_MAX_DIM; ++a) {
-        if (a < NDIM) {
-          axis_window(p, a, it.q_lo[a] + tq[a], it.L[a], ws[a], we[a]);
-        } else {
-          ws[a] = 0; we[a] = 1;
-        }
-        wse[a] = (uint32_t)ws[a] | ((uint32_t)we[a] << 16);
-      }
+      for (int a = 0; a < B200NA_MAX_DIM; ++a) wse[a] = (uint32_t)ws[a] | ((uint32_t)we[a] << 16);
       float m = -INFINITY, sum = 0.f;   // sum covers this thread's columns only
       bool alive = true;
       for (int iter = 0; iter < n_tiles; ++iter) {
@@ -703,13 +707,15 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         if (row == 0 && part == 0) TRACE(half, 2)
       }
       if (!alive) break;
+      // The next item's descriptor was published while this item's second tile was loaded: its
+      // window arithmetic is done here, in the time this thread would otherwise wait for the
+      // last P.V.
+      const Item* nxt = fetch_item(desc_sm, bars, seq + 1, abort_flag, p.status, 1);
+      int nws[B200NA_MAX_DIM] = {0, 0, 0}, nwe[B200NA_MAX_DIM] = {1, 1, 1};
+      if (__all_sync(0xffffffffu, nxt != nullptr) && nxt->n_tiles >= 0) row_window(*nxt, nws, nwe);
       // ---- epilogue: O / sum -> global, LSE ----
-      if (!__all_sync(0xffffffffu, wait_bar(bars.o_full + half, ph_o, abort_flag, p.status,
-                                            (1 << 8) | kStOFull)))
-        break;
-      ph_o ^= 1;
-      PROF_MARK(4)
-      ptx::tc_fence_after_sync();
+      // Everything that does not need the accumulator comes before the wait for the last P.V:
+      // the row sums are final once the last tile's exponentials are.
       float* xs = xsum + half * 2 * kHalf;
       xs[part * kHalf + row] = sum;
       named_bar_sync(bar_id, kSoftmaxThreadsPerHalf);
@@ -736,6 +742,12 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         out_row = ((long long)it.bp * p.Sq + q_row) * p.Hq + it.h;
       }
       const float inv = total > 0.f ? 1.f / total : 0.f;
+      if (!__all_sync(0xffffffffu, wait_bar(bars.o_full + half, ph_o, abort_flag, p.status,
+                                            (1 << 8) | kStOFull)))
+        break;
+      ph_o ^= 1;
+      PROF_MARK(4)
+      ptx::tc_fence_after_sync();
       // This thread's share of its output row: D/2 elements = kChunks 16-byte chunks. A store of
       // one chunk per lane would touch 32 rows (32 separate lines) per instruction, and the
       // load/store unit would spend more time on the epilogue than the arithmetic does. The
@@ -787,6 +799,9 @@ fna_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       ptx::mbar_arrive(bars.o_empty + half);
       release_item(bars, seq);
       PROF_MARK(5)
+      itp = nxt;
+#pragma unroll
+      for (int a = 0; a < B200NA_MAX_DIM; ++a) { ws[a] = nws[a]; we[a] = nwe[a]; }
     }
     if (row == 0 && part == 0) { PROF_FLUSH(half) }
   } else if (warp == kMmaWarp) {
