@@ -120,10 +120,10 @@ def algorithmic_flops(cfg, units=None) -> float:
 # cases (dram__bytes_read.sum + dram__bytes_write.sum of one launch / units in that launch),
 # summarised in profiles/fna_fwd_kernel_c2.md and profiles/fna_fwd_kernel_c5_c4_c3.md; scaled by
 # the units of a launch.
-NCU_TRAFFIC_PER_UNIT = {"c2": (202.86e6 + 49.00e6) / 8,
+NCU_TRAFFIC_PER_UNIT = {"c2": (202.29e6 + 48.23e6) / 8,
                         "c3": (50.48e6 + 2.54e6) / 4,
-                        "c4": (204.81e6 + 51.43e6) / 4,
-                        "c5": (453.22e6 + 122.89e6) / 4}
+                        "c4": (203.21e6 + 46.08e6) / 4,
+                        "c5": (429.39e6 + 118.13e6) / 4}
 
 
 def read_peaks():
