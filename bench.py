@@ -121,7 +121,7 @@ def algorithmic_flops(cfg, units=None) -> float:
 # summarised in profiles/fna_fwd_kernel_c2.md and profiles/fna_fwd_kernel_c5_c4_c3.md; scaled by
 # the units of a launch.
 NCU_TRAFFIC_PER_UNIT = {"c2": (202.29e6 + 48.23e6) / 8,
-                        "c3": (50.48e6 + 2.54e6) / 4,
+                        "c3": (408.15e6 + 118.48e6) / 32,
                         "c4": (203.21e6 + 46.08e6) / 4,
                         "c5": (429.39e6 + 118.13e6) / 4}
 
